@@ -1,0 +1,189 @@
+/*
+ * oco_moe.h — C ABI of the B200 (sm_100a) mixture-of-experts layer.
+ *
+ * This is the boundary a CUDA backend of the reference's `src/gpu` would bind through a thin FFI
+ * crate: plain pointers and sizes, no C++ or framework types. One call enqueues the whole MoE
+ * layer (router -> top-k -> token-to-expert permutation -> quantised expert products ->
+ * activation -> weighted combine onto the residual) on a CUDA stream and returns; stream order
+ * replaces the reference's dispatch barriers (reference `src/gpu/dispatch.rs:303-311`).
+ *
+ * Ownership: the caller owns all device memory (weights, x, residual, workspace) and keeps it
+ * valid until the stream reaches the end of the call; the library owns only the plan object.
+ * Weight tensors are the GGUF byte spans staged into device memory unchanged (block layouts of
+ * reference `src/tensor.rs:24-36`). They may start at any byte address; kernels read whole
+ * 16-byte-aligned chunks, so the 16-byte-aligned envelope of every weight tensor must be
+ * readable (true for anything carved out of a cudaMalloc allocation with 16 bytes of slack).
+ * x, residual and the workspace must be 256-byte aligned.
+ *
+ * Errors: every entry point returns an `oco_status`; nothing aborts or throws across the ABI.
+ * Numerical failure keeps the reference's convention (reference `shaders/experts/routing.metal:69-70`,
+ * `src/weights/session.rs:254-257`): a reserved E8M0 scale (255) or a non-finite logit yields NaN
+ * in the output while the expert ids stay valid, so the caller's final-logit check still fires.
+ * Device-side waits are bounded; a wait that gives up sets a status word that `oco_moe_poll`
+ * reports as OCO_DEVICE_TIMEOUT.
+ *
+ * Threading: a plan with its bound workspace serves one stream at a time. Weights are immutable
+ * and may be shared by several plans.
+ */
+#ifndef OCO_MOE_H
+#define OCO_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    OCO_OK = 0,
+    OCO_INVALID_ARGUMENT = 1,
+    OCO_UNSUPPORTED_SHAPE = 2,
+    OCO_CUDA_ERROR = 3,
+    OCO_NCCL_ERROR = 4,
+    OCO_DEVICE_TIMEOUT = 5
+} oco_status;
+
+/* Layer families. Each fixes the router, the activation and the combine rule:
+ *  GPT_OSS   top-k of bf16-rounded-weight logits, softmax over the winners, clipped SwiGLU with
+ *            biases, expert sum rounded to bf16 before the residual
+ *            (reference `Bindings::experts`, src/weights/compute/feed_forward.rs:107-275)
+ *  NEMOTRON  sigmoid router with selection bias, non-gated squared-ReLU experts, optional shared
+ *            expert, single-rounding weighted add
+ *            (reference `Bindings::relu_experts`, src/weights/compute/nemotron.rs:286-545)
+ *  QWEN      softmax over all experts, top-k renormalised, SiLU-gated experts (no counterpart
+ *            operator in the reference, which runs Qwen as a dense FFN; semantics are composed
+ *            from its SiLU gate, shaders/elementwise.metal:67-87, and its Q4_K decoder). */
+typedef enum { OCO_ARCH_GPT_OSS = 0, OCO_ARCH_NEMOTRON = 1, OCO_ARCH_QWEN = 2 } oco_arch;
+
+/* GGUF tensor type codes (reference `src/tensor.rs:9-22`). */
+typedef enum { OCO_FMT_Q4_0 = 2, OCO_FMT_Q4_K = 12, OCO_FMT_MXFP4 = 39 } oco_weight_format;
+
+/* Geometry lowered once per model, as the reference's `ExpertPlan::new`
+ * (feed_forward.rs:43-72) and `ReluExpertPlan::new` (compute/nemotron.rs:142-184). */
+typedef struct {
+    int32_t arch;           /* oco_arch */
+    int32_t hidden;         /* model width (k of up/gate, n of down) */
+    int32_t ffn;            /* expert width */
+    int32_t experts;        /* <= 128 */
+    int32_t top_k;          /* <= 8 */
+    int32_t shared_ffn;     /* NEMOTRON: width of the always-on shared expert, 0 = none */
+    int32_t weight_format;  /* oco_weight_format of every expert bank */
+    int32_t normalize;      /* NEMOTRON: divide the weights by their sum */
+    float scale;            /* NEMOTRON: routed scaling factor */
+    int32_t gemm_impl;      /* 0 = tcgen05 tiles (the product path); 1 = plain CUDA-core tiles, a
+                               slow second implementation kept for cross-checking */
+} oco_moe_desc;
+
+/* Device pointers of one layer (reference `Experts{gate,up,down,router}`, src/weights/gpt_oss.rs:33-38;
+ * `ReluExperts`, src/weights/nemotron.rs:60-66). Unused members are NULL. */
+typedef struct {
+    const float* router_w;        /* f32 [experts, hidden] */
+    const float* router_b;        /* f32 [experts]: GPT_OSS logit bias / NEMOTRON selection bias */
+    const uint8_t* gate_w;        /* [experts][ffn][hidden packed] (gated families) */
+    const uint8_t* up_w;          /* [experts][ffn][hidden packed] */
+    const uint8_t* down_w;        /* [experts][hidden][ffn packed] */
+    const float* gate_b;          /* GPT_OSS f32 [experts, ffn] */
+    const float* up_b;            /* GPT_OSS f32 [experts, ffn] */
+    const float* down_b;          /* GPT_OSS f32 [experts, hidden] */
+    const uint8_t* shared_up_w;   /* NEMOTRON [shared_ffn][hidden packed] */
+    const uint8_t* shared_down_w; /* NEMOTRON [hidden][shared_ffn packed] */
+} oco_moe_weights;
+
+/* Addresses of the routing side-outputs inside the bound workspace, valid after a forward call
+ * has completed (reference `Routing{ids,plan,prob}`, src/weights/state.rs:112-117). The
+ * permutation is kept in flat form: `offsets` is the exclusive scan of per-expert route counts,
+ * `row_of_route` the expert-sorted row of each route (a stable sort of route indices by expert
+ * id, as `route_plan_tiled` produces, shaders/experts/routing.metal:4-39), `route_of_row` its
+ * inverse (the concatenated per-expert route lists). */
+typedef struct {
+    const float* logits;          /* f32 [rows, experts] */
+    const uint32_t* ids;          /* u32 [rows * top_k] */
+    const float* probs;           /* f32 [rows * top_k] */
+    const uint32_t* offsets;      /* u32 [experts + 1]  (rows > 1 only) */
+    const uint32_t* row_of_route; /* u32 [rows * top_k] (rows > 1 only) */
+    const uint32_t* route_of_row; /* u32 [rows * top_k] (rows > 1 only) */
+    const uint32_t* tiles;        /* u32 pairs (expert, first row in expert), rows > 1 only */
+    const uint32_t* tile_count;   /* u32 [1] */
+    const uint16_t* act;          /* f16 [routes, ffn] activated intermediate, expert-sorted rows (rows > 1) */
+    const uint16_t* y;            /* bf16 [routes, hidden] expert outputs in route order */
+} oco_moe_routing_view;
+
+typedef struct oco_moe_plan oco_moe_plan;
+
+/* ---- the operator ------------------------------------------------------------------------ */
+
+/* Replaces ExpertPlan::new / ReluExpertPlan::new plus Builder::experts / Builder::nemotron
+ * (src/weights/pipelines.rs:456-501): validates the geometry and fixes launch shapes. */
+int oco_moe_plan_create(const oco_moe_desc* desc, oco_moe_plan** out);
+void oco_moe_plan_destroy(oco_moe_plan* plan);
+
+/* Replaces the workspace sizing of CommonScratch::plan / Memory::new
+ * (src/weights/state.rs:148-177, src/weights/gpt_oss.rs:48-74). */
+size_t oco_moe_workspace_bytes(const oco_moe_plan* plan, int max_rows);
+
+/* Hands the plan a caller-owned device workspace of at least oco_moe_workspace_bytes(max_rows)
+ * bytes. Must be called with the owning device current; builds the TMA descriptors over it. */
+int oco_moe_bind_workspace(oco_moe_plan* plan, void* workspace, size_t bytes, int max_rows);
+
+/* Replaces binding `w: &Experts` / `w: &ReluExperts` at the call site. */
+int oco_moe_bind_weights(oco_moe_plan* plan, const oco_moe_weights* weights);
+
+/* Replaces Bindings::experts (feed_forward.rs:107-114) and Bindings::relu_experts
+ * (compute/nemotron.rs:286-293): reads x bf16 [rows, hidden] (the reference's `scratch.norm`),
+ * accumulates the layer's output into residual bf16 [rows, hidden] in place. rows == 1 takes the
+ * single-token kernels, rows > 1 the tiled ones, as in the reference. Only enqueues. */
+int oco_moe_forward(oco_moe_plan* plan, const uint16_t* x_bf16, uint16_t* residual_bf16, int rows,
+                    void* cuda_stream);
+
+/* The same call for host buffers: copies x and the residual to the device, runs the layer and
+ * copies the residual back, all on `cuda_stream`, then waits for the stream. Uses staging space
+ * inside the bound workspace. */
+int oco_moe_forward_host(oco_moe_plan* plan, const uint16_t* x_bf16_host, uint16_t* residual_bf16_host,
+                         int rows, void* cuda_stream);
+
+/* Waits for `cuda_stream`, then reports OCO_DEVICE_TIMEOUT if any bounded device wait gave up
+ * since the last poll, OCO_CUDA_ERROR on a CUDA failure, else OCO_OK. Maps to the completion of
+ * the reference's `submit` future (src/weights/compute/submission.rs:56-98). */
+int oco_moe_poll(oco_moe_plan* plan, void* cuda_stream);
+
+int oco_moe_routing(const oco_moe_plan* plan, oco_moe_routing_view* out);
+const char* oco_moe_last_error(const oco_moe_plan* plan);
+
+/* Number of kernels the last oco_moe_forward call launched. */
+int oco_moe_last_launch_count(const oco_moe_plan* plan);
+
+/* Per-kernel device timestamps, the counterpart of the reference's OCO_PROFILE counter heap
+ * (src/gpu/profile.rs:1-31, src/gpu/dispatch.rs:189-208). When enabled, oco_moe_forward records
+ * one CUDA event on the stream ahead of every kernel. After the stream has been waited for,
+ * oco_moe_phase_times fills up to `capacity` durations in milliseconds and the phase names of
+ * the last forward call and returns the number of phases (negative on a bad argument). */
+int oco_moe_set_profiling(oco_moe_plan* plan, int enabled);
+int oco_moe_phase_times(oco_moe_plan* plan, int capacity, float* ms, const char** names);
+
+/* ---- block decoders, exposed for bit-exact checks ------------------------------------------- */
+
+/* Decodes n_elems weights of a packed tensor to f32 exactly as the single-token kernels see
+ * them (reference `weight()`, shaders/matrix/weights.metal:48-77). */
+int oco_moe_dequant_f32(int weight_format, const uint8_t* w, size_t n_elems, float* out,
+                        void* cuda_stream);
+/* The tile kernels' operand: the same value rounded to half (reference projections.metal:227). */
+int oco_moe_dequant_f16(int weight_format, const uint8_t* w, size_t n_elems, uint16_t* out,
+                        void* cuda_stream);
+
+/* ---- runtime seam (replaces the Metal side of reference src/gpu.rs, src/gpu/buffer.rs) ------- */
+int oco_cuda_device_open(int device);                       /* Gpu::new, src/gpu.rs:40-60 */
+int oco_cuda_malloc(void** out, size_t bytes);              /* Gpu::new_buffer, src/gpu/buffer.rs */
+int oco_cuda_free(void* ptr);
+int oco_cuda_upload(void* dst_device, const void* src_host, size_t bytes, void* cuda_stream);   /* MappedRegions::new: GGUF spans byte for byte */
+int oco_cuda_download(void* dst_host, const void* src_device, size_t bytes, void* cuda_stream);
+int oco_cuda_stream_create(void** out);
+int oco_cuda_stream_destroy(void* cuda_stream);
+int oco_cuda_stream_sync(void* cuda_stream);
+
+const char* oco_moe_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OCO_MOE_H */

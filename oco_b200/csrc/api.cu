@@ -1,0 +1,647 @@
+// C ABI of the MoE layer: plan object, workspace carve-up, TMA descriptors and launch sequencing.
+// The sequencing mirrors the reference operators it replaces:
+//   Bindings::experts        src/weights/compute/feed_forward.rs:107-275
+//   Bindings::relu_experts   src/weights/compute/nemotron.rs:286-545
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+#include "decode.cuh"
+#include "gemm.cuh"
+#include "plan.cuh"
+#include "router.cuh"
+
+using namespace oco;
+
+namespace {
+
+constexpr int kTileSizes[3] = {32, 64, 128};
+constexpr int kMaxMarks = 16;
+
+struct Workspace {
+    uint32_t* status = nullptr;
+    float* logits = nullptr;
+    uint32_t* ids = nullptr;
+    float* probs = nullptr;
+    uint32_t* offsets = nullptr;
+    uint32_t* tile_count = nullptr;
+    uint32_t* tiles = nullptr;
+    uint32_t* row_of_route = nullptr;
+    uint32_t* route_of_row = nullptr;
+    uint16_t* xs = nullptr;       // half [R, H] expert-sorted input rows
+    uint16_t* act = nullptr;      // half [R, F] expert-sorted activated rows
+    uint16_t* y = nullptr;        // bf16 [R, H] expert outputs, route order
+    float* act1 = nullptr;        // f32 [K, F] single-token activations
+    __half* actfrag = nullptr;    // single-token B fragments of the down projection
+    uint16_t* xh = nullptr;       // half [T, H] token-order input rows (shared expert)
+    uint16_t* mid = nullptr;      // half [T, S] shared expert intermediate
+    uint16_t* shared_out = nullptr;  // bf16 [T, H]
+    float* sh_act1 = nullptr;
+    __half* sh_actfrag = nullptr;
+    uint32_t* sh_ids = nullptr;
+    uint16_t* host_x = nullptr;   // staging for the host-buffer entry point
+    uint16_t* host_res = nullptr;
+    size_t total = 0;
+};
+
+}  // namespace
+
+struct oco_moe_plan {
+    oco_moe_desc d{};
+    oco_moe_weights w{};
+    Workspace ws{};
+    bool have_ws = false, have_w = false;
+    int max_rows = 0;
+    int sm_count = 148;
+    int launches = 0;
+    int last_tile_rows = 0;
+    uint32_t up_row_bytes = 0, down_row_bytes = 0, shared_up_row_bytes = 0, shared_down_row_bytes = 0;
+    CUtensorMap map_xs[3], map_act[3], map_xh[3], map_mid[3];
+    // Per-phase timestamps (the counterpart of the reference's OCO_PROFILE counter heap,
+    // src/gpu/profile.rs:1-31, src/gpu/dispatch.rs:189-208): one event before each kernel.
+    bool profiling = false;
+    int n_marks = 0;
+    cudaEvent_t marks[kMaxMarks] = {};
+    const char* mark_names[kMaxMarks] = {};
+    char err[256] = {0};
+};
+
+namespace {
+
+int fail(oco_moe_plan* p, int code, const char* fmt, ...) {
+    if (p) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(p->err, sizeof(p->err), fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+#define CK(call)                                                                                     \
+    do {                                                                                             \
+        cudaError_t e_ = (call);                                                                     \
+        if (e_ != cudaSuccess) return fail(plan, OCO_CUDA_ERROR, "%s: %s", #call, cudaGetErrorString(e_)); \
+    } while (0)
+
+// Stamps the stream ahead of the phase called `name`; "end" closes the last phase.
+void mark(oco_moe_plan* plan, cudaStream_t st, const char* name) {
+    if (!plan->profiling || plan->n_marks >= kMaxMarks) return;
+    int i = plan->n_marks;
+    if (!plan->marks[i] && cudaEventCreate(&plan->marks[i]) != cudaSuccess) return;
+    if (cudaEventRecord(plan->marks[i], st) != cudaSuccess) return;
+    plan->mark_names[i] = name;
+    plan->n_marks = i + 1;
+}
+
+uint32_t packed_row_bytes(int fmt, int k) {
+    switch (fmt) {
+        case OCO_FMT_MXFP4: return (uint32_t)(k / 32 * 17);
+        case OCO_FMT_Q4_0: return (uint32_t)(k / 32 * 18);
+        case OCO_FMT_Q4_K: return (uint32_t)(k / 256 * 144);
+    }
+    return 0;
+}
+int block_elems(int fmt) { return fmt == OCO_FMT_Q4_K ? 256 : 32; }
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Lays the workspace out; with base == nullptr only the total is meaningful.
+Workspace carve(const oco_moe_desc& d, int max_rows, unsigned char* base) {
+    Workspace w;
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        unsigned char* p = base ? base + off : nullptr;
+        off = align_up(off + bytes, 256);
+        return p;
+    };
+    const size_t T = (size_t)max_rows, K = (size_t)d.top_k, R = T * K, E = (size_t)d.experts;
+    const size_t H = (size_t)d.hidden, F = (size_t)d.ffn, S = (size_t)d.shared_ffn;
+    const size_t P = (K + 1) / 2;
+    w.status = (uint32_t*)take(256);
+    w.logits = (float*)take(T * E * 4);
+    w.ids = (uint32_t*)take(R * 4);
+    w.probs = (float*)take(R * 4);
+    w.offsets = (uint32_t*)take((E + 1) * 4);
+    w.tile_count = (uint32_t*)take(4);
+    w.tiles = (uint32_t*)take(2 * (R / 32 + E + 1) * 4);
+    w.row_of_route = (uint32_t*)take(R * 4);
+    w.route_of_row = (uint32_t*)take(R * 4);
+    w.xs = (uint16_t*)take(R * H * 2);
+    w.act = (uint16_t*)take(R * F * 2);
+    w.y = (uint16_t*)take(R * H * 2);
+    w.act1 = (float*)take(K * F * 4);
+    w.actfrag = (__half*)take(P * (F / 32) * 128 * 2);
+    if (S) {
+        w.xh = (uint16_t*)take(T * H * 2);
+        w.mid = (uint16_t*)take(T * S * 2);
+        w.shared_out = (uint16_t*)take(T * H * 2);
+        w.sh_act1 = (float*)take(S * 4);
+        w.sh_actfrag = (__half*)take((S / 32) * 128 * 2);
+        w.sh_ids = (uint32_t*)take(256);
+    }
+    w.host_x = (uint16_t*)take(T * H * 2);
+    w.host_res = (uint16_t*)take(T * H * 2);
+    w.total = off;
+    return w;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int make_row_map(oco_moe_plan* plan, CUtensorMap* map, void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    static EncodeTiledFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        CK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+        if (q != cudaDriverEntryPointSuccess || !fn) return fail(plan, OCO_CUDA_ERROR, "cuTensorMapEncodeTiled unavailable");
+        encode = (EncodeTiledFn)fn;
+    }
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {64, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(plan, OCO_CUDA_ERROR, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return OCO_OK;
+}
+
+int pick_tile_index(int routes, int experts) {
+    int avg = routes / (experts > 0 ? experts : 1);
+    return avg >= 96 ? 2 : (avg >= 40 ? 1 : 0);
+}
+
+// ---- launch helpers ---------------------------------------------------------------------------
+// Opts a kernel into the full 227 KB of dynamic shared memory; each launch then asks for what it needs.
+constexpr size_t kMaxDynamicSmem = 232448;
+template <typename Kern>
+cudaError_t allow_smem(Kern k) {
+    return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynamicSmem);
+}
+
+template <int FMT, int EPI, int NT>
+int launch_gemm(oco_moe_plan* plan, const GemmParams& gp, const CUtensorMap& map, int max_tiles, cudaStream_t st) {
+    using S = GemmShape<EPI, NT>;
+    dim3 grid((gp.n + 127) / 128, max_tiles);
+    if (plan->d.gemm_impl == 1) {
+        grouped_gemm_simt_kernel<FMT, EPI, NT><<<grid, 128, 0, st>>>(gp);
+    } else {
+        static bool attr_set = false;
+        if (!attr_set) {
+            CK(allow_smem(grouped_gemm_tc_kernel<FMT, EPI, NT>));
+            attr_set = true;
+        }
+        grouped_gemm_tc_kernel<FMT, EPI, NT><<<grid, kGemmThreads, S::kSmemBytes, st>>>(gp, map);
+    }
+    plan->launches++;
+    CK(cudaGetLastError());
+    return OCO_OK;
+}
+
+template <int FMT, int EPI>
+int launch_gemm_nt(oco_moe_plan* plan, const GemmParams& gp, const CUtensorMap* maps, int nt_index, int max_tiles,
+                   cudaStream_t st) {
+    switch (nt_index) {
+        case 0: return launch_gemm<FMT, EPI, 32>(plan, gp, maps[0], max_tiles, st);
+        case 1: return launch_gemm<FMT, EPI, 64>(plan, gp, maps[1], max_tiles, st);
+        default: return launch_gemm<FMT, EPI, 128>(plan, gp, maps[2], max_tiles, st);
+    }
+}
+
+size_t decode_span_cap(uint32_t row_bytes) { return align_up((size_t)8 * row_bytes + 15, 16) + 32; }
+
+template <int ARCH, int FMT>
+int launch_expand(oco_moe_plan* plan, const DecodeExpandParams& ep, int grid, cudaStream_t st) {
+    size_t smem = (size_t)(ep.H / 32) * 2 * 4 * 16 + 2 * kDecodeWarps * 16 * 2 * 4 + (size_t)kExpandStages * 2 * ep.span_cap;
+    if (smem > kMaxDynamicSmem) return fail(plan, OCO_UNSUPPORTED_SHAPE, "hidden %d too large for the single-token kernels", ep.H);
+    static bool attr_set = false;
+    if (!attr_set) {
+        CK(allow_smem(decode_expand_kernel<ARCH, FMT>));
+        attr_set = true;
+    }
+    decode_expand_kernel<ARCH, FMT><<<grid, kDecodeThreads, smem, st>>>(ep);
+    plan->launches++;
+    CK(cudaGetLastError());
+    return OCO_OK;
+}
+
+template <int ARCH>
+struct Family;
+template <>
+struct Family<OCO_ARCH_GPT_OSS> {
+    static constexpr int kFmt = OCO_FMT_MXFP4, kEpiUp = kEpiSwigluF16;
+};
+template <>
+struct Family<OCO_ARCH_NEMOTRON> {
+    static constexpr int kFmt = OCO_FMT_Q4_0, kEpiUp = kEpiRelu2F16;
+};
+template <>
+struct Family<OCO_ARCH_QWEN> {
+    static constexpr int kFmt = OCO_FMT_Q4_K, kEpiUp = kEpiSiluF16;
+};
+
+// ---- single-token path ------------------------------------------------------------------------
+// rows == 1 of Bindings::experts (feed_forward.rs:125-163,241-257) and relu_experts_single
+// (compute/nemotron.rs:410-545): logits -> (selection fused into) expand -> down -> combine.
+template <int ARCH>
+int forward_single(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, cudaStream_t st) {
+    constexpr int FMT = Family<ARCH>::kFmt;
+    const oco_moe_desc& d = plan->d;
+    Workspace& ws = plan->ws;
+    const int H = d.hidden, F = d.ffn, E = d.experts, K = d.top_k;
+    mark(plan, st, "router_logits");
+    router_logits_small_kernel<ARCH><<<dim3((E + 7) / 8, 1), 256, 0, st>>>(x, plan->w.router_w, plan->w.router_b,
+                                                                          ws.logits, H, E);
+    plan->launches++;
+    const int grid = 2 * plan->sm_count;
+    if constexpr (FMT == OCO_FMT_MXFP4 || FMT == OCO_FMT_Q4_0) {
+        auto expand = [&](const uint8_t* gate_w, const uint8_t* up_w, const float* logits, int k, int f,
+                          uint32_t* ids, float* probs, float* act1, __half* actfrag) -> int {
+            DecodeExpandParams ep{};
+            ep.gate_w = gate_w; ep.up_w = up_w; ep.gate_b = plan->w.gate_b; ep.up_b = plan->w.up_b;
+            ep.x = x; ep.logits = logits; ep.sel_bias = plan->w.router_b;
+            ep.ids = ids; ep.probs = probs; ep.act = act1; ep.actfrag = actfrag;
+            ep.H = H; ep.F = f; ep.E = E; ep.K = k; ep.normalize = d.normalize; ep.scale = d.scale;
+            ep.row_bytes = plan->up_row_bytes; ep.span_cap = (uint32_t)decode_span_cap(plan->up_row_bytes);
+            return launch_expand<ARCH, FMT>(plan, ep, grid, st);
+        };
+        auto down = [&](const uint8_t* down_w, const float* bias, const uint32_t* ids, const __half* actfrag, int k,
+                        int f, uint32_t row_bytes, uint16_t* y) -> int {
+            DecodeDownParams dp{};
+            dp.down_w = down_w; dp.down_b = bias; dp.ids = ids; dp.actfrag = actfrag; dp.y = y;
+            dp.H = H; dp.F = f; dp.K = k; dp.row_bytes = row_bytes; dp.span_cap = (uint32_t)decode_span_cap(row_bytes);
+            size_t smem = (size_t)(f / 32) * 4 * 4 * 16 + 2 * kDecodeWarps * 16 * 2 * 4 +
+                          (size_t)kDownStages * 2 * dp.span_cap;
+            if (smem > kMaxDynamicSmem) return fail(plan, OCO_UNSUPPORTED_SHAPE, "expert width %d too large for the single-token kernels", f);
+            static bool attr_set = false;
+            if (!attr_set) {
+                CK(allow_smem(decode_down_kernel<FMT>));
+                attr_set = true;
+            }
+            decode_down_kernel<FMT><<<grid, kDecodeThreads, smem, st>>>(dp);
+            plan->launches++;
+            CK(cudaGetLastError());
+            return OCO_OK;
+        };
+        mark(plan, st, "expand");
+        int rc = expand(plan->w.gate_w, plan->w.up_w, ws.logits, K, F, ws.ids, ws.probs, ws.act1, ws.actfrag);
+        if (rc) return rc;
+        mark(plan, st, "down");
+        rc = down(plan->w.down_w, plan->w.down_b, ws.ids, ws.actfrag, K, F, plan->down_row_bytes, ws.y);
+        if (rc) return rc;
+        int shared_mode = 0;
+        if (ARCH == OCO_ARCH_NEMOTRON && d.shared_ffn) {
+            // The always-on expert runs through the same kernels as a one-expert bank
+            // (compute/nemotron.rs:460-509 runs it as dense matvecs beside the routed ones).
+            DecodeExpandParams ep{};
+            ep.gate_w = nullptr; ep.up_w = plan->w.shared_up_w; ep.x = x; ep.logits = nullptr;
+            ep.ids = ws.sh_ids + 8; ep.probs = (float*)(ws.sh_ids + 16); ep.act = ws.sh_act1; ep.actfrag = ws.sh_actfrag;
+            ep.H = H; ep.F = d.shared_ffn; ep.E = 1; ep.K = 1; ep.normalize = 0; ep.scale = 1.f;
+            ep.row_bytes = plan->shared_up_row_bytes; ep.span_cap = (uint32_t)decode_span_cap(plan->shared_up_row_bytes);
+            mark(plan, st, "shared_expand");
+            rc = launch_expand<ARCH, FMT>(plan, ep, grid, st);
+            if (rc) return rc;
+            mark(plan, st, "shared_down");
+            rc = down(plan->w.shared_down_w, nullptr, ws.sh_ids, ws.sh_actfrag, 1, d.shared_ffn,
+                      plan->shared_down_row_bytes, ws.shared_out);
+            if (rc) return rc;
+            shared_mode = 1;
+        }
+        const int pairs = H / 2;
+        mark(plan, st, "combine");
+        moe_combine_kernel<<<(pairs + 255) / 256, 256, 0, st>>>(ws.y, ws.probs, residual, ws.shared_out, H, 1, K,
+                                                               ARCH == OCO_ARCH_GPT_OSS ? 1 : 0, shared_mode);
+        plan->launches++;
+        CK(cudaGetLastError());
+        mark(plan, st, "end");
+        return OCO_OK;
+    } else {
+        return fail(plan, OCO_UNSUPPORTED_SHAPE, "no single-token kernels for this weight format");
+    }
+}
+
+// ---- tiled path ---------------------------------------------------------------------------------
+// rows > 1 of Bindings::experts (feed_forward.rs:164-240,258-274) and relu_experts
+// (compute/nemotron.rs:294-406): router -> plan -> gather -> up tiles (+activation) -> down tiles
+// -> combine.
+template <int ARCH>
+int forward_tiled(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int rows, cudaStream_t st) {
+    constexpr int FMT = Family<ARCH>::kFmt;
+    constexpr int EPI_UP = Family<ARCH>::kEpiUp;
+    const oco_moe_desc& d = plan->d;
+    Workspace& ws = plan->ws;
+    const int H = d.hidden, F = d.ffn, E = d.experts, K = d.top_k, R = rows * K;
+
+    size_t rsmem = (size_t)H * 4 + (size_t)8 * H * 2;
+    static bool router_attr = false;
+    if (!router_attr) {
+        CK(allow_smem(router_batched_kernel<ARCH>));
+        router_attr = true;
+    }
+    mark(plan, st, "router");
+    router_batched_kernel<ARCH><<<(rows + 7) / 8, 256, rsmem, st>>>(x, plan->w.router_w, plan->w.router_b, rows, H, E,
+                                                                  K, d.normalize, d.scale, ws.logits, ws.ids, ws.probs);
+    plan->launches++;
+    CK(cudaGetLastError());
+
+    const int nt_index = pick_tile_index(R, E);
+    const int NT = kTileSizes[nt_index];
+    plan->last_tile_rows = NT;
+    mark(plan, st, "route_plan");
+    route_plan_kernel<<<1, 1024, 0, st>>>(ws.ids, (uint32_t)R, (uint32_t)E, (uint32_t)NT, ws.offsets, ws.row_of_route,
+                                          ws.route_of_row, ws.tiles, ws.tile_count);
+    plan->launches++;
+    mark(plan, st, "permute");
+    permute_rows_kernel<<<R, 256, 0, st>>>(x, ws.route_of_row, K, H, ws.xs);
+    plan->launches++;
+    CK(cudaGetLastError());
+    const int max_tiles = R / NT + (E < R ? E : R);
+
+    GemmParams up{};
+    up.w0 = ARCH == OCO_ARCH_NEMOTRON ? plan->w.up_w : plan->w.gate_w;
+    up.w1 = ARCH == OCO_ARCH_NEMOTRON ? nullptr : plan->w.up_w;
+    up.b0 = ARCH == OCO_ARCH_GPT_OSS ? plan->w.gate_b : nullptr;
+    up.b1 = ARCH == OCO_ARCH_GPT_OSS ? plan->w.up_b : nullptr;
+    up.n = F; up.K = H; up.row_bytes = plan->up_row_bytes;
+    up.tiles = ws.tiles; up.tile_count = ws.tile_count; up.offsets = ws.offsets; up.route_of_row = nullptr;
+    up.xs = ws.xs; up.out = ws.act; up.status = ws.status; up.dense_rows = 0; up.tile_rows = NT;
+    mark(plan, st, "up_tiles");
+    int rc = launch_gemm_nt<FMT, EPI_UP>(plan, up, plan->map_xs, nt_index, max_tiles, st);
+    if (rc) return rc;
+
+    GemmParams dn{};
+    dn.w0 = plan->w.down_w; dn.w1 = nullptr;
+    dn.b0 = ARCH == OCO_ARCH_GPT_OSS ? plan->w.down_b : nullptr; dn.b1 = nullptr;
+    dn.n = H; dn.K = F; dn.row_bytes = plan->down_row_bytes;
+    dn.tiles = ws.tiles; dn.tile_count = ws.tile_count; dn.offsets = ws.offsets; dn.route_of_row = ws.route_of_row;
+    dn.xs = ws.act; dn.out = ws.y; dn.status = ws.status; dn.dense_rows = 0; dn.tile_rows = NT;
+    mark(plan, st, "down_tiles");
+    rc = launch_gemm_nt<FMT, kEpiDownBf16>(plan, dn, plan->map_act, nt_index, max_tiles, st);
+    if (rc) return rc;
+
+    int shared_mode = 0;
+    if (ARCH == OCO_ARCH_NEMOTRON && d.shared_ffn) {
+        // Shared expert as dense tiles over all rows: up -> relu^2 (bf16) -> down, joined to the
+        // residual as a bf16 add ahead of the routed sum (compute/nemotron.rs:302-316).
+        const int S = d.shared_ffn;
+        mark(plan, st, "shared_expert");
+        permute_rows_kernel<<<rows, 256, 0, st>>>(x, nullptr, 1, H, ws.xh);   // identity gather: bf16 -> half
+        plan->launches++;
+        const int snt = rows >= 96 ? 2 : (rows >= 40 ? 1 : 0);
+        const int SNT = kTileSizes[snt];
+        GemmParams su{};
+        su.w0 = plan->w.shared_up_w; su.n = S; su.K = H; su.row_bytes = plan->shared_up_row_bytes;
+        su.xs = ws.xh; su.out = ws.mid; su.status = ws.status; su.dense_rows = rows; su.tile_rows = SNT;
+        rc = launch_gemm_nt<FMT, kEpiRelu2Bf16F16>(plan, su, plan->map_xh, snt, (rows + SNT - 1) / SNT, st);
+        if (rc) return rc;
+        GemmParams sd{};
+        sd.w0 = plan->w.shared_down_w; sd.n = H; sd.K = S; sd.row_bytes = plan->shared_down_row_bytes;
+        sd.xs = ws.mid; sd.out = ws.shared_out; sd.status = ws.status; sd.dense_rows = rows; sd.tile_rows = SNT;
+        rc = launch_gemm_nt<FMT, kEpiDownBf16>(plan, sd, plan->map_mid, snt, (rows + SNT - 1) / SNT, st);
+        if (rc) return rc;
+        shared_mode = 2;
+    }
+    const size_t pairs = (size_t)rows * H / 2;
+    mark(plan, st, "combine");
+    moe_combine_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, st>>>(ws.y, ws.probs, residual, ws.shared_out, H,
+                                                                        rows, K, ARCH == OCO_ARCH_GPT_OSS ? 1 : 0,
+                                                                        shared_mode);
+    plan->launches++;
+    CK(cudaGetLastError());
+    mark(plan, st, "end");
+    return OCO_OK;
+}
+
+template <int ARCH>
+int forward_family(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int rows, cudaStream_t st) {
+    constexpr int FMT = Family<ARCH>::kFmt;
+    if (rows == 1 && (FMT == OCO_FMT_MXFP4 || FMT == OCO_FMT_Q4_0)) return forward_single<ARCH>(plan, x, residual, st);
+    return forward_tiled<ARCH>(plan, x, residual, rows, st);
+}
+
+}  // namespace
+
+// =================================================================================================
+extern "C" {
+
+const char* oco_moe_version(void) { return "oco-moe-b200 0.1 (sm_100a)"; }
+
+int oco_moe_plan_create(const oco_moe_desc* desc, oco_moe_plan** out) {
+    if (!desc || !out) return OCO_INVALID_ARGUMENT;
+    *out = nullptr;
+    oco_moe_plan* plan = new (std::nothrow) oco_moe_plan();
+    if (!plan) return OCO_INVALID_ARGUMENT;
+    plan->d = *desc;
+    *out = plan;  // handed out even on failure so the caller can read the message, then destroy
+    const oco_moe_desc& d = plan->d;
+    if (d.arch < OCO_ARCH_GPT_OSS || d.arch > OCO_ARCH_QWEN) return fail(plan, OCO_INVALID_ARGUMENT, "unknown arch %d", d.arch);
+    const int want = d.arch == OCO_ARCH_GPT_OSS ? OCO_FMT_MXFP4 : (d.arch == OCO_ARCH_NEMOTRON ? OCO_FMT_Q4_0 : OCO_FMT_Q4_K);
+    if (d.weight_format != want)
+        return fail(plan, OCO_UNSUPPORTED_SHAPE, "arch %d is built for weight format %d, got %d", d.arch, want, d.weight_format);
+    if (d.experts < 1 || d.experts > kMaxExperts) return fail(plan, OCO_UNSUPPORTED_SHAPE, "experts must be 1..128");
+    if (d.top_k < 1 || d.top_k > kMaxTopK || d.top_k > d.experts) return fail(plan, OCO_UNSUPPORTED_SHAPE, "top_k must be 1..8");
+    const int be = block_elems(d.weight_format);
+    if (d.hidden <= 0 || d.ffn <= 0 || d.hidden % be || d.ffn % be || (d.shared_ffn % be))
+        return fail(plan, OCO_UNSUPPORTED_SHAPE, "hidden, ffn and shared_ffn must be multiples of the %d-element block", be);
+    if (d.hidden % 32 || d.ffn % 32) return fail(plan, OCO_UNSUPPORTED_SHAPE, "hidden and ffn must be multiples of 32");
+    if (d.shared_ffn && d.arch != OCO_ARCH_NEMOTRON) return fail(plan, OCO_UNSUPPORTED_SHAPE, "shared expert only with NEMOTRON");
+    if (d.gemm_impl != 0 && d.gemm_impl != 1) return fail(plan, OCO_INVALID_ARGUMENT, "gemm_impl must be 0 or 1");
+    plan->up_row_bytes = packed_row_bytes(d.weight_format, d.hidden);
+    plan->down_row_bytes = packed_row_bytes(d.weight_format, d.ffn);
+    if (d.shared_ffn) {
+        plan->shared_up_row_bytes = packed_row_bytes(d.weight_format, d.hidden);
+        plan->shared_down_row_bytes = packed_row_bytes(d.weight_format, d.shared_ffn);
+    }
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0)
+        plan->sm_count = sms;
+    (void)cudaGetLastError();
+    return OCO_OK;
+}
+
+void oco_moe_plan_destroy(oco_moe_plan* plan) {
+    if (!plan) return;
+    for (int i = 0; i < kMaxMarks; i++)
+        if (plan->marks[i]) cudaEventDestroy(plan->marks[i]);
+    delete plan;
+}
+
+int oco_moe_set_profiling(oco_moe_plan* plan, int enabled) {
+    if (!plan) return OCO_INVALID_ARGUMENT;
+    plan->profiling = enabled != 0;
+    plan->n_marks = 0;
+    return OCO_OK;
+}
+
+int oco_moe_phase_times(oco_moe_plan* plan, int capacity, float* ms, const char** names) {
+    if (!plan || capacity < 0) return -1;
+    int phases = plan->n_marks > 0 ? plan->n_marks - 1 : 0;
+    for (int i = 0; i < phases && i < capacity; i++) {
+        float t = 0.f;
+        if (cudaEventElapsedTime(&t, plan->marks[i], plan->marks[i + 1]) != cudaSuccess) t = -1.f;
+        if (ms) ms[i] = t;
+        if (names) names[i] = plan->mark_names[i];
+    }
+    return phases;
+}
+
+size_t oco_moe_workspace_bytes(const oco_moe_plan* plan, int max_rows) {
+    if (!plan || max_rows < 1) return 0;
+    return carve(plan->d, max_rows, nullptr).total;
+}
+
+int oco_moe_bind_workspace(oco_moe_plan* plan, void* workspace, size_t bytes, int max_rows) {
+    if (!plan || !workspace || max_rows < 1) return fail(plan, OCO_INVALID_ARGUMENT, "null workspace or max_rows < 1");
+    if (((uintptr_t)workspace & 255u) != 0) return fail(plan, OCO_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
+    Workspace ws = carve(plan->d, max_rows, (unsigned char*)workspace);
+    if (bytes < ws.total) return fail(plan, OCO_INVALID_ARGUMENT, "workspace too small: %zu < %zu", bytes, ws.total);
+    const oco_moe_desc& d = plan->d;
+    // Control words and the never-written columns of the single-token fragments start at zero.
+    CK(cudaMemset(ws.status, 0, 256));
+    CK(cudaMemset(ws.actfrag, 0, (size_t)((d.top_k + 1) / 2) * (d.ffn / 32) * 128 * 2));
+    if (d.shared_ffn) {
+        CK(cudaMemset(ws.sh_actfrag, 0, (size_t)(d.shared_ffn / 32) * 128 * 2));
+        CK(cudaMemset(ws.sh_ids, 0, 256));
+    }
+    const uint64_t R = (uint64_t)max_rows * d.top_k;
+    for (int i = 0; i < 3; i++) {
+        int rc = make_row_map(plan, &plan->map_xs[i], ws.xs, R, d.hidden, kTileSizes[i]);
+        if (rc) return rc;
+        rc = make_row_map(plan, &plan->map_act[i], ws.act, R, d.ffn, kTileSizes[i]);
+        if (rc) return rc;
+        if (d.shared_ffn) {
+            rc = make_row_map(plan, &plan->map_xh[i], ws.xh, max_rows, d.hidden, kTileSizes[i]);
+            if (rc) return rc;
+            rc = make_row_map(plan, &plan->map_mid[i], ws.mid, max_rows, d.shared_ffn, kTileSizes[i]);
+            if (rc) return rc;
+        }
+    }
+    CK(cudaDeviceSynchronize());
+    plan->ws = ws;
+    plan->max_rows = max_rows;
+    plan->have_ws = true;
+    return OCO_OK;
+}
+
+int oco_moe_bind_weights(oco_moe_plan* plan, const oco_moe_weights* w) {
+    if (!plan || !w) return fail(plan, OCO_INVALID_ARGUMENT, "null weights");
+    const oco_moe_desc& d = plan->d;
+    if (!w->router_w || !w->up_w || !w->down_w) return fail(plan, OCO_INVALID_ARGUMENT, "router_w, up_w and down_w are required");
+    if (d.arch != OCO_ARCH_NEMOTRON && !w->gate_w) return fail(plan, OCO_INVALID_ARGUMENT, "gate_w is required for gated experts");
+    if (d.arch == OCO_ARCH_GPT_OSS && (!w->router_b || !w->gate_b || !w->up_b || !w->down_b))
+        return fail(plan, OCO_INVALID_ARGUMENT, "GPT_OSS needs router, gate, up and down biases");
+    if (d.arch == OCO_ARCH_NEMOTRON && !w->router_b) return fail(plan, OCO_INVALID_ARGUMENT, "NEMOTRON needs the selection bias");
+    if (d.shared_ffn && (!w->shared_up_w || !w->shared_down_w)) return fail(plan, OCO_INVALID_ARGUMENT, "shared expert weights missing");
+    if (((uintptr_t)w->router_w & 15u) != 0) return fail(plan, OCO_INVALID_ARGUMENT, "router_w must be 16-byte aligned");
+    plan->w = *w;
+    plan->have_w = true;
+    return OCO_OK;
+}
+
+int oco_moe_forward(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int rows, void* cuda_stream) {
+    if (!plan) return OCO_INVALID_ARGUMENT;
+    if (!plan->have_ws || !plan->have_w) return fail(plan, OCO_INVALID_ARGUMENT, "bind a workspace and weights first");
+    if (!x || !residual) return fail(plan, OCO_INVALID_ARGUMENT, "null x or residual");
+    if (rows < 1 || rows > plan->max_rows) return fail(plan, OCO_INVALID_ARGUMENT, "rows %d outside 1..%d", rows, plan->max_rows);
+    if (((uintptr_t)x & 15u) || ((uintptr_t)residual & 15u)) return fail(plan, OCO_INVALID_ARGUMENT, "x and residual must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    plan->launches = 0;
+    plan->n_marks = 0;
+    switch (plan->d.arch) {
+        case OCO_ARCH_GPT_OSS: return forward_family<OCO_ARCH_GPT_OSS>(plan, x, residual, rows, st);
+        case OCO_ARCH_NEMOTRON: return forward_family<OCO_ARCH_NEMOTRON>(plan, x, residual, rows, st);
+        default: return forward_family<OCO_ARCH_QWEN>(plan, x, residual, rows, st);
+    }
+}
+
+int oco_moe_forward_host(oco_moe_plan* plan, const uint16_t* x_host, uint16_t* residual_host, int rows,
+                         void* cuda_stream) {
+    if (!plan) return OCO_INVALID_ARGUMENT;
+    if (!plan->have_ws) return fail(plan, OCO_INVALID_ARGUMENT, "bind a workspace first");
+    if (!x_host || !residual_host || rows < 1 || rows > plan->max_rows) return fail(plan, OCO_INVALID_ARGUMENT, "bad host buffers or rows");
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    const size_t bytes = (size_t)rows * plan->d.hidden * 2;
+    CK(cudaMemcpyAsync(plan->ws.host_x, x_host, bytes, cudaMemcpyHostToDevice, st));
+    CK(cudaMemcpyAsync(plan->ws.host_res, residual_host, bytes, cudaMemcpyHostToDevice, st));
+    int rc = oco_moe_forward(plan, plan->ws.host_x, plan->ws.host_res, rows, cuda_stream);
+    if (rc) return rc;
+    CK(cudaMemcpyAsync(residual_host, plan->ws.host_res, bytes, cudaMemcpyDeviceToHost, st));
+    CK(cudaStreamSynchronize(st));
+    return OCO_OK;
+}
+
+int oco_moe_poll(oco_moe_plan* plan, void* cuda_stream) {
+    if (!plan || !plan->have_ws) return OCO_INVALID_ARGUMENT;
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    uint32_t word = 0;
+    CK(cudaMemcpyAsync(&word, plan->ws.status, 4, cudaMemcpyDeviceToHost, st));
+    CK(cudaStreamSynchronize(st));
+    if (word != 0) {
+        CK(cudaMemsetAsync(plan->ws.status, 0, 4, st));
+        CK(cudaStreamSynchronize(st));
+        return fail(plan, OCO_DEVICE_TIMEOUT, "a bounded device wait gave up (status %u)", word);
+    }
+    return OCO_OK;
+}
+
+int oco_moe_routing(const oco_moe_plan* plan, oco_moe_routing_view* out) {
+    if (!plan || !out || !plan->have_ws) return OCO_INVALID_ARGUMENT;
+    const Workspace& ws = plan->ws;
+    out->logits = ws.logits; out->ids = ws.ids; out->probs = ws.probs; out->offsets = ws.offsets;
+    out->row_of_route = ws.row_of_route; out->route_of_row = ws.route_of_row; out->tiles = ws.tiles;
+    out->tile_count = ws.tile_count; out->act = ws.act; out->y = ws.y;
+    return OCO_OK;
+}
+
+const char* oco_moe_last_error(const oco_moe_plan* plan) { return plan ? plan->err : "null plan"; }
+int oco_moe_last_launch_count(const oco_moe_plan* plan) { return plan ? plan->launches : 0; }
+
+static int dequant_any(int fmt, const uint8_t* w, size_t n, float* o32, uint16_t* o16, void* stream) {
+    if (!w || (!o32 && !o16)) return OCO_INVALID_ARGUMENT;
+    size_t chunks = (n + 63) / 64;
+    unsigned blocks = (unsigned)((chunks + 127) / 128);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (fmt) {
+        case OCO_FMT_MXFP4: dequant_kernel<OCO_FMT_MXFP4><<<blocks, 128, 0, st>>>(w, n, o32, o16); break;
+        case OCO_FMT_Q4_0: dequant_kernel<OCO_FMT_Q4_0><<<blocks, 128, 0, st>>>(w, n, o32, o16); break;
+        case OCO_FMT_Q4_K: dequant_kernel<OCO_FMT_Q4_K><<<blocks, 128, 0, st>>>(w, n, o32, o16); break;
+        default: return OCO_UNSUPPORTED_SHAPE;
+    }
+    return cudaGetLastError() == cudaSuccess ? OCO_OK : OCO_CUDA_ERROR;
+}
+int oco_moe_dequant_f32(int fmt, const uint8_t* w, size_t n, float* out, void* stream) {
+    return dequant_any(fmt, w, n, out, nullptr, stream);
+}
+int oco_moe_dequant_f16(int fmt, const uint8_t* w, size_t n, uint16_t* out, void* stream) {
+    return dequant_any(fmt, w, n, nullptr, out, stream);
+}
+
+// ---- runtime seam -----------------------------------------------------------------------------
+static int cu(cudaError_t e) { return e == cudaSuccess ? OCO_OK : OCO_CUDA_ERROR; }
+int oco_cuda_device_open(int device) { return cu(cudaSetDevice(device)); }
+int oco_cuda_malloc(void** out, size_t bytes) { return out ? cu(cudaMalloc(out, bytes)) : OCO_INVALID_ARGUMENT; }
+int oco_cuda_free(void* ptr) { return cu(cudaFree(ptr)); }
+int oco_cuda_upload(void* dst, const void* src, size_t bytes, void* stream) {
+    return cu(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+}
+int oco_cuda_download(void* dst, const void* src, size_t bytes, void* stream) {
+    return cu(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+}
+int oco_cuda_stream_create(void** out) {
+    if (!out) return OCO_INVALID_ARGUMENT;
+    cudaStream_t s;
+    cudaError_t e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
+    *out = (void*)s;
+    return cu(e);
+}
+int oco_cuda_stream_destroy(void* stream) { return cu(cudaStreamDestroy((cudaStream_t)stream)); }
+int oco_cuda_stream_sync(void* stream) { return cu(cudaStreamSynchronize((cudaStream_t)stream)); }
+
+}  // extern "C"

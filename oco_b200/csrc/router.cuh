@@ -1,0 +1,250 @@
+// Router: logits in the canonical summation order, top-k selection and combination weights.
+//
+// Canonical order (shared with the host checker so expert ids agree bit for bit): lane l of a
+// warp owns k = 4*l + 128*i, keeps four FMA chains (one per vector component), combines them as
+// (x+y)+(z+w), and the 32 lane sums are reduced by an xor butterfly 16,8,4,2,1. This is the lane
+// mapping of the reference's router kernels (shaders/experts/routing.metal:105-112,136-143;
+// shaders/nemotron.metal:156-162) with its unspecified `simd_sum` order fixed.
+#pragma once
+#include "common.cuh"
+
+namespace oco {
+
+__device__ __forceinline__ float warp_butterfly_sum(float s) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, off));
+    return s;
+}
+__device__ __forceinline__ float warp_max(float s) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) s = fmaxf(s, __shfl_xor_sync(0xffffffffu, s, off));
+    return s;
+}
+__device__ __forceinline__ uint32_t warp_min_u32(uint32_t s) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) s = min(s, __shfl_xor_sync(0xffffffffu, s, off));
+    return s;
+}
+__device__ __forceinline__ bool warp_any(bool p) { return __any_sync(0xffffffffu, p) != 0; }
+
+// One logit by one warp. x: bf16 row (global or shared), w: f32 row (global or shared).
+// RoundW rounds each weight to bf16 first (gpt-oss, routing.metal:108-109).
+template <bool RoundW>
+__device__ __forceinline__ float canonical_logit(const uint16_t* x, const float* w, int n, int lane) {
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    for (int k = lane * 4; k < n; k += 128) {
+        uint2 xv = *reinterpret_cast<const uint2*>(x + k);
+        float4 wv = *reinterpret_cast<const float4*>(w + k);
+        if (RoundW) {
+            wv.x = bf16_round(wv.x); wv.y = bf16_round(wv.y); wv.z = bf16_round(wv.z); wv.w = bf16_round(wv.w);
+        }
+        a0 = __fmaf_rn(__uint_as_float(xv.x << 16), wv.x, a0);
+        a1 = __fmaf_rn(__uint_as_float(xv.x & 0xffff0000u), wv.y, a1);
+        a2 = __fmaf_rn(__uint_as_float(xv.y << 16), wv.z, a2);
+        a3 = __fmaf_rn(__uint_as_float(xv.y & 0xffff0000u), wv.w, a3);
+    }
+    return warp_butterfly_sum(__fadd_rn(__fadd_rn(a0, a1), __fadd_rn(a2, a3)));
+}
+
+// Top-k selection by one warp over logits distributed as logit[j] = expert (lane + 32*j).
+// Every lane returns the same ids / probs.
+//   GPT_OSS  (routing.metal:71-94): ties to the lowest index; winners rounded to bf16; softmax over
+//            the winners; probabilities rounded to bf16; any non-finite logit makes all probs NaN.
+//   NEMOTRON (nemotron.metal:167-211): score = sigmoid(logit); selection on score + bias; weights
+//            are the unbiased scores, optionally normalised (floor 2^-14) and scaled.
+//   QWEN     top-k of the logits, softmax over the winners (= softmax over all, renormalised).
+template <int ARCH>
+__device__ __forceinline__ void select_experts(const float (&logit)[4], int E, int K, const float* sel_bias,
+                                               int normalize, float scale, int lane,
+                                               uint32_t (&ids)[kMaxTopK], float (&probs)[kMaxTopK]) {
+    const float ninf = __uint_as_float(0xff800000u);
+    float v[4], score[4];
+    bool invalid = false;
+    uint32_t avail = 0;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        int e = lane + 32 * j;
+        bool valid = e < E;
+        float l = valid ? logit[j] : 0.0f;
+        bool fin = !nonfinite(l);
+        invalid = invalid || (valid && !fin);
+        if (valid) avail |= 1u << j;
+        if (ARCH == OCO_ARCH_NEMOTRON) {
+            score[j] = __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_det(-l)));
+            v[j] = valid ? __fadd_rn(score[j], sel_bias[e]) : ninf;
+        } else {
+            score[j] = 0.f;
+            v[j] = (valid && fin) ? l : ninf;
+        }
+    }
+    invalid = warp_any(invalid);
+    float chosen[kMaxTopK];
+    float total = 0.f;
+#pragma unroll
+    for (int r = 0; r < kMaxTopK; r++) {
+        ids[r] = 0; probs[r] = 0.f; chosen[r] = 0.f;
+        if (r >= K) continue;
+        if (ARCH == OCO_ARCH_NEMOTRON) {
+            float bv = ninf;
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (v[j] > bv) bv = v[j];
+            float peak = warp_max(bv);
+            uint32_t cand = 0xffffffffu;
+#pragma unroll
+            for (int j = 3; j >= 0; j--)
+                if (((avail >> j) & 1u) && v[j] == peak) cand = (uint32_t)(lane + 32 * j);
+            uint32_t id = warp_min_u32(cand);
+            if (id == 0xffffffffu) id = 0;
+            ids[r] = id;
+            float mine = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if ((int)(id >> 5) == j) { mine = score[j]; if ((int)(id & 31u) == lane) v[j] = ninf; }
+            float w = __shfl_sync(0xffffffffu, mine, (int)(id & 31u));
+            chosen[r] = w;
+            total = __fadd_rn(total, w);
+        } else {
+            float bv = ninf;
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (((avail >> j) & 1u) && v[j] > bv) bv = v[j];
+            float peak = warp_max(bv);
+            uint32_t cand = 0xffffffffu;
+#pragma unroll
+            for (int j = 3; j >= 0; j--)
+                if (((avail >> j) & 1u) && v[j] == peak) cand = (uint32_t)(lane + 32 * j);
+            uint32_t id = warp_min_u32(cand);
+            if (id == 0xffffffffu) id = 0;
+            ids[r] = id;
+            chosen[r] = ARCH == OCO_ARCH_GPT_OSS ? bf16_round(peak) : peak;
+            if ((int)(id & 31u) == lane) avail &= ~(1u << (id >> 5));
+        }
+    }
+    if (ARCH == OCO_ARCH_NEMOTRON) {
+        float divisor = normalize ? fmaxf(total, 6.103515625e-5f) : 1.0f;
+#pragma unroll
+        for (int r = 0; r < kMaxTopK; r++)
+            if (r < K) probs[r] = invalid ? qnan() : __fmul_rn(__fdiv_rn(chosen[r], divisor), scale);
+    } else {
+#pragma unroll
+        for (int r = 0; r < kMaxTopK; r++)
+            if (r < K) invalid = invalid || nonfinite(chosen[r]);
+        float sum = 0.f;
+        float ex[kMaxTopK];
+#pragma unroll
+        for (int r = 0; r < kMaxTopK; r++) {
+            ex[r] = 0.f;
+            if (r < K && !invalid) {
+                ex[r] = exp_det(__fadd_rn(chosen[r], -chosen[0]));
+                sum = __fadd_rn(sum, ex[r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < kMaxTopK; r++)
+            if (r < K) {
+                float p = invalid ? qnan() : __fdiv_rn(ex[r], sum);
+                probs[r] = (ARCH == OCO_ARCH_GPT_OSS && !invalid) ? bf16_round(p) : p;
+            }
+    }
+}
+
+// Reads the E logits of one token into the distributed form select_experts takes.
+__device__ __forceinline__ void load_logits(const float* logits, int E, int lane, float (&v)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        int e = lane + 32 * j;
+        v[j] = e < E ? logits[e] : 0.0f;
+    }
+}
+
+// ---- kernels ------------------------------------------------------------------------------------
+
+// A few tokens: one warp per (expert, token), operands straight from global memory
+// (reference router_logits, routing.metal:131-146). grid (ceil(E/8), T), 256 threads.
+template <int ARCH>
+__global__ void __launch_bounds__(256) router_logits_small_kernel(const uint16_t* __restrict__ x,
+                                                                  const float* __restrict__ w,
+                                                                  const float* __restrict__ bias,
+                                                                  float* __restrict__ logits, int H, int E) {
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int e = blockIdx.x * 8 + warp, t = blockIdx.y;
+    if (e >= E) return;
+    float s = canonical_logit<ARCH == OCO_ARCH_GPT_OSS>(x + (size_t)t * H, w + (size_t)e * H, H, lane);
+    if (ARCH == OCO_ARCH_GPT_OSS) s = __fadd_rn(s, bf16_round(bias[e]));
+    if (lane == 0) logits[(size_t)t * E + e] = s;
+}
+
+// Selection for tokens whose logits are already in memory. grid T, 32 threads.
+template <int ARCH>
+__global__ void __launch_bounds__(32) router_select_kernel(const float* __restrict__ logits,
+                                                           const float* __restrict__ sel_bias, int E, int K,
+                                                           int normalize, float scale, uint32_t* __restrict__ ids,
+                                                           float* __restrict__ probs) {
+    int t = blockIdx.x, lane = threadIdx.x;
+    float v[4];
+    load_logits(logits + (size_t)t * E, E, lane, v);
+    uint32_t id[kMaxTopK];
+    float p[kMaxTopK];
+    select_experts<ARCH>(v, E, K, sel_bias, normalize, scale, lane, id, p);
+#pragma unroll
+    for (int r = 0; r < kMaxTopK; r++)
+        if (r < K && lane == r) { ids[(size_t)t * K + r] = id[r]; probs[(size_t)t * K + r] = p[r]; }
+}
+
+// Many tokens: eight tokens per CTA (one per warp) share each router row through shared memory,
+// then each warp selects for its token (reference router, routing.metal:96-128;
+// router_sigmoid, nemotron.metal:140-212). Dynamic shared memory: 8*H bf16 + H f32.
+template <int ARCH>
+__global__ void __launch_bounds__(256) router_batched_kernel(const uint16_t* __restrict__ x,
+                                                             const float* __restrict__ w,
+                                                             const float* __restrict__ bias, int T, int H, int E,
+                                                             int K, int normalize, float scale,
+                                                             float* __restrict__ logits, uint32_t* __restrict__ ids,
+                                                             float* __restrict__ probs) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    float* ws = reinterpret_cast<float*>(smem);                      // [H]
+    uint16_t* xs = reinterpret_cast<uint16_t*>(smem + (size_t)H * 4);  // [8][H]
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int t0 = blockIdx.x * 8;
+    int t = t0 + warp;
+    // Stage the CTA's eight token rows (8-byte chunks; H is a multiple of 4).
+    int rows = min(8, T - t0);
+    for (int i = threadIdx.x; i < rows * (H / 4); i += 256) {
+        int r = i / (H / 4), c = i % (H / 4);
+        reinterpret_cast<uint2*>(xs + (size_t)r * H)[c] = reinterpret_cast<const uint2*>(x + (size_t)(t0 + r) * H)[c];
+    }
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int e = 0; e < E; e++) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < H / 4; i += 256) {
+            float4 wv = reinterpret_cast<const float4*>(w + (size_t)e * H)[i];
+            if (ARCH == OCO_ARCH_GPT_OSS) {
+                wv.x = bf16_round(wv.x); wv.y = bf16_round(wv.y); wv.z = bf16_round(wv.z); wv.w = bf16_round(wv.w);
+            }
+            reinterpret_cast<float4*>(ws)[i] = wv;
+        }
+        __syncthreads();
+        if (t < T) {
+            float s = canonical_logit<false>(xs + (size_t)warp * H, ws, H, lane);
+            if (ARCH == OCO_ARCH_GPT_OSS) s = __fadd_rn(s, bf16_round(bias[e]));
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if ((e >> 5) == j && (e & 31) == lane) v[j] = s;
+        }
+    }
+    if (t >= T) return;
+    if (logits) {
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (lane + 32 * j < E) logits[(size_t)t * E + lane + 32 * j] = v[j];
+    }
+    uint32_t id[kMaxTopK];
+    float p[kMaxTopK];
+    select_experts<ARCH>(v, E, K, ARCH == OCO_ARCH_NEMOTRON ? bias : nullptr, normalize, scale, lane, id, p);
+#pragma unroll
+    for (int r = 0; r < kMaxTopK; r++)
+        if (r < K && lane == r) { ids[(size_t)t * K + r] = id[r]; probs[(size_t)t * K + r] = p[r]; }
+}
+
+}  // namespace oco
