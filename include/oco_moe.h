@@ -161,6 +161,24 @@ int oco_moe_last_launch_count(const oco_moe_plan* plan);
 int oco_moe_set_profiling(oco_moe_plan* plan, int enabled);
 int oco_moe_phase_times(oco_moe_plan* plan, int capacity, float* ms, const char** names);
 
+/* Expert ids and combination weights of ONE token, computed without any device allocation and
+ * without a bound workspace. This call has no counterpart in the reference. It serves hosts that
+ * may not allocate once a session is set up: an engine that plans its whole device budget up
+ * front the way oco's arena does, a plugin living beside a framework allocator that already
+ * owns the GPU's free memory, or a loop that cannot take the device-wide stall of cudaMalloc.
+ * The scratch it needs (one token's router logits and an arrival counter) sits in a 1024-byte
+ * device array inside the library image, held by every GPU that loads the library until exit.
+ * Limits: experts <= 128 (what the array holds), top_k <= 8, hidden a multiple of 4 and <= 16384;
+ * anything larger is refused with OCO_UNSUPPORTED_SHAPE and a message in `err` (if given).
+ * x_bf16, router_w, router_b, ids_out [top_k] and probs_out [top_k] are device pointers.
+ * All calls on a GPU share the array, which keeps the last call's contents; calls that overlap on
+ * the same GPU race on it and must be serialised by the caller. The first call on each device
+ * looks the array's address up and should come before any stream capture starts.
+ * Results equal those of oco_moe_forward at rows == 1 (same logits order, same selection). */
+int oco_moe_route_token_static(int arch, const uint16_t* x_bf16, const float* router_w, const float* router_b,
+                               int hidden, int experts, int top_k, int normalize, float scale,
+                               uint32_t* ids_out, float* probs_out, void* cuda_stream, char* err, size_t err_len);
+
 /* ---- block decoders, exposed for bit-exact checks ------------------------------------------- */
 
 /* Decodes n_elems weights of a packed tensor to f32 exactly as the single-token kernels see

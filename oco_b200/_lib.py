@@ -45,6 +45,9 @@ SIGNATURES = {
     "oco_moe_last_launch_count": (C.c_int, [C.c_void_p]),
     "oco_moe_set_profiling": (C.c_int, [C.c_void_p, C.c_int]),
     "oco_moe_phase_times": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_char_p)]),
+    "oco_moe_route_token_static": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                              C.c_int, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p, C.c_char_p,
+                                              C.c_size_t]),
     "oco_moe_dequant_f32": (C.c_int, [C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
     "oco_moe_dequant_f16": (C.c_int, [C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
     "oco_cuda_device_open": (C.c_int, [C.c_int]),
