@@ -105,7 +105,10 @@ typedef struct {
     const uint32_t* route_of_row; /* u32 [rows * top_k] (rows > 1 only) */
     const uint32_t* tiles;        /* u32 pairs (expert, first row in expert), rows > 1 only */
     const uint32_t* tile_count;   /* u32 [1] */
-    const uint16_t* act;          /* f16 [routes, ffn] activated intermediate, expert-sorted rows (rows > 1) */
+    const uint16_t* act;          /* f16 [routes, ffn] activated intermediate, expert-sorted rows (rows > 1).
+                                     Columns are in the tiles' operand order: within each 32-element block
+                                     (64 for Q4_K) element j sits at 2*(j mod h) + j div h, h = 16 (32 for Q4_K),
+                                     the order in which the packed code bytes hold their two nibbles. */
     const uint16_t* y;            /* bf16 [routes, hidden] expert outputs in route order */
 } oco_moe_routing_view;
 

@@ -5,11 +5,13 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 #include <new>
 
 #include "common.cuh"
 #include "decode.cuh"
 #include "gemm.cuh"
+#include "gemm_wide.cuh"
 #include "plan.cuh"
 #include "router.cuh"
 
@@ -17,7 +19,8 @@ using namespace oco;
 
 namespace {
 
-constexpr int kTileSizes[3] = {32, 64, 128};
+constexpr int kTileSizes[4] = {32, 64, 128, 256};
+constexpr int kTileKinds = 4;
 constexpr int kMaxMarks = 16;
 
 struct Workspace {
@@ -58,9 +61,10 @@ struct oco_moe_plan {
     int launches = 0;
     int last_tile_rows = 0;
     uint32_t up_row_bytes = 0, down_row_bytes = 0, shared_up_row_bytes = 0, shared_down_row_bytes = 0;
-    CUtensorMap map_xs[3], map_act[3], map_xh[3], map_mid[3];
+    CUtensorMap map_xs[kTileKinds], map_act[kTileKinds], map_xh[kTileKinds], map_mid[kTileKinds];
     // Per-phase timestamps (the counterpart of the reference's OCO_PROFILE counter heap,
     // src/gpu/profile.rs:1-31, src/gpu/dispatch.rs:189-208): one event before each kernel.
+    bool narrow_tiles = false;   // OCO_MOE_NARROW_TILES=1: keep the generic tile kernel for 256-route tiles too
     bool profiling = false;
     int n_marks = 0;
     cudaEvent_t marks[kMaxMarks] = {};
@@ -172,9 +176,11 @@ int make_row_map(oco_moe_plan* plan, CUtensorMap* map, void* base, uint64_t rows
     return OCO_OK;
 }
 
+// Route-tile height by the average number of routes per expert: wide tiles decode an expert's
+// weights fewer times, narrow ones waste fewer MMA columns on small experts.
 int pick_tile_index(int routes, int experts) {
     int avg = routes / (experts > 0 ? experts : 1);
-    return avg >= 96 ? 2 : (avg >= 40 ? 1 : 0);
+    return avg >= 192 ? 3 : (avg >= 96 ? 2 : (avg >= 40 ? 1 : 0));
 }
 
 // ---- launch helpers ---------------------------------------------------------------------------
@@ -197,8 +203,28 @@ int launch_gemm(oco_moe_plan* plan, const GemmParams& gp, const CUtensorMap& map
             CK(allow_smem(grouped_gemm_tc_kernel<FMT, EPI, NT>));
             attr_set = true;
         }
-        grouped_gemm_tc_kernel<FMT, EPI, NT><<<grid, kGemmThreads, S::kSmemBytes, st>>>(gp, map);
+        grouped_gemm_tc_kernel<FMT, EPI, NT><<<grid, S::kThreads, S::kSmemBytes, st>>>(gp, map);
     }
+    plan->launches++;
+    CK(cudaGetLastError());
+    return OCO_OK;
+}
+
+// 256-route tiles of the 32-element block formats take the wide kernel (two A tiles per CTA,
+// coalesced weight streaming); the CUDA-core cross-check and Q4_K keep the generic one.
+template <int FMT, int EPI>
+int launch_gemm_wide(oco_moe_plan* plan, GemmParams gp, const CUtensorMap& map, int max_tiles, int experts,
+                     cudaStream_t st) {
+    const size_t bytes = (size_t)experts * gp.n * gp.row_bytes;
+    gp.w0_end = (const uint8_t*)(((uintptr_t)gp.w0 + bytes + 15) & ~(uintptr_t)15);
+    gp.w1_end = gp.w1 ? (const uint8_t*)(((uintptr_t)gp.w1 + bytes + 15) & ~(uintptr_t)15) : nullptr;
+    static bool attr_set = false;
+    if (!attr_set) {
+        CK(allow_smem(grouped_gemm_wide_kernel<FMT, EPI>));
+        attr_set = true;
+    }
+    dim3 grid((gp.n + (epi_gated(EPI) ? 127 : 255)) / (epi_gated(EPI) ? 128 : 256), max_tiles);
+    grouped_gemm_wide_kernel<FMT, EPI><<<grid, WideShape::kThreads, WideShape::kSmemBytes, st>>>(gp, map);
     plan->launches++;
     CK(cudaGetLastError());
     return OCO_OK;
@@ -207,10 +233,15 @@ int launch_gemm(oco_moe_plan* plan, const GemmParams& gp, const CUtensorMap& map
 template <int FMT, int EPI>
 int launch_gemm_nt(oco_moe_plan* plan, const GemmParams& gp, const CUtensorMap* maps, int nt_index, int max_tiles,
                    cudaStream_t st) {
+    if constexpr (FMT != OCO_FMT_Q4_K) {
+        if (nt_index == 3 && plan->d.gemm_impl == 0 && !plan->narrow_tiles)
+            return launch_gemm_wide<FMT, EPI>(plan, gp, maps[3], max_tiles, gp.tiles ? plan->d.experts : 1, st);
+    }
     switch (nt_index) {
         case 0: return launch_gemm<FMT, EPI, 32>(plan, gp, maps[0], max_tiles, st);
         case 1: return launch_gemm<FMT, EPI, 64>(plan, gp, maps[1], max_tiles, st);
-        default: return launch_gemm<FMT, EPI, 128>(plan, gp, maps[2], max_tiles, st);
+        case 2: return launch_gemm<FMT, EPI, 128>(plan, gp, maps[2], max_tiles, st);
+        default: return launch_gemm<FMT, EPI, 256>(plan, gp, maps[3], max_tiles, st);
     }
 }
 
@@ -358,7 +389,7 @@ int forward_tiled(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int
                                           ws.route_of_row, ws.tiles, ws.tile_count);
     plan->launches++;
     mark(plan, st, "permute");
-    permute_rows_kernel<<<R, 256, 0, st>>>(x, ws.route_of_row, K, H, ws.xs);
+    permute_rows_kernel<<<R, 256, 0, st>>>(x, ws.route_of_row, K, H, FMT == OCO_FMT_Q4_K ? 32 : 16, ws.xs);
     plan->launches++;
     CK(cudaGetLastError());
     const int max_tiles = R / NT + (E < R ? E : R);
@@ -391,9 +422,9 @@ int forward_tiled(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int
         // residual as a bf16 add ahead of the routed sum (compute/nemotron.rs:302-316).
         const int S = d.shared_ffn;
         mark(plan, st, "shared_expert");
-        permute_rows_kernel<<<rows, 256, 0, st>>>(x, nullptr, 1, H, ws.xh);   // identity gather: bf16 -> half
+        permute_rows_kernel<<<rows, 256, 0, st>>>(x, nullptr, 1, H, FMT == OCO_FMT_Q4_K ? 32 : 16, ws.xh);  // identity gather
         plan->launches++;
-        const int snt = rows >= 96 ? 2 : (rows >= 40 ? 1 : 0);
+        const int snt = rows >= 192 ? 3 : (rows >= 96 ? 2 : (rows >= 40 ? 1 : 0));
         const int SNT = kTileSizes[snt];
         GemmParams su{};
         su.w0 = plan->w.shared_up_w; su.n = S; su.K = H; su.row_bytes = plan->shared_up_row_bytes;
@@ -458,6 +489,7 @@ int oco_moe_plan_create(const oco_moe_desc* desc, oco_moe_plan** out) {
         plan->shared_up_row_bytes = packed_row_bytes(d.weight_format, d.hidden);
         plan->shared_down_row_bytes = packed_row_bytes(d.weight_format, d.shared_ffn);
     }
+    { const char* e = getenv("OCO_MOE_NARROW_TILES"); plan->narrow_tiles = e && e[0] == '1'; }
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) == cudaSuccess &&
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0)
@@ -511,7 +543,7 @@ int oco_moe_bind_workspace(oco_moe_plan* plan, void* workspace, size_t bytes, in
         CK(cudaMemset(ws.sh_ids, 0, 256));
     }
     const uint64_t R = (uint64_t)max_rows * d.top_k;
-    for (int i = 0; i < 3; i++) {
+    for (int i = 0; i < kTileKinds; i++) {
         int rc = make_row_map(plan, &plan->map_xs[i], ws.xs, R, d.hidden, kTileSizes[i]);
         if (rc) return rc;
         rc = make_row_map(plan, &plan->map_act[i], ws.act, R, d.ffn, kTileSizes[i]);

@@ -52,139 +52,166 @@ struct GemmParams {
     uint32_t* status;
     int dense_rows;      // dense mode: number of rows (single expert 0)
     int tile_rows;       // NT
+    const uint8_t* w0_end;  // first byte past the 16-byte-aligned envelope of w0 / w1 (wide kernel)
+    const uint8_t* w1_end;
 };
 
-// ---- packed block -> 32 halves -------------------------------------------------------------------
-// out[0..3]: elements 0-7, out[4..7]: 8-15, out[8..11]: 16-23, out[12..15]: 24-31 (half2 each).
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) { return __byte_perm(a, b, sel); }
+// ---- operand order ---------------------------------------------------------------------------------
+// A code byte holds two elements of its block: byte j of an MXFP4 / Q4_0 block holds elements j and
+// j + 16, byte i of a Q4_K 64-element chunk holds elements i and i + 32. Decoding a byte yields the
+// two as one half2, and the tiles keep them adjacent: within every block the contraction index runs
+// in "operand order" (byte 0 low nibble, byte 0 high nibble, byte 1 low nibble, ...). The activation
+// rows are written in the same order, so no decoded value is ever moved to another lane or
+// register before it is stored; a dot product does not care in which order k is visited.
+__host__ __device__ inline int operand_pos(int fmt, int k) {
+    if (fmt == OCO_FMT_Q4_K) return (k & ~63) + (((k & 31) << 1) | ((k >> 5) & 1));
+    return (k & ~31) + (((k & 15) << 1) | ((k >> 4) & 1));
+}
+
 __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
     __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
     return *reinterpret_cast<uint32_t*>(&r);
 }
+// The four code bytes of a word -> four half2 (low nibble in .x, high nibble in .y).
+__device__ __forceinline__ void cvt_e2m1x2_x4(uint32_t w, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+        : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+        : "r"(w));
+}
+// Two copies of an f32 rounded to half (round to nearest even, subnormals kept).
+__device__ __forceinline__ uint32_t f32_to_half2_dup(float f) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %1;" : "=r"(r) : "f"(f));
+    return r;
+}
 
-// Raw words of one 64-element slice of a packed row, fetched ahead of use so the next slice's
-// global loads overlap the current slice's decode.
-//   MXFP4: 2 blocks x 5 aligned words;  Q4_0: 2 blocks x 6 aligned words;
-//   Q4_K : 4 header words (d, dmin, 12 scale bytes) + 8 code words of one sub-block pair.
+// Raw words of one half-slice (32 operand positions = four 16-byte chunks of the A tile) of a
+// packed row, fetched ahead of use so global-load latency hides behind the decode of earlier ones.
+//   MXFP4: block 2*kb64 + h, 5 aligned words;  Q4_0: likewise, 6 aligned words;
+//   Q4_K : 4 header words (d, dmin, 12 scale bytes) + code bytes 16h..16h+15 of the sub-block pair.
 template <int FMT>
-struct RawK64 {
-    static constexpr int kWords = FMT == OCO_FMT_MXFP4 ? 10 : 12;
+struct RawHalf {
+    static constexpr int kWords = FMT == OCO_FMT_MXFP4 ? 5 : (FMT == OCO_FMT_Q4_0 ? 6 : 8);
     uint32_t w[kWords];
 };
 
 template <int FMT>
-__device__ __forceinline__ void load_raw_k64(const uint8_t* row, int kb64, int K, RawK64<FMT>& raw) {
+__device__ __forceinline__ void load_half(const uint8_t* row, int kb64, int h, int K, RawHalf<FMT>& raw) {
     if (FMT == OCO_FMT_Q4_K) {
         // Super-blocks are 144 bytes; rows are whole super-blocks, so 4-byte alignment of the
         // tensor base carries to every word read here. Unaligned bases take the byte path.
         const uint8_t* b = row + (size_t)(kb64 >> 2) * 144;
-        const uint8_t* codes = b + 16 + (kb64 & 3) * 32;
+        const uint8_t* codes = b + 16 + (kb64 & 3) * 32 + 16 * h;
         if ((((uintptr_t)b) & 3u) == 0) {
             const uint32_t* hw = reinterpret_cast<const uint32_t*>(b);
             const uint32_t* cw = reinterpret_cast<const uint32_t*>(codes);
 #pragma unroll
             for (int i = 0; i < 4; i++) raw.w[i] = __ldg(hw + i);
 #pragma unroll
-            for (int i = 0; i < 8; i++) raw.w[4 + i] = __ldg(cw + i);
+            for (int i = 0; i < 4; i++) raw.w[4 + i] = __ldg(cw + i);
         } else {
 #pragma unroll
             for (int i = 0; i < 4; i++) raw.w[i] = ldg_u32_unaligned(b + 4 * i);
 #pragma unroll
-            for (int i = 0; i < 8; i++) raw.w[4 + i] = ldg_u32_unaligned(codes + 4 * i);
+            for (int i = 0; i < 4; i++) raw.w[4 + i] = ldg_u32_unaligned(codes + 4 * i);
         }
     } else {
         constexpr int kBytes = FMT == OCO_FMT_MXFP4 ? 17 : 18;
-        constexpr int kW = FMT == OCO_FMT_MXFP4 ? 5 : 6;
-        const int nblk = K >> 5;
+        const int blk = 2 * kb64 + h;
+        if (blk < (K >> 5)) {
+            uintptr_t a = (uintptr_t)(row + (size_t)blk * kBytes);
+            const uint32_t* w = (const uint32_t*)(a & ~(uintptr_t)3);
 #pragma unroll
-        for (int b = 0; b < 2; b++) {
-            int blk = 2 * kb64 + b;
-            if (blk < nblk) {
-                uintptr_t a = (uintptr_t)(row + (size_t)blk * kBytes);
-                const uint32_t* w = (const uint32_t*)(a & ~(uintptr_t)3);
+            for (int i = 0; i < RawHalf<FMT>::kWords; i++) raw.w[i] = __ldg(w + i);
+        } else {
 #pragma unroll
-                for (int i = 0; i < kW; i++) raw.w[b * kW + i] = __ldg(w + i);
-            } else {
-#pragma unroll
-                for (int i = 0; i < kW; i++) raw.w[b * kW + i] = 0;
-            }
+            for (int i = 0; i < RawHalf<FMT>::kWords; i++) raw.w[i] = 0;
         }
     }
 }
 
-// MXFP4 block (17 bytes starting `sh` bits into w[0]) -> 32 halves
-// (reference decoder: shaders/matrix/weights.metal:40-46; half rounding: projections.metal:227).
-// out[0..3]: elements 0-7, [4..7]: 8-15, [8..11]: 16-23, [12..15]: 24-31 (half2 each).
+// MXFP4 block (17 bytes starting `sh` bits into w[0]) -> 16 half2 in operand order, each
+// half( e2m1 * 2^(e-127) ) (reference decoder: shaders/matrix/weights.metal:40-46; half rounding:
+// projections.metal:227). Scales 2^-24..2^15 are halves themselves and one multiply rounds once.
+// Any other header (including 0, the reserved 255 and powers beyond the half range) takes two
+// multiplies: the first by a power of two that keeps every product a normal half (exact), the
+// second carrying the single rounding, so the result equals rounding the exact product once.
 __device__ __forceinline__ void decode_mxfp4_block(const uint32_t* w, uint32_t sh, uint32_t* out) {
-    uint32_t e = (w[0] >> sh) & 0xffu;
-    uint32_t s1 = sh + 8u;
-    uint32_t q[4] = {__funnelshift_rc(w[0], w[1], s1), __funnelshift_rc(w[1], w[2], s1),
-                     __funnelshift_rc(w[2], w[3], s1), __funnelshift_rc(w[3], w[4], s1)};
-    bool fast = (e - 103u) <= 39u;  // 2^-24 .. 2^15: the scale itself is a half
-    uint32_t sc = 0;
-    if (fast) {
-        uint32_t hb = e >= 113u ? ((e - 112u) << 10) : (1u << (e - 103u));
-        sc = hb | (hb << 16);
-    }
-    float fs = e8m0_scale(e);
+    const uint32_t e = (w[0] >> sh) & 0xffu;
+    const uint32_t s1 = sh + 8u;
+    const uint32_t q[4] = {__funnelshift_rc(w[0], w[1], s1), __funnelshift_rc(w[1], w[2], s1),
+                           __funnelshift_rc(w[2], w[3], s1), __funnelshift_rc(w[3], w[4], s1)};
+    const bool plain = (e - 103u) <= 39u;
+    if (__all_sync(__activemask(), plain)) {
+        const uint32_t sc = f32_to_half2_dup(__uint_as_float(e << 23));
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        uint32_t A0 = e2m1x2_to_half2(q[i]), A1 = e2m1x2_to_half2(q[i] >> 8), A2 = e2m1x2_to_half2(q[i] >> 16),
-                 A3 = e2m1x2_to_half2(q[i] >> 24);
-        uint32_t r[4] = {prmt(A0, A1, 0x5410), prmt(A2, A3, 0x5410), prmt(A0, A1, 0x7632), prmt(A2, A3, 0x7632)};
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            if (fast) {
-                r[j] = hmul2_u32(r[j], sc);
-            } else {
-                __half2 h = *reinterpret_cast<__half2*>(&r[j]);
-                __half2 o = __floats2half2_rn(__fmul_rn(__low2float(h), fs), __fmul_rn(__high2float(h), fs));
-                r[j] = *reinterpret_cast<uint32_t*>(&o);
-            }
+        for (int i = 0; i < 4; i++) {
+            uint32_t r0, r1, r2, r3;
+            cvt_e2m1x2_x4(q[i], r0, r1, r2, r3);
+            out[4 * i] = hmul2_u32(r0, sc); out[4 * i + 1] = hmul2_u32(r1, sc);
+            out[4 * i + 2] = hmul2_u32(r2, sc); out[4 * i + 3] = hmul2_u32(r3, sc);
         }
-        out[2 * i] = r[0]; out[2 * i + 1] = r[1];
-        out[8 + 2 * i] = r[2]; out[8 + 2 * i + 1] = r[3];
+    } else {
+        const int t = (int)e - 127;
+        const int t1 = max(-13, min(13, t));
+        const int t2 = t - t1;
+        const uint32_t h1 = (uint32_t)(t1 + 15) << 10;
+        const uint32_t sa = h1 | (h1 << 16);
+        uint32_t sb;
+        if (e == 255u) sb = 0x7e007e00u;                                   // NaN
+        else if (t2 > 15) sb = 0x7bff7bffu;                                // 65504: any non-zero product overflows
+        else sb = f32_to_half2_dup(t2 < -126 ? 0.0f : __uint_as_float((uint32_t)(t2 + 127) << 23));
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            uint32_t r0, r1, r2, r3;
+            cvt_e2m1x2_x4(q[i], r0, r1, r2, r3);
+            out[4 * i] = hmul2_u32(hmul2_u32(r0, sa), sb); out[4 * i + 1] = hmul2_u32(hmul2_u32(r1, sa), sb);
+            out[4 * i + 2] = hmul2_u32(hmul2_u32(r2, sa), sb); out[4 * i + 3] = hmul2_u32(hmul2_u32(r3, sa), sb);
+        }
     }
 }
 
-// Q4_0 block (18 bytes starting `sh` bits into w[0]): half( d * (q - 8) ) (reference q4_decode,
-// shaders/matrix/q4_tile.metal:24-37). d*(q-8) is exact in f32, so one half multiply rounds once.
+// Q4_0 block (18 bytes starting `sh` bits into w[0]) -> 16 half2 in operand order:
+// half( d * (q - 8) ) (reference q4_decode, shaders/matrix/q4_tile.metal:24-37). q - 8 is exact as
+// a half and d is a half, so one half multiply rounds the exact product once.
 __device__ __forceinline__ void decode_q4_0_block(const uint32_t* w, uint32_t sh, uint32_t* out) {
-    uint32_t hd = __funnelshift_rc(w[0], w[1], sh) & 0xffffu;  // sh <= 24
-    uint32_t d2 = hd | (hd << 16);
-    uint32_t s2 = sh + 16u;  // 16..40
+    const uint32_t hd = __funnelshift_rc(w[0], w[1], sh) & 0xffffu;  // sh <= 24
+    const uint32_t d2 = hd | (hd << 16);
+    const uint32_t s2 = sh + 16u;  // 16..40
     uint32_t q[4];
     if (s2 <= 32u) {
         q[0] = __funnelshift_rc(w[0], w[1], s2); q[1] = __funnelshift_rc(w[1], w[2], s2);
         q[2] = __funnelshift_rc(w[2], w[3], s2); q[3] = __funnelshift_rc(w[3], w[4], s2);
     } else {
-        uint32_t s3 = s2 - 32u;
+        const uint32_t s3 = s2 - 32u;
         q[0] = __funnelshift_rc(w[1], w[2], s3); q[1] = __funnelshift_rc(w[2], w[3], s3);
         q[2] = __funnelshift_rc(w[3], w[4], s3); q[3] = __funnelshift_rc(w[4], w[5], s3);
     }
-    const uint32_t magic = 0x64006400u, bias = 0x64086408u;  // 1024 and 1032 as halves
+    const uint32_t bias = 0x64086408u;  // 1032 as halves: (1024 + q) - 1032 = q - 8
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        // bytes b0..b3 hold codes j..j+3 (low nibbles) and j+16..j+19 (high nibbles)
-        uint32_t lo = q[i] & 0x0f0f0f0fu, hi = (q[i] >> 4) & 0x0f0f0f0fu;
-        uint32_t r[4] = {prmt(lo, 0, 0x4140) | magic, prmt(lo, 0, 0x4342) | magic, prmt(hi, 0, 0x4140) | magic,
-                         prmt(hi, 0, 0x4342) | magic};
+        const uint32_t lo = q[i] & 0x0f0f0f0fu, hi = (q[i] >> 4) & 0x0f0f0f0fu;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            __half2 h = __hsub2(*reinterpret_cast<__half2*>(&r[j]), *reinterpret_cast<const __half2*>(&bias));
-            __half2 o = __hmul2(h, *reinterpret_cast<__half2*>(&d2));
-            r[j] = *reinterpret_cast<uint32_t*>(&o);
+            // byte j of lo -> bits 0..7, byte j of hi -> bits 16..23, 0x64 above each: halves 1024 + q
+            uint32_t v = (__byte_perm(lo, hi, (uint32_t)(j | ((4 + j) << 8))) & 0x00ff00ffu) | 0x64006400u;
+            __half2 h = __hsub2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&bias));
+            __half2 o = __hmul2(h, *reinterpret_cast<const __half2*>(&d2));
+            out[4 * i + j] = *reinterpret_cast<uint32_t*>(&o);
         }
-        out[2 * i] = r[0]; out[2 * i + 1] = r[1];
-        out[8 + 2 * i] = r[2]; out[8 + 2 * i + 1] = r[3];
     }
 }
 
-// Q4_K: sub-blocks 2c and 2c+1 of one super-block -> 64 halves: half( d*sc*q - dmin*m ) with one
-// f32 rounding in the subtraction (weights.metal:67-77). hdr = the super-block's first 16 bytes,
-// codes = the pair's 32 code bytes. out[0..15]: elements 0-31 (low nibbles), [16..31]: 32-63.
-__device__ __forceinline__ void decode_q4_k_pair(const uint32_t* hdr, const uint32_t* codes, int c, uint32_t* out) {
-    float d = f16_bits_to_f32((uint16_t)(hdr[0] & 0xffffu)), dm = f16_bits_to_f32((uint16_t)(hdr[0] >> 16));
+// Q4_K: code bytes 16h..16h+15 of sub-blocks 2c and 2c+1 of one super-block -> 16 half2 in operand
+// order: each byte gives half2( d*sc0*q_lo - dmin*m0 , d*sc1*q_hi - dmin*m1 ), with one f32 rounding
+// in the subtraction before the half rounding (weights.metal:67-77).
+__device__ __forceinline__ void decode_q4_k_half(const uint32_t* hdr, const uint32_t* codes, int c, uint32_t* out) {
+    const float d = f16_bits_to_f32((uint16_t)(hdr[0] & 0xffffu)), dm = f16_bits_to_f32((uint16_t)(hdr[0] >> 16));
     auto sbyte = [&](int i) -> uint32_t {  // scale byte i of 12 (hdr words 1..3)
         uint32_t word = i < 4 ? hdr[1] : (i < 8 ? hdr[2] : hdr[3]);
         return (word >> (8 * (i & 3))) & 0xffu;
@@ -192,7 +219,7 @@ __device__ __forceinline__ void decode_q4_k_pair(const uint32_t* hdr, const uint
     float scale[2], minimum[2];
 #pragma unroll
     for (int h = 0; h < 2; h++) {
-        int s = 2 * c + h;
+        const int s = 2 * c + h;
         uint32_t sc, mn;
         if (s < 4) {
             sc = sbyte(s) & 63u;
@@ -205,60 +232,76 @@ __device__ __forceinline__ void decode_q4_k_pair(const uint32_t* hdr, const uint
         minimum[h] = __fmul_rn(dm, (float)mn);
     }
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        uint32_t word = codes[i];
+    for (int i = 0; i < 4; i++) {
+        const uint32_t word = codes[i];
 #pragma unroll
-        for (int j = 0; j < 2; j++) {
-            uint32_t b0 = (word >> (16 * j)) & 0xffu, b1 = (word >> (16 * j + 8)) & 0xffu;
-            __half2 lo = __floats2half2_rn(__fsub_rn(__fmul_rn(scale[0], (float)(b0 & 15u)), minimum[0]),
-                                           __fsub_rn(__fmul_rn(scale[0], (float)(b1 & 15u)), minimum[0]));
-            __half2 hi = __floats2half2_rn(__fsub_rn(__fmul_rn(scale[1], (float)(b0 >> 4)), minimum[1]),
-                                           __fsub_rn(__fmul_rn(scale[1], (float)(b1 >> 4)), minimum[1]));
-            out[2 * i + j] = *reinterpret_cast<uint32_t*>(&lo);
-            out[16 + 2 * i + j] = *reinterpret_cast<uint32_t*>(&hi);
+        for (int j = 0; j < 4; j++) {
+            const uint32_t b = (word >> (8 * j)) & 0xffu;
+            __half2 v = __floats2half2_rn(__fsub_rn(__fmul_rn(scale[0], (float)(b & 15u)), minimum[0]),
+                                          __fsub_rn(__fmul_rn(scale[1], (float)(b >> 4)), minimum[1]));
+            out[4 * i + j] = *reinterpret_cast<uint32_t*>(&v);
         }
     }
 }
 
-// Decodes a fetched slice into `out` (32 half2, ascending k); positions at or past K are zero.
+// Decodes a fetched half-slice into `out` (16 half2 in operand order); positions at or past K are zero.
 template <int FMT>
-__device__ __forceinline__ void decode_raw_k64(const RawK64<FMT>& raw, const uint8_t* row, int kb64, int K,
-                                               uint32_t (&out)[32]) {
+__device__ __forceinline__ void decode_half(const RawHalf<FMT>& raw, const uint8_t* row, int kb64, int h, int K,
+                                            uint32_t (&out)[16]) {
     if (FMT == OCO_FMT_Q4_K) {
-        decode_q4_k_pair(raw.w, raw.w + 4, kb64 & 3, out);
+        decode_q4_k_half(raw.w, raw.w + 4, kb64 & 3, out);
     } else {
         constexpr int kBytes = FMT == OCO_FMT_MXFP4 ? 17 : 18;
-        constexpr int kW = FMT == OCO_FMT_MXFP4 ? 5 : 6;
-        const int nblk = K >> 5;
+        const int blk = 2 * kb64 + h;
+        if (blk < (K >> 5)) {
+            const uint32_t sh = ((uint32_t)(uintptr_t)(row + (size_t)blk * kBytes) & 3u) * 8u;
+            if (FMT == OCO_FMT_MXFP4) decode_mxfp4_block(raw.w, sh, out);
+            else decode_q4_0_block(raw.w, sh, out);
+        } else {
 #pragma unroll
-        for (int b = 0; b < 2; b++) {
-            int blk = 2 * kb64 + b;
-            if (blk < nblk) {
-                uint32_t sh = ((uint32_t)(uintptr_t)(row + (size_t)blk * kBytes) & 3u) * 8u;
-                if (FMT == OCO_FMT_MXFP4) decode_mxfp4_block(raw.w + b * kW, sh, out + 16 * b);
-                else decode_q4_0_block(raw.w + b * kW, sh, out + 16 * b);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 16; i++) out[16 * b + i] = 0;
-            }
+            for (int i = 0; i < 16; i++) out[i] = 0;
         }
     }
 }
 
-// Decodes the 64 weights [64*kb64, 64*kb64 + 64) of one packed row (fetch + decode).
+// Decodes the 64 weights [64*kb64, 64*kb64 + 64) of one packed row (fetch + decode), operand order.
 template <int FMT>
 __device__ __forceinline__ void decode_row_k64(const uint8_t* row, int kb64, int K, uint32_t (&out)[32]) {
-    RawK64<FMT> raw;
-    load_raw_k64<FMT>(row, kb64, K, raw);
-    decode_raw_k64<FMT>(raw, row, kb64, K, out);
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        RawHalf<FMT> raw;
+        uint32_t v[16];
+        load_half<FMT>(row, kb64, h, K, raw);
+        decode_half<FMT>(raw, row, kb64, h, K, v);
+#pragma unroll
+        for (int i = 0; i < 16; i++) out[16 * h + i] = v[i];
+    }
 }
 
 // ---- epilogue arithmetic -------------------------------------------------------------------------
+// Tile epilogues evaluate the activations with the hardware exp2 / reciprocal approximations
+// (relative error about 1e-6, far inside the half rounding of the stored value). Routing never
+// goes through these: ids and weights use the exact sequence shared with the host checker.
+__device__ __forceinline__ float sigmoid_times(float g, float scale) {   // sigmoid(scale * g), g finite
+    float e = __expf(-fabsf(g) * scale);
+    return __fdividef(g < 0 ? e : 1.0f, 1.0f + e);
+}
+__device__ __forceinline__ float swiglu_clipped_fast(float g, float u) {
+    if (nonfinite(g) || nonfinite(u)) return qnan();
+    g = fminf(g, 7.0f);
+    u = fminf(fmaxf(u, -6.0f), 8.0f);
+    return sigmoid_times(g, 1.702f) * g * u;
+}
+__device__ __forceinline__ float silu_gate_bf16_fast(float a, float b) {
+    if (nonfinite(a) || nonfinite(b)) return qnan();
+    return bf16_round(bf16_round(sigmoid_times(a, 1.0f) * a) * b);
+}
+
 // a: accumulator of w0 (+ bias), b: accumulator of w1 (+ bias); returns the stored 16-bit pattern.
 template <int EPI>
 __device__ __forceinline__ uint16_t epilogue_value(float a, float b) {
-    if (EPI == kEpiSwigluF16) return f32_to_f16_bits(swiglu_clipped(a, b));
-    if (EPI == kEpiSiluF16) return f32_to_f16_bits(silu_gate_bf16(bf16_round(a), bf16_round(b)));
+    if (EPI == kEpiSwigluF16) return f32_to_f16_bits(swiglu_clipped_fast(a, b));
+    if (EPI == kEpiSiluF16) return f32_to_f16_bits(silu_gate_bf16_fast(bf16_round(a), bf16_round(b)));
     if (EPI == kEpiRelu2F16 || EPI == kEpiRelu2Bf16F16) {
         float r = bf16_round(a);
         float u = fmaxf(r, 0.0f);
@@ -319,26 +362,56 @@ __device__ __forceinline__ uint32_t umma_idesc_f16(uint32_t n) {
     return (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
-constexpr int kGemmThreads = 160;  // warps 0-3: producers then epilogue; warp 4: MMA issue + TMEM
-
+// Thread layout: producer warps first (they turn into the epilogue), then one warp that owns the
+// tensor memory allocation and issues the MMAs. A 64-element slice of the tile's weight rows is
+// (matrices x 2) half-slices per row; the 128 rows x kParts producer threads share them so that a
+// thread decodes one or two 32-element blocks per slice. Many light producer warps hide the
+// decode's dependent-instruction latency better than few heavy ones.
+//   gated, NT = 256: 4 parts (16 producer warps): part = matrix + 2 * half; both accumulators fill
+//                    all 512 tensor-memory columns, one CTA per SM.
+//   otherwise:       2 parts (8 producer warps), two CTAs per SM; gated: part = matrix (both
+//                    halves), single matrix: part = half.
 template <int EPI, int NT>
 struct GemmShape {
     static constexpr bool kGated = epi_gated(EPI);
-    static constexpr int kABytes = 128 * 128;                 // 128 rows x 64 halves
+    static constexpr int kMats = kGated ? 2 : 1;
+    static constexpr bool kWide = kGated && NT == 256;
+    static constexpr int kParts = kWide ? 4 : 2;
+    static constexpr int kHalvesPerThread = kMats * 2 / kParts;       // 1 or 2
+    static constexpr int kProducerWarps = 4 * kParts;
+    static constexpr int kThreads = (kProducerWarps + 1) * 32;
+    static constexpr int kABytes = 128 * 128;                          // 128 rows x 64 halves
     static constexpr int kBBytes = NT * 128;
-    static constexpr int kStageBytes = (kGated ? 2 : 1) * kABytes + kBBytes;
-    static constexpr int kBudget = 110 * 1024;                // two CTAs per SM
+    static constexpr int kStageBytes = kMats * kABytes + kBBytes;
+    static constexpr int kCtasPerSm = kWide ? 1 : 2;
+    static constexpr int kBudget = kWide ? 200 * 1024 : 110 * 1024;
     static constexpr int kStagesRaw = kBudget / kStageBytes;
     static constexpr int kStages = kStagesRaw > 4 ? 4 : kStagesRaw;
-    static constexpr int kTmemCols = (kGated ? 2 : 1) * NT;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr int kTmemCols = kMats * NT;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/ + NT * 4 /*row map*/;
 };
 
+// Decodes one half-slice of a weight row and stores it as four 16-byte chunks of the K-major,
+// 128-byte-swizzled A tile (chunk c of row r lives at chunk c ^ (r & 7)).
+template <int FMT>
+__device__ __forceinline__ void produce_half(const RawHalf<FMT>& raw, const uint8_t* row, int kb, int h, int K,
+                                             uint32_t tile_row_addr, uint32_t sw) {
+    uint32_t v[16];
+    decode_half<FMT>(raw, row, kb, h, K, v);
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        const uint32_t addr = tile_row_addr + ((((uint32_t)(4 * h + c)) ^ sw) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v[4 * c]), "r"(v[4 * c + 1]),
+                     "r"(v[4 * c + 2]), "r"(v[4 * c + 3]) : "memory");
+    }
+}
+
 template <int FMT, int EPI, int NT>
-__global__ void __launch_bounds__(kGemmThreads, 2)
+__global__ void __launch_bounds__(GemmShape<EPI, NT>::kThreads, GemmShape<EPI, NT>::kCtasPerSm)
 grouped_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_b) {
     using S = GemmShape<EPI, NT>;
     constexpr bool GATED = S::kGated;
+    constexpr int PW = S::kProducerWarps;
     extern __shared__ unsigned char smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -370,14 +443,19 @@ grouped_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
     const uint32_t accum_bar = bars + 8u * (2 * S::kStages);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + S::kStages * S::kStageBytes + 8 * (2 * S::kStages + 1));
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    // Destination row of every live column of the tile (the scatter of the down projection).
+    uint32_t* out_rows = reinterpret_cast<uint32_t*>(gen_base + S::kStages * S::kStageBytes + 256);
+    for (uint32_t i = tid; i < nv; i += S::kThreads)
+        out_rows[i] = (EPI == kEpiDownBf16 && p.route_of_row) ? p.route_of_row[row0 + i] : row0 + i;
 
     if (tid == 0) {
-        for (int s = 0; s < S::kStages; s++) { mbar_init(full_bar(s), 129); mbar_init(empty_bar(s), 1); }
+        // full: one arrival per producer warp plus the thread that announces the TMA bytes
+        for (int s = 0; s < S::kStages; s++) { mbar_init(full_bar(s), PW + 1); mbar_init(empty_bar(s), 1); }
         mbar_init(accum_bar, 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == 4) {
+    if (warp == PW) {
         tmem_alloc(smem_u32(tmem_slot), S::kTmemCols);
         tmem_relinquish();
     }
@@ -386,63 +464,76 @@ grouped_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp < 4) {
+    if (warp < PW) {
         // ===== producers ==========================================================================
-        const int frow = min(f0 + tid, p.n - 1);
-        const uint8_t* row0p = p.w0 + ((size_t)expert * p.n + frow) * p.row_bytes;
-        const uint8_t* row1p = GATED ? p.w1 + ((size_t)expert * p.n + frow) * p.row_bytes : nullptr;
-        const uint32_t row_off = (uint32_t)(tid >> 3) * 1024u + (uint32_t)(tid & 7) * 128u;
-        const uint32_t sw = (uint32_t)(tid & 7);
-        RawK64<FMT> cur0, cur1, nxt0, nxt1;
-        load_raw_k64<FMT>(row0p, 0, p.K, cur0);
-        if (GATED) load_raw_k64<FMT>(row1p, 0, p.K, cur1);
-        for (int kb = 0; kb < nkb; kb++) {
-            const int s = kb % S::kStages;
-            const uint32_t ph = (uint32_t)(kb / S::kStages) & 1u;
-            const uint32_t stage = base + (uint32_t)s * S::kStageBytes;
-            if (kb + 1 < nkb) {  // next slice's loads fly while this one is decoded
-                load_raw_k64<FMT>(row0p, kb + 1, p.K, nxt0);
-                if (GATED) load_raw_k64<FMT>(row1p, kb + 1, p.K, nxt1);
-            }
-            mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status);
-            if (tid == 0) {
-                mbar_arrive_expect_tx(full_bar(s), (uint32_t)S::kBBytes);
-                tma_load_2d(stage + (GATED ? 2 : 1) * S::kABytes, &tmap_b, kb * 64, (int)row0, full_bar(s));
-            }
-            uint32_t v[32];
-            decode_raw_k64<FMT>(cur0, row0p, kb, p.K, v);
+        const int prow = tid & 127;                                   // weight row within the tile
+        const int part = tid >> 7;
+        const int mat = GATED ? (part & 1) : 0;                        // which weight matrix this thread decodes
+        const int half0 = S::kHalvesPerThread == 2 ? 0 : (GATED ? part >> 1 : part);  // first (or only) half-slice
+        const int frow = min(f0 + prow, p.n - 1);
+        const uint8_t* wrow = (mat ? p.w1 : p.w0) + ((size_t)expert * p.n + frow) * p.row_bytes;
+        const uint32_t row_off = (uint32_t)(prow >> 3) * 1024u + (uint32_t)(prow & 7) * 128u + (uint32_t)mat * S::kABytes;
+        const uint32_t sw = (uint32_t)(prow & 7);
+        // Packed words of the next slices ride in registers while the current one is decoded.
+        constexpr int kAhead = 1;
+        constexpr int HPT = S::kHalvesPerThread;
+        RawHalf<FMT> ring[kAhead + 1][HPT];
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
-                uint32_t addr = stage + row_off + (((uint32_t)c ^ sw) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v[4 * c]), "r"(v[4 * c + 1]),
-                             "r"(v[4 * c + 2]), "r"(v[4 * c + 3]) : "memory");
-            }
-            if (GATED) {
-                decode_raw_k64<FMT>(cur1, row1p, kb, p.K, v);
+        for (int u = 0; u < kAhead; u++) {
+            if (u < nkb) {
 #pragma unroll
-                for (int c = 0; c < 8; c++) {
-                    uint32_t addr = stage + S::kABytes + row_off + (((uint32_t)c ^ sw) << 4);
-                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v[4 * c]), "r"(v[4 * c + 1]),
-                                 "r"(v[4 * c + 2]), "r"(v[4 * c + 3]) : "memory");
+                for (int q = 0; q < HPT; q++) load_half<FMT>(wrow, u, half0 + q, p.K, ring[u][q]);
+            }
+        }
+        for (int kb0 = 0; kb0 < nkb; kb0 += kAhead + 1) {
+#pragma unroll
+            for (int u = 0; u <= kAhead; u++) {
+                const int kb = kb0 + u;
+                if (kb < nkb) {
+                    if (kb + kAhead < nkb) {
+#pragma unroll
+                        for (int q = 0; q < HPT; q++)
+                            load_half<FMT>(wrow, kb + kAhead, half0 + q, p.K, ring[(u + kAhead) & kAhead][q]);
+                    }
+                    const int s = kb % S::kStages;
+                    const uint32_t ph = (uint32_t)(kb / S::kStages) & 1u;
+                    const uint32_t stage = base + (uint32_t)s * S::kStageBytes;
+                    // One lane per warp waits and, below, arrives: hundreds of threads arriving on one
+                    // barrier serialise on its shared-memory word and cost more than the decode.
+                    if (lane == 0) mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status);
+                    __syncwarp();
+                    if (tid == 0) {
+                        mbar_arrive_expect_tx(full_bar(s), (uint32_t)S::kBBytes);
+                        tma_load_2d(stage + S::kMats * S::kABytes, &tmap_b, kb * 64, (int)row0, full_bar(s));
+                    }
+#pragma unroll
+                    for (int q = 0; q < HPT; q++)
+                        produce_half<FMT>(ring[u][q], wrow, kb, half0 + q, p.K, stage + row_off, sw);
+                    fence_proxy_async_smem();      // every lane: its stores, visible to the tensor core
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(full_bar(s));
                 }
             }
-            fence_proxy_async_smem();
-            mbar_arrive(full_bar(s));
-            cur0 = nxt0;
-            if (GATED) cur1 = nxt1;
         }
         // ===== epilogue ===========================================================================
-        mbar_wait(accum_bar, 0u, abort_flag, p.status);
+        if (lane == 0) mbar_wait(accum_bar, 0u, abort_flag, p.status);
+        __syncwarp();
         tc_fence_after();
-        const int f = f0 + tid;
+        const int f = f0 + prow;
         const bool live = f < p.n;
         float bias0 = 0.f, bias1 = 0.f;
         if (live) {
             if (p.b0) bias0 = bf16_round(p.b0[(size_t)expert * p.n + f]);
             if (EPI == kEpiSwigluF16) bias1 = bf16_round(__fadd_rn(p.b1[(size_t)expert * p.n + f], 1.0f));
         }
-        const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
-        for (uint32_t c = 0; c < nv; c += 16) {
+        // Rows written for a later tile kernel keep the operand order within each block.
+        const int fcol = EPI == kEpiDownBf16 ? f : operand_pos(FMT, f);
+        // Each warp may touch the 32 tensor-memory lanes of its quarter (warp & 3); the kParts warps
+        // that share a quarter split the tile's columns between them.
+        const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t c_begin = (uint32_t)part * (NT / S::kParts);
+        const uint32_t c_end = min(nv, c_begin + NT / S::kParts);
+        for (uint32_t c = c_begin; c < c_end; c += 16) {
             uint32_t ra[16], rb[16];
             tmem_ld16(taddr + c, ra);
             if (GATED) tmem_ld16(taddr + NT + c, rb);
@@ -454,9 +545,7 @@ grouped_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
                         float a = __fadd_rn(__uint_as_float(ra[j]), bias0);
                         float b = GATED ? __fadd_rn(__uint_as_float(rb[j]), bias1) : 0.f;
                         uint16_t h = epilogue_value<EPI>(a, b);
-                        uint32_t row = row0 + c + j;
-                        if (EPI == kEpiDownBf16 && p.route_of_row) row = p.route_of_row[row];
-                        p.out[(size_t)row * p.n + f] = h;
+                        p.out[(size_t)out_rows[c + j] * p.n + fcol] = h;
                     }
                 }
             }
@@ -472,7 +561,7 @@ grouped_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
             mbar_wait(full_bar(s), ph, abort_flag, p.status);
             tc_fence_after();
             const uint64_t a0 = umma_desc(stage), a1 = umma_desc(stage + S::kABytes);
-            const uint64_t b = umma_desc(stage + (GATED ? 2 : 1) * S::kABytes);
+            const uint64_t b = umma_desc(stage + S::kMats * S::kABytes);
 #pragma unroll
             for (int kk = 0; kk < 4; kk++) {
                 const uint32_t acc = (kb | kk) != 0 ? 1u : 0u;
@@ -493,7 +582,7 @@ grouped_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
         for (int i = 0; i < 64; i++) __nanosleep(1000);
         __syncthreads();
     }
-    if (warp == 4) {
+    if (warp == PW) {
         tc_fence_after();
         tmem_dealloc(tmem_base, S::kTmemCols);
     }
@@ -560,7 +649,7 @@ __global__ void __launch_bounds__(128) grouped_gemm_simt_kernel(const GemmParams
                 uint16_t h = epilogue_value<EPI>(__fadd_rn(acc0[j], bias0), __fadd_rn(acc1[j], bias1));
                 uint32_t row = row0 + c + j;
                 if (EPI == kEpiDownBf16 && p.route_of_row) row = p.route_of_row[row];
-                p.out[(size_t)row * p.n + f] = h;
+                p.out[(size_t)row * p.n + (EPI == kEpiDownBf16 ? f : operand_pos(FMT, f))] = h;
             }
         }
     }
@@ -579,10 +668,9 @@ __global__ void dequant_kernel(const uint8_t* __restrict__ w, size_t n_elems, fl
     int K = (int)min((size_t)0x7fffffc0, kend);
     if (out16) {
         decode_row_k64<FMT>(w, (int)chunk, K, v);
-        for (int i = 0; i < 32; i++) {
-            size_t k = k0 + 2 * i;
-            if (k < n_elems) out16[k] = (uint16_t)(v[i] & 0xffffu);
-            if (k + 1 < n_elems) out16[k + 1] = (uint16_t)(v[i] >> 16);
+        for (int k = 0; k < 64; k++) {       // element k of the chunk sits at its operand position
+            int pos = operand_pos(FMT, k);
+            if (k0 + k < n_elems) out16[k0 + k] = (uint16_t)(pos & 1 ? v[pos >> 1] >> 16 : v[pos >> 1] & 0xffffu);
         }
     }
     if (out32) {

@@ -1,0 +1,279 @@
+// Wide grouped tile kernel for large experts: 256 routes x 256 weight rows per CTA.
+//
+// Same product as grouped_gemm_tc_kernel (D[feature, route] = sum_k W[feature, k] * X[row, k], half
+// operands, fp32 accumulators in tensor memory), reorganised around what limits it on B200:
+//
+//   * Two A tiles share one B tile. Gated layers pair the gate rows with the up rows of the same
+//     128 features; the down projection pairs two neighbouring 128-feature tiles. Both
+//     accumulators (2 x 256 columns) fill the SM's 512 tensor-memory columns; one CTA per SM.
+//   * Weight bytes are fetched coalesced. A thread-per-row load touches 32 different cache lines
+//     per request and the L1 tag stage, not DRAM, becomes the limit. Here every producer warp
+//     owns 16 consecutive weight rows and streams their packed bytes through a private
+//     shared-memory ring with 16-byte cp.async copies, consecutive lanes taking consecutive chunks
+//     of a row; each lane then decodes one 32-element block per 64-wide K slice from the ring.
+//   * A and B stages are separate rings: A tiles are produced in the SM just in time (2 stages),
+//     B tiles travel from L2 by TMA and get 3 stages. A dedicated warp issues the TMA loads, one
+//     thread issues the MMAs, each barrier has one arrival per warp.
+//
+// All waits are bounded (see mbar_wait); a wait that gives up sets the status word.
+#pragma once
+#include "gemm.cuh"
+
+namespace oco {
+
+struct WideShape {
+    static constexpr int kNT = 256;                   // routes per tile (MMA N)
+    static constexpr int kProducerWarps = 16;         // 256 row streams / 16 rows per warp
+    static constexpr int kMmaWarp = 16, kTmaWarp = 17;
+    static constexpr int kThreads = 18 * 32;
+    static constexpr int kATile = 128 * 128;          // one A tile: 128 rows x 64 halves
+    static constexpr int kAStage = 2 * kATile;        // both A tiles
+    static constexpr int kAStages = 2;
+    static constexpr int kBStage = kNT * 128;
+    static constexpr int kBStages = 3;
+    static constexpr int kChunkSlices = 2;            // K slices per raw-ring buffer
+    static constexpr int kPitch = 112;                // ring bytes per row: 2 slices (<= 72 B) + 15 alignment, 16-byte chunks
+    static constexpr int kRowChunks = 6;              // 16-byte chunks fetched per row per buffer
+    static constexpr int kRingBufs = 2;
+    static constexpr int kRingWarp = kRingBufs * 16 * kPitch;
+    static constexpr int kRing = kProducerWarps * kRingWarp;
+    static constexpr int kCtrl = 512 + kNT * 4;       // barriers, tmem slot, abort flag, row map
+    static constexpr int kSmemBytes = kAStages * kAStage + kBStages * kBStage + kRing + kCtrl + 1024;
+    static constexpr int kTmemCols = 512;
+};
+
+// FMT: MXFP4 or Q4_0 (32-element blocks of 17 / 18 bytes). EPI as in gemm.cuh.
+// grid: (ceil(n / (gated ? 128 : 256)), max_tiles). `w_end`: first byte past the 16-byte-aligned
+// envelope of the weight tensors (no copy starts at or beyond it).
+template <int FMT, int EPI>
+__global__ void __launch_bounds__(WideShape::kThreads, 1)
+grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_b) {
+    using S = WideShape;
+    constexpr bool GATED = epi_gated(EPI);
+    constexpr int NT = S::kNT;
+    constexpr int kBlockBytes = FMT == OCO_FMT_MXFP4 ? 17 : 18;
+    constexpr int kSliceBytes = 2 * kBlockBytes;
+    extern __shared__ unsigned char smem_raw[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    // ---- which tile ----------------------------------------------------------------------------
+    uint32_t expert, begin, count, row0;
+    if (p.tiles) {
+        if (blockIdx.y >= *p.tile_count) return;
+        expert = p.tiles[2 * blockIdx.y];
+        begin = p.tiles[2 * blockIdx.y + 1];
+        row0 = p.offsets[expert] + begin;
+        count = p.offsets[expert + 1] - p.offsets[expert];
+    } else {
+        expert = 0; begin = blockIdx.y * NT; row0 = begin; count = (uint32_t)p.dense_rows;
+        if (begin >= count) return;
+    }
+    if (__syncthreads_or(tid == 0 && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u)) return;
+    const uint32_t nv = min((uint32_t)NT, count - begin);
+    const uint32_t n_mma = max(16u, (nv + 15u) & ~15u);
+    const int f0 = blockIdx.x * (GATED ? 128 : 256);     // first feature of A tile 0
+    const int nkb = (p.K + 63) / 64;
+    const int nblk = p.K >> 5;
+
+    // ---- shared memory carve-up ----------------------------------------------------------------
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t a_base = base, b_base = base + S::kAStages * S::kAStage;
+    const uint32_t ring_base = b_base + S::kBStages * S::kBStage;
+    const uint32_t ctrl = ring_base + S::kRing;
+    unsigned char* ctrl_gen = gen_base + (ctrl - base);
+    auto full_a = [&](int s) { return ctrl + 8u * s; };
+    auto empty_a = [&](int s) { return ctrl + 8u * (2 + s); };
+    auto full_b = [&](int s) { return ctrl + 8u * (4 + s); };
+    auto empty_b = [&](int s) { return ctrl + 8u * (7 + s); };
+    const uint32_t accum_bar = ctrl + 8u * 10;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl_gen + 96);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    uint32_t* out_rows = reinterpret_cast<uint32_t*>(ctrl_gen + 512);
+    for (uint32_t i = tid; i < nv; i += S::kThreads)
+        out_rows[i] = (EPI == kEpiDownBf16 && p.route_of_row) ? p.route_of_row[row0 + i] : row0 + i;
+
+    if (tid == 0) {
+        for (int s = 0; s < S::kAStages; s++) { mbar_init(full_a(s), S::kProducerWarps); mbar_init(empty_a(s), 1); }
+        for (int s = 0; s < S::kBStages; s++) { mbar_init(full_b(s), 1); mbar_init(empty_b(s), 1); }
+        mbar_init(accum_bar, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == S::kMmaWarp) {
+        tmem_alloc(smem_u32(tmem_slot), S::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < S::kProducerWarps) {
+        // ===== producers ==========================================================================
+        // Row stream rs = 16 * warp + r: A tile (rs >> 7), tile row (rs & 127).
+        const int tile = warp >> 3;                                  // which A tile this warp feeds
+        const uint8_t* wmat = (GATED && tile) ? p.w1 : p.w0;
+        const int feat0 = GATED ? f0 : f0 + 128 * tile;              // feature of tile row 0
+        const int trow0 = (warp & 7) * 16;                           // first tile row of this warp
+        auto row_ptr = [&](int r) -> const uint8_t* {                // packed bytes of tile row trow0 + r
+            int f = min(feat0 + trow0 + r, p.n - 1);
+            return wmat + ((size_t)expert * p.n + f) * p.row_bytes;
+        };
+        // copy role: three 16-byte chunks per buffer: chunk index (lane + 32 i) -> (row, column)
+        const uint8_t* crow[3];
+        uint32_t cdst[3];
+#pragma unroll
+        for (int i = 0; i < 3; i++) {
+            int idx = lane + 32 * i, r = idx / S::kRowChunks, c = idx % S::kRowChunks;
+            crow[i] = row_ptr(r);
+            cdst[i] = (uint32_t)(r * S::kPitch + c * 16);
+        }
+        const uint32_t ring = ring_base + (uint32_t)warp * S::kRingWarp;
+        const uint8_t* w_end = (GATED && tile) ? p.w1_end : p.w0_end;
+        auto issue = [&](int chunk) {                                // K slices 2*chunk, 2*chunk + 1
+            if (chunk * S::kChunkSlices < nkb) {
+                const uint32_t buf = ring + (uint32_t)(chunk & 1) * (16 * S::kPitch);
+#pragma unroll
+                for (int i = 0; i < 3; i++) {
+                    const uint8_t* src = crow[i] + (size_t)chunk * (S::kChunkSlices * kSliceBytes);
+                    const uint8_t* a16 = (const uint8_t*)(((uintptr_t)src & ~(uintptr_t)15)) + (cdst[i] % S::kPitch);
+                    if (a16 < w_end) cp_async16(buf + cdst[i], a16);
+                }
+            }
+            cp_async_commit();
+        };
+        // decode role: lane -> (row r = lane >> 1, half-slice h = lane & 1)
+        const int r = lane >> 1, h = lane & 1;
+        const uint8_t* wrow = row_ptr(r);
+        const int prow = trow0 + r;
+        const uint32_t a_row = (uint32_t)tile * S::kATile + (uint32_t)(prow >> 3) * 1024u + (uint32_t)(prow & 7) * 128u;
+        const uint32_t sw = (uint32_t)(prow & 7);
+        issue(0);
+        for (int kb = 0; kb < nkb; kb++) {
+            const int chunk = kb >> 1;
+            if ((kb & 1) == 0) {
+                issue(chunk + 1);                                    // other buffer: decoded two slices ago
+                cp_async_wait<1>();                                  // this chunk's copies have landed
+                __syncwarp();
+            }
+            uint32_t v[16];
+            const int blk = 2 * kb + h;
+            if (blk < nblk) {
+                const uint8_t* src = wrow + (size_t)blk * kBlockBytes;                        // global address of the block
+                const uint8_t* chunk_src = wrow + (size_t)chunk * (S::kChunkSlices * kSliceBytes);
+                const uint32_t off = (uint32_t)(src - (const uint8_t*)((uintptr_t)chunk_src & ~(uintptr_t)15));
+                const uint32_t at = ring + (uint32_t)(chunk & 1) * (16 * S::kPitch) + (uint32_t)r * S::kPitch + off;
+                const uint32_t a4 = at & ~3u, sh = (at & 3u) * 8u;
+                uint32_t w[6];
+#pragma unroll
+                for (int i = 0; i < (FMT == OCO_FMT_MXFP4 ? 5 : 6); i++)
+                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w[i]) : "r"(a4 + 4u * i));
+                if (FMT == OCO_FMT_MXFP4) decode_mxfp4_block(w, sh, v);
+                else decode_q4_0_block(w, sh, v);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; i++) v[i] = 0;
+            }
+            const int s = kb % S::kAStages;
+            const uint32_t ph = (uint32_t)(kb / S::kAStages) & 1u;
+            if (lane == 0) mbar_wait(empty_a(s), ph ^ 1u, abort_flag, p.status);
+            __syncwarp();
+            const uint32_t dst = a_base + (uint32_t)s * S::kAStage + a_row;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const uint32_t addr = dst + ((((uint32_t)(4 * h + c)) ^ sw) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v[4 * c]), "r"(v[4 * c + 1]),
+                             "r"(v[4 * c + 2]), "r"(v[4 * c + 3]) : "memory");
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_a(s));
+        }
+        cp_async_wait<0>();
+        // ===== epilogue ===========================================================================
+        if (lane == 0) mbar_wait(accum_bar, 0u, abort_flag, p.status);
+        __syncwarp();
+        tc_fence_after();
+        // warp -> tensor-memory lanes 32 * (warp & 3) (tile rows), columns [64 * (warp >> 2), +64)
+        const int erow = (warp & 3) * 32 + lane;
+        const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t c_begin = (uint32_t)(warp >> 2) * 64u;
+        const uint32_t c_end = min(nv, c_begin + 64u);
+        const int fa = f0 + erow, fb = GATED ? fa : fa + 128;        // features of accumulator 0 / 1
+        float bias_a = 0.f, bias_b = 0.f;
+        if (fa < p.n && p.b0) bias_a = bf16_round(p.b0[(size_t)expert * p.n + fa]);
+        if (GATED) {
+            if (EPI == kEpiSwigluF16 && fa < p.n) bias_b = bf16_round(__fadd_rn(p.b1[(size_t)expert * p.n + fa], 1.0f));
+        } else if (fb < p.n && p.b0) {
+            bias_b = bf16_round(p.b0[(size_t)expert * p.n + fb]);
+        }
+        const int col_a = EPI == kEpiDownBf16 ? fa : operand_pos(FMT, fa);
+        const int col_b = EPI == kEpiDownBf16 ? fb : operand_pos(FMT, fb);
+        for (uint32_t c = c_begin; c < c_end; c += 16) {
+            uint32_t ra[16], rb[16];
+            tmem_ld16(taddr + c, ra);
+            tmem_ld16(taddr + NT + c, rb);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                if (c + j < nv) {
+                    const size_t orow = (size_t)out_rows[c + j] * p.n;
+                    const float a = __fadd_rn(__uint_as_float(ra[j]), bias_a);
+                    const float b = __fadd_rn(__uint_as_float(rb[j]), bias_b);
+                    if (GATED) {
+                        if (fa < p.n) p.out[orow + col_a] = epilogue_value<EPI>(a, b);
+                    } else {
+                        if (fa < p.n) p.out[orow + col_a] = epilogue_value<EPI>(a, 0.f);
+                        if (fb < p.n) p.out[orow + col_b] = epilogue_value<EPI>(b, 0.f);
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+    } else if (warp == S::kMmaWarp) {
+        if (lane == 0) {
+            // ===== MMA issue ======================================================================
+            const uint32_t idesc = umma_idesc_f16(n_mma);
+            for (int kb = 0; kb < nkb; kb++) {
+                const int sa = kb % S::kAStages, sb = kb % S::kBStages;
+                mbar_wait(full_a(sa), (uint32_t)(kb / S::kAStages) & 1u, abort_flag, p.status);
+                mbar_wait(full_b(sb), (uint32_t)(kb / S::kBStages) & 1u, abort_flag, p.status);
+                tc_fence_after();
+                const uint32_t a_stage = a_base + (uint32_t)sa * S::kAStage;
+                const uint64_t a0 = umma_desc(a_stage), a1 = umma_desc(a_stage + S::kATile);
+                const uint64_t b = umma_desc(b_base + (uint32_t)sb * S::kBStage);
+#pragma unroll
+                for (int kk = 0; kk < 4; kk++) {
+                    const uint32_t acc = (kb | kk) != 0 ? 1u : 0u;
+                    umma_f16(tmem_base, a0 + 2u * kk, b + 2u * kk, idesc, acc);
+                    umma_f16(tmem_base + NT, a1 + 2u * kk, b + 2u * kk, idesc, acc);
+                }
+                umma_commit(empty_a(sa));
+                umma_commit(empty_b(sb));
+            }
+            umma_commit(accum_bar);
+            mbar_wait(accum_bar, 0u, abort_flag, p.status);      // every MMA has retired
+            tc_fence_before();
+        }
+    } else if (lane == 0) {
+        // ===== B tiles by TMA =========================================================================
+        for (int kb = 0; kb < nkb; kb++) {
+            const int sb = kb % S::kBStages;
+            mbar_wait(empty_b(sb), ((uint32_t)(kb / S::kBStages) & 1u) ^ 1u, abort_flag, p.status);
+            mbar_arrive_expect_tx(full_b(sb), (uint32_t)S::kBStage);
+            tma_load_2d(b_base + (uint32_t)sb * S::kBStage, &tmap_b, kb * 64, (int)row0, full_b(sb));
+        }
+    }
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 64; i++) __nanosleep(1000);   // let copies in flight land before the CTA retires
+        __syncthreads();
+    }
+    if (warp == S::kMmaWarp) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, S::kTmemCols);
+    }
+}
+
+}  // namespace oco

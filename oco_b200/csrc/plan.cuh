@@ -76,24 +76,24 @@ __global__ void __launch_bounds__(1024) route_plan_kernel(const uint32_t* __rest
     }
 }
 
-// Gathers token rows into expert-sorted order, converting bf16 to the tiles' half operand
-// (the reference gathers inside its tiles, shaders/experts/projections.metal:208-233).
-// One CTA per sorted row.
+// Gathers token rows into expert-sorted order, converting bf16 to the tiles' half operand and
+// laying each block out in the tiles' operand order (see operand_pos in gemm.cuh): `half_span` is
+// the distance between the two elements a code byte holds (16 for MXFP4 / Q4_0, 32 for Q4_K).
+// The reference gathers inside its tiles (shaders/experts/projections.metal:208-233).
+// One CTA per sorted row; each thread emits one half2 = (x[k], x[k + half_span]).
 __global__ void __launch_bounds__(256) permute_rows_kernel(const uint16_t* __restrict__ x,
                                                            const uint32_t* __restrict__ route_of_row, int K,
-                                                           int H, uint16_t* __restrict__ xs) {
+                                                           int H, int half_span, uint16_t* __restrict__ xs) {
     uint32_t row = blockIdx.x;
     uint32_t token = route_of_row ? route_of_row[row] / (uint32_t)K : row;  // null: rows keep token order
-    const uint2* src = reinterpret_cast<const uint2*>(x + (size_t)token * H);
-    uint2* dst = reinterpret_cast<uint2*>(xs + (size_t)row * H);
-    for (int i = threadIdx.x; i < H / 4; i += 256) {
-        uint2 v = src[i];
-        __half2 a = __floats2half2_rn(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u));
-        __half2 b = __floats2half2_rn(__uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
-        uint2 o;
-        o.x = *reinterpret_cast<uint32_t*>(&a);
-        o.y = *reinterpret_cast<uint32_t*>(&b);
-        dst[i] = o;
+    const uint16_t* src = x + (size_t)token * H;
+    uint32_t* dst = reinterpret_cast<uint32_t*>(xs + (size_t)row * H);
+    for (int i = threadIdx.x; i < H / 2; i += 256) {
+        int blk = i / half_span, j = i % half_span;           // pair i of the row: block, byte index
+        int k = blk * 2 * half_span + j;
+        __half2 h = __floats2half2_rn(__uint_as_float((uint32_t)src[k] << 16),
+                                      __uint_as_float((uint32_t)src[k + half_span] << 16));
+        dst[i] = *reinterpret_cast<uint32_t*>(&h);
     }
 }
 

@@ -199,6 +199,15 @@ class ReluExperts(_Weights):
     """reference `ReluExperts{router, up, down, shared_up, shared_down}` (src/weights/nemotron.rs:60-66)."""
 
 
+def operand_order(fmt: int, n: int) -> np.ndarray:
+    """Column of element k in rows kept in the tile kernels' operand order: a packed code byte holds
+    elements j and j + h of its block (h = 16, or 32 for Q4_K), and the tiles keep the two adjacent."""
+    k = np.arange(n)
+    if fmt == synth.FMT_Q4_K:
+        return (k & ~63) + (((k & 31) << 1) | ((k >> 5) & 1))
+    return (k & ~31) + (((k & 15) << 1) | ((k >> 4) & 1))
+
+
 class Routing:
     """Expert selections and combination weights of the last call (reference `Routing`,
     src/weights/state.rs:112-117), read back from the plan's workspace."""
@@ -237,7 +246,8 @@ class Routing:
             out["route_of_row"] = self._read(v.route_of_row, R, np.uint32)
             n = int(self._read(v.tile_count, 1, np.uint32)[0])
             out["tiles"] = self._read(v.tiles, 2 * n, np.uint32).reshape(n, 2)
-            out["act"] = self._read(v.act, R * d.ffn, np.uint16).reshape(R, d.ffn)
+            act = self._read(v.act, R * d.ffn, np.uint16).reshape(R, d.ffn)
+            out["act"] = act[:, operand_order(d.weight_format, d.ffn)]   # back to element order
         return out
 
 

@@ -104,6 +104,22 @@ def test_gpt_oss_medium(moe, oracle, tokens):
     check_layer(moe, oracle, layer, tokens, seed=100 + tokens)
 
 
+@pytest.mark.parametrize("hidden,ffn,tokens", [(96, 96, 700), (640, 384, 520), (320, 288, 1100)],
+                         ids=["k96", "k640", "k320"])
+def test_gpt_oss_wide_tiles(moe, oracle, hidden, ffn, tokens):
+    """Few large experts: more than 192 routes per expert on average selects the 256-route tiles
+    (two weight tiles per CTA, coalesced weight streaming). Shapes cover a partial last K slice
+    (96, 288), partial 128- and 256-row feature tiles and experts spanning several route tiles."""
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, hidden, ffn, 4, 2, synth.FMT_MXFP4, seed=31)
+    check_layer(moe, oracle, layer, tokens, seed=tokens)
+
+
+def test_nemotron_wide_tiles(moe, oracle):
+    layer = synth.make_layer(synth.ARCH_NEMOTRON, 256, 160, 4, 2, synth.FMT_Q4_0, seed=32, shared_ffn=320,
+                             normalize=True, scale=2.5)
+    check_layer(moe, oracle, layer, 450, seed=5)
+
+
 def test_gpt_oss_forced_routes_reference_ids(moe, oracle):
     """Ids forced as in the reference's tile test: every token sends routes to experts 31 and 30,
     the rest stay sparse (mxfp4.rs:345-347), through a router whose bias alone decides."""
