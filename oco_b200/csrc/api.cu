@@ -26,6 +26,7 @@ constexpr int kMaxMarks = 16;
 struct Workspace {
     uint32_t* status = nullptr;
     float* logits = nullptr;
+    float* router_rounded = nullptr;  // gpt-oss: router weights rounded to bf16, as f32
     uint32_t* ids = nullptr;
     float* probs = nullptr;
     uint32_t* offsets = nullptr;
@@ -56,6 +57,7 @@ struct oco_moe_plan {
     oco_moe_weights w{};
     Workspace ws{};
     bool have_ws = false, have_w = false;
+    bool router_ready = false;   // the rounded router copy matches the bound weights and workspace
     int max_rows = 0;
     int sm_count = 148;
     int launches = 0;
@@ -126,6 +128,7 @@ Workspace carve(const oco_moe_desc& d, int max_rows, unsigned char* base) {
     const size_t P = (K + 1) / 2;
     w.status = (uint32_t*)take(256);
     w.logits = (float*)take(T * E * 4);
+    w.router_rounded = (float*)take(d.arch == OCO_ARCH_GPT_OSS ? E * H * 4 : 4);
     w.ids = (uint32_t*)take(R * 4);
     w.probs = (float*)take(R * 4);
     w.offsets = (uint32_t*)take((E + 1) * 4);
@@ -369,15 +372,36 @@ int forward_tiled(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int
     Workspace& ws = plan->ws;
     const int H = d.hidden, F = d.ffn, E = d.experts, K = d.top_k, R = rows * K;
 
-    size_t rsmem = (size_t)H * 4 + (size_t)8 * H * 2;
-    static bool router_attr = false;
-    if (!router_attr) {
-        CK(allow_smem(router_batched_kernel<ARCH>));
-        router_attr = true;
-    }
     mark(plan, st, "router");
-    router_batched_kernel<ARCH><<<(rows + 7) / 8, 256, rsmem, st>>>(x, plan->w.router_w, plan->w.router_b, rows, H, E,
-                                                                  K, d.normalize, d.scale, ws.logits, ws.ids, ws.probs);
+    if (H <= 3072 && H % 4 == 0) {
+        const float* rw = plan->w.router_w;
+        if (ARCH == OCO_ARCH_GPT_OSS) {
+            if (!plan->router_ready) {   // once per bound weight set
+                const size_t n = (size_t)E * H;
+                round_router_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(rw, ws.router_rounded, n);
+                plan->launches++;
+                plan->router_ready = true;
+            }
+            rw = ws.router_rounded;
+        }
+        static bool stream_attr = false;
+        if (!stream_attr) {
+            CK(allow_smem(router_stream_kernel<ARCH, 24>));
+            stream_attr = true;
+        }
+        router_stream_kernel<ARCH, 24><<<(rows + 7) / 8, 256, (size_t)4 * H * 4, st>>>(
+            x, rw, plan->w.router_b, rows, H, E, K, d.normalize, d.scale, ws.logits, ws.ids, ws.probs);
+    } else {
+        size_t rsmem = (size_t)H * 4 + (size_t)8 * H * 2;
+        static bool router_attr = false;
+        if (!router_attr) {
+            CK(allow_smem(router_batched_kernel<ARCH>));
+            router_attr = true;
+        }
+        router_batched_kernel<ARCH><<<(rows + 7) / 8, 256, rsmem, st>>>(x, plan->w.router_w, plan->w.router_b, rows, H,
+                                                                      E, K, d.normalize, d.scale, ws.logits, ws.ids,
+                                                                      ws.probs);
+    }
     plan->launches++;
     CK(cudaGetLastError());
 
@@ -559,6 +583,7 @@ int oco_moe_bind_workspace(oco_moe_plan* plan, void* workspace, size_t bytes, in
     plan->ws = ws;
     plan->max_rows = max_rows;
     plan->have_ws = true;
+    plan->router_ready = false;
     return OCO_OK;
 }
 
@@ -574,6 +599,7 @@ int oco_moe_bind_weights(oco_moe_plan* plan, const oco_moe_weights* w) {
     if (((uintptr_t)w->router_w & 15u) != 0) return fail(plan, OCO_INVALID_ARGUMENT, "router_w must be 16-byte aligned");
     plan->w = *w;
     plan->have_w = true;
+    plan->router_ready = false;
     return OCO_OK;
 }
 

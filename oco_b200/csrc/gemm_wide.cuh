@@ -121,74 +121,80 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
             return wmat + ((size_t)expert * p.n + f) * p.row_bytes;
         };
         // copy role: three 16-byte chunks per buffer: chunk index (lane + 32 i) -> (row, column)
-        const uint8_t* crow[3];
+        constexpr uint32_t kChunkBytes = S::kChunkSlices * kSliceBytes;      // packed bytes per row per buffer
+        constexpr uint32_t kBufBytes = 16 * S::kPitch;
+        const uint32_t ring = ring_base + (uint32_t)warp * S::kRingWarp;
+        const uint8_t* w_end = (GATED && tile) ? p.w1_end : p.w0_end;
+        const uint8_t* csrc[3];                                             // running source: row start + column
         uint32_t cdst[3];
 #pragma unroll
         for (int i = 0; i < 3; i++) {
-            int idx = lane + 32 * i, r = idx / S::kRowChunks, c = idx % S::kRowChunks;
-            crow[i] = row_ptr(r);
-            cdst[i] = (uint32_t)(r * S::kPitch + c * 16);
+            int idx = lane + 32 * i, rr = idx / S::kRowChunks, c = idx % S::kRowChunks;
+            csrc[i] = row_ptr(rr);
+            cdst[i] = ring + (uint32_t)(rr * S::kPitch + c * 16);
         }
-        const uint32_t ring = ring_base + (uint32_t)warp * S::kRingWarp;
-        const uint8_t* w_end = (GATED && tile) ? p.w1_end : p.w0_end;
-        auto issue = [&](int chunk) {                                // K slices 2*chunk, 2*chunk + 1
-            if (chunk * S::kChunkSlices < nkb) {
-                const uint32_t buf = ring + (uint32_t)(chunk & 1) * (16 * S::kPitch);
+        const int nchunks = (nkb + S::kChunkSlices - 1) / S::kChunkSlices;
+        auto issue = [&](int chunk) {                                        // K slices 2*chunk, 2*chunk + 1
+            if (chunk < nchunks) {
+                const uint32_t bsel = (uint32_t)(chunk & 1) * kBufBytes;
 #pragma unroll
                 for (int i = 0; i < 3; i++) {
-                    const uint8_t* src = crow[i] + (size_t)chunk * (S::kChunkSlices * kSliceBytes);
-                    const uint8_t* a16 = (const uint8_t*)(((uintptr_t)src & ~(uintptr_t)15)) + (cdst[i] % S::kPitch);
-                    if (a16 < w_end) cp_async16(buf + cdst[i], a16);
+                    // 16-byte-aligned envelope of the row's bytes for this chunk, column (cdst offset)
+                    const uint8_t* a16 = (const uint8_t*)(((uintptr_t)(csrc[i] + (size_t)chunk * kChunkBytes)) & ~(uintptr_t)15) +
+                                         ((cdst[i] - ring) % S::kPitch);
+                    if (a16 < w_end) cp_async16(cdst[i] + bsel, a16);
                 }
             }
             cp_async_commit();
         };
         // decode role: lane -> (row r = lane >> 1, half-slice h = lane & 1)
         const int r = lane >> 1, h = lane & 1;
-        const uint8_t* wrow = row_ptr(r);
         const int prow = trow0 + r;
-        const uint32_t a_row = (uint32_t)tile * S::kATile + (uint32_t)(prow >> 3) * 1024u + (uint32_t)(prow & 7) * 128u;
+        const uint32_t a_lo = (uint32_t)(uintptr_t)row_ptr(r) & 15u;        // alignment of the row start
+        const uint32_t ring_row = ring + (uint32_t)r * S::kPitch + (uint32_t)h * kBlockBytes;
         const uint32_t sw = (uint32_t)(prow & 7);
+        const uint32_t a_row = (uint32_t)tile * S::kATile + (uint32_t)(prow >> 3) * 1024u + (uint32_t)(prow & 7) * 128u;
+        uint32_t st_off[4];
+#pragma unroll
+        for (int c = 0; c < 4; c++) st_off[c] = a_base + a_row + ((((uint32_t)(4 * h + c)) ^ sw) << 4);
+        const bool ragged = (nblk & 1) != 0;                                 // K is not a multiple of 64
         issue(0);
-        for (int kb = 0; kb < nkb; kb++) {
-            const int chunk = kb >> 1;
-            if ((kb & 1) == 0) {
-                issue(chunk + 1);                                    // other buffer: decoded two slices ago
-                cp_async_wait<1>();                                  // this chunk's copies have landed
-                __syncwarp();
-            }
-            uint32_t v[16];
-            const int blk = 2 * kb + h;
-            if (blk < nblk) {
-                const uint8_t* src = wrow + (size_t)blk * kBlockBytes;                        // global address of the block
-                const uint8_t* chunk_src = wrow + (size_t)chunk * (S::kChunkSlices * kSliceBytes);
-                const uint32_t off = (uint32_t)(src - (const uint8_t*)((uintptr_t)chunk_src & ~(uintptr_t)15));
-                const uint32_t at = ring + (uint32_t)(chunk & 1) * (16 * S::kPitch) + (uint32_t)r * S::kPitch + off;
-                const uint32_t a4 = at & ~3u, sh = (at & 3u) * 8u;
-                uint32_t w[6];
-#pragma unroll
-                for (int i = 0; i < (FMT == OCO_FMT_MXFP4 ? 5 : 6); i++)
-                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w[i]) : "r"(a4 + 4u * i));
-                if (FMT == OCO_FMT_MXFP4) decode_mxfp4_block(w, sh, v);
-                else decode_q4_0_block(w, sh, v);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 16; i++) v[i] = 0;
-            }
-            const int s = kb % S::kAStages;
-            const uint32_t ph = (uint32_t)(kb / S::kAStages) & 1u;
-            if (lane == 0) mbar_wait(empty_a(s), ph ^ 1u, abort_flag, p.status);
+        for (int chunk = 0; chunk < nchunks; chunk++) {
+            issue(chunk + 1);                                                // other buffer: decoded one chunk ago
+            cp_async_wait<1>();                                              // this chunk's copies have landed
             __syncwarp();
-            const uint32_t dst = a_base + (uint32_t)s * S::kAStage + a_row;
+            // the row's bytes for this chunk start ((a_lo + chunk * kChunkBytes) & 15) into its ring slot
+            const uint32_t rbuf = ring_row + (uint32_t)(chunk & 1) * kBufBytes + ((a_lo + (uint32_t)chunk * kChunkBytes) & 15u);
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                const uint32_t addr = dst + ((((uint32_t)(4 * h + c)) ^ sw) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v[4 * c]), "r"(v[4 * c + 1]),
-                             "r"(v[4 * c + 2]), "r"(v[4 * c + 3]) : "memory");
+            for (int kk = 0; kk < S::kChunkSlices; kk++) {
+                const int kb = chunk * S::kChunkSlices + kk;
+                if (kb < nkb) {
+                    uint32_t v[16];
+                    const uint32_t at = rbuf + (uint32_t)kk * kSliceBytes;
+                    const uint32_t a4 = at & ~3u, sh = (at & 3u) * 8u;
+                    uint32_t w[6];
+#pragma unroll
+                    for (int i = 0; i < (FMT == OCO_FMT_MXFP4 ? 5 : 6); i++)
+                        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w[i]) : "r"(a4 + 4u * i));
+                    if (FMT == OCO_FMT_MXFP4) decode_mxfp4_block(w, sh, v);
+                    else decode_q4_0_block(w, sh, v);
+                    if (ragged && h && kb == nkb - 1) {                      // the slice's second block is past K
+#pragma unroll
+                        for (int i = 0; i < 16; i++) v[i] = 0;
+                    }
+                    const int s = kb % S::kAStages;
+                    if (lane == 0) mbar_wait(empty_a(s), ((uint32_t)(kb / S::kAStages) & 1u) ^ 1u, abort_flag, p.status);
+                    __syncwarp();
+                    const uint32_t soff = (uint32_t)s * S::kAStage;
+#pragma unroll
+                    for (int c = 0; c < 4; c++)
+                        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(st_off[c] + soff), "r"(v[4 * c]),
+                                     "r"(v[4 * c + 1]), "r"(v[4 * c + 2]), "r"(v[4 * c + 3]) : "memory");
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(full_a(s));
+                }
             }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(full_a(s));
         }
         cp_async_wait<0>();
         // ===== epilogue ===========================================================================

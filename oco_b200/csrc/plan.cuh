@@ -97,6 +97,13 @@ __global__ void __launch_bounds__(256) permute_rows_kernel(const uint16_t* __res
     }
 }
 
+// gpt-oss rounds every router weight to bf16 when it is used (routing.metal:108-109). The rounded
+// copy is made once per bound weight set so the per-token kernels read plain f32.
+__global__ void __launch_bounds__(256) round_router_kernel(const float* __restrict__ w, float* __restrict__ out, size_t n) {
+    size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i < n) out[i] = bf16_round(w[i]);
+}
+
 // Weighted combine onto the residual.
 //   round_sum = 1: moe_sum (routing.metal:154-168): s = sum_r y_r * p_r; out = bf16(res + bf16(s))
 //   round_sum = 0: moe_add (nemotron.metal:222-236): s = [shared] + sum_r fma(y_r, p_r); out = bf16(res + s)

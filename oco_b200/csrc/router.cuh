@@ -247,4 +247,80 @@ __global__ void __launch_bounds__(256) router_batched_kernel(const uint16_t* __r
         if (r < K && lane == r) { ids[(size_t)t * K + r] = id[r]; probs[(size_t)t * K + r] = p[r]; }
 }
 
+// Many tokens, hidden <= 128 * ITERS: one token per warp with its row held in registers as f32;
+// the router rows stream through a four-deep shared-memory ring filled with cp.async, one
+// __syncthreads per expert. `w` holds the weights as they enter the FMAs (already rounded for
+// gpt-oss). Same canonical order as canonical_logit. Dynamic shared memory: 4 * H floats.
+template <int ARCH, int ITERS>
+__global__ void __launch_bounds__(256) router_stream_kernel(const uint16_t* __restrict__ x,
+                                                            const float* __restrict__ w,
+                                                            const float* __restrict__ bias, int T, int H, int E, int K,
+                                                            int normalize, float scale, float* __restrict__ logits,
+                                                            uint32_t* __restrict__ ids, float* __restrict__ probs) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    float* ring = reinterpret_cast<float*>(smem);                  // [4][H]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 8 + warp;
+    const bool live = t < T;
+    float xr[ITERS][4];
+#pragma unroll
+    for (int i = 0; i < ITERS; i++) {
+        const int k = lane * 4 + 128 * i;
+        if (live && k < H) {
+            uint2 xv = *reinterpret_cast<const uint2*>(x + (size_t)t * H + k);
+            xr[i][0] = __uint_as_float(xv.x << 16); xr[i][1] = __uint_as_float(xv.x & 0xffff0000u);
+            xr[i][2] = __uint_as_float(xv.y << 16); xr[i][3] = __uint_as_float(xv.y & 0xffff0000u);
+        } else {
+            xr[i][0] = xr[i][1] = xr[i][2] = xr[i][3] = 0.f;
+        }
+    }
+    const int chunks = H / 4;                                       // 16-byte chunks per router row
+    auto issue = [&](int e) {
+        if (e < E) {
+            const float* src = w + (size_t)e * H;
+            const uint32_t dst = smem_u32(ring + (size_t)(e & 3) * H);
+            for (int c = threadIdx.x; c < chunks; c += 256) cp_async16(dst + 16u * c, src + 4 * c);
+        }
+        cp_async_commit();
+    };
+    issue(0); issue(1); issue(2);
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int e = 0; e < E; e++) {
+        cp_async_wait<2>();
+        __syncthreads();            // row e has landed for everyone; row e - 1 is no longer read
+        issue(e + 3);               // into the buffer row e - 1 used
+        const float* wr = ring + (size_t)(e & 3) * H;
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < ITERS; i++) {
+            const int k = lane * 4 + 128 * i;
+            if (k < H) {
+                float4 wv = *reinterpret_cast<const float4*>(wr + k);
+                a0 = __fmaf_rn(xr[i][0], wv.x, a0);
+                a1 = __fmaf_rn(xr[i][1], wv.y, a1);
+                a2 = __fmaf_rn(xr[i][2], wv.z, a2);
+                a3 = __fmaf_rn(xr[i][3], wv.w, a3);
+            }
+        }
+        float sres = warp_butterfly_sum(__fadd_rn(__fadd_rn(a0, a1), __fadd_rn(a2, a3)));
+        if (ARCH == OCO_ARCH_GPT_OSS) sres = __fadd_rn(sres, bf16_round(bias[e]));
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if ((e >> 5) == j && (e & 31) == lane) v[j] = sres;
+    }
+    cp_async_wait<0>();
+    if (!live) return;
+    if (logits) {
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (lane + 32 * j < E) logits[(size_t)t * E + lane + 32 * j] = v[j];
+    }
+    uint32_t id[kMaxTopK];
+    float pr[kMaxTopK];
+    select_experts<ARCH>(v, E, K, ARCH == OCO_ARCH_NEMOTRON ? bias : nullptr, normalize, scale, lane, id, pr);
+#pragma unroll
+    for (int r = 0; r < kMaxTopK; r++)
+        if (r < K && lane == r) { ids[(size_t)t * K + r] = id[r]; probs[(size_t)t * K + r] = pr[r]; }
+}
+
 }  // namespace oco
