@@ -166,6 +166,7 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--cpu-tokens", type=int, default=32, help="tokens in the CPU baseline's bounded sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="single-token workloads: launch kernels directly instead of replaying CUDA graphs")
     ap.add_argument("--layers", type=int, default=0, help="distinct weight copies rotated per step (0 = auto)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -208,16 +209,35 @@ def main():
     res = torch.from_numpy(res_bits.view(np.int16).copy()).cuda()
     stream = torch.cuda.current_stream()
 
+    graphs = [None] * copies
+
     def step(i, profile=False):
         p = plans[i % copies]
+        if graphs[i % copies] is not None and not profile:
+            graphs[i % copies].replay()       # launch-bound single-token step: one graph launch
+            return p
         p.set_profiling(profile)
         p.forward(x, res, tokens)
         return p
 
-    for i in range(args.warmup):
+    for i in range(max(args.warmup, copies if decode else 0)):
         step(i)
     torch.cuda.synchronize()
     plans[0].poll()
+    if decode and not args.no_graph:
+        # A single token is a handful of microsecond kernels: capture each weight copy's step in a
+        # CUDA graph so the timed region measures the GPU, not the host's launch rate.
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for c in range(copies):
+                plans[c].set_profiling(False)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    plans[c].forward(x, res, tokens)
+                graphs[c] = g
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
     # routing of this batch (for the algorithmic byte count)
     routing = moe.Routing(); routing.plan, routing.rows = plans[(args.warmup - 1) % copies if args.warmup else 0], tokens
     if not args.warmup:
@@ -239,7 +259,7 @@ def main():
     t_wall = time.perf_counter()
     for i in range(args.steps):
         starts[i].record(stream)
-        p = step(args.warmup + i, profile=True)
+        p = step(args.warmup + i, profile=graphs[0] is None)
         ends[i].record(stream)
         launches += p.launch_count()
     torch.cuda.synchronize()
@@ -305,7 +325,8 @@ def main():
         if decode:
             # bandwidth-bound: the phase streams the selected experts' packed rows once
             rb_up, rb_dn = synth.row_bytes(layer.fmt, H), synth.row_bytes(layer.fmt, F)
-            per = {"expand": layer.top_k * n_up * F * rb_up, "down": layer.top_k * H * rb_dn}
+            per = {"expand": layer.top_k * n_up * F * rb_up, "down": layer.top_k * H * rb_dn,
+                   "down_combine": layer.top_k * H * rb_dn}
             units = per.get(dominant, alg_bytes)
             achieved = units / dur_s / 1e9
             roofline = dict(bound="hbm", kernel=dominant, achieved=achieved, peak=peaks["hbm_gbs"], unit="GB/s",
@@ -338,6 +359,7 @@ def main():
                     experts_touched=touched, weight_copies=copies,
                     cache="every step reads all expert weights (%.0f MB), more than the 126 MB L2" % (per_step_bytes / 1e6)
                     if not decode else "%d weight copies rotated per step (%.0f MB between reuses)" % (copies, copies * per_step_bytes / 1e6),
+                    cuda_graph=graphs[0] is not None,
                     parallelism="replicas" if world > 1 else "single"),
         clocks=clocks, e2e=e2e, gpu_launches=launches, phases_ms=phases, roofline=roofline, cpu_baseline=base,
         step_ms_min=min(step_ms), step_ms_max=max(step_ms))

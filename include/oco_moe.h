@@ -139,6 +139,23 @@ int oco_moe_bind_weights(oco_moe_plan* plan, const oco_moe_weights* weights);
 int oco_moe_forward(oco_moe_plan* plan, const uint16_t* x_bf16, uint16_t* residual_bf16, int rows,
                     void* cuda_stream);
 
+/* The three stages of the layer as calls of their own, for expert parallelism (experts sharded
+ * over GPUs, an all-to-all between the stages). The reference has no multi-GPU path; these follow
+ * the stage boundaries of its tiled operator (feed_forward.rs:165-274): router, then route plan +
+ * up/down tiles, then moe_sum / moe_add.
+ *   oco_moe_route    ids and weights of `rows` tokens into the workspace (read them with
+ *                    oco_moe_routing); the plan needs only router weights bound.
+ *   oco_moe_experts  expert products of `routes` rows that are already routed: row i (bf16
+ *                    [routes, hidden]) goes to expert expert_ids[i] of THIS plan (0 .. experts-1, the
+ *                    local shard), its bf16 output lands in row i of y. routes <= max_rows * top_k.
+ *   oco_moe_combine  residual[t] += sum_r y[t * top_k + r] * probs[t * top_k + r] with the family's
+ *                    rounding rule. */
+int oco_moe_route(oco_moe_plan* plan, const uint16_t* x_bf16, int rows, void* cuda_stream);
+int oco_moe_experts(oco_moe_plan* plan, const uint16_t* rows_bf16, const uint32_t* expert_ids, int routes,
+                    uint16_t* y_bf16, void* cuda_stream);
+int oco_moe_combine(oco_moe_plan* plan, const uint16_t* y_bf16, const float* probs, uint16_t* residual_bf16,
+                    int rows, void* cuda_stream);
+
 /* The same call for host buffers: copies x and the residual to the device, runs the layer and
  * copies the residual back, all on `cuda_stream`, then waits for the stream. Uses staging space
  * inside the bound workspace. */

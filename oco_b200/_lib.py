@@ -38,6 +38,9 @@ SIGNATURES = {
     "oco_moe_bind_workspace": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]),
     "oco_moe_bind_weights": (C.c_int, [C.c_void_p, C.POINTER(Weights)]),
     "oco_moe_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "oco_moe_route": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "oco_moe_experts": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "oco_moe_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "oco_moe_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "oco_moe_poll": (C.c_int, [C.c_void_p, C.c_void_p]),
     "oco_moe_routing": (C.c_int, [C.c_void_p, C.POINTER(RoutingView)]),

@@ -39,6 +39,7 @@ struct Workspace {
     uint16_t* y = nullptr;        // bf16 [R, H] expert outputs, route order
     float* act1 = nullptr;        // f32 [K, F] single-token activations
     __half* actfrag = nullptr;    // single-token B fragments of the down projection
+    uint32_t* arrivals = nullptr; // single-token combine: one counter per eight output rows
     uint16_t* xh = nullptr;       // half [T, H] token-order input rows (shared expert)
     uint16_t* mid = nullptr;      // half [T, S] shared expert intermediate
     uint16_t* shared_out = nullptr;  // bf16 [T, H]
@@ -57,6 +58,7 @@ struct oco_moe_plan {
     oco_moe_weights w{};
     Workspace ws{};
     bool have_ws = false, have_w = false;
+    bool have_experts = false;   // expert banks bound (enough for oco_moe_experts)
     bool router_ready = false;   // the rounded router copy matches the bound weights and workspace
     int max_rows = 0;
     int sm_count = 148;
@@ -141,6 +143,7 @@ Workspace carve(const oco_moe_desc& d, int max_rows, unsigned char* base) {
     w.y = (uint16_t*)take(R * H * 2);
     w.act1 = (float*)take(K * F * 4);
     w.actfrag = (__half*)take(P * (F / 32) * 128 * 2);
+    w.arrivals = (uint32_t*)take((H / 8 + 1) * 4);
     if (S) {
         w.xh = (uint16_t*)take(T * H * 2);
         w.mid = (uint16_t*)take(T * S * 2);
@@ -191,7 +194,12 @@ int pick_tile_index(int routes, int experts) {
 constexpr size_t kMaxDynamicSmem = 232448;
 template <typename Kern>
 cudaError_t allow_smem(Kern k) {
-    return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynamicSmem);
+    cudaFuncAttributes attr;
+    cudaError_t e = cudaFuncGetAttributes(&attr, k);
+    if (e != cudaSuccess) return e;
+    // static and dynamic shared memory share the 227 KB a CTA may opt into
+    return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)(kMaxDynamicSmem - attr.sharedSizeBytes));
 }
 
 template <int FMT, int EPI, int NT>
@@ -306,9 +314,13 @@ int forward_single(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, cu
             return launch_expand<ARCH, FMT>(plan, ep, grid, st);
         };
         auto down = [&](const uint8_t* down_w, const float* bias, const uint32_t* ids, const __half* actfrag, int k,
-                        int f, uint32_t row_bytes, uint16_t* y) -> int {
+                        int f, uint32_t row_bytes, uint16_t* y, bool combine, const uint16_t* shared) -> int {
             DecodeDownParams dp{};
             dp.down_w = down_w; dp.down_b = bias; dp.ids = ids; dp.actfrag = actfrag; dp.y = y;
+            if (combine) {
+                dp.arrivals = ws.arrivals; dp.probs = ws.probs; dp.residual = residual; dp.shared = shared;
+                dp.round_sum = ARCH == OCO_ARCH_GPT_OSS ? 1 : 0;
+            }
             dp.H = H; dp.F = f; dp.K = k; dp.row_bytes = row_bytes; dp.span_cap = (uint32_t)decode_span_cap(row_bytes);
             size_t smem = (size_t)(f / 32) * 4 * 4 * 16 + 2 * kDecodeWarps * 16 * 2 * 4 +
                           (size_t)kDownStages * 2 * dp.span_cap;
@@ -326,13 +338,11 @@ int forward_single(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, cu
         mark(plan, st, "expand");
         int rc = expand(plan->w.gate_w, plan->w.up_w, ws.logits, K, F, ws.ids, ws.probs, ws.act1, ws.actfrag);
         if (rc) return rc;
-        mark(plan, st, "down");
-        rc = down(plan->w.down_w, plan->w.down_b, ws.ids, ws.actfrag, K, F, plan->down_row_bytes, ws.y);
-        if (rc) return rc;
-        int shared_mode = 0;
+        const uint16_t* shared = nullptr;
         if (ARCH == OCO_ARCH_NEMOTRON && d.shared_ffn) {
             // The always-on expert runs through the same kernels as a one-expert bank
-            // (compute/nemotron.rs:460-509 runs it as dense matvecs beside the routed ones).
+            // (compute/nemotron.rs:460-509 runs it as dense matvecs beside the routed ones); its
+            // output joins the routed sum in f32 (moe_add with shared = 1).
             DecodeExpandParams ep{};
             ep.gate_w = nullptr; ep.up_w = plan->w.shared_up_w; ep.x = x; ep.logits = nullptr;
             ep.ids = ws.sh_ids + 8; ep.probs = (float*)(ws.sh_ids + 16); ep.act = ws.sh_act1; ep.actfrag = ws.sh_actfrag;
@@ -343,16 +353,15 @@ int forward_single(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, cu
             if (rc) return rc;
             mark(plan, st, "shared_down");
             rc = down(plan->w.shared_down_w, nullptr, ws.sh_ids, ws.sh_actfrag, 1, d.shared_ffn,
-                      plan->shared_down_row_bytes, ws.shared_out);
+                      plan->shared_down_row_bytes, ws.shared_out, false, nullptr);
             if (rc) return rc;
-            shared_mode = 1;
+            shared = ws.shared_out;
         }
-        const int pairs = H / 2;
-        mark(plan, st, "combine");
-        moe_combine_kernel<<<(pairs + 255) / 256, 256, 0, st>>>(ws.y, ws.probs, residual, ws.shared_out, H, 1, K,
-                                                               ARCH == OCO_ARCH_GPT_OSS ? 1 : 0, shared_mode);
-        plan->launches++;
-        CK(cudaGetLastError());
+        // Routed down products; the last CTA to finish each block of output rows combines them
+        // onto the residual (moe_sum / moe_add), so no separate combine launch is needed.
+        mark(plan, st, "down_combine");
+        rc = down(plan->w.down_w, plan->w.down_b, ws.ids, ws.actfrag, K, F, plan->down_row_bytes, ws.y, true, shared);
+        if (rc) return rc;
         mark(plan, st, "end");
         return OCO_OK;
     } else {
@@ -363,15 +372,15 @@ int forward_single(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, cu
 // ---- tiled path ---------------------------------------------------------------------------------
 // rows > 1 of Bindings::experts (feed_forward.rs:164-240,258-274) and relu_experts
 // (compute/nemotron.rs:294-406): router -> plan -> gather -> up tiles (+activation) -> down tiles
-// -> combine.
+// -> combine. The three stages are also entry points of their own for expert parallelism, where
+// an all-to-all sits between them.
+
+// Stage 1: logits, expert ids and combination weights of `rows` tokens into the workspace.
 template <int ARCH>
-int forward_tiled(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int rows, cudaStream_t st) {
-    constexpr int FMT = Family<ARCH>::kFmt;
-    constexpr int EPI_UP = Family<ARCH>::kEpiUp;
+int stage_route(oco_moe_plan* plan, const uint16_t* x, int rows, cudaStream_t st) {
     const oco_moe_desc& d = plan->d;
     Workspace& ws = plan->ws;
-    const int H = d.hidden, F = d.ffn, E = d.experts, K = d.top_k, R = rows * K;
-
+    const int H = d.hidden, E = d.experts, K = d.top_k;
     mark(plan, st, "router");
     if (H <= 3072 && H % 4 == 0) {
         const float* rw = plan->w.router_w;
@@ -404,16 +413,28 @@ int forward_tiled(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int
     }
     plan->launches++;
     CK(cudaGetLastError());
+    return OCO_OK;
+}
 
+// Stage 2: expert products of R routes. Route i reads input row i / per_row of x (bf16) and goes
+// to expert ids[i]; its bf16 output lands in row i of y.
+template <int ARCH>
+int stage_experts(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, int R, int per_row, uint16_t* y,
+                  cudaStream_t st) {
+    constexpr int FMT = Family<ARCH>::kFmt;
+    constexpr int EPI_UP = Family<ARCH>::kEpiUp;
+    const oco_moe_desc& d = plan->d;
+    Workspace& ws = plan->ws;
+    const int H = d.hidden, F = d.ffn, E = d.experts;
     const int nt_index = pick_tile_index(R, E);
     const int NT = kTileSizes[nt_index];
     plan->last_tile_rows = NT;
     mark(plan, st, "route_plan");
-    route_plan_kernel<<<1, 1024, 0, st>>>(ws.ids, (uint32_t)R, (uint32_t)E, (uint32_t)NT, ws.offsets, ws.row_of_route,
+    route_plan_kernel<<<1, 1024, 0, st>>>(ids, (uint32_t)R, (uint32_t)E, (uint32_t)NT, ws.offsets, ws.row_of_route,
                                           ws.route_of_row, ws.tiles, ws.tile_count);
     plan->launches++;
     mark(plan, st, "permute");
-    permute_rows_kernel<<<R, 256, 0, st>>>(x, ws.route_of_row, K, H, FMT == OCO_FMT_Q4_K ? 32 : 16, ws.xs);
+    permute_rows_kernel<<<R, 256, 0, st>>>(x, ws.route_of_row, per_row, H, FMT == OCO_FMT_Q4_K ? 32 : 16, ws.xs);
     plan->launches++;
     CK(cudaGetLastError());
     const int max_tiles = R / NT + (E < R ? E : R);
@@ -435,11 +456,36 @@ int forward_tiled(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int
     dn.b0 = ARCH == OCO_ARCH_GPT_OSS ? plan->w.down_b : nullptr; dn.b1 = nullptr;
     dn.n = H; dn.K = F; dn.row_bytes = plan->down_row_bytes;
     dn.tiles = ws.tiles; dn.tile_count = ws.tile_count; dn.offsets = ws.offsets; dn.route_of_row = ws.route_of_row;
-    dn.xs = ws.act; dn.out = ws.y; dn.status = ws.status; dn.dense_rows = 0; dn.tile_rows = NT;
+    dn.xs = ws.act; dn.out = y; dn.status = ws.status; dn.dense_rows = 0; dn.tile_rows = NT;
     mark(plan, st, "down_tiles");
-    rc = launch_gemm_nt<FMT, kEpiDownBf16>(plan, dn, plan->map_act, nt_index, max_tiles, st);
-    if (rc) return rc;
+    return launch_gemm_nt<FMT, kEpiDownBf16>(plan, dn, plan->map_act, nt_index, max_tiles, st);
+}
 
+// Stage 3: weighted combine of route-ordered expert outputs onto the residual.
+template <int ARCH>
+int stage_combine(oco_moe_plan* plan, const uint16_t* y, const float* probs, uint16_t* residual, int rows,
+                  int shared_mode, cudaStream_t st) {
+    const oco_moe_desc& d = plan->d;
+    const size_t pairs = (size_t)rows * d.hidden / 2;
+    mark(plan, st, "combine");
+    moe_combine_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, st>>>(y, probs, residual, plan->ws.shared_out,
+                                                                        d.hidden, rows, d.top_k,
+                                                                        ARCH == OCO_ARCH_GPT_OSS ? 1 : 0, shared_mode);
+    plan->launches++;
+    CK(cudaGetLastError());
+    return OCO_OK;
+}
+
+template <int ARCH>
+int forward_tiled(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int rows, cudaStream_t st) {
+    constexpr int FMT = Family<ARCH>::kFmt;
+    const oco_moe_desc& d = plan->d;
+    Workspace& ws = plan->ws;
+    const int H = d.hidden, K = d.top_k;
+    int rc = stage_route<ARCH>(plan, x, rows, st);
+    if (rc) return rc;
+    rc = stage_experts<ARCH>(plan, x, ws.ids, rows * K, K, ws.y, st);
+    if (rc) return rc;
     int shared_mode = 0;
     if (ARCH == OCO_ARCH_NEMOTRON && d.shared_ffn) {
         // Shared expert as dense tiles over all rows: up -> relu^2 (bf16) -> down, joined to the
@@ -462,13 +508,8 @@ int forward_tiled(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int
         if (rc) return rc;
         shared_mode = 2;
     }
-    const size_t pairs = (size_t)rows * H / 2;
-    mark(plan, st, "combine");
-    moe_combine_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, st>>>(ws.y, ws.probs, residual, ws.shared_out, H,
-                                                                        rows, K, ARCH == OCO_ARCH_GPT_OSS ? 1 : 0,
-                                                                        shared_mode);
-    plan->launches++;
-    CK(cudaGetLastError());
+    rc = stage_combine<ARCH>(plan, ws.y, ws.probs, residual, rows, shared_mode, st);
+    if (rc) return rc;
     mark(plan, st, "end");
     return OCO_OK;
 }
@@ -562,6 +603,7 @@ int oco_moe_bind_workspace(oco_moe_plan* plan, void* workspace, size_t bytes, in
     // Control words and the never-written columns of the single-token fragments start at zero.
     CK(cudaMemset(ws.status, 0, 256));
     CK(cudaMemset(ws.actfrag, 0, (size_t)((d.top_k + 1) / 2) * (d.ffn / 32) * 128 * 2));
+    CK(cudaMemset(ws.arrivals, 0, (size_t)(d.hidden / 8 + 1) * 4));
     if (d.shared_ffn) {
         CK(cudaMemset(ws.sh_actfrag, 0, (size_t)(d.shared_ffn / 32) * 128 * 2));
         CK(cudaMemset(ws.sh_ids, 0, 256));
@@ -590,15 +632,25 @@ int oco_moe_bind_workspace(oco_moe_plan* plan, void* workspace, size_t bytes, in
 int oco_moe_bind_weights(oco_moe_plan* plan, const oco_moe_weights* w) {
     if (!plan || !w) return fail(plan, OCO_INVALID_ARGUMENT, "null weights");
     const oco_moe_desc& d = plan->d;
-    if (!w->router_w || !w->up_w || !w->down_w) return fail(plan, OCO_INVALID_ARGUMENT, "router_w, up_w and down_w are required");
-    if (d.arch != OCO_ARCH_NEMOTRON && !w->gate_w) return fail(plan, OCO_INVALID_ARGUMENT, "gate_w is required for gated experts");
-    if (d.arch == OCO_ARCH_GPT_OSS && (!w->router_b || !w->gate_b || !w->up_b || !w->down_b))
-        return fail(plan, OCO_INVALID_ARGUMENT, "GPT_OSS needs router, gate, up and down biases");
-    if (d.arch == OCO_ARCH_NEMOTRON && !w->router_b) return fail(plan, OCO_INVALID_ARGUMENT, "NEMOTRON needs the selection bias");
-    if (d.shared_ffn && (!w->shared_up_w || !w->shared_down_w)) return fail(plan, OCO_INVALID_ARGUMENT, "shared expert weights missing");
-    if (((uintptr_t)w->router_w & 15u) != 0) return fail(plan, OCO_INVALID_ARGUMENT, "router_w must be 16-byte aligned");
+    // A plan may hold only a router (it then serves oco_moe_route), only experts (oco_moe_experts),
+    // or both (oco_moe_forward needs both).
+    const bool has_router = w->router_w != nullptr;
+    const bool has_experts = w->up_w != nullptr || w->down_w != nullptr || w->gate_w != nullptr;
+    if (!has_router && !has_experts) return fail(plan, OCO_INVALID_ARGUMENT, "no weights given");
+    if (has_experts) {
+        if (!w->up_w || !w->down_w) return fail(plan, OCO_INVALID_ARGUMENT, "up_w and down_w are required");
+        if (d.arch != OCO_ARCH_NEMOTRON && !w->gate_w) return fail(plan, OCO_INVALID_ARGUMENT, "gate_w is required for gated experts");
+        if (d.arch == OCO_ARCH_GPT_OSS && (!w->gate_b || !w->up_b || !w->down_b))
+            return fail(plan, OCO_INVALID_ARGUMENT, "GPT_OSS needs gate, up and down biases");
+        if (d.shared_ffn && (!w->shared_up_w || !w->shared_down_w)) return fail(plan, OCO_INVALID_ARGUMENT, "shared expert weights missing");
+    }
+    if (has_router) {
+        if (d.arch != OCO_ARCH_QWEN && !w->router_b) return fail(plan, OCO_INVALID_ARGUMENT, "this family needs router_b");
+        if (((uintptr_t)w->router_w & 15u) != 0) return fail(plan, OCO_INVALID_ARGUMENT, "router_w must be 16-byte aligned");
+    }
     plan->w = *w;
-    plan->have_w = true;
+    plan->have_w = has_router && has_experts;
+    plan->have_experts = has_experts;
     plan->router_ready = false;
     return OCO_OK;
 }
@@ -617,6 +669,61 @@ int oco_moe_forward(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, i
         case OCO_ARCH_NEMOTRON: return forward_family<OCO_ARCH_NEMOTRON>(plan, x, residual, rows, st);
         default: return forward_family<OCO_ARCH_QWEN>(plan, x, residual, rows, st);
     }
+}
+
+// ---- stages as entry points (expert parallelism puts an all-to-all between them) ---------------
+int oco_moe_route(oco_moe_plan* plan, const uint16_t* x, int rows, void* cuda_stream) {
+    if (!plan) return OCO_INVALID_ARGUMENT;
+    if (!plan->have_ws || !plan->w.router_w) return fail(plan, OCO_INVALID_ARGUMENT, "bind a workspace and router weights first");
+    if (!x || rows < 1 || rows > plan->max_rows) return fail(plan, OCO_INVALID_ARGUMENT, "bad x or rows");
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    plan->launches = 0;
+    plan->n_marks = 0;
+    int rc;
+    switch (plan->d.arch) {
+        case OCO_ARCH_GPT_OSS: rc = stage_route<OCO_ARCH_GPT_OSS>(plan, x, rows, st); break;
+        case OCO_ARCH_NEMOTRON: rc = stage_route<OCO_ARCH_NEMOTRON>(plan, x, rows, st); break;
+        default: rc = stage_route<OCO_ARCH_QWEN>(plan, x, rows, st); break;
+    }
+    mark(plan, st, "end");
+    return rc;
+}
+
+int oco_moe_experts(oco_moe_plan* plan, const uint16_t* rows_bf16, const uint32_t* expert_ids, int routes,
+                    uint16_t* y_bf16, void* cuda_stream) {
+    if (!plan) return OCO_INVALID_ARGUMENT;
+    if (!plan->have_ws || !plan->have_experts) return fail(plan, OCO_INVALID_ARGUMENT, "bind a workspace and expert weights first");
+    if (routes == 0) return OCO_OK;
+    if (!rows_bf16 || !expert_ids || !y_bf16 || routes < 0 || routes > plan->max_rows * plan->d.top_k)
+        return fail(plan, OCO_INVALID_ARGUMENT, "bad buffers, or more routes than max_rows * top_k");
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    plan->launches = 0;
+    plan->n_marks = 0;
+    int rc;
+    switch (plan->d.arch) {
+        case OCO_ARCH_GPT_OSS: rc = stage_experts<OCO_ARCH_GPT_OSS>(plan, rows_bf16, expert_ids, routes, 1, y_bf16, st); break;
+        case OCO_ARCH_NEMOTRON: rc = stage_experts<OCO_ARCH_NEMOTRON>(plan, rows_bf16, expert_ids, routes, 1, y_bf16, st); break;
+        default: rc = stage_experts<OCO_ARCH_QWEN>(plan, rows_bf16, expert_ids, routes, 1, y_bf16, st); break;
+    }
+    mark(plan, st, "end");
+    return rc;
+}
+
+int oco_moe_combine(oco_moe_plan* plan, const uint16_t* y_bf16, const float* probs, uint16_t* residual_bf16, int rows,
+                    void* cuda_stream) {
+    if (!plan) return OCO_INVALID_ARGUMENT;
+    if (!y_bf16 || !probs || !residual_bf16 || rows < 1) return fail(plan, OCO_INVALID_ARGUMENT, "bad buffers or rows");
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    plan->launches = 0;
+    plan->n_marks = 0;
+    int rc;
+    switch (plan->d.arch) {
+        case OCO_ARCH_GPT_OSS: rc = stage_combine<OCO_ARCH_GPT_OSS>(plan, y_bf16, probs, residual_bf16, rows, 0, st); break;
+        case OCO_ARCH_NEMOTRON: rc = stage_combine<OCO_ARCH_NEMOTRON>(plan, y_bf16, probs, residual_bf16, rows, 0, st); break;
+        default: rc = stage_combine<OCO_ARCH_QWEN>(plan, y_bf16, probs, residual_bf16, rows, 0, st); break;
+    }
+    mark(plan, st, "end");
+    return rc;
 }
 
 int oco_moe_forward_host(oco_moe_plan* plan, const uint16_t* x_host, uint16_t* residual_host, int rows,

@@ -82,6 +82,17 @@ __device__ __forceinline__ uint32_t e2m1x2_to_half2(uint32_t byte) {
     return (uint32_t)r.x | ((uint32_t)r.y << 16);
 }
 
+// The four code bytes of a word -> four half2 (low nibble in .x, high nibble in .y).
+__device__ __forceinline__ void cvt_e2m1x2_x4(uint32_t w, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+        : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+        : "r"(w));
+}
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 // ---- unaligned byte access through aligned words -----------------------------------------------

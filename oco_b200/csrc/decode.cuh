@@ -27,6 +27,14 @@ constexpr int kDecodeWarps = 8;
 constexpr int kExpandStages = 4;  // ring depth of the up/gate kernel
 constexpr int kDownStages = 3;    // the down kernel also holds four fragment columns per block
 
+// D = A * B with a zero accumulator, then D += A * B (fp32 accumulate, half operands).
+__device__ __forceinline__ void mma16816_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -34,31 +42,41 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-
-// 4 bytes at an arbitrary byte offset of shared memory.
-__device__ __forceinline__ uint32_t lds_u32_unaligned(const uint8_t* p) {
-    uintptr_t a = (uintptr_t)p;
-    const uint32_t* w = (const uint32_t*)(a & ~(uintptr_t)3);
-    uint32_t sh = ((uint32_t)a & 3u) * 8u;
-    return __funnelshift_r(w[0], w[1], sh);
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds8(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
 }
 
 // Block codecs for the 32-element formats whose code byte j holds elements j (low nibble) and
 // j + 16 (high nibble): MXFP4 (17 bytes, E8M0 scale) and Q4_0 (18 bytes, f16 scale, code - 8).
+// `block` is the shared-memory byte address of the block; quads() turns a word of four code
+// bytes into four half2 (element j, element j + 16).
 template <int FMT>
 struct Block32;
 template <>
 struct Block32<OCO_FMT_MXFP4> {
     static constexpr int kBytes = 17, kHeader = 1;
-    __device__ static __forceinline__ float scale(const uint8_t* blk) { return e8m0_scale(blk[0]); }
-    // one code byte -> half2 (element j, element j + 16)
-    __device__ static __forceinline__ uint32_t pair(uint32_t byte) { return e2m1x2_to_half2(byte); }
+    __device__ static __forceinline__ float scale(uint32_t block) { return e8m0_scale(lds8(block)); }
+    __device__ static __forceinline__ void quads(uint32_t w, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+        cvt_e2m1x2_x4(w, r0, r1, r2, r3);
+    }
 };
 template <>
 struct Block32<OCO_FMT_Q4_0> {
     static constexpr int kBytes = 18, kHeader = 2;
-    __device__ static __forceinline__ float scale(const uint8_t* blk) {
-        return f16_bits_to_f32((uint16_t)(blk[0] | ((uint16_t)blk[1] << 8)));
+    __device__ static __forceinline__ float scale(uint32_t block) {
+        return f16_bits_to_f32((uint16_t)(lds8(block) | (lds8(block + 1) << 8)));
     }
     __device__ static __forceinline__ uint32_t pair(uint32_t byte) {
         // 0x6400 | q is the half 1024 + q; subtracting 1032 leaves q - 8 exactly.
@@ -66,7 +84,47 @@ struct Block32<OCO_FMT_Q4_0> {
         __half2 h = __hsub2(*reinterpret_cast<__half2*>(&v), __half2half2(__ushort_as_half((unsigned short)0x6408)));
         return *reinterpret_cast<uint32_t*>(&h);
     }
+    __device__ static __forceinline__ void quads(uint32_t w, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+        r0 = pair(w); r1 = pair(w >> 8); r2 = pair(w >> 16); r3 = pair(w >> 24);
+    }
 };
+
+// Dot products of 16 packed rows with the activation fragments, for the blocks kb = warp, warp + 8, ...
+// rowA / rowB: shared-memory byte addresses of this lane's row g of the first / second span;
+// xlane: address of this lane's fragment (uint4) for block 0; xstride: fragment bytes per block.
+// sum[0..1] accumulate row g (two columns), sum[2..3] row g + 8. The warp's blocks are 8 apart, so
+// every address advances by a multiple of four bytes per step and the word alignment of the code
+// bytes is fixed for the whole loop.
+template <int FMT>
+__device__ __forceinline__ void rows_dot(uint32_t rowA, uint32_t rowB, uint32_t xlane, uint32_t xstride, int nkb,
+                                         int warp, int tig, float (&sum)[4]) {
+    using B = Block32<FMT>;
+    constexpr uint32_t kStep = kDecodeWarps * B::kBytes;                 // 136 or 144 bytes
+    uint32_t ba = rowA + (uint32_t)warp * B::kBytes, bb = rowB + (uint32_t)warp * B::kBytes;
+    const uint32_t ca = ba + B::kHeader + 4u * tig, cb = bb + B::kHeader + 4u * tig;
+    const uint32_t shA = (ca & 3u) * 8u, shB = (cb & 3u) * 8u;
+    uint32_t a4 = ca & ~3u, b4 = cb & ~3u;
+    uint32_t xa = xlane + (uint32_t)warp * xstride;
+    const uint32_t xstep = kDecodeWarps * xstride;
+#pragma unroll 2
+    for (int kb = warp; kb < nkb; kb += kDecodeWarps) {
+        const uint32_t wa = __funnelshift_r(lds32(a4), lds32(a4 + 4), shA);
+        const uint32_t wb = __funnelshift_r(lds32(b4), lds32(b4 + 4), shB);
+        const float sa = B::scale(ba), sb = B::scale(bb);
+        const uint4 xf = lds128(xa);
+        uint32_t qa0, qa1, qa2, qa3, qb0, qb1, qb2, qb3;
+        B::quads(wa, qa0, qa1, qa2, qa3);
+        B::quads(wb, qb0, qb1, qb2, qb3);
+        float acc[4];
+        mma16816_first(acc, qa0, qb0, qa1, qb1, xf.x, xf.y);
+        mma16816(acc, qa2, qb2, qa3, qb3, xf.z, xf.w);
+        sum[0] = __fmaf_rn(acc[0], sa, sum[0]);
+        sum[1] = __fmaf_rn(acc[1], sa, sum[1]);
+        sum[2] = __fmaf_rn(acc[2], sb, sum[2]);
+        sum[3] = __fmaf_rn(acc[3], sb, sum[3]);
+        a4 += kStep; b4 += kStep; ba += kStep; bb += kStep; xa += xstep;
+    }
+}
 
 // Issues the cp.async copies of one byte span [src, src + bytes) into `dst` (16-byte aligned),
 // widened to whole 16-byte chunks. Returns nothing; the span's first byte lands at dst + (src & 15).
@@ -187,33 +245,20 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_expand_kernel(const Dec
         for (int q = 0; q < kMaxTopK; q++)
             if (q == r) e = ids[q];
         size_t off = ((size_t)e * p.F + c0) * p.row_bytes;
-        const uint8_t* s0 = ring + (size_t)(it % kDecodeStages) * stage_bytes;
+        const uint32_t s0 = smem_u32(ring) + (uint32_t)(it % kDecodeStages) * stage_bytes;
         // rows g (first span) and g + 8 (second span)
-        const uint8_t* rowA;
-        const uint8_t* rowB;
+        uint32_t rowA, rowB;
         if (GATED) {
-            rowA = s0 + ((uintptr_t)(p.gate_w + off) & 15) + (size_t)g * p.row_bytes;
-            rowB = s0 + p.span_cap + ((uintptr_t)(p.up_w + off) & 15) + (size_t)g * p.row_bytes;
+            rowA = s0 + ((uint32_t)(uintptr_t)(p.gate_w + off) & 15u) + (uint32_t)g * p.row_bytes;
+            rowB = s0 + p.span_cap + ((uint32_t)(uintptr_t)(p.up_w + off) & 15u) + (uint32_t)g * p.row_bytes;
         } else {
-            rowA = s0 + ((uintptr_t)(p.up_w + off) & 15) + (size_t)g * p.row_bytes;
-            rowB = s0 + p.span_cap + ((uintptr_t)(p.up_w + off + (size_t)8 * p.row_bytes) & 15) + (size_t)g * p.row_bytes;
+            rowA = s0 + ((uint32_t)(uintptr_t)(p.up_w + off) & 15u) + (uint32_t)g * p.row_bytes;
+            rowB = s0 + p.span_cap + ((uint32_t)(uintptr_t)(p.up_w + off + (size_t)8 * p.row_bytes) & 15u) + (uint32_t)g * p.row_bytes;
         }
         float sum[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int kb = warp; kb < nkb; kb += kDecodeWarps) {
-            const uint8_t* ba = rowA + (size_t)kb * B::kBytes;
-            const uint8_t* bb = rowB + (size_t)kb * B::kBytes;
-            uint32_t ca = lds_u32_unaligned(ba + B::kHeader + 4 * tig);
-            uint32_t cb = lds_u32_unaligned(bb + B::kHeader + 4 * tig);
-            float sa = B::scale(ba), sb = B::scale(bb);
-            uint4 xf = g < 2 ? xfrag[(kb * 2 + g) * 4 + tig] : make_uint4(0, 0, 0, 0);
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            mma16816(acc, B::pair(ca), B::pair(cb), B::pair(ca >> 8), B::pair(cb >> 8), xf.x, xf.y);
-            mma16816(acc, B::pair(ca >> 16), B::pair(cb >> 16), B::pair(ca >> 24), B::pair(cb >> 24), xf.z, xf.w);
-            sum[0] = __fmaf_rn(acc[0], sa, sum[0]);
-            sum[1] = __fmaf_rn(acc[1], sa, sum[1]);
-            sum[2] = __fmaf_rn(acc[2], sb, sum[2]);
-            sum[3] = __fmaf_rn(acc[3], sb, sum[3]);
-        }
+        // columns 0 / 1 of the fragments hold the token's hi / lo halves; lanes of other columns
+        // re-read them (their products are never looked at)
+        rows_dot<FMT>(rowA, rowB, smem_u32(xfrag) + (uint32_t)(((g & 1) * 4 + tig) * 16), 2 * 4 * 16, nkb, warp, tig, sum);
         float* part = partial + (size_t)(it & 1) * kDecodeWarps * 32;
         if (tig == 0) {
             part[(warp * 16 + g) * 2 + 0] = __fadd_rn(sum[0], sum[1]);      // row g: hi + lo columns
@@ -258,6 +303,14 @@ struct DecodeDownParams {
     int H, F, K;
     uint32_t row_bytes;       // bytes of one packed row of length F
     uint32_t span_cap;
+    // Fused combine (null residual = off): the CTA that completes the last route pair of a block
+    // of eight output rows adds the weighted expert outputs to the residual
+    // (reference moe_sum, routing.metal:154-168; moe_add, nemotron.metal:222-236).
+    uint32_t* arrivals;       // one zeroed counter per block of eight output rows; left at zero again
+    const float* probs;       // [K]
+    uint16_t* residual;       // bf16 [H], in place
+    const uint16_t* shared;   // bf16 [H] shared-expert output joining the sum, or null
+    int round_sum;            // 1: the expert sum is rounded to bf16 before the residual add
 };
 
 // Down products for one token: item = 8 output rows of route 2p and the same 8 rows of route 2p+1
@@ -308,27 +361,13 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_down_kernel(const Decod
         cp_async_wait<kDecodeStages - 1>();
         __syncthreads();
         const int d0 = rb * 8;
-        const uint8_t* s0 = ring + (size_t)(it % kDecodeStages) * stage_bytes;
+        const uint32_t s0 = smem_u32(ring) + (uint32_t)(it % kDecodeStages) * stage_bytes;
         const uint8_t* ga = p.down_w + ((size_t)e0 * p.H + d0) * p.row_bytes;
         const uint8_t* gb = p.down_w + ((size_t)e1 * p.H + d0) * p.row_bytes;
-        const uint8_t* rowA = s0 + ((uintptr_t)ga & 15) + (size_t)g * p.row_bytes;
-        const uint8_t* rowB = s0 + p.span_cap + ((uintptr_t)gb & 15) + (size_t)g * p.row_bytes;
+        const uint32_t rowA = s0 + ((uint32_t)(uintptr_t)ga & 15u) + (uint32_t)g * p.row_bytes;
+        const uint32_t rowB = s0 + p.span_cap + ((uint32_t)(uintptr_t)gb & 15u) + (uint32_t)g * p.row_bytes;
         float sum[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int kb = warp; kb < nkb; kb += kDecodeWarps) {
-            const uint8_t* ba = rowA + (size_t)kb * B::kBytes;
-            const uint8_t* bb = rowB + (size_t)kb * B::kBytes;
-            uint32_t ca = lds_u32_unaligned(ba + B::kHeader + 4 * tig);
-            uint32_t cb = lds_u32_unaligned(bb + B::kHeader + 4 * tig);
-            float sa = B::scale(ba), sb = B::scale(bb);
-            uint4 xf = g < 4 ? xfrag[(kb * 4 + g) * 4 + tig] : make_uint4(0, 0, 0, 0);
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            mma16816(acc, B::pair(ca), B::pair(cb), B::pair(ca >> 8), B::pair(cb >> 8), xf.x, xf.y);
-            mma16816(acc, B::pair(ca >> 16), B::pair(cb >> 16), B::pair(ca >> 24), B::pair(cb >> 24), xf.z, xf.w);
-            sum[0] = __fmaf_rn(acc[0], sa, sum[0]);
-            sum[1] = __fmaf_rn(acc[1], sa, sum[1]);
-            sum[2] = __fmaf_rn(acc[2], sb, sum[2]);
-            sum[3] = __fmaf_rn(acc[3], sb, sum[3]);
-        }
+        rows_dot<FMT>(rowA, rowB, smem_u32(xfrag) + (uint32_t)(((g & 3) * 4 + tig) * 16), 4 * 4 * 16, nkb, warp, tig, sum);
         // route r0: rows g, columns 0,1 (tig 0: acc 0,1); route r1: rows g+8, columns 2,3 (tig 1: acc 2,3)
         float* part = partial + (size_t)(it & 1) * kDecodeWarps * 32;
         if (tig == 0) part[(warp * 16 + g) * 2] = __fadd_rn(sum[0], sum[1]);
@@ -342,6 +381,26 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_down_kernel(const Decod
                 uint32_t e = q ? e1 : e0;
                 if (p.down_b) a = __fadd_rn(a, bf16_round(p.down_b[(size_t)e * p.H + row]));
                 p.y[(size_t)route * p.H + row] = f32_to_bf16_bits(a);
+            }
+        }
+        if (p.residual) {
+            // Whoever finishes a row block last combines it. No CTA waits for another.
+            __shared__ int is_last;
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) {
+                is_last = atomicAdd(p.arrivals + rb, 1u) == (uint32_t)(P - 1);
+                if (is_last) p.arrivals[rb] = 0;      // ready for the next call on this stream
+            }
+            __syncthreads();
+            if (is_last && tid < 8 && d0 + tid < p.H) {
+                __threadfence();
+                const int row = d0 + tid;
+                float sres = p.shared ? bf16_bits_to_f32(p.shared[row]) : 0.0f;
+                for (int r = 0; r < p.K; r++)
+                    sres = __fmaf_rn(bf16_bits_to_f32(__ldcg(p.y + (size_t)r * p.H + row)), p.probs[r], sres);
+                if (p.round_sum) sres = bf16_round(sres);
+                p.residual[row] = f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(p.residual[row]), sres));
             }
         }
     }

@@ -72,17 +72,6 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
     __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
     return *reinterpret_cast<uint32_t*>(&r);
 }
-// The four code bytes of a word -> four half2 (low nibble in .x, high nibble in .y).
-__device__ __forceinline__ void cvt_e2m1x2_x4(uint32_t w, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
-        "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
-        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
-        "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
-        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
-        "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
-        : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-        : "r"(w));
-}
 // Two copies of an f32 rounded to half (round to nearest even, subnormals kept).
 __device__ __forceinline__ uint32_t f32_to_half2_dup(float f) {
     uint32_t r;

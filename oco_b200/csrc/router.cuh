@@ -46,6 +46,39 @@ __device__ __forceinline__ float canonical_logit(const uint16_t* x, const float*
     return warp_butterfly_sum(__fadd_rn(__fadd_rn(a0, a1), __fadd_rn(a2, a3)));
 }
 
+// The same logit with every load issued before the first FMA (n <= 128 * ITERS): a single token
+// has no other work to hide the memory latency of a load-then-FMA loop behind.
+template <bool RoundW, int ITERS>
+__device__ __forceinline__ float canonical_logit_prefetch(const uint16_t* x, const float* w, int n, int lane) {
+    uint2 xv[ITERS];
+    float4 wv[ITERS];
+#pragma unroll
+    for (int i = 0; i < ITERS; i++) {
+        const int k = lane * 4 + 128 * i;
+        if (k < n) {
+            xv[i] = *reinterpret_cast<const uint2*>(x + k);
+            wv[i] = *reinterpret_cast<const float4*>(w + k);
+        } else {
+            xv[i] = make_uint2(0u, 0u);
+            wv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITERS; i++) {
+        const int k = lane * 4 + 128 * i;
+        if (k < n) {
+            float4 v = wv[i];
+            if (RoundW) { v.x = bf16_round(v.x); v.y = bf16_round(v.y); v.z = bf16_round(v.z); v.w = bf16_round(v.w); }
+            a0 = __fmaf_rn(__uint_as_float(xv[i].x << 16), v.x, a0);
+            a1 = __fmaf_rn(__uint_as_float(xv[i].x & 0xffff0000u), v.y, a1);
+            a2 = __fmaf_rn(__uint_as_float(xv[i].y << 16), v.z, a2);
+            a3 = __fmaf_rn(__uint_as_float(xv[i].y & 0xffff0000u), v.w, a3);
+        }
+    }
+    return warp_butterfly_sum(__fadd_rn(__fadd_rn(a0, a1), __fadd_rn(a2, a3)));
+}
+
 // Top-k selection by one warp over logits distributed as logit[j] = expert (lane + 32*j).
 // Every lane returns the same ids / probs.
 //   GPT_OSS  (routing.metal:71-94): ties to the lowest index; winners rounded to bf16; softmax over
@@ -170,7 +203,9 @@ __global__ void __launch_bounds__(256) router_logits_small_kernel(const uint16_t
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int e = blockIdx.x * 8 + warp, t = blockIdx.y;
     if (e >= E) return;
-    float s = canonical_logit<ARCH == OCO_ARCH_GPT_OSS>(x + (size_t)t * H, w + (size_t)e * H, H, lane);
+    float s = H <= 128 * 24
+                  ? canonical_logit_prefetch<ARCH == OCO_ARCH_GPT_OSS, 24>(x + (size_t)t * H, w + (size_t)e * H, H, lane)
+                  : canonical_logit<ARCH == OCO_ARCH_GPT_OSS>(x + (size_t)t * H, w + (size_t)e * H, H, lane);
     if (ARCH == OCO_ARCH_GPT_OSS) s = __fadd_rn(s, bf16_round(bias[e]));
     if (lane == 0) logits[(size_t)t * E + e] = s;
 }
