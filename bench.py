@@ -37,7 +37,12 @@ WORKLOADS = {
     "qwen3-30b-a3b-prefill": ("qwen3-30b-a3b", 512),
     "nemotron-h-prefill": ("nemotron-h", 1024),
     "nemotron-h-decode": ("nemotron-h", 1),
+    # 128 experts: one GPU holds them all; with N > 1 ranks the experts are sharded 128/N per GPU and
+    # the batch (fixed in total: strong scaling) is dispatched and combined with all-to-all
+    "gpt-oss-120b-prefill": ("gpt-oss-120b", 8192),
+    "gpt-oss-120b-decode64": ("gpt-oss-120b", 64),
 }
+EXPERT_PARALLEL = {"gpt-oss-120b-prefill", "gpt-oss-120b-decode64"}
 
 
 def measured_peaks():
@@ -155,6 +160,131 @@ def run_reference(args):
     return 0
 
 
+class _Recorded:
+    """all_to_all_single that keeps what each call received, so that a later pass can replay the
+    same step with device-local copies in place of the exchange."""
+
+    def __init__(self, dist):
+        self.dist, self.log = dist, []
+
+    def __call__(self, out, inp, out_split=None, in_split=None, group=None):
+        self.dist.all_to_all_single(out, inp, out_split, in_split, group=group)
+        self.log.append(out.clone())
+
+
+class _Replayed:
+    def __init__(self, log):
+        self.log, self.i = log, 0
+
+    def __call__(self, out, inp, out_split=None, in_split=None, group=None):
+        out.copy_(self.log[self.i % len(self.log)])
+        self.i += 1
+
+
+def run_expert_parallel(args, torch, dist, world, rank, local):
+    """Experts sharded over the ranks, the batch split evenly between them (its total is fixed as N
+    grows), dispatch and combine as all-to-all over NCCL."""
+    from oco_b200 import ep
+    cfg, default_tokens = WORKLOADS[args.workload]
+    total = args.tokens or default_tokens
+    if total % world:
+        raise SystemExit(f"{total} tokens do not divide over {world} ranks")
+    T = total // world
+    layer = synth.make_config(cfg, seed=args.seed)
+    E, K, H, F = layer.experts, layer.top_k, layer.hidden, layer.ffn
+    be = ep.CudaBackend(layer, rank, world, max_rows=T)
+    backend = be.backend()
+    x_bits, res_bits = synth.make_tokens(H, total, args.seed, "normal")
+    x_bits, res_bits = x_bits[rank * T:(rank + 1) * T], res_bits[rank * T:(rank + 1) * T]
+    hx = torch.from_numpy(x_bits.view(np.int16).copy()).pin_memory()
+    hres = torch.from_numpy(res_bits.view(np.int16).copy()).pin_memory()
+    x, res = hx.cuda(), hres.cuda()
+    stream = torch.cuda.current_stream()
+
+    def timed(n, exchange=None):
+        dist.barrier(); torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        launches = 0
+        for _ in range(n):
+            ep.forward(x, res, backend, E, exchange=exchange)
+            launches += be.launches()
+        b.record(stream)
+        torch.cuda.synchronize(); dist.barrier()
+        t = torch.tensor([a.elapsed_time(b) / n], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), launches
+
+    for _ in range(max(3, args.warmup)):
+        ep.forward(x, res, backend, E)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start(); time.sleep(0.3)
+    ms_per_step, launches = timed(args.steps)
+    clocks = sampler.stop() if rank == 0 else {}
+    be.router_plan.poll(); be.expert_plan.poll()
+    # the same step with the exchange replaced by device-local copies of what it delivered
+    rec = _Recorded(dist)
+    ep.forward(x, res, backend, E, exchange=rec)
+    ms_local, _ = timed(args.steps, exchange=_Replayed(rec.log))
+    # per-stage times of single steps
+    tm, acc = {}, {}
+    be.expert_plan.set_profiling(True)
+    for _ in range(min(5, args.steps)):
+        ep.forward(x, res, backend, E, timings=tm)
+        for k, v in tm.items():
+            acc.setdefault(k, []).append(v)
+        for k, v in be.expert_plan.phase_times().items():
+            acc.setdefault(k, []).append(v)
+    be.expert_plan.set_profiling(False)
+    phases = {k: float(np.mean(v)) for k, v in acc.items()}
+    routes_here = int(phases.pop("routes_received"))
+    # end to end: pinned host rows in, the layer, residual rows back
+    e2e_steps = max(3, min(args.steps, 10))
+    dist.barrier(); torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        x.copy_(hx, non_blocking=True); res.copy_(hres, non_blocking=True)
+        ep.forward(x, res, backend, E)
+        hres.copy_(res, non_blocking=True)
+        torch.cuda.synchronize()
+    t = torch.tensor([1e3 * (time.perf_counter() - t0) / e2e_steps], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    if rank != 0:
+        dist.destroy_process_group()
+        return 0
+    peaks = measured_peaks()
+    row_bytes = T * H * 2
+    e2e = dict(value=total / (e2e_ms / 1e3), unit="tokens/s", ms_per_step=e2e_ms, h2d_bytes_per_step=2 * row_bytes,
+               d2h_bytes_per_step=row_bytes, api="oco_b200.ep.forward (pinned host rows in, residual rows back), per rank")
+    roofline = None
+    if "up_tiles" in phases:
+        flops = 2.0 * routes_here * 2 * F * H
+        ach = flops / (phases["up_tiles"] / 1e3) / 1e12
+        roofline = dict(bound="tensor", kernel="up_tiles", achieved=ach, peak=peaks["tflops"], unit="TFLOP/s",
+                        frac=ach / peaks["tflops"], traffic=None, peak_source=f"{peaks['source']} dense bf16 cuBLAS, burst",
+                        algorithmic_flops_per_launch=flops, launch_ms=phases["up_tiles"], routes_on_rank0=routes_here)
+    base = None
+    if not args.no_cpu_baseline:
+        base, _ = cpu_baseline(layer, total, args.seed, args.cpu_tokens)
+    line = dict(
+        metric=METRIC, value=total / (ms_per_step / 1e3), unit="tokens/s", n_gpus=world, steps=args.steps,
+        warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True, scaling="strong", vs_baseline=None,
+        dtype="f16", data="synthetic",
+        config=dict(workload=args.workload, tokens_total=total, tokens_per_gpu=T, hidden=H, ffn=F, experts=E, top_k=K,
+                    weight_format="MXFP4", experts_per_gpu=E // world, parallelism=f"ep{world}",
+                    cache="every step reads the rank's whole expert shard (%.0f MB), more than the 126 MB L2"
+                          % (E // world * layer.expert_bytes() / 1e6)),
+        all_to_all=dict(exposed_ms=ms_per_step - ms_local, ms_per_step_with_local_copies=ms_local,
+                        dispatch_ms=phases.get("dispatch_ms"), combine_ms=phases.get("combine_a2a_ms"),
+                        route_bytes_each_way_per_gpu=T * K * H * 2),
+        clocks=clocks, e2e=e2e, gpu_launches=launches, phases_ms=phases, roofline=roofline, cpu_baseline=base)
+    print(json.dumps(line))
+    dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -187,6 +317,9 @@ def main():
         build.build()
     if world > 1:
         dist.barrier()
+
+    if world > 1 and args.workload in EXPERT_PARALLEL:
+        return run_expert_parallel(args, torch, dist, world, rank, local)
 
     cfg, default_tokens = WORKLOADS[args.workload]
     tokens = args.tokens or default_tokens

@@ -39,6 +39,7 @@ struct Workspace {
     uint16_t* y = nullptr;        // bf16 [R, H] expert outputs, route order
     float* act1 = nullptr;        // f32 [K, F] single-token activations
     __half* actfrag = nullptr;    // single-token B fragments of the down projection
+    __half* xfrag = nullptr;      // single-token B fragments of the token itself
     uint32_t* arrivals = nullptr; // single-token combine: one counter per eight output rows
     uint16_t* xh = nullptr;       // half [T, H] token-order input rows (shared expert)
     uint16_t* mid = nullptr;      // half [T, S] shared expert intermediate
@@ -143,6 +144,7 @@ Workspace carve(const oco_moe_desc& d, int max_rows, unsigned char* base) {
     w.y = (uint16_t*)take(R * H * 2);
     w.act1 = (float*)take(K * F * 4);
     w.actfrag = (__half*)take(P * (F / 32) * 128 * 2);
+    w.xfrag = (__half*)take((H / 32) * 128);
     w.arrivals = (uint32_t*)take((H / 8 + 1) * 4);
     if (S) {
         w.xh = (uint16_t*)take(T * H * 2);
@@ -256,18 +258,43 @@ int launch_gemm_nt(oco_moe_plan* plan, const GemmParams& gp, const CUtensorMap* 
     }
 }
 
-size_t decode_span_cap(uint32_t row_bytes) { return align_up((size_t)8 * row_bytes + 15, 16) + 32; }
+// Warps per unit of the single-token kernels: as many as keep every warp of the grid busy.
+int pick_ksplit(int units, int warps) {
+    for (int k : {10, 5, 4, 2})
+        if (kTokWarps % k == 0 && units * k <= warps) return k;
+    return 1;
+}
+
+// Ring depth of the single-token kernels by what fits in shared memory (0: nothing fits).
 
 template <int ARCH, int FMT>
-int launch_expand(oco_moe_plan* plan, const DecodeExpandParams& ep, int grid, cudaStream_t st) {
-    size_t smem = (size_t)(ep.H / 32) * 2 * 4 * 16 + 2 * kDecodeWarps * 16 * 2 * 4 + (size_t)kExpandStages * 2 * ep.span_cap;
-    if (smem > kMaxDynamicSmem) return fail(plan, OCO_UNSUPPORTED_SHAPE, "hidden %d too large for the single-token kernels", ep.H);
+int launch_expand(oco_moe_plan* plan, DecodeExpandParams ep, cudaStream_t st) {
+    const int grid = plan->sm_count;
+    if (token_smem_bytes(ep.H / 32, 2) > kMaxDynamicSmem) return fail(plan, OCO_UNSUPPORTED_SHAPE, "hidden %d too large for the single-token kernels", ep.H);
+    ep.ksplit = pick_ksplit(ep.K * (ep.F / (ARCH == OCO_ARCH_NEMOTRON ? 16 : 8)), grid * kTokWarps);
     static bool attr_set = false;
     if (!attr_set) {
-        CK(allow_smem(decode_expand_kernel<ARCH, FMT>));
+        CK(allow_smem(decode_expand_kernel<ARCH, FMT, 2>));
         attr_set = true;
     }
-    decode_expand_kernel<ARCH, FMT><<<grid, kDecodeThreads, smem, st>>>(ep);
+    decode_expand_kernel<ARCH, FMT, 2><<<grid, kTokThreads, token_smem_bytes(ep.H / 32, 2), st>>>(ep);
+    plan->launches++;
+    CK(cudaGetLastError());
+    return OCO_OK;
+}
+
+template <int FMT>
+int launch_down(oco_moe_plan* plan, DecodeDownParams dp, cudaStream_t st) {
+    const int grid = plan->sm_count;
+    if (token_smem_bytes(dp.F / 32, 2) > kMaxDynamicSmem) return fail(plan, OCO_UNSUPPORTED_SHAPE, "expert width %d too large for the single-token kernels", dp.F);
+    if (dp.K > grid) return fail(plan, OCO_UNSUPPORTED_SHAPE, "more routes than multiprocessors");
+    dp.ksplit = pick_ksplit(dp.H / 16, (grid / dp.K) * kTokWarps);
+    static bool attr_set = false;
+    if (!attr_set) {
+        CK(allow_smem(decode_down_kernel<FMT, 2>));
+        attr_set = true;
+    }
+    decode_down_kernel<FMT, 2><<<grid, kTokThreads, token_smem_bytes(dp.F / 32, 2), st>>>(dp);
     plan->launches++;
     CK(cudaGetLastError());
     return OCO_OK;
@@ -297,21 +324,19 @@ int forward_single(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, cu
     const oco_moe_desc& d = plan->d;
     Workspace& ws = plan->ws;
     const int H = d.hidden, F = d.ffn, E = d.experts, K = d.top_k;
+    // logits, then (in the CTA that finishes last) the token's experts and weights
     mark(plan, st, "router_logits");
-    router_logits_small_kernel<ARCH><<<dim3((E + 7) / 8, 1), 256, 0, st>>>(x, plan->w.router_w, plan->w.router_b,
-                                                                          ws.logits, H, E);
+    router_token_kernel<ARCH><<<(E + 7) / 8, 256, 0, st>>>(x, plan->w.router_w, plan->w.router_b, H, E, K, d.normalize,
+                                                          d.scale, ws.logits, ws.ids, ws.probs, ws.xfrag, ws.arrivals + H / 8);
     plan->launches++;
-    const int grid = 2 * plan->sm_count;
     if constexpr (FMT == OCO_FMT_MXFP4 || FMT == OCO_FMT_Q4_0) {
-        auto expand = [&](const uint8_t* gate_w, const uint8_t* up_w, const float* logits, int k, int f,
-                          uint32_t* ids, float* probs, float* act1, __half* actfrag) -> int {
+        auto expand = [&](const uint8_t* gate_w, const uint8_t* up_w, const uint32_t* ids, int k, int f, float* act1,
+                          __half* actfrag, uint32_t row_bytes) -> int {
             DecodeExpandParams ep{};
             ep.gate_w = gate_w; ep.up_w = up_w; ep.gate_b = plan->w.gate_b; ep.up_b = plan->w.up_b;
-            ep.x = x; ep.logits = logits; ep.sel_bias = plan->w.router_b;
-            ep.ids = ids; ep.probs = probs; ep.act = act1; ep.actfrag = actfrag;
-            ep.H = H; ep.F = f; ep.E = E; ep.K = k; ep.normalize = d.normalize; ep.scale = d.scale;
-            ep.row_bytes = plan->up_row_bytes; ep.span_cap = (uint32_t)decode_span_cap(plan->up_row_bytes);
-            return launch_expand<ARCH, FMT>(plan, ep, grid, st);
+            ep.xfrag = ws.xfrag; ep.ids = ids; ep.act = act1; ep.actfrag = actfrag;
+            ep.H = H; ep.F = f; ep.K = k; ep.row_bytes = row_bytes; ep.status = ws.status;
+            return launch_expand<ARCH, FMT>(plan, ep, st);
         };
         auto down = [&](const uint8_t* down_w, const float* bias, const uint32_t* ids, const __half* actfrag, int k,
                         int f, uint32_t row_bytes, uint16_t* y, bool combine, const uint16_t* shared) -> int {
@@ -321,43 +346,28 @@ int forward_single(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, cu
                 dp.arrivals = ws.arrivals; dp.probs = ws.probs; dp.residual = residual; dp.shared = shared;
                 dp.round_sum = ARCH == OCO_ARCH_GPT_OSS ? 1 : 0;
             }
-            dp.H = H; dp.F = f; dp.K = k; dp.row_bytes = row_bytes; dp.span_cap = (uint32_t)decode_span_cap(row_bytes);
-            size_t smem = (size_t)(f / 32) * 4 * 4 * 16 + 2 * kDecodeWarps * 16 * 2 * 4 +
-                          (size_t)kDownStages * 2 * dp.span_cap;
-            if (smem > kMaxDynamicSmem) return fail(plan, OCO_UNSUPPORTED_SHAPE, "expert width %d too large for the single-token kernels", f);
-            static bool attr_set = false;
-            if (!attr_set) {
-                CK(allow_smem(decode_down_kernel<FMT>));
-                attr_set = true;
-            }
-            decode_down_kernel<FMT><<<grid, kDecodeThreads, smem, st>>>(dp);
-            plan->launches++;
-            CK(cudaGetLastError());
-            return OCO_OK;
+            dp.H = H; dp.F = f; dp.K = k; dp.row_bytes = row_bytes; dp.status = ws.status;
+            return launch_down<FMT>(plan, dp, st);
         };
         mark(plan, st, "expand");
-        int rc = expand(plan->w.gate_w, plan->w.up_w, ws.logits, K, F, ws.ids, ws.probs, ws.act1, ws.actfrag);
+        int rc = expand(plan->w.gate_w, plan->w.up_w, ws.ids, K, F, ws.act1, ws.actfrag, plan->up_row_bytes);
         if (rc) return rc;
         const uint16_t* shared = nullptr;
         if (ARCH == OCO_ARCH_NEMOTRON && d.shared_ffn) {
             // The always-on expert runs through the same kernels as a one-expert bank
             // (compute/nemotron.rs:460-509 runs it as dense matvecs beside the routed ones); its
             // output joins the routed sum in f32 (moe_add with shared = 1).
-            DecodeExpandParams ep{};
-            ep.gate_w = nullptr; ep.up_w = plan->w.shared_up_w; ep.x = x; ep.logits = nullptr;
-            ep.ids = ws.sh_ids + 8; ep.probs = (float*)(ws.sh_ids + 16); ep.act = ws.sh_act1; ep.actfrag = ws.sh_actfrag;
-            ep.H = H; ep.F = d.shared_ffn; ep.E = 1; ep.K = 1; ep.normalize = 0; ep.scale = 1.f;
-            ep.row_bytes = plan->shared_up_row_bytes; ep.span_cap = (uint32_t)decode_span_cap(plan->shared_up_row_bytes);
             mark(plan, st, "shared_expand");
-            rc = launch_expand<ARCH, FMT>(plan, ep, grid, st);
+            rc = expand(nullptr, plan->w.shared_up_w, nullptr, 1, d.shared_ffn, ws.sh_act1, ws.sh_actfrag,
+                        plan->shared_up_row_bytes);
             if (rc) return rc;
             mark(plan, st, "shared_down");
-            rc = down(plan->w.shared_down_w, nullptr, ws.sh_ids, ws.sh_actfrag, 1, d.shared_ffn,
+            rc = down(plan->w.shared_down_w, nullptr, nullptr, ws.sh_actfrag, 1, d.shared_ffn,
                       plan->shared_down_row_bytes, ws.shared_out, false, nullptr);
             if (rc) return rc;
             shared = ws.shared_out;
         }
-        // Routed down products; the last CTA to finish each block of output rows combines them
+        // Routed down products; the last warp to finish each block of output rows combines them
         // onto the residual (moe_sum / moe_add), so no separate combine launch is needed.
         mark(plan, st, "down_combine");
         rc = down(plan->w.down_w, plan->w.down_b, ws.ids, ws.actfrag, K, F, plan->down_row_bytes, ws.y, true, shared);

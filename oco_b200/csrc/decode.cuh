@@ -1,17 +1,18 @@
 // Single-token expert products: memory-bound streaming of the packed weight rows.
 //
-// Each CTA walks a list of work items. An item is 16 weight rows (8 gate + 8 up rows of one
-// expert, or 8 rows each of two experts for the down projection) over the whole contraction
-// length: two contiguous byte spans in the GGUF tensor. The spans are brought into a shared
-// memory ring with 16-byte cp.async copies (coalesced, several items in flight per SM), the
-// eight warps split the 32-element blocks of the item between them, and each warp multiplies its
-// blocks with m16n8k16 tensor-core MMAs: the A fragment is the block's e2m1 codes converted to
-// half in registers (one cvt per code byte), the B fragment is the activation vector split into
-// hi + lo half parts in two of the eight columns, so the product is exact to f32 rounding. The
-// block scale multiplies the block's partial sum afterwards in f32, as the reference's
-// single-token kernels do (shaders/experts/projections.metal:57-59). A byte holds elements j and
-// j + 16 of its block; the contraction index is permuted accordingly on the activation side
-// instead of shuffling weights.
+// The unit of work is 16 packed weight rows (8 gate + 8 up rows of one expert, or 16 consecutive
+// rows) over a range of 32-element blocks. ONE WARP owns a unit from the first byte to the
+// activation: it brings the rows' bytes into its own shared-memory ring with bulk asynchronous
+// copies (one per row and stage, completion counted on an mbarrier; a stage holds 16 blocks of
+// each of the 16 rows), and multiplies them with m16n8k16
+// tensor-core MMAs: the A fragment is a block's e2m1 codes converted to half in registers (one cvt
+// per code byte), the B fragment is the activation vector split into hi + lo half parts in two of
+// the eight columns, so the product is exact to f32 rounding. The block scale multiplies the
+// block's partial sum afterwards in f32, as the reference's single-token kernels do
+// (shaders/experts/projections.metal:57-59). A byte holds elements j and j + 16 of its block; the
+// contraction index is permuted accordingly on the activation side instead of shuffling weights.
+// Warps never wait for one another inside the stream (no CTA barrier); when there are fewer units
+// than warps, several warps split a unit's blocks and meet once at a named barrier.
 //
 // FP32 FMA pipes cannot keep up with 4.25-bit weights at HBM rate (one FMA plus decode per weight
 // needs more issue slots than an SM has per byte delivered), which is why the dot products ride
@@ -22,62 +23,95 @@
 
 namespace oco {
 
-constexpr int kDecodeThreads = 256;
-constexpr int kDecodeWarps = 8;
-constexpr int kExpandStages = 4;  // ring depth of the up/gate kernel
-constexpr int kDownStages = 3;    // the down kernel also holds four fragment columns per block
+#ifndef OCO_TOK_WARPS
+#define OCO_TOK_WARPS 20
+#endif
+#ifndef OCO_CHUNK_BLOCKS
+#define OCO_CHUNK_BLOCKS 16
+#endif
+constexpr int kTokWarps = OCO_TOK_WARPS;            // one CTA per SM
+constexpr int kTokThreads = kTokWarps * 32;
+constexpr int kChunkBlocks = OCO_CHUNK_BLOCKS;      // blocks of each row per pipeline stage
+// Bytes per row in a stage: room for 15 bytes of misalignment and the blocks, a multiple of 16,
+// and 12 or 20 words modulo 32 so that the eight rows of a fragment start in distinct banks.
+constexpr int row_pitch(int blocks) {
+    int p = (15 + blocks * 18 + 15) / 16 * 16;
+    while ((p / 4) % 32 != 12 && (p / 4) % 32 != 20) p += 16;
+    return p;
+}
+constexpr int kRowPitch = row_pitch(kChunkBlocks);  // 304 for 16 blocks
+constexpr int kStageBytes = 16 * kRowPitch;
+constexpr int kScalePitch = kChunkBlocks * 2 + 16;   // per-warp table of the stage's scales, 16 bits each, padded against bank conflicts
+constexpr int kScaleBytes = 16 * kScalePitch;
+constexpr int kMiscBytes = 2048;                    // split sums (64 B a warp) | mbarriers from 1280 | give-up flag at 1984
+static_assert(kChunkBlocks % 16 == 0 && kTokWarps <= 20, "layout of the token kernels");
+constexpr int kFragBlockBytes = 128;                // B fragments of one block: 2 columns x 4 lanes x 16 bytes
 
 // D = A * B with a zero accumulator, then D += A * B (fp32 accumulate, half operands).
 __device__ __forceinline__ void mma16816_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
         : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
+// Shared-memory accesses as plain loads and stores (base = the kernel's shared array), so that the
+// compiler is free to schedule them; the waits and barriers around them are compiler barriers.
+using SharedBase = const unsigned char*;
+__device__ __forceinline__ uint32_t lds32(SharedBase base, uint32_t off) {
+    return *reinterpret_cast<const uint32_t*>(base + off);
 }
-__device__ __forceinline__ uint32_t lds8(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
+__device__ __forceinline__ uint32_t lds8(SharedBase base, uint32_t off) { return base[off]; }
+__device__ __forceinline__ uint4 lds128(SharedBase base, uint32_t off) {
+    return *reinterpret_cast<const uint4*>(base + off);
 }
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
+__device__ __forceinline__ void sts128(SharedBase base, uint32_t off, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(const_cast<unsigned char*>(base) + off) = make_float4(a, b, c, d);
+}
+// Bulk asynchronous copy global -> shared, counted on an mbarrier. Both addresses and the size are
+// multiples of 16 bytes.
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+// Barrier among the `threads` threads that name the same id (1..15); id 0 is __syncthreads.
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 // Block codecs for the 32-element formats whose code byte j holds elements j (low nibble) and
 // j + 16 (high nibble): MXFP4 (17 bytes, E8M0 scale) and Q4_0 (18 bytes, f16 scale, code - 8).
-// `block` is the shared-memory byte address of the block; quads() turns a word of four code
-// bytes into four half2 (element j, element j + 16).
+// `block` is the byte offset of the block in shared memory; quads() turns a word of four code
+// bytes into four half2 (element j, element j + 16). Blocks kClasses apart start at the same
+// offset within a 32-bit word.
 template <int FMT>
 struct Block32;
 template <>
 struct Block32<OCO_FMT_MXFP4> {
-    static constexpr int kBytes = 17, kHeader = 1;
-    __device__ static __forceinline__ float scale(uint32_t block) { return e8m0_scale(lds8(block)); }
+    static constexpr int kBytes = 17, kHeader = 1, kClasses = 4;
+    // the scale as 16 bits (bf16 holds every power of two, 2^-127 as a subnormal) and back to f32
+    __device__ static __forceinline__ uint32_t scale16(SharedBase base, uint32_t block) {
+        const uint32_t e = lds8(base, block);
+        return e == 255u ? 0x7fc0u : (e == 0u ? 0x0040u : e << 7);
+    }
+    __device__ static __forceinline__ float scale_f32(uint32_t bits) { return __uint_as_float(bits << 16); }
     __device__ static __forceinline__ void quads(uint32_t w, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
         cvt_e2m1x2_x4(w, r0, r1, r2, r3);
     }
 };
 template <>
 struct Block32<OCO_FMT_Q4_0> {
-    static constexpr int kBytes = 18, kHeader = 2;
-    __device__ static __forceinline__ float scale(uint32_t block) {
-        return f16_bits_to_f32((uint16_t)(lds8(block) | (lds8(block + 1) << 8)));
+    static constexpr int kBytes = 18, kHeader = 2, kClasses = 2;
+    __device__ static __forceinline__ uint32_t scale16(SharedBase base, uint32_t block) {
+        return lds8(base, block) | (lds8(base, block + 1) << 8);
     }
+    __device__ static __forceinline__ float scale_f32(uint32_t bits) { return f16_bits_to_f32((uint16_t)bits); }
     __device__ static __forceinline__ uint32_t pair(uint32_t byte) {
         // 0x6400 | q is the half 1024 + q; subtracting 1032 leaves q - 8 exactly.
         uint32_t v = (byte & 0xfu) | ((byte & 0xf0u) << 12) | 0x64006400u;
@@ -89,64 +123,211 @@ struct Block32<OCO_FMT_Q4_0> {
     }
 };
 
-// Dot products of 16 packed rows with the activation fragments, for the blocks kb = warp, warp + 8, ...
-// rowA / rowB: shared-memory byte addresses of this lane's row g of the first / second span;
-// xlane: address of this lane's fragment (uint4) for block 0; xstride: fragment bytes per block.
-// sum[0..1] accumulate row g (two columns), sum[2..3] row g + 8. The warp's blocks are 8 apart, so
-// every address advances by a multiple of four bytes per step and the word alignment of the code
-// bytes is fixed for the whole loop.
-template <int FMT>
-__device__ __forceinline__ void rows_dot(uint32_t rowA, uint32_t rowB, uint32_t xlane, uint32_t xstride, int nkb,
-                                         int warp, int tig, float (&sum)[4]) {
+// One warp's pass over blocks [kb0, kb0 + nb) of 16 packed rows: rows 0..7 of span A and rows
+// 0..7 of span B (each span is 8 consecutive rows of `row_bytes` bytes in a GGUF tensor, at any
+// byte alignment). begin() starts the copies; run() multiplies. After run(), lane (g, tig) holds
+// in sum[0..1] the products of row g of span A with fragment columns 2*tig and 2*tig + 1, and in
+// sum[2..3] the same for row g of span B.
+template <int FMT, int STAGES>
+struct RowStream {
     using B = Block32<FMT>;
-    constexpr uint32_t kStep = kDecodeWarps * B::kBytes;                 // 136 or 144 bytes
-    uint32_t ba = rowA + (uint32_t)warp * B::kBytes, bb = rowB + (uint32_t)warp * B::kBytes;
-    const uint32_t ca = ba + B::kHeader + 4u * tig, cb = bb + B::kHeader + 4u * tig;
-    const uint32_t shA = (ca & 3u) * 8u, shB = (cb & 3u) * 8u;
-    uint32_t a4 = ca & ~3u, b4 = cb & ~3u;
-    uint32_t xa = xlane + (uint32_t)warp * xstride;
-    const uint32_t xstep = kDecodeWarps * xstride;
-#pragma unroll 2
-    for (int kb = warp; kb < nkb; kb += kDecodeWarps) {
-        const uint32_t wa = __funnelshift_r(lds32(a4), lds32(a4 + 4), shA);
-        const uint32_t wb = __funnelshift_r(lds32(b4), lds32(b4 + 4), shB);
-        const float sa = B::scale(ba), sb = B::scale(bb);
-        const uint4 xf = lds128(xa);
-        uint32_t qa0, qa1, qa2, qa3, qb0, qb1, qb2, qb3;
-        B::quads(wa, qa0, qa1, qa2, qa3);
-        B::quads(wb, qb0, qb1, qb2, qb3);
-        float acc[4];
-        mma16816_first(acc, qa0, qb0, qa1, qb1, xf.x, xf.y);
-        mma16816(acc, qa2, qb2, qa3, qb3, xf.z, xf.w);
-        sum[0] = __fmaf_rn(acc[0], sa, sum[0]);
-        sum[1] = __fmaf_rn(acc[1], sa, sum[1]);
-        sum[2] = __fmaf_rn(acc[2], sb, sum[2]);
-        sum[3] = __fmaf_rn(acc[3], sb, sum[3]);
-        a4 += kStep; b4 += kStep; ba += kStep; bb += kStep; xa += xstep;
+    static constexpr uint32_t kChunkBytes = kChunkBlocks * B::kBytes;   // 272 or 288: whole 16-byte pieces
+
+    SharedBase base;           // the kernel's shared array; ring and stab are byte offsets into it
+    uint32_t base_addr;        // its address in the shared window (for the copy and mbarrier instructions)
+    uint32_t ring, stab, bars;
+    uint32_t seq;              // stages used so far by this warp (mbarrier phases run on across units)
+    volatile uint32_t* abort_flag;
+    uint32_t* status;
+    // warp-uniform description of the unit
+    const uint8_t* spanA;
+    const uint8_t* spanB;      // both advanced to the first block of the range
+    uint32_t row_bytes, total_bytes;
+    int nchunks, nb;
+    // per lane
+    uint32_t mA, mB;           // misalignment of row g of each span
+    uint32_t alA[B::kClasses], alB[B::kClasses], shA[B::kClasses], shB[B::kClasses];
+    int g, tig, lane;
+
+    // Once per kernel: this warp's ring, scale table and mbarriers (STAGES of them, 8 bytes each).
+    __device__ __forceinline__ void init(SharedBase smem_base, uint32_t ring_off, uint32_t stab_off, uint32_t bars_off,
+                                         volatile uint32_t* abort_word, uint32_t* status_word, int lane_) {
+        base = smem_base; base_addr = smem_u32(smem_base);
+        ring = ring_off; stab = stab_off; bars = base_addr + bars_off; abort_flag = abort_word; status = status_word;
+        lane = lane_; g = lane >> 2; tig = lane & 3; seq = 0;
+        if (lane == 0) {
+#pragma unroll
+            for (int s = 0; s < STAGES; s++) mbar_init(bars + 8u * s, 1);
+            fence_barrier_init();
+        }
+        __syncwarp();
+    }
+
+    // a, b, rb, kb0, nblocks: the same in every lane.
+    __device__ __forceinline__ void begin(const uint8_t* a, const uint8_t* b, uint32_t rb, int kb0, int nblocks) {
+        nb = nblocks; row_bytes = rb;
+        const size_t skip = (size_t)kb0 * B::kBytes;
+        spanA = a + skip; spanB = b + skip;
+        nchunks = (nb + kChunkBlocks - 1) / kChunkBlocks;
+        total_bytes = (uint32_t)nb * B::kBytes;
+        mA = (uint32_t)(uintptr_t)(spanA + (size_t)g * row_bytes) & 15u;
+        mB = (uint32_t)(uintptr_t)(spanB + (size_t)g * row_bytes) & 15u;
+#pragma unroll
+        for (int c = 0; c < B::kClasses; c++) {
+            const uint32_t qa = (uint32_t)g * kRowPitch + mA + (uint32_t)(c * B::kBytes + B::kHeader) + 4u * tig;
+            const uint32_t qb = (uint32_t)(8 + g) * kRowPitch + mB + (uint32_t)(c * B::kBytes + B::kHeader) + 4u * tig;
+            alA[c] = qa & ~3u; shA[c] = (qa & 3u) * 8u;
+            alB[c] = qb & ~3u; shB[c] = (qb & 3u) * 8u;
+        }
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; s++) issue(s);
+    }
+
+    // Starts the copies of chunk c of the unit (nothing past the last chunk). The stage was read
+    // for the last time before the __syncwarp that precedes this call.
+    __device__ __forceinline__ void issue(int c) {
+        if (c >= nchunks) return;
+        const uint32_t off = (uint32_t)c * kChunkBytes;
+        const uint32_t len = min(kChunkBytes, total_bytes - off);
+        const uint32_t stage = (seq + (uint32_t)c) % STAGES;
+        const uint32_t bar = bars + 8u * stage;
+        const uint32_t dst = base_addr + ring + stage * kStageBytes;
+        // lanes 0..15 copy one row each; the byte total of the stage is summed over them first
+        const uint8_t* row = (lane < 8 ? spanA : spanB) + (size_t)(lane & 7) * row_bytes;
+        const uint32_t m = (uint32_t)(uintptr_t)row & 15u;
+        const uint32_t bytes = lane < 16 ? ((m + len + 15u) & ~15u) : 0u;
+        uint32_t total = bytes;
+#pragma unroll
+        for (int d = 8; d >= 1; d >>= 1) total += __shfl_xor_sync(0xffffffffu, total, d);
+        if (lane == 0) mbar_arrive_expect_tx(bar, total);
+        __syncwarp();
+        if (lane < 16) bulk_copy(dst + (uint32_t)lane * kRowPitch, row - m + off, bytes, bar);
+    }
+
+    // The blocks of one stage. FULL: all 16 blocks are present. xa: byte offset in shared memory of
+    // this lane's B fragment of the stage's first block. Only columns 0 and 1 carry the token, so
+    // only the lanes that feed them (g < 2) load; the other columns multiply zeros.
+    template <bool FULL>
+    __device__ __forceinline__ void chunk(uint32_t st, uint32_t xa, int nbc, float (&sum)[4]) {
+#pragma unroll
+        for (int q = 0; q < kChunkBlocks / 4; q++) {
+            if (FULL || q * 4 < nbc) {
+                const uint2 sa = *reinterpret_cast<const uint2*>(base + stab + (uint32_t)g * kScalePitch + q * 8);
+                const uint2 sb = *reinterpret_cast<const uint2*>(base + stab + (uint32_t)(8 + g) * kScalePitch + q * 8);
+                const float fa[4] = {B::scale_f32(sa.x & 0xffffu), B::scale_f32(sa.x >> 16), B::scale_f32(sa.y & 0xffffu),
+                                     B::scale_f32(sa.y >> 16)};
+                const float fb[4] = {B::scale_f32(sb.x & 0xffffu), B::scale_f32(sb.x >> 16), B::scale_f32(sb.y & 0xffffu),
+                                     B::scale_f32(sb.y >> 16)};
+#pragma unroll
+                for (int t = 0; t < 4; t++) {
+                    const int i = q * 4 + t;
+                    if (FULL || i < nbc) {
+                        constexpr int kC = B::kClasses;
+                        const uint32_t pa = st + alA[i % kC] + (uint32_t)((i / kC) * kC * B::kBytes);
+                        const uint32_t pb = st + alB[i % kC] + (uint32_t)((i / kC) * kC * B::kBytes);
+                        const uint32_t wa = __funnelshift_r(lds32(base, pa), lds32(base, pa + 4), shA[i % kC]);
+                        const uint32_t wb = __funnelshift_r(lds32(base, pb), lds32(base, pb + 4), shB[i % kC]);
+                        uint4 xf = make_uint4(0u, 0u, 0u, 0u);
+                        if (g < 2) xf = lds128(base, xa + (uint32_t)i * kFragBlockBytes);
+                        uint32_t qa0, qa1, qa2, qa3, qb0, qb1, qb2, qb3;
+                        B::quads(wa, qa0, qa1, qa2, qa3);
+                        B::quads(wb, qb0, qb1, qb2, qb3);
+                        float acc[4];
+                        mma16816_first(acc, qa0, qb0, qa1, qb1, xf.x, xf.y);
+                        mma16816(acc, qa2, qb2, qa3, qb3, xf.z, xf.w);
+                        sum[0] = __fmaf_rn(acc[0], fa[t], sum[0]);
+                        sum[1] = __fmaf_rn(acc[1], fa[t], sum[1]);
+                        sum[2] = __fmaf_rn(acc[2], fb[t], sum[2]);
+                        sum[3] = __fmaf_rn(acc[3], fb[t], sum[3]);
+                    }
+                }
+            }
+        }
+    }
+
+    // xaddr: byte offset in shared memory of this lane's B fragment (uint4) for block kb0.
+    __device__ __forceinline__ void run(uint32_t xaddr, float (&sum)[4]) {
+        for (int c = 0; c < nchunks; c++) {
+            issue(c + STAGES - 1);
+            const uint32_t n = seq + (uint32_t)c, stage = n % STAGES;
+            mbar_wait(bars + 8u * stage, (n / STAGES) & 1u, abort_flag, status);
+            const uint32_t st = ring + stage * kStageBytes;
+            const int nbc = min(kChunkBlocks, nb - c * kChunkBlocks);
+            {   // the stage's scales, 16 bits each: lane (g, tig) gathers a quarter of the blocks of its two rows
+                constexpr int kPer = kChunkBlocks / 4;
+                const uint32_t ra = st + (uint32_t)g * kRowPitch + mA + (uint32_t)(tig * kPer * B::kBytes);
+                const uint32_t rb = st + (uint32_t)(8 + g) * kRowPitch + mB + (uint32_t)(tig * kPer * B::kBytes);
+                unsigned char* tab = const_cast<unsigned char*>(base) + stab;
+#pragma unroll
+                for (int b = 0; b < kPer; b += 4) {
+                    uint32_t ha[4], hb[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        ha[u] = B::scale16(base, ra + (b + u) * B::kBytes);
+                        hb[u] = B::scale16(base, rb + (b + u) * B::kBytes);
+                    }
+                    *reinterpret_cast<uint2*>(tab + (uint32_t)g * kScalePitch + (tig * kPer + b) * 2) =
+                        make_uint2(ha[0] | (ha[1] << 16), ha[2] | (ha[3] << 16));
+                    *reinterpret_cast<uint2*>(tab + (uint32_t)(8 + g) * kScalePitch + (tig * kPer + b) * 2) =
+                        make_uint2(hb[0] | (hb[1] << 16), hb[2] | (hb[3] << 16));
+                }
+            }
+            __syncwarp();
+            const uint32_t xa = xaddr + (uint32_t)(c * kChunkBlocks) * kFragBlockBytes;
+            if (nbc == kChunkBlocks) chunk<true>(st, xa, nbc, sum);
+            else chunk<false>(st, xa, nbc, sum);
+            __syncwarp();
+        }
+        seq += (uint32_t)nchunks;
+    }
+};
+
+// The B fragments of one token or route (nkb blocks of 128 bytes, global memory) into shared
+// memory at offset 0 with one bulk copy by warp 0; every warp then waits on `bar` (phase 0).
+__device__ __forceinline__ void fetch_fragments(SharedBase smem, const void* frag, int nkb, uint32_t bar, int warp, int lane) {
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_init(bar, 1);
+            fence_barrier_init();
+            mbar_arrive_expect_tx(bar, (uint32_t)nkb * kFragBlockBytes);
+            bulk_copy(smem_u32(smem), frag, (uint32_t)nkb * kFragBlockBytes, bar);
+        }
     }
 }
 
-// Issues the cp.async copies of one byte span [src, src + bytes) into `dst` (16-byte aligned),
-// widened to whole 16-byte chunks. Returns nothing; the span's first byte lands at dst + (src & 15).
-__device__ __forceinline__ void copy_span_async(uint8_t* dst, const uint8_t* src, uint32_t bytes, int tid) {
-    uintptr_t a = (uintptr_t)src;
-    const uint8_t* base = (const uint8_t*)(a & ~(uintptr_t)15);
-    uint32_t chunks = (((uint32_t)a & 15u) + bytes + 15u) >> 4;
-    uint32_t d = smem_u32(dst);
-    for (uint32_t i = tid; i < chunks; i += kDecodeThreads) cp_async16(d + i * 16u, base + (size_t)i * 16u);
+// Shared memory of the token kernels: B fragments | 2 KB (split sums, mbarriers, give-up flag) |
+// per-warp scale tables | rings.
+__host__ __device__ inline size_t token_smem_bytes(int nkb, int stages) {
+    return (size_t)nkb * kFragBlockBytes + kMiscBytes + (size_t)kTokWarps * kScaleBytes +
+           (size_t)kTokWarps * stages * kStageBytes + 16;
 }
 
 // Splits f32 values into hi + lo halves and scatters them into the B-fragment layout:
-// frag[((kb * COLS + col) * 4 + tig) * 4 + slot] is a half2 (element 4*tig+slot, element 4*tig+slot+16)
-// of block kb; hi goes to column `col`, lo to column `col + 1`.
-__device__ __forceinline__ void frag_store(__half* frag, int cols, int col, int k, float v) {
+// frag[((kb * 2 + col) * 4 + tig) * 4 + slot] is a half2 (element 4*tig+slot, element 4*tig+slot+16)
+// of block kb; hi goes to column 0, lo to column 1.
+__device__ __forceinline__ void frag_store(__half* frag, int k, float v) {
     __half hi = __float2half_rn(v);
     float rem = nonfinite(v) ? 0.0f : v - __half2float(hi);
     __half lo = __float2half_rn(rem);
     int kb = k >> 5, j = k & 31, jj = j & 15, sel = j >> 4, tig = jj >> 2, slot = jj & 3;
-    size_t at = ((((size_t)kb * cols + col) * 4 + tig) * 4 + slot) * 2 + sel;
+    size_t at = ((((size_t)kb * 2) * 4 + tig) * 4 + slot) * 2 + sel;
     frag[at] = hi;
     frag[at + (size_t)16 * 2] = lo;  // next column: 4 tig * 4 slots * 2 halves further
+}
+
+// Sums the per-warp partial results of a unit split over `ksplit` adjacent warps. `part`: shared
+// scratch, 16 floats per warp. Returns the totals in the first warp of the group (lanes tig == 0).
+__device__ __forceinline__ void join_split(float* part, int warp, int group, int s, int ksplit, int g, int tig,
+                                           float& r0, float& r1) {
+    if (ksplit == 1) return;
+    if (s > 0 && tig == 0) { part[warp * 16 + g] = r0; part[warp * 16 + 8 + g] = r1; }
+    named_barrier(1 + group, 32 * ksplit);
+    if (s == 0 && tig == 0)
+        for (int q = 1; q < ksplit; q++) {
+            r0 = __fadd_rn(r0, part[(warp + q) * 16 + g]);
+            r1 = __fadd_rn(r1, part[(warp + q) * 16 + 8 + g]);
+        }
+    named_barrier(1 + group, 32 * ksplit);   // the scratch may be written again after this
 }
 
 struct DecodeExpandParams {
@@ -154,248 +335,173 @@ struct DecodeExpandParams {
     const uint8_t* up_w;
     const float* gate_b;
     const float* up_b;
-    const uint16_t* x;       // bf16 [H]
-    const float* logits;     // f32 [E]
-    const float* sel_bias;
-    uint32_t* ids;           // out [K]
-    float* probs;            // out [K]
+    const __half* xfrag;     // the token as B fragments, [H/32] blocks of 128 bytes (written by the router kernel)
+    const uint32_t* ids;     // [K] selected experts; null = expert 0 (a one-expert bank)
     float* act;              // out f32 [K, F] (for inspection)
-    __half* actfrag;         // out: B fragments of the down projection, [ceil(K/2)][F/32][4][4][4] half2
-    int H, F, E, K, normalize;
-    float scale;
+    __half* actfrag;         // out: B fragments of the down projection, [K][F/32] blocks of 128 bytes
+    int H, F, K;
+    int ksplit;              // warps per unit: a divisor of the warps per CTA
     uint32_t row_bytes;      // bytes of one packed row of length H
-    uint32_t span_cap;       // shared-memory bytes reserved per span
+    uint32_t* status;        // device status word: a copy that never arrives is reported here
 };
 
 // Up (and gate) products of the K selected experts for one token, with the activation fused
 // (reference expert_expand, projections.metal:78-137; matvec_q4 + relu^2, vector.metal:155-228).
-// Every CTA repeats the top-k selection from the logits, as the reference does per SIMD group.
-// GATED: item = 8 gate rows + 8 up rows (columns c0..c0+7); otherwise 16 up rows.
-template <int ARCH, int FMT>
-__global__ void __launch_bounds__(kDecodeThreads) decode_expand_kernel(const DecodeExpandParams p) {
-    constexpr int kDecodeStages = kExpandStages;
+// GATED: unit = 8 gate rows + 8 up rows (columns c0..c0+7); otherwise 16 up rows.
+template <int ARCH, int FMT, int STAGES>
+__global__ void __launch_bounds__(kTokThreads, 1) decode_expand_kernel(const DecodeExpandParams p) {
     constexpr bool GATED = ARCH != OCO_ARCH_NEMOTRON;
-    constexpr int COLS_PER_ITEM = GATED ? 8 : 16;
-    using B = Block32<FMT>;
+    constexpr int COLS = GATED ? 8 : 16;
     extern __shared__ __align__(16) unsigned char smem[];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
+    const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, tig = lane & 3;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // known to the compiler as the same in all lanes
     const int nkb = p.H / 32;
-    // shared layout: xfrag [nkb][2][4] uint4 | partial [2][8 warps][16][2] f32 | ring
-    uint4* xfrag = reinterpret_cast<uint4*>(smem);
-    float* partial = reinterpret_cast<float*>(smem + (size_t)nkb * 2 * 4 * 16);
-    uint8_t* ring = reinterpret_cast<uint8_t*>(partial) + 2 * kDecodeWarps * 16 * 2 * 4;
-    const uint32_t stage_bytes = 2 * p.span_cap;
+    const uint32_t part_off = (uint32_t)nkb * kFragBlockBytes;
+    float* part = reinterpret_cast<float*>(smem + part_off);
+    volatile uint32_t* give_up = reinterpret_cast<volatile uint32_t*>(part) + 496;
+    const uint32_t xbar = smem_u32(smem) + part_off + 1920u;
+    const uint32_t stab = part_off + kMiscBytes + (uint32_t)warp * kScaleBytes;
+    const uint32_t ring = part_off + kMiscBytes + (uint32_t)kTokWarps * kScaleBytes + (uint32_t)warp * STAGES * kStageBytes;
+    if (tid == 0) *give_up = 0u;
+    fetch_fragments(smem, p.xfrag, nkb, xbar, warp, lane);
 
-    // ---- selection (all warps, identical) -----------------------------------------------------
-    uint32_t ids[kMaxTopK];
-    float probs[kMaxTopK];
-    if (p.logits) {
-        float lv[4];
-        load_logits(p.logits, p.E, lane, lv);
-        select_experts<ARCH>(lv, p.E, p.K, p.sel_bias, p.normalize, p.scale, lane, ids, probs);
-    } else {  // a one-expert bank (the always-on shared expert): nothing to select
-#pragma unroll
-        for (int r = 0; r < kMaxTopK; r++) { ids[r] = 0; probs[r] = 1.0f; }
-    }
-    if (blockIdx.x == 0 && warp == 0) {
-#pragma unroll
-        for (int r = 0; r < kMaxTopK; r++)
-            if (r < p.K && lane == r) { p.ids[r] = ids[r]; p.probs[r] = probs[r]; }
-    }
-    // ---- activation vector into B fragments (hi, lo columns) ----------------------------------
-    for (int k = tid; k < p.H; k += kDecodeThreads)
-        frag_store(reinterpret_cast<__half*>(xfrag), 2, 0, k, bf16_bits_to_f32(p.x[k]));
+    const int ksplit = p.ksplit, group = warp / ksplit, s = warp - group * ksplit;
+    const int groups = kTokWarps / ksplit;
+    const int col_blocks = p.F / COLS;
+    const int units = p.K * col_blocks;
+    const int nslots = gridDim.x * groups;
+    const int bps = (nkb + ksplit - 1) / ksplit;
+    const int kb0 = s * bps, nb = max(0, min(bps, nkb - kb0));
+    const uint32_t xlane = (uint32_t)kb0 * kFragBlockBytes + (uint32_t)(((g & 1) * 4 + tig) * 16);
 
-    const int col_blocks = (p.F + COLS_PER_ITEM - 1) / COLS_PER_ITEM;
-    const int items = p.K * col_blocks;
-    auto issue = [&](int item, int stage) {
-        if (item < items) {
-            int r = item / col_blocks, c0 = (item % col_blocks) * COLS_PER_ITEM;
-            uint32_t e = 0;
-#pragma unroll
-            for (int q = 0; q < kMaxTopK; q++)
-                if (q == r) e = ids[q];
-            int rows = min(COLS_PER_ITEM, p.F - c0);
-            size_t off = ((size_t)e * p.F + c0) * p.row_bytes;
-            uint8_t* s0 = ring + (size_t)stage * stage_bytes;
-            if (GATED) {
-                copy_span_async(s0, p.gate_w + off, rows * p.row_bytes, tid);
-                copy_span_async(s0 + p.span_cap, p.up_w + off, rows * p.row_bytes, tid);
-            } else {
-                int r0 = min(8, rows);
-                copy_span_async(s0, p.up_w + off, r0 * p.row_bytes, tid);
-                if (rows > 8)
-                    copy_span_async(s0 + p.span_cap, p.up_w + off + (size_t)8 * p.row_bytes, (rows - 8) * p.row_bytes, tid);
-            }
-        }
-        cp_async_commit();
-    };
-    int it = 0;
-    const int first = blockIdx.x, step = gridDim.x;
-#pragma unroll
-    for (int s = 0; s < kDecodeStages - 1; s++) issue(first + s * step, s);
-
-    for (int item = first; item < items; item += step, it++) {
-        issue(item + (kDecodeStages - 1) * step, (it + kDecodeStages - 1) % kDecodeStages);
-        cp_async_wait<kDecodeStages - 1>();
-        __syncthreads();
-        int r = item / col_blocks, c0 = (item % col_blocks) * COLS_PER_ITEM;
-        uint32_t e = 0;
-#pragma unroll
-        for (int q = 0; q < kMaxTopK; q++)
-            if (q == r) e = ids[q];
-        size_t off = ((size_t)e * p.F + c0) * p.row_bytes;
-        const uint32_t s0 = smem_u32(ring) + (uint32_t)(it % kDecodeStages) * stage_bytes;
-        // rows g (first span) and g + 8 (second span)
-        uint32_t rowA, rowB;
-        if (GATED) {
-            rowA = s0 + ((uint32_t)(uintptr_t)(p.gate_w + off) & 15u) + (uint32_t)g * p.row_bytes;
-            rowB = s0 + p.span_cap + ((uint32_t)(uintptr_t)(p.up_w + off) & 15u) + (uint32_t)g * p.row_bytes;
-        } else {
-            rowA = s0 + ((uint32_t)(uintptr_t)(p.up_w + off) & 15u) + (uint32_t)g * p.row_bytes;
-            rowB = s0 + p.span_cap + ((uint32_t)(uintptr_t)(p.up_w + off + (size_t)8 * p.row_bytes) & 15u) + (uint32_t)g * p.row_bytes;
+    RowStream<FMT, STAGES> rs;
+    rs.init(smem, ring, stab, part_off + 1280u + (uint32_t)warp * (STAGES * 8), give_up, p.status, lane);
+    __syncthreads();          // the mbarriers exist
+    bool fetched = false;
+    for (int unit = blockIdx.x * groups + group; unit < units; unit += nslots) {
+        const int r = unit / col_blocks, c0 = (unit - r * col_blocks) * COLS;
+        const uint32_t e = __shfl_sync(0xffffffffu, p.ids ? __ldg(p.ids + r) : 0u, 0);
+        const size_t off = ((size_t)e * p.F + c0) * p.row_bytes;
+        if (GATED) rs.begin(p.gate_w + off, p.up_w + off, p.row_bytes, kb0, nb);
+        else rs.begin(p.up_w + off, p.up_w + off + (size_t)8 * p.row_bytes, p.row_bytes, kb0, nb);
+        float b0 = 0.f, b1 = 0.f;
+        if (ARCH == OCO_ARCH_GPT_OSS && s == 0 && tig == 0) {   // biases travel while the rows stream
+            b0 = __ldg(p.gate_b + (size_t)e * p.F + c0 + g);
+            b1 = __ldg(p.up_b + (size_t)e * p.F + c0 + g);
         }
         float sum[4] = {0.f, 0.f, 0.f, 0.f};
-        // columns 0 / 1 of the fragments hold the token's hi / lo halves; lanes of other columns
-        // re-read them (their products are never looked at)
-        rows_dot<FMT>(rowA, rowB, smem_u32(xfrag) + (uint32_t)(((g & 1) * 4 + tig) * 16), 2 * 4 * 16, nkb, warp, tig, sum);
-        float* part = partial + (size_t)(it & 1) * kDecodeWarps * 32;
-        if (tig == 0) {
-            part[(warp * 16 + g) * 2 + 0] = __fadd_rn(sum[0], sum[1]);      // row g: hi + lo columns
-            part[(warp * 16 + g + 8) * 2 + 0] = __fadd_rn(sum[2], sum[3]);  // row g + 8
-        }
-        __syncthreads();
-        if (tid < COLS_PER_ITEM && c0 + tid < p.F) {
-            int col = c0 + tid;
-            float a = 0.f, b = 0.f;
-            for (int w = 0; w < kDecodeWarps; w++) {
-                if (GATED) {
-                    a = __fadd_rn(a, part[(w * 16 + tid) * 2]);
-                    b = __fadd_rn(b, part[(w * 16 + tid + 8) * 2]);
-                } else {
-                    a = __fadd_rn(a, part[(w * 16 + tid) * 2]);
-                }
-            }
-            float v;
+        if (!fetched) { mbar_wait(xbar, 0u, give_up, p.status); fetched = true; }
+        rs.run(xlane, sum);
+        float r0 = __fadd_rn(sum[0], sum[1]), r1 = __fadd_rn(sum[2], sum[3]);   // hi + lo columns (lanes tig == 0)
+        join_split(part, warp, group, s, ksplit, g, tig, r0, r1);
+        if (s == 0 && tig == 0) {
+            auto put = [&](int col, float v) {
+                p.act[(size_t)r * p.F + col] = v;
+                frag_store(p.actfrag + (size_t)r * (p.F / 32) * (kFragBlockBytes / 2), col, v);
+            };
             if (ARCH == OCO_ARCH_GPT_OSS) {
-                float gate = __fadd_rn(a, bf16_round(p.gate_b[(size_t)e * p.F + col]));
-                float up = __fadd_rn(b, bf16_round(__fadd_rn(p.up_b[(size_t)e * p.F + col], 1.0f)));
-                v = swiglu_clipped(gate, up);
+                float gate = __fadd_rn(r0, bf16_round(b0));
+                float up = __fadd_rn(r1, bf16_round(__fadd_rn(b1, 1.0f)));
+                put(c0 + g, swiglu_clipped(gate, up));
             } else if (ARCH == OCO_ARCH_QWEN) {
-                v = silu_gate_bf16(bf16_round(a), bf16_round(b));
+                put(c0 + g, silu_gate_bf16(bf16_round(r0), bf16_round(r1)));
             } else {
-                float u = fmaxf(bf16_round(a), 0.0f);
-                v = bf16_round(a) != bf16_round(a) ? qnan() : __fmul_rn(u, u);
+                float a = bf16_round(r0), b = bf16_round(r1);
+                float ua = fmaxf(a, 0.0f), ub = fmaxf(b, 0.0f);
+                put(c0 + g, a != a ? qnan() : __fmul_rn(ua, ua));
+                put(c0 + 8 + g, b != b ? qnan() : __fmul_rn(ub, ub));
             }
-            p.act[(size_t)r * p.F + col] = v;
-            frag_store(p.actfrag + (size_t)(r >> 1) * (p.F / 32) * 4 * 4 * 4 * 2, 4, (r & 1) * 2, col, v);
         }
     }
-    cp_async_wait<0>();
 }
 
 struct DecodeDownParams {
     const uint8_t* down_w;
     const float* down_b;      // null when the family has no bias
-    const uint32_t* ids;      // [K]
-    const __half* actfrag;    // [ceil(K/2)][F/32][4][4] uint4
+    const uint32_t* ids;      // [K]; null = expert 0
+    const __half* actfrag;    // [K][F/32] blocks of 128 bytes
     uint16_t* y;              // out bf16 [K, H]
     int H, F, K;
+    int ksplit;
     uint32_t row_bytes;       // bytes of one packed row of length F
-    uint32_t span_cap;
-    // Fused combine (null residual = off): the CTA that completes the last route pair of a block
-    // of eight output rows adds the weighted expert outputs to the residual
+    // Fused combine (null residual = off): the warp that completes the last route of a block of 16
+    // output rows adds the weighted expert outputs to the residual
     // (reference moe_sum, routing.metal:154-168; moe_add, nemotron.metal:222-236).
-    uint32_t* arrivals;       // one zeroed counter per block of eight output rows; left at zero again
+    uint32_t* arrivals;       // one zeroed counter per block of 16 output rows; left at zero again
     const float* probs;       // [K]
     uint16_t* residual;       // bf16 [H], in place
     const uint16_t* shared;   // bf16 [H] shared-expert output joining the sum, or null
     int round_sum;            // 1: the expert sum is rounded to bf16 before the residual add
+    uint32_t* status;         // device status word
 };
 
-// Down products for one token: item = 8 output rows of route 2p and the same 8 rows of route 2p+1
+// Down products for one token: unit = 16 output rows of one route
 // (reference matvec_mxfp4, projections.metal:140-182; matvec_q4, vector.metal:155-228).
-// CTA c serves route pair c % P.
-template <int FMT>
-__global__ void __launch_bounds__(kDecodeThreads) decode_down_kernel(const DecodeDownParams p) {
-    constexpr int kDecodeStages = kDownStages;
-    using B = Block32<FMT>;
+// CTA c serves route c % K, so a CTA needs one route's fragments only.
+template <int FMT, int STAGES>
+__global__ void __launch_bounds__(kTokThreads, 1) decode_down_kernel(const DecodeDownParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
+    const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, tig = lane & 3;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const int nkb = p.F / 32;
-    const int P = (p.K + 1) / 2;
-    const int pair = blockIdx.x % P;
-    uint4* xfrag = reinterpret_cast<uint4*>(smem);                       // [nkb][4][4] uint4
-    float* partial = reinterpret_cast<float*>(smem + (size_t)nkb * 4 * 4 * 16);
-    uint8_t* ring = reinterpret_cast<uint8_t*>(partial) + 2 * kDecodeWarps * 16 * 2 * 4;
-    const uint32_t stage_bytes = 2 * p.span_cap;
-    const int r0 = 2 * pair, r1 = min(2 * pair + 1, p.K - 1);
-    const uint32_t e0 = p.ids[r0], e1 = p.ids[r1];
+    const int route = blockIdx.x % p.K, idx = blockIdx.x / p.K, ctas = gridDim.x / p.K;
+    if (idx >= ctas) return;
+    const uint32_t part_off = (uint32_t)nkb * kFragBlockBytes;
+    float* part = reinterpret_cast<float*>(smem + part_off);
+    volatile uint32_t* give_up = reinterpret_cast<volatile uint32_t*>(part) + 496;
+    const uint32_t xbar = smem_u32(smem) + part_off + 1920u;
+    const uint32_t stab = part_off + kMiscBytes + (uint32_t)warp * kScaleBytes;
+    const uint32_t ring = part_off + kMiscBytes + (uint32_t)kTokWarps * kScaleBytes + (uint32_t)warp * STAGES * kStageBytes;
+    if (tid == 0) *give_up = 0u;
+    // the route's activation fragments (written by the expand kernel)
+    fetch_fragments(smem, p.actfrag + (size_t)route * nkb * (kFragBlockBytes / 2), nkb, xbar, warp, lane);
+    const uint32_t e = __shfl_sync(0xffffffffu, p.ids ? __ldg(p.ids + route) : 0u, 0);
 
-    // the pair's activation fragments (written by the expand kernel) -> shared memory
-    {
-        const uint4* src = reinterpret_cast<const uint4*>(p.actfrag) + (size_t)pair * nkb * 16;
-        uint32_t d = smem_u32(xfrag);
-        for (int i = tid; i < nkb * 16; i += kDecodeThreads) cp_async16(d + i * 16u, src + i);
-        cp_async_commit();
-    }
-    const int row_blocks = (p.H + 7) / 8;
-    const int ctas = gridDim.x / P;          // CTAs serving this pair
-    const int first = blockIdx.x / P;
-    auto issue = [&](int rb, int stage) {
-        if (rb < row_blocks && first < ctas) {
-            int d0 = rb * 8, rows = min(8, p.H - d0);
-            uint8_t* s0 = ring + (size_t)stage * stage_bytes;
-            copy_span_async(s0, p.down_w + ((size_t)e0 * p.H + d0) * p.row_bytes, rows * p.row_bytes, tid);
-            copy_span_async(s0 + p.span_cap, p.down_w + ((size_t)e1 * p.H + d0) * p.row_bytes, rows * p.row_bytes, tid);
+    const int ksplit = p.ksplit, group = warp / ksplit, s = warp - group * ksplit;
+    const int groups = kTokWarps / ksplit;
+    const int row_blocks = p.H / 16;
+    const int nslots = ctas * groups;
+    const int bps = (nkb + ksplit - 1) / ksplit;
+    const int kb0 = s * bps, nb = max(0, min(bps, nkb - kb0));
+    const uint32_t xlane = (uint32_t)kb0 * kFragBlockBytes + (uint32_t)(((g & 1) * 4 + tig) * 16);
+
+    RowStream<FMT, STAGES> rs;
+    rs.init(smem, ring, stab, part_off + 1280u + (uint32_t)warp * (STAGES * 8), give_up, p.status, lane);
+    __syncthreads();          // the mbarriers exist
+    bool fetched = false;
+    for (int rb = idx * groups + group; rb < row_blocks; rb += nslots) {
+        const int d0 = rb * 16;
+        const uint8_t* span = p.down_w + ((size_t)e * p.H + d0) * p.row_bytes;
+        rs.begin(span, span + (size_t)8 * p.row_bytes, p.row_bytes, kb0, nb);
+        float b0 = 0.f, b1 = 0.f;
+        if (p.down_b && s == 0 && tig == 0) {
+            b0 = __ldg(p.down_b + (size_t)e * p.H + d0 + g);
+            b1 = __ldg(p.down_b + (size_t)e * p.H + d0 + 8 + g);
         }
-        cp_async_commit();
-    };
-    int it = 0;
-#pragma unroll
-    for (int s = 0; s < kDecodeStages - 1; s++) issue(first + s * ctas, s);
-    if (first >= ctas) { cp_async_wait<0>(); return; }
-
-    for (int rb = first; rb < row_blocks; rb += ctas, it++) {
-        issue(rb + (kDecodeStages - 1) * ctas, (it + kDecodeStages - 1) % kDecodeStages);
-        cp_async_wait<kDecodeStages - 1>();
-        __syncthreads();
-        const int d0 = rb * 8;
-        const uint32_t s0 = smem_u32(ring) + (uint32_t)(it % kDecodeStages) * stage_bytes;
-        const uint8_t* ga = p.down_w + ((size_t)e0 * p.H + d0) * p.row_bytes;
-        const uint8_t* gb = p.down_w + ((size_t)e1 * p.H + d0) * p.row_bytes;
-        const uint32_t rowA = s0 + ((uint32_t)(uintptr_t)ga & 15u) + (uint32_t)g * p.row_bytes;
-        const uint32_t rowB = s0 + p.span_cap + ((uint32_t)(uintptr_t)gb & 15u) + (uint32_t)g * p.row_bytes;
         float sum[4] = {0.f, 0.f, 0.f, 0.f};
-        rows_dot<FMT>(rowA, rowB, smem_u32(xfrag) + (uint32_t)(((g & 3) * 4 + tig) * 16), 4 * 4 * 16, nkb, warp, tig, sum);
-        // route r0: rows g, columns 0,1 (tig 0: acc 0,1); route r1: rows g+8, columns 2,3 (tig 1: acc 2,3)
-        float* part = partial + (size_t)(it & 1) * kDecodeWarps * 32;
-        if (tig == 0) part[(warp * 16 + g) * 2] = __fadd_rn(sum[0], sum[1]);
-        if (tig == 1) part[(warp * 16 + g + 8) * 2] = __fadd_rn(sum[2], sum[3]);
-        __syncthreads();
-        if (tid < 16) {
-            int q = tid >> 3, row = d0 + (tid & 7), route = 2 * pair + q;
-            if (row < p.H && route < p.K) {
-                float a = 0.f;
-                for (int w = 0; w < kDecodeWarps; w++) a = __fadd_rn(a, part[(w * 16 + tid) * 2]);
-                uint32_t e = q ? e1 : e0;
-                if (p.down_b) a = __fadd_rn(a, bf16_round(p.down_b[(size_t)e * p.H + row]));
-                p.y[(size_t)route * p.H + row] = f32_to_bf16_bits(a);
-            }
+        if (!fetched) { mbar_wait(xbar, 0u, give_up, p.status); fetched = true; }
+        rs.run(xlane, sum);
+        float r0 = __fadd_rn(sum[0], sum[1]), r1 = __fadd_rn(sum[2], sum[3]);
+        join_split(part, warp, group, s, ksplit, g, tig, r0, r1);
+        if (s != 0) continue;
+        if (tig == 0) {
+            if (p.down_b) { r0 = __fadd_rn(r0, bf16_round(b0)); r1 = __fadd_rn(r1, bf16_round(b1)); }
+            p.y[(size_t)route * p.H + d0 + g] = f32_to_bf16_bits(r0);
+            p.y[(size_t)route * p.H + d0 + 8 + g] = f32_to_bf16_bits(r1);
         }
         if (p.residual) {
-            // Whoever finishes a row block last combines it. No CTA waits for another.
-            __shared__ int is_last;
+            // Whoever finishes a row block last combines it. No warp waits for another.
             __threadfence();
-            __syncthreads();
-            if (tid == 0) {
-                is_last = atomicAdd(p.arrivals + rb, 1u) == (uint32_t)(P - 1);
-                if (is_last) p.arrivals[rb] = 0;      // ready for the next call on this stream
+            __syncwarp();
+            uint32_t seen = 0;
+            if (lane == 0) {
+                seen = atomicAdd(p.arrivals + rb, 1u);
+                if (seen == (uint32_t)(p.K - 1)) p.arrivals[rb] = 0;   // ready for the next call on this stream
             }
-            __syncthreads();
-            if (is_last && tid < 8 && d0 + tid < p.H) {
+            seen = __shfl_sync(0xffffffffu, seen, 0);
+            if (seen == (uint32_t)(p.K - 1) && lane < 16) {
                 __threadfence();
-                const int row = d0 + tid;
+                const int row = d0 + lane;
                 float sres = p.shared ? bf16_bits_to_f32(p.shared[row]) : 0.0f;
                 for (int r = 0; r < p.K; r++)
                     sres = __fmaf_rn(bf16_bits_to_f32(__ldcg(p.y + (size_t)r * p.H + row)), p.probs[r], sres);
@@ -404,7 +510,50 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_down_kernel(const Decod
             }
         }
     }
-    cp_async_wait<0>();
+}
+
+// Router of one token: logits (one warp per expert, reference router_logits, routing.metal:131-146),
+// then the CTA that finishes last selects the experts and their weights for the whole token
+// (routing.metal:71-94; nemotron.metal:167-211). On the side, the CTAs turn the token into the B
+// fragments the expert kernels multiply with. grid ceil(E/8), 256 threads.
+template <int ARCH>
+__global__ void __launch_bounds__(256) router_token_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w,
+                                                           const float* __restrict__ bias, int H, int E, int K,
+                                                           int normalize, float scale, float* __restrict__ logits,
+                                                           uint32_t* __restrict__ ids, float* __restrict__ probs,
+                                                           __half* __restrict__ xfrag, uint32_t* __restrict__ arrival) {
+    __shared__ int is_last;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * 8 + warp;
+    if (e < E) {
+        float s = H <= 128 * 24 ? canonical_logit_prefetch<ARCH == OCO_ARCH_GPT_OSS, 24>(x, w + (size_t)e * H, H, lane)
+                                : canonical_logit<ARCH == OCO_ARCH_GPT_OSS>(x, w + (size_t)e * H, H, lane);
+        if (ARCH == OCO_ARCH_GPT_OSS) s = __fadd_rn(s, bf16_round(bias[e]));
+        if (lane == 0) logits[e] = s;
+    }
+    for (int k = blockIdx.x * 256 + threadIdx.x; k < H; k += gridDim.x * 256) frag_store(xfrag, k, bf16_bits_to_f32(x[k]));
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t seen = atomicAdd(arrival, 1u);
+        is_last = seen == gridDim.x - 1;
+        if (is_last) *arrival = 0;
+    }
+    __syncthreads();
+    if (!is_last || warp != 0) return;
+    __threadfence();
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int q = lane + 32 * j;
+        v[j] = q < E ? __ldcg(logits + q) : 0.0f;
+    }
+    uint32_t id[kMaxTopK];
+    float pr[kMaxTopK];
+    select_experts<ARCH>(v, E, K, ARCH == OCO_ARCH_NEMOTRON ? bias : nullptr, normalize, scale, lane, id, pr);
+#pragma unroll
+    for (int r = 0; r < kMaxTopK; r++)
+        if (r < K && lane == r) { ids[r] = id[r]; probs[r] = pr[r]; }
 }
 
 }  // namespace oco

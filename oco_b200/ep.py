@@ -52,8 +52,12 @@ class Backend:
 
 
 def forward(x: torch.Tensor, residual: torch.Tensor, backend: Backend, experts_total: int,
-            group: Optional[dist.ProcessGroup] = None, timings: Optional[dict] = None) -> None:
-    """One expert-parallel MoE layer over this rank's tokens. x, residual: int16 [T, H]."""
+            group: Optional[dist.ProcessGroup] = None, timings: Optional[dict] = None,
+            exchange: Optional[Callable] = None) -> None:
+    """One expert-parallel MoE layer over this rank's tokens. x, residual: int16 [T, H].
+    `exchange` has the signature of `dist.all_to_all_single` and replaces it when given (a
+    benchmark passes a local stand-in to find how much of the step the exchange costs)."""
+    a2a = exchange or dist.all_to_all_single
     world = dist.get_world_size(group)
     epr = experts_total // world
     T, H = x.shape
@@ -63,7 +67,7 @@ def forward(x: torch.Tensor, residual: torch.Tensor, backend: Backend, experts_t
     send_rows = x.index_select(0, order // K)
     # counts first, then the rows and their expert ids
     recv_counts = torch.empty_like(send_counts)
-    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    a2a(recv_counts, send_counts, group=group)
     send_split = send_counts.tolist()
     recv_split = recv_counts.tolist()
     R = int(sum(recv_split))
@@ -73,17 +77,16 @@ def forward(x: torch.Tensor, residual: torch.Tensor, backend: Backend, experts_t
         ev[0].record()
     recv_rows = torch.empty((R, H), dtype=x.dtype, device=x.device)
     # rows travel as bytes: every backend moves uint8, not every one moves 16-bit integers
-    dist.all_to_all_single(recv_rows.view(torch.uint8), send_rows.contiguous().view(torch.uint8), recv_split, send_split,
-                           group=group)
+    a2a(recv_rows.view(torch.uint8), send_rows.contiguous().view(torch.uint8), recv_split, send_split, group=group)
     recv_ids = torch.empty(R, dtype=torch.int32, device=x.device)
-    dist.all_to_all_single(recv_ids, local_ids.to(torch.int32), recv_split, send_split, group=group)
+    a2a(recv_ids, local_ids.to(torch.int32), recv_split, send_split, group=group)
     if ev:
         ev[1].record()
     y_recv = backend.experts(recv_rows, recv_ids)
     if ev:
         ev[2].record()
     y_back = torch.empty((T * K, H), dtype=x.dtype, device=x.device)
-    dist.all_to_all_single(y_back.view(torch.uint8), y_recv.contiguous().view(torch.uint8), send_split, recv_split, group=group)
+    a2a(y_back.view(torch.uint8), y_recv.contiguous().view(torch.uint8), send_split, recv_split, group=group)
     if ev:
         ev[3].record()
     y_routes = torch.empty_like(y_back)
@@ -165,6 +168,12 @@ class CudaBackend:
         p._check(self._lib.lib().oco_moe_combine(p.handle, C.c_void_p(y_routes.data_ptr()),
                                                 C.c_void_p(probs.contiguous().data_ptr()),
                                                 C.c_void_p(residual.data_ptr()), residual.shape[0], self._stream()))
+
+    def launches(self) -> int:
+        """Kernels launched by the last route, experts and combine calls together."""
+        # combine runs on the router plan after route, so the router plan's count is combine's; the
+        # route call before it launched one kernel (two on the first call of a weight set)
+        return self.router_plan.launch_count() + 1 + self.expert_plan.launch_count()
 
     def backend(self) -> Backend:
         return Backend(self.route, self.experts, self.combine)

@@ -1,0 +1,58 @@
+"""Worker of the expert-parallel GPU test: one process per GPU over NCCL, the C-ABI stage calls
+(route, experts, combine) doing the arithmetic. Launched by tests/test_gpu_ep.py through
+torch.distributed.run; the oracle checks each rank's rows."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import oracle  # noqa: E402
+from oco_b200 import ep, synth  # noqa: E402
+
+REL_L2 = 1e-3
+
+
+def rel_l2(got_bits, ref_bits):
+    g = synth.bf16_bits_to_f32(got_bits).astype(np.float64)
+    r = synth.bf16_bits_to_f32(ref_bits).astype(np.float64)
+    return np.linalg.norm(g - r) / max(np.linalg.norm(r), 1e-30)
+
+
+def main():
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    cases = [(synth.ARCH_GPT_OSS, 16, 4, 320, 288, 203, synth.FMT_MXFP4),
+             (synth.ARCH_GPT_OSS, 8, 2, 64, 96, 11, synth.FMT_MXFP4),
+             (synth.ARCH_NEMOTRON, 16, 6, 256, 192, 150, synth.FMT_Q4_0)]
+    for n, (arch, E, K, H, F, T, fmt) in enumerate(cases):
+        layer = synth.make_layer(arch, H, F, E, K, fmt, seed=31 + n)
+        layer.shared_ffn, layer.shared_up_w, layer.shared_down_w = 0, None, None   # routed experts only
+        x_all, res_all = synth.make_tokens(H, T, 9 + n, "normal")
+        bounds = np.linspace(0, T, world + 1).astype(int)
+        lo, hi = bounds[rank], bounds[rank + 1]
+        be = ep.CudaBackend(layer, rank, world, max_rows=T)
+        x = torch.from_numpy(x_all[lo:hi].view(np.int16).copy()).cuda()
+        res = torch.from_numpy(res_all[lo:hi].view(np.int16).copy()).cuda()
+        ep.forward(x, res, be.backend(), E)
+        torch.cuda.synchronize()
+        be.router_plan.poll(); be.expert_plan.poll()
+        ref = oracle.moe_forward(layer, x_all, res_all, mode=2)
+        got = res.cpu().numpy().view(np.uint16)
+        err = rel_l2(got, ref.out[lo:hi])
+        assert err <= REL_L2, f"rank {rank} case {n}: rel-L2 {err}"
+        ids, _ = be.route(x)
+        assert np.array_equal(ids.cpu().numpy().astype(np.uint32), ref.ids[lo:hi].astype(np.uint32)), "expert ids differ"
+    dist.barrier()
+    dist.destroy_process_group()
+    print(f"rank {rank} ok")
+
+
+if __name__ == "__main__":
+    main()
