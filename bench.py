@@ -43,6 +43,15 @@ WORKLOADS = {
     "gpt-oss-120b-decode64": ("gpt-oss-120b", 64),
 }
 EXPERT_PARALLEL = {"gpt-oss-120b-prefill", "gpt-oss-120b-decode64"}
+# DRAM bytes (read + write) of one launch of the dominant kernels, from the ncu captures that are
+# summarised under profiles/ (grouped_gemm_wide_gpt-oss-20b-prefill.md,
+# token_kernels_gpt-oss-20b-decode.md); a profiler is never attached to a timed run.
+NCU_TRAFFIC = {
+    ("gpt-oss-20b-prefill", "up_tiles"): 330.0e6 + 40.9e6,
+    ("gpt-oss-20b-prefill", "down_tiles"): 188.9e6 + 29.4e6,
+    ("gpt-oss-20b-decode", "expand"): 35.39e6,
+    ("gpt-oss-20b-decode", "down_combine"): 17.76e6,
+}
 
 
 def measured_peaks():
@@ -117,8 +126,8 @@ def cpu_baseline(layer, tokens, seed, budget_tokens, threads=None):
     """Times the CPU restatement (f32 FMA accumulation, all host threads) on a bounded sample of
     the same workload: the first `budget_tokens` tokens of the batch."""
     import oracle
-    if threads:
-        oracle.set_num_threads(threads)
+    # all the cores this process may use, whatever OMP_NUM_THREADS says (torchrun sets it to 1)
+    oracle.set_num_threads(threads or len(os.sched_getaffinity(0)))
     n = max(1, min(tokens, budget_tokens))
     x, res = synth.make_tokens(layer.hidden, tokens, seed, "normal")
     x, res = x[:n], res[:n]
@@ -463,7 +472,8 @@ def main():
             units = per.get(dominant, alg_bytes)
             achieved = units / dur_s / 1e9
             roofline = dict(bound="hbm", kernel=dominant, achieved=achieved, peak=peaks["hbm_gbs"], unit="GB/s",
-                            frac=achieved / peaks["hbm_gbs"], traffic=None, peak_source=f"{peaks['source']} copy bandwidth",
+                            frac=achieved / peaks["hbm_gbs"], traffic=NCU_TRAFFIC.get((args.workload, dominant)),
+                            peak_source=f"{peaks['source']} copy bandwidth",
                             algorithmic_bytes_per_launch=units, launch_ms=phases[dominant],
                             whole_step=dict(bytes=alg_bytes, gbs=alg_bytes / (ms_per_step / 1e3) / 1e9,
                                             frac=alg_bytes / (ms_per_step / 1e3) / 1e9 / peaks["hbm_gbs"]))
@@ -474,7 +484,7 @@ def main():
             long_run = wall > 2.0 and peaks.get("tflops_sustained")
             peak = peaks["tflops_sustained"] if long_run else peaks["tflops"]
             roofline = dict(bound="tensor", kernel=dominant, achieved=achieved, peak=peak, unit="TFLOP/s",
-                            frac=achieved / peak, traffic=None,
+                            frac=achieved / peak, traffic=NCU_TRAFFIC.get((args.workload, dominant)) if tokens == default_tokens else None,
                             peak_source=f"{peaks['source']} dense bf16 cuBLAS, {'sustained' if long_run else 'burst'}",
                             algorithmic_flops_per_launch=units, launch_ms=phases[dominant],
                             whole_step=dict(flops=alg_flops, tflops=alg_flops / (ms_per_step / 1e3) / 1e12,
