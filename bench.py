@@ -37,6 +37,7 @@ WORKLOADS = {
     "qwen3-30b-a3b-prefill": ("qwen3-30b-a3b", 512),
     "nemotron-h-prefill": ("nemotron-h", 1024),
     "nemotron-h-decode": ("nemotron-h", 1),
+    "qwen3-30b-a3b-decode": ("qwen3-30b-a3b", 1),
     # 128 experts: one GPU holds them all; with N > 1 ranks the experts are sharded 128/N per GPU and
     # the batch (fixed in total: strong scaling) is dispatched and combined with all-to-all
     "gpt-oss-120b-prefill": ("gpt-oss-120b", 8192),
@@ -464,11 +465,15 @@ def main():
         dur_s = phases[dominant] / 1e3
         H, F, R = layer.hidden, layer.ffn, tokens * layer.top_k
         n_up = 1 if layer.arch == synth.ARCH_NEMOTRON else 2
-        if decode:
-            # bandwidth-bound: the phase streams the selected experts' packed rows once
+        # below the ridge (FLOP per byte at which the tensor peak meets the copy bandwidth) the step is memory-bound
+        hbm_bound = alg_flops / alg_bytes < peaks["tflops"] * 1e12 / (peaks["hbm_gbs"] * 1e9)
+        if hbm_bound:
+            # the phase streams the packed rows of the experts it touches once
             rb_up, rb_dn = synth.row_bytes(layer.fmt, H), synth.row_bytes(layer.fmt, F)
-            per = {"expand": layer.top_k * n_up * F * rb_up, "down": layer.top_k * H * rb_dn,
-                   "down_combine": layer.top_k * H * rb_dn}
+            n_exp = layer.top_k if decode else touched
+            up_bytes, dn_bytes = n_exp * n_up * F * rb_up, n_exp * H * rb_dn
+            per = {"expand": up_bytes, "down": dn_bytes, "down_combine": dn_bytes, "up_rows": up_bytes, "down_rows": dn_bytes,
+                   "up_tiles": up_bytes, "down_tiles": dn_bytes}
             units = per.get(dominant, alg_bytes)
             achieved = units / dur_s / 1e9
             roofline = dict(bound="hbm", kernel=dominant, achieved=achieved, peak=peaks["hbm_gbs"], unit="GB/s",

@@ -156,9 +156,11 @@ int oco_moe_experts(oco_moe_plan* plan, const uint16_t* rows_bf16, const uint32_
 int oco_moe_combine(oco_moe_plan* plan, const uint16_t* y_bf16, const float* probs, uint16_t* residual_bf16,
                     int rows, void* cuda_stream);
 
-/* The same call for host buffers: copies x and the residual to the device, runs the layer and
- * copies the residual back, all on `cuda_stream`, then waits for the stream. Uses staging space
- * inside the bound workspace. */
+/* The same call for host buffers: copies x to the device on `cuda_stream`, the residual rows on a
+ * second stream the plan owns (they are needed by the last kernel only, so their copy overlaps the
+ * router and the expert products), runs the layer, copies the residual back on `cuda_stream` and
+ * waits for it. Uses staging space inside the bound workspace. Pinned host buffers make the
+ * copies asynchronous. */
 int oco_moe_forward_host(oco_moe_plan* plan, const uint16_t* x_bf16_host, uint16_t* residual_bf16_host,
                          int rows, void* cuda_stream);
 

@@ -10,6 +10,7 @@
 
 #include "common.cuh"
 #include "decode.cuh"
+#include "batch.cuh"
 #include "gemm.cuh"
 #include "gemm_wide.cuh"
 #include "plan.cuh"
@@ -40,6 +41,8 @@ struct Workspace {
     float* act1 = nullptr;        // f32 [K, F] single-token activations
     __half* actfrag = nullptr;    // single-token B fragments of the down projection
     __half* xfrag = nullptr;      // single-token B fragments of the token itself
+    __half* bfrag_in = nullptr;   // few-token path: B fragments of each route group, input rows
+    __half* bfrag_out = nullptr;  //                 and activations
     uint32_t* arrivals = nullptr; // single-token combine: one counter per eight output rows
     uint16_t* xh = nullptr;       // half [T, H] token-order input rows (shared expert)
     uint16_t* mid = nullptr;      // half [T, S] shared expert intermediate
@@ -69,6 +72,9 @@ struct oco_moe_plan {
     CUtensorMap map_xs[kTileKinds], map_act[kTileKinds], map_xh[kTileKinds], map_mid[kTileKinds];
     // Per-phase timestamps (the counterpart of the reference's OCO_PROFILE counter heap,
     // src/gpu/profile.rs:1-31, src/gpu/dispatch.rs:189-208): one event before each kernel.
+    cudaStream_t copy_stream = nullptr;   // oco_moe_forward_host: the residual rows' own stream
+    cudaEvent_t ev_fork = nullptr, ev_residual = nullptr;
+    bool no_batch_path = false;  // OCO_MOE_NO_BATCH=1: few tokens take the tile kernels too
     bool narrow_tiles = false;   // OCO_MOE_NARROW_TILES=1: keep the generic tile kernel for 256-route tiles too
     bool profiling = false;
     int n_marks = 0;
@@ -118,6 +124,9 @@ int block_elems(int fmt) { return fmt == OCO_FMT_Q4_K ? 256 : 32; }
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Lays the workspace out; with base == nullptr only the total is meaningful.
+// Route groups (up to eight routes of one expert) that R routes over E experts can form.
+size_t batch_max_groups(size_t R, size_t E) { return R / 8 + (E < R ? E : R); }
+
 Workspace carve(const oco_moe_desc& d, int max_rows, unsigned char* base) {
     Workspace w;
     size_t off = 0;
@@ -136,7 +145,7 @@ Workspace carve(const oco_moe_desc& d, int max_rows, unsigned char* base) {
     w.probs = (float*)take(R * 4);
     w.offsets = (uint32_t*)take((E + 1) * 4);
     w.tile_count = (uint32_t*)take(4);
-    w.tiles = (uint32_t*)take(2 * (R / 32 + E + 1) * 4);
+    w.tiles = (uint32_t*)take(2 * (R / 8 + E + 1) * 4);
     w.row_of_route = (uint32_t*)take(R * 4);
     w.route_of_row = (uint32_t*)take(R * 4);
     w.xs = (uint16_t*)take(R * H * 2);
@@ -145,6 +154,11 @@ Workspace carve(const oco_moe_desc& d, int max_rows, unsigned char* base) {
     w.act1 = (float*)take(K * F * 4);
     w.actfrag = (__half*)take(P * (F / 32) * 128 * 2);
     w.xfrag = (__half*)take((H / 32) * 128);
+    {
+        const size_t groups = batch_max_groups(R < 4 * E ? R : 4 * E, E);
+        w.bfrag_in = (__half*)take(groups * (H / 32) * kBatchFragBlock);
+        w.bfrag_out = (__half*)take(groups * (F / 32) * kBatchFragBlock);
+    }
     w.arrivals = (uint32_t*)take((H / 8 + 1) * 4);
     if (S) {
         w.xh = (uint16_t*)take(T * H * 2);
@@ -436,6 +450,49 @@ int stage_experts(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, in
     const oco_moe_desc& d = plan->d;
     Workspace& ws = plan->ws;
     const int H = d.hidden, F = d.ffn, E = d.experts;
+    if (FMT != OCO_FMT_Q4_K && R <= 4 * E && !plan->no_batch_path) {
+        // A few routes per expert: memory-bound, streamed with up to eight routes per MMA (batch.cuh).
+        if constexpr (FMT != OCO_FMT_Q4_K) {
+            if (batch_smem_bytes(H / 32) > kMaxDynamicSmem || batch_smem_bytes(F / 32) > kMaxDynamicSmem)
+                return fail(plan, OCO_UNSUPPORTED_SHAPE, "layer too wide for the few-token kernels");
+            plan->last_tile_rows = kBatchCols;
+            mark(plan, st, "route_plan");
+            route_plan_kernel<<<1, 1024, 0, st>>>(ids, (uint32_t)R, (uint32_t)E, (uint32_t)kBatchCols, ws.offsets,
+                                                  ws.row_of_route, ws.route_of_row, ws.tiles, ws.tile_count);
+            const int groups = (int)batch_max_groups((size_t)R, (size_t)E);
+            mark(plan, st, "fragments");
+            batch_fragments_kernel<<<groups, 256, 0, st>>>(x, ws.tiles, ws.tile_count, ws.offsets, ws.route_of_row, per_row,
+                                                           H, reinterpret_cast<uint4*>(ws.bfrag_in));
+            plan->launches += 2;
+            const int parts = std::max(1, std::min(8, (4 * plan->sm_count + groups - 1) / groups));
+            static bool attr_set = false;
+            if (!attr_set) {
+                CK(allow_smem(batch_rows_kernel<FMT, EPI_UP>));
+                CK(allow_smem(batch_rows_kernel<FMT, kEpiDownBf16>));
+                attr_set = true;
+            }
+            BatchParams bp{};
+            bp.tiles = ws.tiles; bp.tile_count = ws.tile_count; bp.offsets = ws.offsets; bp.route_of_row = ws.route_of_row;
+            bp.parts = parts; bp.status = ws.status;
+            bp.w0 = ARCH == OCO_ARCH_NEMOTRON ? plan->w.up_w : plan->w.gate_w;
+            bp.w1 = ARCH == OCO_ARCH_NEMOTRON ? nullptr : plan->w.up_w;
+            bp.b0 = ARCH == OCO_ARCH_GPT_OSS ? plan->w.gate_b : nullptr;
+            bp.b1 = ARCH == OCO_ARCH_GPT_OSS ? plan->w.up_b : nullptr;
+            bp.frag_in = ws.bfrag_in; bp.frag_out = ws.bfrag_out; bp.out = ws.act;
+            bp.n_in = H; bp.n_out = F; bp.row_bytes = plan->up_row_bytes;
+            mark(plan, st, "up_rows");
+            batch_rows_kernel<FMT, EPI_UP><<<groups * parts, kBatchThreads, batch_smem_bytes(H / 32), st>>>(bp);
+            bp.w0 = plan->w.down_w; bp.w1 = nullptr;
+            bp.b0 = ARCH == OCO_ARCH_GPT_OSS ? plan->w.down_b : nullptr; bp.b1 = nullptr;
+            bp.frag_in = ws.bfrag_out; bp.frag_out = nullptr; bp.out = y;
+            bp.n_in = F; bp.n_out = H; bp.row_bytes = plan->down_row_bytes;
+            mark(plan, st, "down_rows");
+            batch_rows_kernel<FMT, kEpiDownBf16><<<groups * parts, kBatchThreads, batch_smem_bytes(F / 32), st>>>(bp);
+            plan->launches += 2;
+            CK(cudaGetLastError());
+            return OCO_OK;
+        }
+    }
     const int nt_index = pick_tile_index(R, E);
     const int NT = kTileSizes[nt_index];
     plan->last_tile_rows = NT;
@@ -486,8 +543,10 @@ int stage_combine(oco_moe_plan* plan, const uint16_t* y, const float* probs, uin
     return OCO_OK;
 }
 
+// residual_ready: an event after which the residual rows may be read (null: they are ready).
 template <int ARCH>
-int forward_tiled(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int rows, cudaStream_t st) {
+int forward_tiled(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int rows, cudaStream_t st,
+                  cudaEvent_t residual_ready = nullptr) {
     constexpr int FMT = Family<ARCH>::kFmt;
     const oco_moe_desc& d = plan->d;
     Workspace& ws = plan->ws;
@@ -518,6 +577,7 @@ int forward_tiled(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int
         if (rc) return rc;
         shared_mode = 2;
     }
+    if (residual_ready) CK(cudaStreamWaitEvent(st, residual_ready, 0));
     rc = stage_combine<ARCH>(plan, ws.y, ws.probs, residual, rows, shared_mode, st);
     if (rc) return rc;
     mark(plan, st, "end");
@@ -525,10 +585,25 @@ int forward_tiled(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int
 }
 
 template <int ARCH>
-int forward_family(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int rows, cudaStream_t st) {
+int forward_family(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int rows, cudaStream_t st,
+                   cudaEvent_t residual_ready = nullptr) {
     constexpr int FMT = Family<ARCH>::kFmt;
-    if (rows == 1 && (FMT == OCO_FMT_MXFP4 || FMT == OCO_FMT_Q4_0)) return forward_single<ARCH>(plan, x, residual, st);
-    return forward_tiled<ARCH>(plan, x, residual, rows, st);
+    if (rows == 1 && (FMT == OCO_FMT_MXFP4 || FMT == OCO_FMT_Q4_0)) {
+        if (residual_ready) CK(cudaStreamWaitEvent(st, residual_ready, 0));
+        return forward_single<ARCH>(plan, x, residual, st);
+    }
+    return forward_tiled<ARCH>(plan, x, residual, rows, st, residual_ready);
+}
+
+int forward_any(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int rows, cudaStream_t st,
+                cudaEvent_t residual_ready) {
+    plan->launches = 0;
+    plan->n_marks = 0;
+    switch (plan->d.arch) {
+        case OCO_ARCH_GPT_OSS: return forward_family<OCO_ARCH_GPT_OSS>(plan, x, residual, rows, st, residual_ready);
+        case OCO_ARCH_NEMOTRON: return forward_family<OCO_ARCH_NEMOTRON>(plan, x, residual, rows, st, residual_ready);
+        default: return forward_family<OCO_ARCH_QWEN>(plan, x, residual, rows, st, residual_ready);
+    }
 }
 
 }  // namespace
@@ -565,6 +640,7 @@ int oco_moe_plan_create(const oco_moe_desc* desc, oco_moe_plan** out) {
         plan->shared_down_row_bytes = packed_row_bytes(d.weight_format, d.shared_ffn);
     }
     { const char* e = getenv("OCO_MOE_NARROW_TILES"); plan->narrow_tiles = e && e[0] == '1'; }
+    { const char* e = getenv("OCO_MOE_NO_BATCH"); plan->no_batch_path = e && e[0] == '1'; }
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) == cudaSuccess &&
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0)
@@ -577,6 +653,9 @@ void oco_moe_plan_destroy(oco_moe_plan* plan) {
     if (!plan) return;
     for (int i = 0; i < kMaxMarks; i++)
         if (plan->marks[i]) cudaEventDestroy(plan->marks[i]);
+    if (plan->ev_fork) cudaEventDestroy(plan->ev_fork);
+    if (plan->ev_residual) cudaEventDestroy(plan->ev_residual);
+    if (plan->copy_stream) cudaStreamDestroy(plan->copy_stream);
     delete plan;
 }
 
@@ -743,9 +822,20 @@ int oco_moe_forward_host(oco_moe_plan* plan, const uint16_t* x_host, uint16_t* r
     if (!x_host || !residual_host || rows < 1 || rows > plan->max_rows) return fail(plan, OCO_INVALID_ARGUMENT, "bad host buffers or rows");
     cudaStream_t st = (cudaStream_t)cuda_stream;
     const size_t bytes = (size_t)rows * plan->d.hidden * 2;
+    if (!plan->have_w) return fail(plan, OCO_INVALID_ARGUMENT, "bind weights first");
+    // The residual rows are only needed by the last kernel: they travel on a second stream while
+    // the router and the expert products run.
+    if (!plan->copy_stream) {
+        CK(cudaStreamCreateWithFlags(&plan->copy_stream, cudaStreamNonBlocking));
+        CK(cudaEventCreateWithFlags(&plan->ev_fork, cudaEventDisableTiming));
+        CK(cudaEventCreateWithFlags(&plan->ev_residual, cudaEventDisableTiming));
+    }
     CK(cudaMemcpyAsync(plan->ws.host_x, x_host, bytes, cudaMemcpyHostToDevice, st));
-    CK(cudaMemcpyAsync(plan->ws.host_res, residual_host, bytes, cudaMemcpyHostToDevice, st));
-    int rc = oco_moe_forward(plan, plan->ws.host_x, plan->ws.host_res, rows, cuda_stream);
+    CK(cudaEventRecord(plan->ev_fork, st));       // the bus is free for the residual rows once x has arrived
+    CK(cudaStreamWaitEvent(plan->copy_stream, plan->ev_fork, 0));
+    CK(cudaMemcpyAsync(plan->ws.host_res, residual_host, bytes, cudaMemcpyHostToDevice, plan->copy_stream));
+    CK(cudaEventRecord(plan->ev_residual, plan->copy_stream));
+    int rc = forward_any(plan, plan->ws.host_x, plan->ws.host_res, rows, st, plan->ev_residual);
     if (rc) return rc;
     CK(cudaMemcpyAsync(residual_host, plan->ws.host_res, bytes, cudaMemcpyDeviceToHost, st));
     CK(cudaStreamSynchronize(st));

@@ -80,6 +80,10 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
+__device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
+    __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
 // Barrier among the `threads` threads that name the same id (1..15); id 0 is __syncthreads.
 __device__ __forceinline__ void named_barrier(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -128,10 +132,16 @@ struct Block32<OCO_FMT_Q4_0> {
 // byte alignment). begin() starts the copies; run() multiplies. After run(), lane (g, tig) holds
 // in sum[0..1] the products of row g of span A with fragment columns 2*tig and 2*tig + 1, and in
 // sum[2..3] the same for row g of span B.
-template <int FMT, int STAGES>
+// COLS: columns of the B fragments kept per block (2: one token as hi + lo; 8: up to eight routes).
+template <int FMT, int STAGES, int COLS = 2>
 struct RowStream {
     using B = Block32<FMT>;
     static constexpr uint32_t kChunkBytes = kChunkBlocks * B::kBytes;   // 272 or 288: whole 16-byte pieces
+    static constexpr uint32_t kFragBlock = COLS * 64;                   // bytes of one block's B fragments
+    // Several tokens follow the tile kernels' numerics: weights enter the MMA as half(code * scale), as the
+    // reference's tiles hold them. E8M0 scales are powers of two, so only Q4_0 rounds there.
+    static constexpr bool kPrescale = FMT == OCO_FMT_Q4_0 && COLS == 8;
+    int ncols = 2;             // columns in use: only the lanes that feed them load B fragments
 
     SharedBase base;           // the kernel's shared array; ring and stab are byte offsets into it
     uint32_t base_addr;        // its address in the shared window (for the copy and mbarrier instructions)
@@ -205,8 +215,8 @@ struct RowStream {
     }
 
     // The blocks of one stage. FULL: all 16 blocks are present. xa: byte offset in shared memory of
-    // this lane's B fragment of the stage's first block. Only columns 0 and 1 carry the token, so
-    // only the lanes that feed them (g < 2) load; the other columns multiply zeros.
+    // this lane's B fragment of the stage's first block. Only the lanes that feed a column in use
+    // (g < ncols) load; the other columns multiply zeros.
     template <bool FULL>
     __device__ __forceinline__ void chunk(uint32_t st, uint32_t xa, int nbc, float (&sum)[4]) {
 #pragma unroll
@@ -228,17 +238,29 @@ struct RowStream {
                         const uint32_t wa = __funnelshift_r(lds32(base, pa), lds32(base, pa + 4), shA[i % kC]);
                         const uint32_t wb = __funnelshift_r(lds32(base, pb), lds32(base, pb + 4), shB[i % kC]);
                         uint4 xf = make_uint4(0u, 0u, 0u, 0u);
-                        if (g < 2) xf = lds128(base, xa + (uint32_t)i * kFragBlockBytes);
+                        if (g < ncols) xf = lds128(base, xa + (uint32_t)i * kFragBlock);
                         uint32_t qa0, qa1, qa2, qa3, qb0, qb1, qb2, qb3;
                         B::quads(wa, qa0, qa1, qa2, qa3);
                         B::quads(wb, qb0, qb1, qb2, qb3);
                         float acc[4];
+                        if (kPrescale) {
+                            const uint32_t ha = (t < 2 ? sa.x : sa.y) >> (16 * (t & 1)) & 0xffffu;
+                            const uint32_t hb = (t < 2 ? sb.x : sb.y) >> (16 * (t & 1)) & 0xffffu;
+                            const uint32_t da = ha | (ha << 16), db = hb | (hb << 16);
+                            qa0 = hmul2_bits(qa0, da); qa1 = hmul2_bits(qa1, da); qa2 = hmul2_bits(qa2, da); qa3 = hmul2_bits(qa3, da);
+                            qb0 = hmul2_bits(qb0, db); qb1 = hmul2_bits(qb1, db); qb2 = hmul2_bits(qb2, db); qb3 = hmul2_bits(qb3, db);
+                        }
                         mma16816_first(acc, qa0, qb0, qa1, qb1, xf.x, xf.y);
                         mma16816(acc, qa2, qb2, qa3, qb3, xf.z, xf.w);
-                        sum[0] = __fmaf_rn(acc[0], fa[t], sum[0]);
-                        sum[1] = __fmaf_rn(acc[1], fa[t], sum[1]);
-                        sum[2] = __fmaf_rn(acc[2], fb[t], sum[2]);
-                        sum[3] = __fmaf_rn(acc[3], fb[t], sum[3]);
+                        if (kPrescale) {
+                            sum[0] = __fadd_rn(sum[0], acc[0]); sum[1] = __fadd_rn(sum[1], acc[1]);
+                            sum[2] = __fadd_rn(sum[2], acc[2]); sum[3] = __fadd_rn(sum[3], acc[3]);
+                        } else {
+                            sum[0] = __fmaf_rn(acc[0], fa[t], sum[0]);
+                            sum[1] = __fmaf_rn(acc[1], fa[t], sum[1]);
+                            sum[2] = __fmaf_rn(acc[2], fb[t], sum[2]);
+                            sum[3] = __fmaf_rn(acc[3], fb[t], sum[3]);
+                        }
                     }
                 }
             }
@@ -273,7 +295,7 @@ struct RowStream {
                 }
             }
             __syncwarp();
-            const uint32_t xa = xaddr + (uint32_t)(c * kChunkBlocks) * kFragBlockBytes;
+            const uint32_t xa = xaddr + (uint32_t)(c * kChunkBlocks) * kFragBlock;
             if (nbc == kChunkBlocks) chunk<true>(st, xa, nbc, sum);
             else chunk<false>(st, xa, nbc, sum);
             __syncwarp();
@@ -282,15 +304,15 @@ struct RowStream {
     }
 };
 
-// The B fragments of one token or route (nkb blocks of 128 bytes, global memory) into shared
+// The B fragments of one token, route or route group (`bytes` of global memory) into shared
 // memory at offset 0 with one bulk copy by warp 0; every warp then waits on `bar` (phase 0).
-__device__ __forceinline__ void fetch_fragments(SharedBase smem, const void* frag, int nkb, uint32_t bar, int warp, int lane) {
+__device__ __forceinline__ void fetch_fragments(SharedBase smem, const void* frag, uint32_t bytes, uint32_t bar, int warp, int lane) {
     if (warp == 0) {
         if (lane == 0) {
             mbar_init(bar, 1);
             fence_barrier_init();
-            mbar_arrive_expect_tx(bar, (uint32_t)nkb * kFragBlockBytes);
-            bulk_copy(smem_u32(smem), frag, (uint32_t)nkb * kFragBlockBytes, bar);
+            mbar_arrive_expect_tx(bar, bytes);
+            bulk_copy(smem_u32(smem), frag, bytes, bar);
         }
     }
 }
@@ -363,7 +385,7 @@ __global__ void __launch_bounds__(kTokThreads, 1) decode_expand_kernel(const Dec
     const uint32_t stab = part_off + kMiscBytes + (uint32_t)warp * kScaleBytes;
     const uint32_t ring = part_off + kMiscBytes + (uint32_t)kTokWarps * kScaleBytes + (uint32_t)warp * STAGES * kStageBytes;
     if (tid == 0) *give_up = 0u;
-    fetch_fragments(smem, p.xfrag, nkb, xbar, warp, lane);
+    fetch_fragments(smem, p.xfrag, (uint32_t)nkb * kFragBlockBytes, xbar, warp, lane);
 
     const int ksplit = p.ksplit, group = warp / ksplit, s = warp - group * ksplit;
     const int groups = kTokWarps / ksplit;
@@ -454,7 +476,7 @@ __global__ void __launch_bounds__(kTokThreads, 1) decode_down_kernel(const Decod
     const uint32_t ring = part_off + kMiscBytes + (uint32_t)kTokWarps * kScaleBytes + (uint32_t)warp * STAGES * kStageBytes;
     if (tid == 0) *give_up = 0u;
     // the route's activation fragments (written by the expand kernel)
-    fetch_fragments(smem, p.actfrag + (size_t)route * nkb * (kFragBlockBytes / 2), nkb, xbar, warp, lane);
+    fetch_fragments(smem, p.actfrag + (size_t)route * nkb * (kFragBlockBytes / 2), (uint32_t)nkb * kFragBlockBytes, xbar, warp, lane);
     const uint32_t e = __shfl_sync(0xffffffffu, p.ids ? __ldg(p.ids + route) : 0u, 0);
 
     const int ksplit = p.ksplit, group = warp / ksplit, s = warp - group * ksplit;

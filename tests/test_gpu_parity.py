@@ -259,6 +259,41 @@ def _sampled_full_size(moe, oracle, name, tokens, sample, seed, mode):
     assert err <= REL_L2, f"{name} rel-L2 {err}"
 
 
+@pytest.mark.parametrize("tokens", [2, 5, 12, 31], ids=["t2", "t5", "t12", "t31"])
+def test_gpt_oss_few_tokens_streamed(moe, oracle, tokens):
+    """At most four routes per expert on average: the streamed few-token kernels (up to eight routes
+    of an expert in the columns of one MMA), K not a multiple of 16 blocks, partial last group."""
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, 640, 384, 32, 4, synth.FMT_MXFP4, seed=41)
+    check_layer(moe, oracle, layer, tokens, seed=300 + tokens)
+
+
+def test_few_tokens_crowded_expert(moe, oracle):
+    """One expert gets a route from every token (13 routes: two groups, 8 + 5) while the average
+    stays small; the other routes are spread by the router."""
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, 320, 288, 32, 4, synth.FMT_MXFP4, seed=43)
+    layer.router_b[9] = 50.0
+    check_layer(moe, oracle, layer, 13, seed=77, residual="normal")
+
+
+@pytest.mark.parametrize("tokens", [2, 20])
+def test_nemotron_few_tokens_streamed(moe, oracle, tokens):
+    layer = synth.make_layer(synth.ARCH_NEMOTRON, 256, 192, 32, 6, synth.FMT_Q4_0, seed=44, shared_ffn=320,
+                             normalize=True, scale=2.5)
+    check_layer(moe, oracle, layer, tokens, seed=tokens)
+
+
+def test_few_tokens_tile_kernels(moe, oracle, monkeypatch):
+    """The same small batches through the tile kernels (the path they took before the streamed one)."""
+    monkeypatch.setenv("OCO_MOE_NO_BATCH", "1")
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, 640, 384, 32, 4, synth.FMT_MXFP4, seed=41)
+    for tokens in (2, 12):
+        check_layer(moe, oracle, layer, tokens, seed=300 + tokens)
+
+
+def test_gpt_oss_120b_decode_batch_full_size(moe, oracle):
+    _sampled_full_size(moe, oracle, "gpt-oss-120b", 64, 4, seed=0, mode=2)
+
+
 def test_gpt_oss_20b_decode_full_size(moe, oracle):
     _sampled_full_size(moe, oracle, "gpt-oss-20b", 1, 1, seed=0, mode=1)
 
