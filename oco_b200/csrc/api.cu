@@ -273,9 +273,9 @@ int launch_gemm_nt(oco_moe_plan* plan, const GemmParams& gp, const CUtensorMap* 
 }
 
 // Warps per unit of the single-token kernels: as many as keep every warp of the grid busy.
-int pick_ksplit(int units, int warps) {
-    for (int k : {10, 5, 4, 2})
-        if (kTokWarps % k == 0 && units * k <= warps) return k;
+int pick_ksplit(int units, int ctas, int warps_per_cta) {
+    for (int k : {10, 8, 5, 4, 2})
+        if (warps_per_cta % k == 0 && units * k <= ctas * warps_per_cta) return k;
     return 1;
 }
 
@@ -284,14 +284,14 @@ int pick_ksplit(int units, int warps) {
 template <int ARCH, int FMT>
 int launch_expand(oco_moe_plan* plan, DecodeExpandParams ep, cudaStream_t st) {
     const int grid = plan->sm_count;
-    if (token_smem_bytes(ep.H / 32, 2) > kMaxDynamicSmem) return fail(plan, OCO_UNSUPPORTED_SHAPE, "hidden %d too large for the single-token kernels", ep.H);
-    ep.ksplit = pick_ksplit(ep.K * (ep.F / (ARCH == OCO_ARCH_NEMOTRON ? 16 : 8)), grid * kTokWarps);
+    if (token_smem_bytes(FMT, ep.H / 32, 2) > kMaxDynamicSmem) return fail(plan, OCO_UNSUPPORTED_SHAPE, "hidden %d too large for the single-token kernels", ep.H);
+    ep.ksplit = pick_ksplit(ep.K * (ep.F / (ARCH == OCO_ARCH_NEMOTRON ? 16 : 8)), grid, tok_warps(FMT));
     static bool attr_set = false;
     if (!attr_set) {
         CK(allow_smem(decode_expand_kernel<ARCH, FMT, 2>));
         attr_set = true;
     }
-    decode_expand_kernel<ARCH, FMT, 2><<<grid, kTokThreads, token_smem_bytes(ep.H / 32, 2), st>>>(ep);
+    decode_expand_kernel<ARCH, FMT, 2><<<grid, tok_warps(FMT) * 32, token_smem_bytes(FMT, ep.H / 32, 2), st>>>(ep);
     plan->launches++;
     CK(cudaGetLastError());
     return OCO_OK;
@@ -300,15 +300,15 @@ int launch_expand(oco_moe_plan* plan, DecodeExpandParams ep, cudaStream_t st) {
 template <int FMT>
 int launch_down(oco_moe_plan* plan, DecodeDownParams dp, cudaStream_t st) {
     const int grid = plan->sm_count;
-    if (token_smem_bytes(dp.F / 32, 2) > kMaxDynamicSmem) return fail(plan, OCO_UNSUPPORTED_SHAPE, "expert width %d too large for the single-token kernels", dp.F);
+    if (token_smem_bytes(FMT, dp.F / 32, 2) > kMaxDynamicSmem) return fail(plan, OCO_UNSUPPORTED_SHAPE, "expert width %d too large for the single-token kernels", dp.F);
     if (dp.K > grid) return fail(plan, OCO_UNSUPPORTED_SHAPE, "more routes than multiprocessors");
-    dp.ksplit = pick_ksplit(dp.H / 16, (grid / dp.K) * kTokWarps);
+    dp.ksplit = pick_ksplit(dp.H / 16, grid / dp.K, tok_warps(FMT));
     static bool attr_set = false;
     if (!attr_set) {
         CK(allow_smem(decode_down_kernel<FMT, 2>));
         attr_set = true;
     }
-    decode_down_kernel<FMT, 2><<<grid, kTokThreads, token_smem_bytes(dp.F / 32, 2), st>>>(dp);
+    decode_down_kernel<FMT, 2><<<grid, tok_warps(FMT) * 32, token_smem_bytes(FMT, dp.F / 32, 2), st>>>(dp);
     plan->launches++;
     CK(cudaGetLastError());
     return OCO_OK;
@@ -341,9 +341,9 @@ int forward_single(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, cu
     // logits, then (in the CTA that finishes last) the token's experts and weights
     mark(plan, st, "router_logits");
     router_token_kernel<ARCH><<<(E + 7) / 8, 256, 0, st>>>(x, plan->w.router_w, plan->w.router_b, H, E, K, d.normalize,
-                                                          d.scale, ws.logits, ws.ids, ws.probs, ws.xfrag, ws.arrivals + H / 8);
+                                                          d.scale, ws.logits, ws.ids, ws.probs, ws.xfrag, FMT, ws.arrivals + H / 8);
     plan->launches++;
-    if constexpr (FMT == OCO_FMT_MXFP4 || FMT == OCO_FMT_Q4_0) {
+    {
         auto expand = [&](const uint8_t* gate_w, const uint8_t* up_w, const uint32_t* ids, int k, int f, float* act1,
                           __half* actfrag, uint32_t row_bytes) -> int {
             DecodeExpandParams ep{};
@@ -388,8 +388,6 @@ int forward_single(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, cu
         if (rc) return rc;
         mark(plan, st, "end");
         return OCO_OK;
-    } else {
-        return fail(plan, OCO_UNSUPPORTED_SHAPE, "no single-token kernels for this weight format");
     }
 }
 
@@ -422,8 +420,17 @@ int stage_route(oco_moe_plan* plan, const uint16_t* x, int rows, cudaStream_t st
             CK(allow_smem(router_stream_kernel<ARCH, 24>));
             stream_attr = true;
         }
-        router_stream_kernel<ARCH, 24><<<(rows + 7) / 8, 256, (size_t)4 * H * 4, st>>>(
+        // few tokens: split the experts over several CTAs per token group so that the grid fills the GPU
+        const int ctas = (rows + 7) / 8;
+        int splits = 1;
+        while (splits * 2 * ctas <= plan->sm_count && E / (splits * 2) >= 4) splits *= 2;
+        router_stream_kernel<ARCH, 24><<<dim3(ctas, splits), 256, (size_t)4 * H * 4, st>>>(
             x, rw, plan->w.router_b, rows, H, E, K, d.normalize, d.scale, ws.logits, ws.ids, ws.probs);
+        if (splits > 1) {
+            router_select_kernel<ARCH><<<rows, 32, 0, st>>>(ws.logits, ARCH == OCO_ARCH_NEMOTRON ? plan->w.router_b : nullptr, E, K,
+                                                           d.normalize, d.scale, ws.ids, ws.probs);
+            plan->launches++;
+        }
     } else {
         size_t rsmem = (size_t)H * 4 + (size_t)8 * H * 2;
         static bool router_attr = false;
@@ -588,7 +595,7 @@ template <int ARCH>
 int forward_family(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int rows, cudaStream_t st,
                    cudaEvent_t residual_ready = nullptr) {
     constexpr int FMT = Family<ARCH>::kFmt;
-    if (rows == 1 && (FMT == OCO_FMT_MXFP4 || FMT == OCO_FMT_Q4_0)) {
+    if (rows == 1) {
         if (residual_ready) CK(cudaStreamWaitEvent(st, residual_ready, 0));
         return forward_single<ARCH>(plan, x, residual, st);
     }

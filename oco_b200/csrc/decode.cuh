@@ -45,6 +45,15 @@ constexpr int kScalePitch = kChunkBlocks * 2 + 16;   // per-warp table of the st
 constexpr int kScaleBytes = 16 * kScalePitch;
 constexpr int kMiscBytes = 2048;                    // split sums (64 B a warp) | mbarriers from 1280 | give-up flag at 1984
 static_assert(kChunkBlocks % 16 == 0 && kTokWarps <= 20, "layout of the token kernels");
+// Q4_K keeps two floats per sub-block in its table, so fewer warps fit.
+constexpr int kKTablePitch = 144;                   // 16 sub-blocks x (scale, offset) + 16 bytes against bank conflicts
+constexpr int kKTableBytes = 16 * kKTablePitch;
+__host__ __device__ constexpr int tok_warps(int fmt) { return fmt == OCO_FMT_Q4_K ? 16 : kTokWarps; }
+__host__ __device__ constexpr int scale_table_bytes(int fmt) { return fmt == OCO_FMT_Q4_K ? kKTableBytes : kScaleBytes; }
+// B fragments of nkb blocks, followed for Q4_K by the per-block sums of the fragments' columns.
+__host__ __device__ constexpr uint32_t frag_region_bytes(int fmt, int nkb) {
+    return (uint32_t)(nkb * 128 + (fmt == OCO_FMT_Q4_K ? nkb * 8 : 0) + 15) & ~15u;
+}
 constexpr int kFragBlockBytes = 128;                // B fragments of one block: 2 columns x 4 lanes x 16 bytes
 
 // D = A * B with a zero accumulator, then D += A * B (fp32 accumulate, half operands).
@@ -127,6 +136,15 @@ struct Block32<OCO_FMT_Q4_0> {
     }
 };
 
+// Q4_K (144-byte super-blocks of 256 elements: f16 d, f16 dmin, 12 bytes of 6-bit scales and
+// minima, 128 code bytes; byte l of each 32-byte run holds elements l and l + 32 of a 64-element
+// group) is streamed as sub-blocks of 32 elements, 18 bytes on average; a stage holds two
+// super-blocks of each row. The codecs of the other formats do not apply.
+template <>
+struct Block32<OCO_FMT_Q4_K> {
+    static constexpr int kBytes = 18, kHeader = 0, kClasses = 1;
+};
+
 // One warp's pass over blocks [kb0, kb0 + nb) of 16 packed rows: rows 0..7 of span A and rows
 // 0..7 of span B (each span is 8 consecutive rows of `row_bytes` bytes in a GGUF tensor, at any
 // byte alignment). begin() starts the copies; run() multiplies. After run(), lane (g, tig) holds
@@ -153,8 +171,10 @@ struct RowStream {
     const uint8_t* spanA;
     const uint8_t* spanB;      // both advanced to the first block of the range
     uint32_t row_bytes, total_bytes;
-    int nchunks, nb;
+    int nchunks, nb, kb_first;
     // per lane
+    uint32_t mK = 0;           // Q4_K: misalignment of row lane / 2 (the row whose scales this lane unpacks)
+    uint32_t xsum = 0;         // Q4_K: byte offset in shared memory of the fragments' per-block sums
     uint32_t mA, mB;           // misalignment of row g of each span
     uint32_t alA[B::kClasses], alB[B::kClasses], shA[B::kClasses], shB[B::kClasses];
     int g, tig, lane;
@@ -175,13 +195,17 @@ struct RowStream {
 
     // a, b, rb, kb0, nblocks: the same in every lane.
     __device__ __forceinline__ void begin(const uint8_t* a, const uint8_t* b, uint32_t rb, int kb0, int nblocks) {
-        nb = nblocks; row_bytes = rb;
+        nb = nblocks; row_bytes = rb; kb_first = kb0;
         const size_t skip = (size_t)kb0 * B::kBytes;
         spanA = a + skip; spanB = b + skip;
         nchunks = (nb + kChunkBlocks - 1) / kChunkBlocks;
         total_bytes = (uint32_t)nb * B::kBytes;
         mA = (uint32_t)(uintptr_t)(spanA + (size_t)g * row_bytes) & 15u;
         mB = (uint32_t)(uintptr_t)(spanB + (size_t)g * row_bytes) & 15u;
+        if (FMT == OCO_FMT_Q4_K) {
+            const int rr = lane >> 1;
+            mK = (uint32_t)(uintptr_t)((rr < 8 ? spanA : spanB) + (size_t)(rr & 7) * row_bytes) & 15u;
+        }
 #pragma unroll
         for (int c = 0; c < B::kClasses; c++) {
             const uint32_t qa = (uint32_t)g * kRowPitch + mA + (uint32_t)(c * B::kBytes + B::kHeader) + 4u * tig;
@@ -217,6 +241,78 @@ struct RowStream {
     // The blocks of one stage. FULL: all 16 blocks are present. xa: byte offset in shared memory of
     // this lane's B fragment of the stage's first block. Only the lanes that feed a column in use
     // (g < ncols) load; the other columns multiply zeros.
+    // Q4_K: unpacks the scales of the stage: lane l takes row l / 2, super-block l & 1, and leaves
+    // per sub-block (d * scale, 1024 * d * scale + dmin * minimum): the codes enter the MMA as
+    // 1024 + q (a half built with two bit operations), and sum(x) of the sub-block takes both the
+    // 1024 and the minimum out again.
+    __device__ __forceinline__ void scales_k(uint32_t st, int nbc) {
+        const int rr = lane >> 1, sb = lane & 1;
+        if (sb * 8 < nbc) {
+            const uint32_t at = st + (uint32_t)rr * kRowPitch + mK + (uint32_t)sb * 144u;
+            const uint32_t a4 = at & ~3u, sh = (at & 3u) * 8u;
+            const uint32_t r0 = lds32(base, a4), r1 = lds32(base, a4 + 4), r2 = lds32(base, a4 + 8), r3 = lds32(base, a4 + 12),
+                           r4 = lds32(base, a4 + 16);
+            const uint32_t w0 = __funnelshift_r(r0, r1, sh), w1 = __funnelshift_r(r1, r2, sh), w2 = __funnelshift_r(r2, r3, sh),
+                           w3 = __funnelshift_r(r3, r4, sh);
+            const float d = f16_bits_to_f32((uint16_t)(w0 & 0xffffu)), dmin = f16_bits_to_f32((uint16_t)(w0 >> 16));
+            const uint32_t scl = w1 & 0x3f3f3f3fu, mnl = w2 & 0x3f3f3f3fu;
+            const uint32_t sch = (w3 & 0x0f0f0f0fu) | ((w1 >> 2) & 0x30303030u);
+            const uint32_t mnh = ((w3 >> 4) & 0x0f0f0f0fu) | ((w2 >> 2) & 0x30303030u);
+            float2* tab = reinterpret_cast<float2*>(const_cast<unsigned char*>(base) + stab + (uint32_t)rr * kKTablePitch + (uint32_t)sb * 64u);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float s1 = __fmul_rn(d, (float)((scl >> (8 * j)) & 0xffu));
+                tab[j] = make_float2(s1, __fmaf_rn(1024.0f, s1, __fmul_rn(dmin, (float)((mnl >> (8 * j)) & 0xffu))));
+                const float t1 = __fmul_rn(d, (float)((sch >> (8 * j)) & 0xffu));
+                tab[4 + j] = make_float2(t1, __fmaf_rn(1024.0f, t1, __fmul_rn(dmin, (float)((mnh >> (8 * j)) & 0xffu))));
+            }
+        }
+    }
+
+    // Q4_K: the sub-blocks of one stage (two super-blocks). xa: this lane's B fragment of the
+    // stage's first sub-block; xs: byte offset of the stage's first (sum hi, sum lo) pair.
+    template <bool FULL>
+    __device__ __forceinline__ void chunk_k(uint32_t st, uint32_t xa, uint32_t xs, int nbc, float (&sum)[4]) {
+        const uint32_t pA = st + (((uint32_t)g * kRowPitch + mA) & ~3u), sA = (mA & 3u) * 8u;
+        const uint32_t pB = st + (((uint32_t)(8 + g) * kRowPitch + mB) & ~3u), sB = (mB & 3u) * 8u;
+        auto nib = [](uint32_t w, int shift) { return ((w >> shift) & 0x000f000fu) | 0x64006400u; };   // two halves 1024 + q
+#pragma unroll
+        for (int sb = 0; sb < 2; sb++) {
+            if (FULL || sb * 8 < nbc) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint32_t off = (uint32_t)(sb * 144 + 16 + 32 * j) + 8u * tig;
+                    const uint32_t a0 = lds32(base, pA + off), a1 = lds32(base, pA + off + 4), a2 = lds32(base, pA + off + 8);
+                    const uint32_t b0 = lds32(base, pB + off), b1 = lds32(base, pB + off + 4), b2 = lds32(base, pB + off + 8);
+                    const uint32_t wa0 = __funnelshift_r(a0, a1, sA), wa1 = __funnelshift_r(a1, a2, sA);
+                    const uint32_t wb0 = __funnelshift_r(b0, b1, sB), wb1 = __funnelshift_r(b1, b2, sB);
+                    const int kb = sb * 8 + 2 * j;                 // low nibbles: sub-block kb, high nibbles: kb + 1
+                    uint4 xl = make_uint4(0u, 0u, 0u, 0u), xh = make_uint4(0u, 0u, 0u, 0u);
+                    if (g < ncols) {
+                        xl = lds128(base, xa + (uint32_t)kb * kFragBlock);
+                        xh = lds128(base, xa + (uint32_t)(kb + 1) * kFragBlock);
+                    }
+                    const float4 ta = *reinterpret_cast<const float4*>(base + stab + (uint32_t)g * kKTablePitch + kb * 8);
+                    const float4 tb = *reinterpret_cast<const float4*>(base + stab + (uint32_t)(8 + g) * kKTablePitch + kb * 8);
+                    const float4 xv = *reinterpret_cast<const float4*>(base + xs + kb * 8);   // (hi, lo) sums of kb and kb + 1
+                    float lo[4], hi[4];
+                    mma16816_first(lo, nib(wa0, 0), nib(wb0, 0), nib(wa0, 8), nib(wb0, 8), xl.x, xl.y);
+                    mma16816(lo, nib(wa1, 0), nib(wb1, 0), nib(wa1, 8), nib(wb1, 8), xl.z, xl.w);
+                    mma16816_first(hi, nib(wa0, 4), nib(wb0, 4), nib(wa0, 12), nib(wb0, 12), xh.x, xh.y);
+                    mma16816(hi, nib(wa1, 4), nib(wb1, 4), nib(wa1, 12), nib(wb1, 12), xh.z, xh.w);
+                    sum[0] = __fmaf_rn(lo[0], ta.x, __fmaf_rn(-ta.y, xv.x, sum[0]));
+                    sum[1] = __fmaf_rn(lo[1], ta.x, __fmaf_rn(-ta.y, xv.y, sum[1]));
+                    sum[2] = __fmaf_rn(lo[2], tb.x, __fmaf_rn(-tb.y, xv.x, sum[2]));
+                    sum[3] = __fmaf_rn(lo[3], tb.x, __fmaf_rn(-tb.y, xv.y, sum[3]));
+                    sum[0] = __fmaf_rn(hi[0], ta.z, __fmaf_rn(-ta.w, xv.z, sum[0]));
+                    sum[1] = __fmaf_rn(hi[1], ta.z, __fmaf_rn(-ta.w, xv.w, sum[1]));
+                    sum[2] = __fmaf_rn(hi[2], tb.z, __fmaf_rn(-tb.w, xv.z, sum[2]));
+                    sum[3] = __fmaf_rn(hi[3], tb.z, __fmaf_rn(-tb.w, xv.w, sum[3]));
+                }
+            }
+        }
+    }
+
     template <bool FULL>
     __device__ __forceinline__ void chunk(uint32_t st, uint32_t xa, int nbc, float (&sum)[4]) {
 #pragma unroll
@@ -275,29 +371,37 @@ struct RowStream {
             mbar_wait(bars + 8u * stage, (n / STAGES) & 1u, abort_flag, status);
             const uint32_t st = ring + stage * kStageBytes;
             const int nbc = min(kChunkBlocks, nb - c * kChunkBlocks);
-            {   // the stage's scales, 16 bits each: lane (g, tig) gathers a quarter of the blocks of its two rows
-                constexpr int kPer = kChunkBlocks / 4;
-                const uint32_t ra = st + (uint32_t)g * kRowPitch + mA + (uint32_t)(tig * kPer * B::kBytes);
-                const uint32_t rb = st + (uint32_t)(8 + g) * kRowPitch + mB + (uint32_t)(tig * kPer * B::kBytes);
-                unsigned char* tab = const_cast<unsigned char*>(base) + stab;
-#pragma unroll
-                for (int b = 0; b < kPer; b += 4) {
-                    uint32_t ha[4], hb[4];
-#pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        ha[u] = B::scale16(base, ra + (b + u) * B::kBytes);
-                        hb[u] = B::scale16(base, rb + (b + u) * B::kBytes);
-                    }
-                    *reinterpret_cast<uint2*>(tab + (uint32_t)g * kScalePitch + (tig * kPer + b) * 2) =
-                        make_uint2(ha[0] | (ha[1] << 16), ha[2] | (ha[3] << 16));
-                    *reinterpret_cast<uint2*>(tab + (uint32_t)(8 + g) * kScalePitch + (tig * kPer + b) * 2) =
-                        make_uint2(hb[0] | (hb[1] << 16), hb[2] | (hb[3] << 16));
-                }
-            }
-            __syncwarp();
             const uint32_t xa = xaddr + (uint32_t)(c * kChunkBlocks) * kFragBlock;
-            if (nbc == kChunkBlocks) chunk<true>(st, xa, nbc, sum);
-            else chunk<false>(st, xa, nbc, sum);
+            if constexpr (FMT == OCO_FMT_Q4_K) {
+                scales_k(st, nbc);
+                __syncwarp();
+                const uint32_t xs = xsum + (uint32_t)(kb_first + c * kChunkBlocks) * 8u;
+                if (nbc == kChunkBlocks) chunk_k<true>(st, xa, xs, nbc, sum);
+                else chunk_k<false>(st, xa, xs, nbc, sum);
+            } else {
+                {   // the stage's scales, 16 bits each: lane (g, tig) gathers a quarter of the blocks of its two rows
+                    constexpr int kPer = kChunkBlocks / 4;
+                    const uint32_t ra = st + (uint32_t)g * kRowPitch + mA + (uint32_t)(tig * kPer * B::kBytes);
+                    const uint32_t rb = st + (uint32_t)(8 + g) * kRowPitch + mB + (uint32_t)(tig * kPer * B::kBytes);
+                    unsigned char* tab = const_cast<unsigned char*>(base) + stab;
+#pragma unroll
+                    for (int b = 0; b < kPer; b += 4) {
+                        uint32_t ha[4], hb[4];
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            ha[u] = B::scale16(base, ra + (b + u) * B::kBytes);
+                            hb[u] = B::scale16(base, rb + (b + u) * B::kBytes);
+                        }
+                        *reinterpret_cast<uint2*>(tab + (uint32_t)g * kScalePitch + (tig * kPer + b) * 2) =
+                            make_uint2(ha[0] | (ha[1] << 16), ha[2] | (ha[3] << 16));
+                        *reinterpret_cast<uint2*>(tab + (uint32_t)(8 + g) * kScalePitch + (tig * kPer + b) * 2) =
+                            make_uint2(hb[0] | (hb[1] << 16), hb[2] | (hb[3] << 16));
+                    }
+                }
+                __syncwarp();
+                if (nbc == kChunkBlocks) chunk<true>(st, xa, nbc, sum);
+                else chunk<false>(st, xa, nbc, sum);
+            }
             __syncwarp();
         }
         seq += (uint32_t)nchunks;
@@ -317,21 +421,48 @@ __device__ __forceinline__ void fetch_fragments(SharedBase smem, const void* fra
     }
 }
 
+// Q4_K: (sum of the hi column, sum of the lo column) of every block of the fragments in shared memory,
+// written behind them; called by all threads of the CTA once the fragments have landed.
+__device__ __forceinline__ void fragment_sums(unsigned char* smem, int nkb, int tid, int threads) {
+    for (int kb = tid; kb < nkb; kb += threads) {
+        float s[2] = {0.f, 0.f};
+#pragma unroll
+        for (int col = 0; col < 2; col++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint4 v = *reinterpret_cast<const uint4*>(smem + ((size_t)(kb * 2 + col) * 4 + i) * 16);
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[q]));
+                    s[col] = __fadd_rn(s[col], __fadd_rn(f.x, f.y));
+                }
+            }
+        *reinterpret_cast<float2*>(smem + (size_t)nkb * kFragBlockBytes + (size_t)kb * 8) = make_float2(s[0], s[1]);
+    }
+}
+
 // Shared memory of the token kernels: B fragments | 2 KB (split sums, mbarriers, give-up flag) |
 // per-warp scale tables | rings.
-__host__ __device__ inline size_t token_smem_bytes(int nkb, int stages) {
-    return (size_t)nkb * kFragBlockBytes + kMiscBytes + (size_t)kTokWarps * kScaleBytes +
-           (size_t)kTokWarps * stages * kStageBytes + 16;
+__host__ __device__ inline size_t token_smem_bytes(int fmt, int nkb, int stages) {
+    return (size_t)frag_region_bytes(fmt, nkb) + kMiscBytes + (size_t)tok_warps(fmt) * scale_table_bytes(fmt) +
+           (size_t)tok_warps(fmt) * stages * kStageBytes + 16;
 }
 
 // Splits f32 values into hi + lo halves and scatters them into the B-fragment layout:
 // frag[((kb * 2 + col) * 4 + tig) * 4 + slot] is a half2 (element 4*tig+slot, element 4*tig+slot+16)
 // of block kb; hi goes to column 0, lo to column 1.
-__device__ __forceinline__ void frag_store(__half* frag, int k, float v) {
+// Q4_K delivers elements 8*tig .. 8*tig+7 of a sub-block to lane tig: slots 0, 1 hold (e0, e2), (e1, e3),
+// slots 2, 3 the same of e4..e7.
+__device__ __forceinline__ void frag_store(__half* frag, int k, float v, int fmt) {
     __half hi = __float2half_rn(v);
     float rem = nonfinite(v) ? 0.0f : v - __half2float(hi);
     __half lo = __float2half_rn(rem);
     int kb = k >> 5, j = k & 31, jj = j & 15, sel = j >> 4, tig = jj >> 2, slot = jj & 3;
+    if (fmt == OCO_FMT_Q4_K) {
+        const int r = j & 7;
+        tig = j >> 3; slot = (r >> 2) * 2 + (r & 1); sel = (r >> 1) & 1;
+    }
     size_t at = ((((size_t)kb * 2) * 4 + tig) * 4 + slot) * 2 + sel;
     frag[at] = hi;
     frag[at + (size_t)16 * 2] = lo;  // next column: 4 tig * 4 slots * 2 halves further
@@ -371,34 +502,42 @@ struct DecodeExpandParams {
 // (reference expert_expand, projections.metal:78-137; matvec_q4 + relu^2, vector.metal:155-228).
 // GATED: unit = 8 gate rows + 8 up rows (columns c0..c0+7); otherwise 16 up rows.
 template <int ARCH, int FMT, int STAGES>
-__global__ void __launch_bounds__(kTokThreads, 1) decode_expand_kernel(const DecodeExpandParams p) {
+__global__ void __launch_bounds__(tok_warps(FMT) * 32, 1) decode_expand_kernel(const DecodeExpandParams p) {
     constexpr bool GATED = ARCH != OCO_ARCH_NEMOTRON;
     constexpr int COLS = GATED ? 8 : 16;
+    constexpr int WARPS = tok_warps(FMT);
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, tig = lane & 3;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // known to the compiler as the same in all lanes
     const int nkb = p.H / 32;
-    const uint32_t part_off = (uint32_t)nkb * kFragBlockBytes;
+    const uint32_t part_off = frag_region_bytes(FMT, nkb);
     float* part = reinterpret_cast<float*>(smem + part_off);
     volatile uint32_t* give_up = reinterpret_cast<volatile uint32_t*>(part) + 496;
     const uint32_t xbar = smem_u32(smem) + part_off + 1920u;
-    const uint32_t stab = part_off + kMiscBytes + (uint32_t)warp * kScaleBytes;
-    const uint32_t ring = part_off + kMiscBytes + (uint32_t)kTokWarps * kScaleBytes + (uint32_t)warp * STAGES * kStageBytes;
+    const uint32_t stab = part_off + kMiscBytes + (uint32_t)warp * scale_table_bytes(FMT);
+    const uint32_t ring = part_off + kMiscBytes + (uint32_t)WARPS * scale_table_bytes(FMT) + (uint32_t)warp * STAGES * kStageBytes;
     if (tid == 0) *give_up = 0u;
     fetch_fragments(smem, p.xfrag, (uint32_t)nkb * kFragBlockBytes, xbar, warp, lane);
 
     const int ksplit = p.ksplit, group = warp / ksplit, s = warp - group * ksplit;
-    const int groups = kTokWarps / ksplit;
+    const int groups = WARPS / ksplit;
     const int col_blocks = p.F / COLS;
     const int units = p.K * col_blocks;
     const int nslots = gridDim.x * groups;
-    const int bps = (nkb + ksplit - 1) / ksplit;
+    int bps = (nkb + ksplit - 1) / ksplit;
+    if (FMT == OCO_FMT_Q4_K) bps = (bps + 7) & ~7;          // whole super-blocks
     const int kb0 = s * bps, nb = max(0, min(bps, nkb - kb0));
     const uint32_t xlane = (uint32_t)kb0 * kFragBlockBytes + (uint32_t)(((g & 1) * 4 + tig) * 16);
 
     RowStream<FMT, STAGES> rs;
     rs.init(smem, ring, stab, part_off + 1280u + (uint32_t)warp * (STAGES * 8), give_up, p.status, lane);
+    rs.xsum = (uint32_t)nkb * kFragBlockBytes;
     __syncthreads();          // the mbarriers exist
+    if (FMT == OCO_FMT_Q4_K) {
+        mbar_wait(xbar, 0u, give_up, p.status);
+        fragment_sums(smem, nkb, tid, WARPS * 32);
+        __syncthreads();
+    }
     bool fetched = false;
     for (int unit = blockIdx.x * groups + group; unit < units; unit += nslots) {
         const int r = unit / col_blocks, c0 = (unit - r * col_blocks) * COLS;
@@ -419,7 +558,7 @@ __global__ void __launch_bounds__(kTokThreads, 1) decode_expand_kernel(const Dec
         if (s == 0 && tig == 0) {
             auto put = [&](int col, float v) {
                 p.act[(size_t)r * p.F + col] = v;
-                frag_store(p.actfrag + (size_t)r * (p.F / 32) * (kFragBlockBytes / 2), col, v);
+                frag_store(p.actfrag + (size_t)r * (p.F / 32) * (kFragBlockBytes / 2), col, v, FMT);
             };
             if (ARCH == OCO_ARCH_GPT_OSS) {
                 float gate = __fadd_rn(r0, bf16_round(b0));
@@ -461,35 +600,43 @@ struct DecodeDownParams {
 // (reference matvec_mxfp4, projections.metal:140-182; matvec_q4, vector.metal:155-228).
 // CTA c serves route c % K, so a CTA needs one route's fragments only.
 template <int FMT, int STAGES>
-__global__ void __launch_bounds__(kTokThreads, 1) decode_down_kernel(const DecodeDownParams p) {
+__global__ void __launch_bounds__(tok_warps(FMT) * 32, 1) decode_down_kernel(const DecodeDownParams p) {
+    constexpr int WARPS = tok_warps(FMT);
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, tig = lane & 3;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const int nkb = p.F / 32;
     const int route = blockIdx.x % p.K, idx = blockIdx.x / p.K, ctas = gridDim.x / p.K;
     if (idx >= ctas) return;
-    const uint32_t part_off = (uint32_t)nkb * kFragBlockBytes;
+    const uint32_t part_off = frag_region_bytes(FMT, nkb);
     float* part = reinterpret_cast<float*>(smem + part_off);
     volatile uint32_t* give_up = reinterpret_cast<volatile uint32_t*>(part) + 496;
     const uint32_t xbar = smem_u32(smem) + part_off + 1920u;
-    const uint32_t stab = part_off + kMiscBytes + (uint32_t)warp * kScaleBytes;
-    const uint32_t ring = part_off + kMiscBytes + (uint32_t)kTokWarps * kScaleBytes + (uint32_t)warp * STAGES * kStageBytes;
+    const uint32_t stab = part_off + kMiscBytes + (uint32_t)warp * scale_table_bytes(FMT);
+    const uint32_t ring = part_off + kMiscBytes + (uint32_t)WARPS * scale_table_bytes(FMT) + (uint32_t)warp * STAGES * kStageBytes;
     if (tid == 0) *give_up = 0u;
     // the route's activation fragments (written by the expand kernel)
     fetch_fragments(smem, p.actfrag + (size_t)route * nkb * (kFragBlockBytes / 2), (uint32_t)nkb * kFragBlockBytes, xbar, warp, lane);
     const uint32_t e = __shfl_sync(0xffffffffu, p.ids ? __ldg(p.ids + route) : 0u, 0);
 
     const int ksplit = p.ksplit, group = warp / ksplit, s = warp - group * ksplit;
-    const int groups = kTokWarps / ksplit;
+    const int groups = WARPS / ksplit;
     const int row_blocks = p.H / 16;
     const int nslots = ctas * groups;
-    const int bps = (nkb + ksplit - 1) / ksplit;
+    int bps = (nkb + ksplit - 1) / ksplit;
+    if (FMT == OCO_FMT_Q4_K) bps = (bps + 7) & ~7;
     const int kb0 = s * bps, nb = max(0, min(bps, nkb - kb0));
     const uint32_t xlane = (uint32_t)kb0 * kFragBlockBytes + (uint32_t)(((g & 1) * 4 + tig) * 16);
 
     RowStream<FMT, STAGES> rs;
     rs.init(smem, ring, stab, part_off + 1280u + (uint32_t)warp * (STAGES * 8), give_up, p.status, lane);
+    rs.xsum = (uint32_t)nkb * kFragBlockBytes;
     __syncthreads();          // the mbarriers exist
+    if (FMT == OCO_FMT_Q4_K) {
+        mbar_wait(xbar, 0u, give_up, p.status);
+        fragment_sums(smem, nkb, tid, WARPS * 32);
+        __syncthreads();
+    }
     bool fetched = false;
     for (int rb = idx * groups + group; rb < row_blocks; rb += nslots) {
         const int d0 = rb * 16;
@@ -543,7 +690,7 @@ __global__ void __launch_bounds__(256) router_token_kernel(const uint16_t* __res
                                                            const float* __restrict__ bias, int H, int E, int K,
                                                            int normalize, float scale, float* __restrict__ logits,
                                                            uint32_t* __restrict__ ids, float* __restrict__ probs,
-                                                           __half* __restrict__ xfrag, uint32_t* __restrict__ arrival) {
+                                                           __half* __restrict__ xfrag, int fmt, uint32_t* __restrict__ arrival) {
     __shared__ int is_last;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int e = blockIdx.x * 8 + warp;
@@ -553,7 +700,7 @@ __global__ void __launch_bounds__(256) router_token_kernel(const uint16_t* __res
         if (ARCH == OCO_ARCH_GPT_OSS) s = __fadd_rn(s, bf16_round(bias[e]));
         if (lane == 0) logits[e] = s;
     }
-    for (int k = blockIdx.x * 256 + threadIdx.x; k < H; k += gridDim.x * 256) frag_store(xfrag, k, bf16_bits_to_f32(x[k]));
+    for (int k = blockIdx.x * 256 + threadIdx.x; k < H; k += gridDim.x * 256) frag_store(xfrag, k, bf16_bits_to_f32(x[k]), fmt);
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {

@@ -286,6 +286,9 @@ __global__ void __launch_bounds__(256) router_batched_kernel(const uint16_t* __r
 // the router rows stream through a four-deep shared-memory ring filled with cp.async, one
 // __syncthreads per expert. `w` holds the weights as they enter the FMAs (already rounded for
 // gpt-oss). Same canonical order as canonical_logit. Dynamic shared memory: 4 * H floats.
+// grid (ceil(T / 8), splits): with one split a CTA goes through all experts and selects; with
+// more (few tokens, so that the grid still fills the GPU) CTA y takes experts [y * E / splits,
+// (y + 1) * E / splits), writes their logits and leaves the selection to router_select_kernel.
 template <int ARCH, int ITERS>
 __global__ void __launch_bounds__(256) router_stream_kernel(const uint16_t* __restrict__ x,
                                                             const float* __restrict__ w,
@@ -310,17 +313,18 @@ __global__ void __launch_bounds__(256) router_stream_kernel(const uint16_t* __re
         }
     }
     const int chunks = H / 4;                                       // 16-byte chunks per router row
+    const int e_begin = (int)(((long long)blockIdx.y * E) / gridDim.y), e_end = (int)(((long long)(blockIdx.y + 1) * E) / gridDim.y);
     auto issue = [&](int e) {
-        if (e < E) {
+        if (e < e_end) {
             const float* src = w + (size_t)e * H;
             const uint32_t dst = smem_u32(ring + (size_t)(e & 3) * H);
             for (int c = threadIdx.x; c < chunks; c += 256) cp_async16(dst + 16u * c, src + 4 * c);
         }
         cp_async_commit();
     };
-    issue(0); issue(1); issue(2);
+    issue(e_begin); issue(e_begin + 1); issue(e_begin + 2);
     float v[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int e = 0; e < E; e++) {
+    for (int e = e_begin; e < e_end; e++) {
         cp_async_wait<2>();
         __syncthreads();            // row e has landed for everyone; row e - 1 is no longer read
         issue(e + 3);               // into the buffer row e - 1 used
@@ -347,9 +351,12 @@ __global__ void __launch_bounds__(256) router_stream_kernel(const uint16_t* __re
     if (!live) return;
     if (logits) {
 #pragma unroll
-        for (int j = 0; j < 4; j++)
-            if (lane + 32 * j < E) logits[(size_t)t * E + lane + 32 * j] = v[j];
+        for (int j = 0; j < 4; j++) {
+            const int e = lane + 32 * j;
+            if (e >= e_begin && e < e_end) logits[(size_t)t * E + e] = v[j];
+        }
     }
+    if (gridDim.y > 1) return;
     uint32_t id[kMaxTopK];
     float pr[kMaxTopK];
     select_experts<ARCH>(v, E, K, ARCH == OCO_ARCH_NEMOTRON ? bias : nullptr, normalize, scale, lane, id, pr);

@@ -240,7 +240,7 @@ class Routing:
                    prob=self._read(v.probs, R, np.float32).reshape(self.rows, d.top_k),
                    logits=self._read(v.logits, self.rows * d.experts, np.float32).reshape(self.rows, d.experts),
                    y=self._read(v.y, R * d.hidden, np.uint16).reshape(R, d.hidden))
-        if self.rows > 1 or d.arch == synth.ARCH_QWEN:
+        if self.rows > 1:
             out["offsets"] = self._read(v.offsets, d.experts + 1, np.uint32)
             out["row_of_route"] = self._read(v.row_of_route, R, np.uint32)
             out["route_of_row"] = self._read(v.route_of_row, R, np.uint32)

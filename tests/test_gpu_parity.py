@@ -213,8 +213,7 @@ def test_sigmoid_router_reference_case(moe, oracle):
 @pytest.mark.parametrize("tokens", [1, 24, 200])
 def test_qwen_small(moe, oracle, tokens):
     layer = synth.make_layer(synth.ARCH_QWEN, 512, 256, 128, 8, synth.FMT_Q4_K, seed=13)
-    # single rows take the tiled kernels for this family, so the oracle runs its tile numerics
-    check_layer(moe, oracle, layer, tokens, seed=tokens, mode=2)
+    check_layer(moe, oracle, layer, tokens, seed=tokens)
 
 
 def test_host_buffer_entry_point(moe, oracle):
@@ -292,6 +291,22 @@ def test_few_tokens_tile_kernels(moe, oracle, monkeypatch):
 
 def test_gpt_oss_120b_decode_batch_full_size(moe, oracle):
     _sampled_full_size(moe, oracle, "gpt-oss-120b", 64, 4, seed=0, mode=2)
+
+
+def test_qwen3_30b_decode_full_size(moe, oracle):
+    _sampled_full_size(moe, oracle, "qwen3-30b-a3b", 1, 1, seed=0, mode=1)
+
+
+def test_nemotron_h_decode_full_size(moe, oracle):
+    _sampled_full_size(moe, oracle, "nemotron-h", 1, 1, seed=0, mode=1)
+
+
+@pytest.mark.parametrize("hidden,ffn", [(256, 256), (768, 512), (2048, 768)])
+def test_qwen_single_token_shapes(moe, oracle, hidden, ffn):
+    """Q4_K single-token kernels: one and several super-blocks per row, splits that end inside a row."""
+    layer = synth.make_layer(synth.ARCH_QWEN, hidden, ffn, 16, 4, synth.FMT_Q4_K, seed=51)
+    check_layer(moe, oracle, layer, 1, seed=hidden, residual="normal")
+    check_layer(moe, oracle, layer, 1, seed=hidden + 1, misalign=3)
 
 
 def test_gpt_oss_20b_decode_full_size(moe, oracle):
