@@ -217,7 +217,7 @@ def run_expert_parallel(args, torch, dist, world, rank, local):
         a.record(stream)
         launches = 0
         for _ in range(n):
-            ep.forward(x, res, backend, E, exchange=exchange)
+            ep.forward(x, res, backend, E, exchange=exchange, uniform=True)
             launches += be.launches()
         b.record(stream)
         torch.cuda.synchronize(); dist.barrier()
@@ -226,7 +226,7 @@ def run_expert_parallel(args, torch, dist, world, rank, local):
         return float(t.item()), launches
 
     for _ in range(max(3, args.warmup)):
-        ep.forward(x, res, backend, E)
+        ep.forward(x, res, backend, E, uniform=True)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start(); time.sleep(0.3)
@@ -241,7 +241,7 @@ def run_expert_parallel(args, torch, dist, world, rank, local):
     tm, acc = {}, {}
     be.expert_plan.set_profiling(True)
     for _ in range(min(5, args.steps)):
-        ep.forward(x, res, backend, E, timings=tm)
+        ep.forward(x, res, backend, E, timings=tm, uniform=True)
         for k, v in tm.items():
             acc.setdefault(k, []).append(v)
         for k, v in be.expert_plan.phase_times().items():
@@ -255,7 +255,7 @@ def run_expert_parallel(args, torch, dist, world, rank, local):
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         x.copy_(hx, non_blocking=True); res.copy_(hres, non_blocking=True)
-        ep.forward(x, res, backend, E)
+        ep.forward(x, res, backend, E, uniform=True)
         hres.copy_(res, non_blocking=True)
         torch.cuda.synchronize()
     t = torch.tensor([1e3 * (time.perf_counter() - t0) / e2e_steps], device="cuda", dtype=torch.float64)
@@ -459,7 +459,8 @@ def main():
     # ---- roofline of the dominant kernel ---------------------------------------------------------
     peaks = measured_peaks()
     phases = {k: float(np.mean(v)) for k, v in phase_acc.items()}
-    dominant = max(phases, key=phases.get) if phases else None
+    expert_phases = {k: v for k, v in phases.items() if k in ("expand", "down", "down_combine", "up_rows", "down_rows", "up_tiles", "down_tiles")}
+    dominant = max(expert_phases, key=expert_phases.get) if expert_phases else None
     roofline = None
     if dominant:
         dur_s = phases[dominant] / 1e3

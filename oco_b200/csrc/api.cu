@@ -75,6 +75,8 @@ struct oco_moe_plan {
     cudaStream_t copy_stream = nullptr;   // oco_moe_forward_host: the residual rows' own stream
     cudaEvent_t ev_fork = nullptr, ev_residual = nullptr;
     bool no_batch_path = false;  // OCO_MOE_NO_BATCH=1: few tokens take the tile kernels too
+    int batch_max_avg = 16;      // routes per expert (on average) up to which the streamed few-token kernels run
+                                 // (measured: they win up to 16-32 at the gpt-oss shapes; OCO_MOE_BATCH_MAX_AVG overrides)
     bool narrow_tiles = false;   // OCO_MOE_NARROW_TILES=1: keep the generic tile kernel for 256-route tiles too
     bool profiling = false;
     int n_marks = 0;
@@ -155,7 +157,7 @@ Workspace carve(const oco_moe_desc& d, int max_rows, unsigned char* base) {
     w.actfrag = (__half*)take(P * (F / 32) * 128 * 2);
     w.xfrag = (__half*)take((H / 32) * 128);
     {
-        const size_t groups = batch_max_groups(R < 4 * E ? R : 4 * E, E);
+        const size_t groups = batch_max_groups(R < 64 * E ? R : 64 * E, E);
         w.bfrag_in = (__half*)take(groups * (H / 32) * kBatchFragBlock);
         w.bfrag_out = (__half*)take(groups * (F / 32) * kBatchFragBlock);
     }
@@ -281,6 +283,19 @@ int pick_ksplit(int units, int ctas, int warps_per_cta) {
 
 // Ring depth of the single-token kernels by what fits in shared memory (0: nothing fits).
 
+// Launches a single-token kernel with programmatic stream serialization: it may start (and set up
+// its shared memory and barriers) while its predecessor still runs, and waits for it inside.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <int ARCH, int FMT>
 int launch_expand(oco_moe_plan* plan, DecodeExpandParams ep, cudaStream_t st) {
     const int grid = plan->sm_count;
@@ -291,7 +306,7 @@ int launch_expand(oco_moe_plan* plan, DecodeExpandParams ep, cudaStream_t st) {
         CK(allow_smem(decode_expand_kernel<ARCH, FMT, 2>));
         attr_set = true;
     }
-    decode_expand_kernel<ARCH, FMT, 2><<<grid, tok_warps(FMT) * 32, token_smem_bytes(FMT, ep.H / 32, 2), st>>>(ep);
+    CK(launch_dependent(decode_expand_kernel<ARCH, FMT, 2>, dim3(grid), dim3(tok_warps(FMT) * 32), token_smem_bytes(FMT, ep.H / 32, 2), st, ep));
     plan->launches++;
     CK(cudaGetLastError());
     return OCO_OK;
@@ -308,7 +323,7 @@ int launch_down(oco_moe_plan* plan, DecodeDownParams dp, cudaStream_t st) {
         CK(allow_smem(decode_down_kernel<FMT, 2>));
         attr_set = true;
     }
-    decode_down_kernel<FMT, 2><<<grid, tok_warps(FMT) * 32, token_smem_bytes(FMT, dp.F / 32, 2), st>>>(dp);
+    CK(launch_dependent(decode_down_kernel<FMT, 2>, dim3(grid), dim3(tok_warps(FMT) * 32), token_smem_bytes(FMT, dp.F / 32, 2), st, dp));
     plan->launches++;
     CK(cudaGetLastError());
     return OCO_OK;
@@ -340,8 +355,8 @@ int forward_single(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, cu
     const int H = d.hidden, F = d.ffn, E = d.experts, K = d.top_k;
     // logits, then (in the CTA that finishes last) the token's experts and weights
     mark(plan, st, "router_logits");
-    router_token_kernel<ARCH><<<(E + 7) / 8, 256, 0, st>>>(x, plan->w.router_w, plan->w.router_b, H, E, K, d.normalize,
-                                                          d.scale, ws.logits, ws.ids, ws.probs, ws.xfrag, FMT, ws.arrivals + H / 8);
+    CK(launch_dependent(router_token_kernel<ARCH>, dim3((E + 7) / 8), dim3(256), 0, st, x, plan->w.router_w, plan->w.router_b, H, E, K,
+                        d.normalize, d.scale, ws.logits, ws.ids, ws.probs, ws.xfrag, (int)FMT, ws.arrivals + H / 8));
     plan->launches++;
     {
         auto expand = [&](const uint8_t* gate_w, const uint8_t* up_w, const uint32_t* ids, int k, int f, float* act1,
@@ -457,7 +472,7 @@ int stage_experts(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, in
     const oco_moe_desc& d = plan->d;
     Workspace& ws = plan->ws;
     const int H = d.hidden, F = d.ffn, E = d.experts;
-    if (FMT != OCO_FMT_Q4_K && R <= 4 * E && !plan->no_batch_path) {
+    if (FMT != OCO_FMT_Q4_K && R <= plan->batch_max_avg * E && !plan->no_batch_path) {
         // A few routes per expert: memory-bound, streamed with up to eight routes per MMA (batch.cuh).
         if constexpr (FMT != OCO_FMT_Q4_K) {
             if (batch_smem_bytes(H / 32) > kMaxDynamicSmem || batch_smem_bytes(F / 32) > kMaxDynamicSmem)
@@ -648,6 +663,7 @@ int oco_moe_plan_create(const oco_moe_desc* desc, oco_moe_plan** out) {
     }
     { const char* e = getenv("OCO_MOE_NARROW_TILES"); plan->narrow_tiles = e && e[0] == '1'; }
     { const char* e = getenv("OCO_MOE_NO_BATCH"); plan->no_batch_path = e && e[0] == '1'; }
+    { const char* e = getenv("OCO_MOE_BATCH_MAX_AVG"); if (e && atoi(e) > 0) plan->batch_max_avg = atoi(e) < 64 ? atoi(e) : 64; }
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) == cudaSuccess &&
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0)

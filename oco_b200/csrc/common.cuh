@@ -155,6 +155,13 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may
+// start while its predecessor in the stream still runs; pdl_wait() returns when the predecessor has
+// completed and its writes are visible. pdl_launch_dependents() lets the successor start launching.
+// Both do nothing in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -516,8 +516,8 @@ __global__ void __launch_bounds__(tok_warps(FMT) * 32, 1) decode_expand_kernel(c
     const uint32_t xbar = smem_u32(smem) + part_off + 1920u;
     const uint32_t stab = part_off + kMiscBytes + (uint32_t)warp * scale_table_bytes(FMT);
     const uint32_t ring = part_off + kMiscBytes + (uint32_t)WARPS * scale_table_bytes(FMT) + (uint32_t)warp * STAGES * kStageBytes;
+    pdl_launch_dependents();
     if (tid == 0) *give_up = 0u;
-    fetch_fragments(smem, p.xfrag, (uint32_t)nkb * kFragBlockBytes, xbar, warp, lane);
 
     const int ksplit = p.ksplit, group = warp / ksplit, s = warp - group * ksplit;
     const int groups = WARPS / ksplit;
@@ -532,6 +532,8 @@ __global__ void __launch_bounds__(tok_warps(FMT) * 32, 1) decode_expand_kernel(c
     RowStream<FMT, STAGES> rs;
     rs.init(smem, ring, stab, part_off + 1280u + (uint32_t)warp * (STAGES * 8), give_up, p.status, lane);
     rs.xsum = (uint32_t)nkb * kFragBlockBytes;
+    pdl_wait();               // the router kernel's ids and fragments are complete
+    fetch_fragments(smem, p.xfrag, (uint32_t)nkb * kFragBlockBytes, xbar, warp, lane);
     __syncthreads();          // the mbarriers exist
     if (FMT == OCO_FMT_Q4_K) {
         mbar_wait(xbar, 0u, give_up, p.status);
@@ -614,10 +616,8 @@ __global__ void __launch_bounds__(tok_warps(FMT) * 32, 1) decode_down_kernel(con
     const uint32_t xbar = smem_u32(smem) + part_off + 1920u;
     const uint32_t stab = part_off + kMiscBytes + (uint32_t)warp * scale_table_bytes(FMT);
     const uint32_t ring = part_off + kMiscBytes + (uint32_t)WARPS * scale_table_bytes(FMT) + (uint32_t)warp * STAGES * kStageBytes;
+    pdl_launch_dependents();
     if (tid == 0) *give_up = 0u;
-    // the route's activation fragments (written by the expand kernel)
-    fetch_fragments(smem, p.actfrag + (size_t)route * nkb * (kFragBlockBytes / 2), (uint32_t)nkb * kFragBlockBytes, xbar, warp, lane);
-    const uint32_t e = __shfl_sync(0xffffffffu, p.ids ? __ldg(p.ids + route) : 0u, 0);
 
     const int ksplit = p.ksplit, group = warp / ksplit, s = warp - group * ksplit;
     const int groups = WARPS / ksplit;
@@ -631,6 +631,10 @@ __global__ void __launch_bounds__(tok_warps(FMT) * 32, 1) decode_down_kernel(con
     RowStream<FMT, STAGES> rs;
     rs.init(smem, ring, stab, part_off + 1280u + (uint32_t)warp * (STAGES * 8), give_up, p.status, lane);
     rs.xsum = (uint32_t)nkb * kFragBlockBytes;
+    pdl_wait();               // the expand kernel's fragments are complete
+    // the route's activation fragments (written by the expand kernel)
+    fetch_fragments(smem, p.actfrag + (size_t)route * nkb * (kFragBlockBytes / 2), (uint32_t)nkb * kFragBlockBytes, xbar, warp, lane);
+    const uint32_t e = __shfl_sync(0xffffffffu, p.ids ? __ldg(p.ids + route) : 0u, 0);
     __syncthreads();          // the mbarriers exist
     if (FMT == OCO_FMT_Q4_K) {
         mbar_wait(xbar, 0u, give_up, p.status);
@@ -694,6 +698,8 @@ __global__ void __launch_bounds__(256) router_token_kernel(const uint16_t* __res
     __shared__ int is_last;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int e = blockIdx.x * 8 + warp;
+    pdl_launch_dependents();  // the expand kernel may set itself up beside this small grid
+    pdl_wait();               // the previous step no longer reads what this kernel writes
     if (e < E) {
         float s = H <= 128 * 24 ? canonical_logit_prefetch<ARCH == OCO_ARCH_GPT_OSS, 24>(x, w + (size_t)e * H, H, lane)
                                 : canonical_logit<ARCH == OCO_ARCH_GPT_OSS>(x, w + (size_t)e * H, H, lane);

@@ -53,24 +53,40 @@ class Backend:
 
 def forward(x: torch.Tensor, residual: torch.Tensor, backend: Backend, experts_total: int,
             group: Optional[dist.ProcessGroup] = None, timings: Optional[dict] = None,
-            exchange: Optional[Callable] = None) -> None:
+            exchange: Optional[Callable] = None, uniform: bool = False) -> None:
     """One expert-parallel MoE layer over this rank's tokens. x, residual: int16 [T, H].
     `exchange` has the signature of `dist.all_to_all_single` and replaces it when given (a
-    benchmark passes a local stand-in to find how much of the step the exchange costs)."""
+    benchmark passes a local stand-in to find how much of the step the exchange costs).
+    `uniform`: every rank holds the same number of tokens; the ranks then gather each other's
+    expert ids once (a few KB) instead of exchanging counts and ids per destination."""
     a2a = exchange or dist.all_to_all_single
     world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
     epr = experts_total // world
     T, H = x.shape
     ids, probs = backend.route(x)
     K = ids.shape[1]
     order, send_counts, local_ids = dispatch_layout(ids, world, epr)
     send_rows = x.index_select(0, order // K)
-    # counts first, then the rows and their expert ids
-    recv_counts = torch.empty_like(send_counts)
-    a2a(recv_counts, send_counts, group=group)
-    send_split = send_counts.tolist()
-    recv_split = recv_counts.tolist()
-    R = int(sum(recv_split))
+    if uniform and exchange is None:
+        ids_flat = torch.empty(world * T * K, dtype=torch.int32, device=x.device)
+        dist.all_gather_into_tensor(ids_flat, ids.reshape(-1).to(torch.int32).contiguous(), group=group)
+        ids_all = ids_flat.view(world, T * K)
+        mine = (ids_all // epr) == rank                      # [world, T*K]: routes each rank sends here
+        recv_counts = mine.sum(dim=1)
+        recv_ids = (ids_all[mine] - rank * epr).to(torch.int32)   # row-major: by source rank, then route order
+        send_split = send_counts.tolist()
+        recv_split = recv_counts.tolist()
+        R = int(sum(recv_split))
+    else:
+        # counts first, then the rows and their expert ids
+        recv_counts = torch.empty_like(send_counts)
+        a2a(recv_counts, send_counts, group=group)
+        send_split = send_counts.tolist()
+        recv_split = recv_counts.tolist()
+        R = int(sum(recv_split))
+        recv_ids = torch.empty(R, dtype=torch.int32, device=x.device)
+        a2a(recv_ids, local_ids.to(torch.int32), recv_split, send_split, group=group)
     ev = None
     if timings is not None and x.is_cuda:
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
@@ -78,8 +94,6 @@ def forward(x: torch.Tensor, residual: torch.Tensor, backend: Backend, experts_t
     recv_rows = torch.empty((R, H), dtype=x.dtype, device=x.device)
     # rows travel as bytes: every backend moves uint8, not every one moves 16-bit integers
     a2a(recv_rows.view(torch.uint8), send_rows.contiguous().view(torch.uint8), recv_split, send_split, group=group)
-    recv_ids = torch.empty(R, dtype=torch.int32, device=x.device)
-    a2a(recv_ids, local_ids.to(torch.int32), recv_split, send_split, group=group)
     if ev:
         ev[1].record()
     y_recv = backend.experts(recv_rows, recv_ids)

@@ -28,8 +28,11 @@ def main():
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     rank, world = dist.get_rank(), dist.get_world_size()
+    # tokens divisible by the world size also run the protocol for equal shares (ids gathered once)
     cases = [(synth.ARCH_GPT_OSS, 16, 4, 320, 288, 203, synth.FMT_MXFP4),
+             (synth.ARCH_GPT_OSS, 16, 4, 320, 288, 200, synth.FMT_MXFP4),
              (synth.ARCH_GPT_OSS, 8, 2, 64, 96, 11, synth.FMT_MXFP4),
+             (synth.ARCH_GPT_OSS, 32, 4, 320, 288, 16, synth.FMT_MXFP4),
              (synth.ARCH_NEMOTRON, 16, 6, 256, 192, 150, synth.FMT_Q4_0)]
     for n, (arch, E, K, H, F, T, fmt) in enumerate(cases):
         layer = synth.make_layer(arch, H, F, E, K, fmt, seed=31 + n)
@@ -40,7 +43,7 @@ def main():
         be = ep.CudaBackend(layer, rank, world, max_rows=T)
         x = torch.from_numpy(x_all[lo:hi].view(np.int16).copy()).cuda()
         res = torch.from_numpy(res_all[lo:hi].view(np.int16).copy()).cuda()
-        ep.forward(x, res, be.backend(), E)
+        ep.forward(x, res, be.backend(), E, uniform=T % world == 0)
         torch.cuda.synchronize()
         be.router_plan.poll(); be.expert_plan.poll()
         ref = oracle.moe_forward(layer, x_all, res_all, mode=2)

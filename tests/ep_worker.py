@@ -17,7 +17,15 @@ from oco_b200 import ep, synth  # noqa: E402
 def main():
     dist.init_process_group("gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
-    E, K, H, F, T = 8, 2, 64, 96, 11          # 11 tokens: ranks hold uneven shares
+    for T, uniform in ((11, False), (12, True)):     # 11 tokens: ranks hold uneven shares; 12: equal shares
+        run_case(rank, world, T, uniform)
+    dist.barrier()
+    dist.destroy_process_group()
+    print(f"rank {rank} ok")
+
+
+def run_case(rank, world, T, uniform):
+    E, K, H, F = 8, 2, 64, 96
     layer = synth.make_layer(synth.ARCH_GPT_OSS, H, F, E, K, synth.FMT_MXFP4, seed=77)
     x_all, res_all = synth.make_tokens(H, T, 5, "normal")
     bounds = np.linspace(0, T, world + 1).astype(int)
@@ -46,7 +54,7 @@ def main():
 
     x = torch.from_numpy(x_all[lo:hi].view(np.int16).copy())
     res = torch.from_numpy(res_all[lo:hi].view(np.int16).copy())
-    ep.forward(x, res, ep.Backend(route, experts, combine), E)
+    ep.forward(x, res, ep.Backend(route, experts, combine), E, uniform=uniform)
     ref = oracle.moe_forward(layer, x_all, res_all, mode=2)
     got = res.numpy().view(np.uint16)
     assert np.array_equal(got, ref.out[lo:hi]), f"rank {rank}: expert-parallel result differs from the single-process oracle"
@@ -59,9 +67,6 @@ def main():
         sel = order[dest == g]
         assert torch.all(sel[1:] > sel[:-1])
     assert counts.sum().item() == ids.numel() and torch.all(local < epr)
-    dist.barrier()
-    dist.destroy_process_group()
-    print(f"rank {rank} ok")
 
 
 if __name__ == "__main__":

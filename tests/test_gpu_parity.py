@@ -114,6 +114,13 @@ def test_gpt_oss_wide_tiles(moe, oracle, hidden, ffn, tokens):
     check_layer(moe, oracle, layer, tokens, seed=tokens)
 
 
+@pytest.mark.parametrize("tokens", [100, 250], ids=["nt64", "nt128"])
+def test_gpt_oss_mid_tiles(moe, oracle, tokens):
+    """50 and 125 routes per expert on average: the 64- and 128-route tiles of the narrow tile kernel."""
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, 320, 288, 4, 2, synth.FMT_MXFP4, seed=33)
+    check_layer(moe, oracle, layer, tokens, seed=tokens)
+
+
 def test_nemotron_wide_tiles(moe, oracle):
     layer = synth.make_layer(synth.ARCH_NEMOTRON, 256, 160, 4, 2, synth.FMT_Q4_0, seed=32, shared_ffn=320,
                              normalize=True, scale=2.5)
