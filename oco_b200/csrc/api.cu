@@ -432,19 +432,21 @@ int stage_route(oco_moe_plan* plan, const uint16_t* x, int rows, cudaStream_t st
         }
         static bool stream_attr = false;
         if (!stream_attr) {
-            CK(allow_smem(router_stream_kernel<ARCH, 24>));
+            CK(allow_smem(router_stream_kernel<ARCH, 24, 1>));
             stream_attr = true;
         }
-        // few tokens: split the experts over several CTAs per token group so that the grid fills the GPU
-        const int ctas = (rows + 7) / 8;
-        int splits = 1;
-        while (splits * 2 * ctas <= plan->sm_count && E / (splits * 2) >= 4) splits *= 2;
-        router_stream_kernel<ARCH, 24><<<dim3(ctas, splits), 256, (size_t)4 * H * 4, st>>>(
-            x, rw, plan->w.router_b, rows, H, E, K, d.normalize, d.scale, ws.logits, ws.ids, ws.probs);
-        if (splits > 1) {
-            router_select_kernel<ARCH><<<rows, 32, 0, st>>>(ws.logits, ARCH == OCO_ARCH_NEMOTRON ? plan->w.router_b : nullptr, E, K,
-                                                           d.normalize, d.scale, ws.ids, ws.probs);
-            plan->launches++;
+        {
+            // few tokens: split the experts over several CTAs per token group so that the grid fills the GPU
+            const int ctas = (rows + 7) / 8;
+            int splits = 1;
+            while (splits * 2 * ctas <= plan->sm_count && E / (splits * 2) >= 4) splits *= 2;
+            router_stream_kernel<ARCH, 24, 1><<<dim3(ctas, splits), 256, (size_t)6 * H * 4, st>>>(
+                x, rw, plan->w.router_b, rows, H, E, K, d.normalize, d.scale, ws.logits, ws.ids, ws.probs);
+            if (splits > 1) {
+                router_select_kernel<ARCH><<<rows, 32, 0, st>>>(ws.logits, ARCH == OCO_ARCH_NEMOTRON ? plan->w.router_b : nullptr, E, K,
+                                                               d.normalize, d.scale, ws.ids, ws.probs);
+                plan->launches++;
+            }
         }
     } else {
         size_t rsmem = (size_t)H * 4 + (size_t)8 * H * 2;

@@ -283,86 +283,125 @@ __global__ void __launch_bounds__(256) router_batched_kernel(const uint16_t* __r
 }
 
 // Many tokens, hidden <= 128 * ITERS: one token per warp with its row held in registers as f32;
-// the router rows stream through a four-deep shared-memory ring filled with cp.async, one
-// __syncthreads per expert. `w` holds the weights as they enter the FMAs (already rounded for
-// gpt-oss). Same canonical order as canonical_logit. Dynamic shared memory: 4 * H floats.
-// grid (ceil(T / 8), splits): with one split a CTA goes through all experts and selects; with
+// the router rows stream through a shared-memory ring filled with cp.async (three stages of two
+// rows), one __syncthreads per pair of experts. `w` holds the weights as they enter the FMAs (already rounded for
+// gpt-oss). Same canonical order as canonical_logit. Dynamic shared memory: 6 * H floats.
+// grid (ceil(T / (8 * TOK)), splits): with one split a CTA goes through all experts and selects; with
 // more (few tokens, so that the grid still fills the GPU) CTA y takes experts [y * E / splits,
 // (y + 1) * E / splits), writes their logits and leaves the selection to router_select_kernel.
-template <int ARCH, int ITERS>
-__global__ void __launch_bounds__(256) router_stream_kernel(const uint16_t* __restrict__ x,
-                                                            const float* __restrict__ w,
-                                                            const float* __restrict__ bias, int T, int H, int E, int K,
-                                                            int normalize, float scale, float* __restrict__ logits,
-                                                            uint32_t* __restrict__ ids, float* __restrict__ probs) {
+// TOK tokens per warp share every router-row load. Measured: two tokens per warp (250 registers, one
+// CTA per SM) lose more to latency than they save in shared-memory bandwidth (gpt-oss-20b prefill
+// 71 us against 49 us), so the launches use TOK = 1.
+template <int ARCH, int ITERS, int TOK>
+__global__ void __launch_bounds__(256, TOK == 1 ? 2 : 1) router_stream_kernel(const uint16_t* __restrict__ x,
+                                                               const float* __restrict__ w,
+                                                               const float* __restrict__ bias, int T, int H, int E, int K,
+                                                               int normalize, float scale, float* __restrict__ logits,
+                                                               uint32_t* __restrict__ ids, float* __restrict__ probs) {
     extern __shared__ __align__(16) unsigned char smem[];
-    float* ring = reinterpret_cast<float*>(smem);                  // [4][H]
+    float* ring = reinterpret_cast<float*>(smem);                  // [3][2][H]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 8 + warp;
-    const bool live = t < T;
-    float xr[ITERS][4];
+    const int t0 = (blockIdx.x * 8 + warp) * TOK;
+    float xr[TOK][ITERS][4];
 #pragma unroll
-    for (int i = 0; i < ITERS; i++) {
-        const int k = lane * 4 + 128 * i;
-        if (live && k < H) {
-            uint2 xv = *reinterpret_cast<const uint2*>(x + (size_t)t * H + k);
-            xr[i][0] = __uint_as_float(xv.x << 16); xr[i][1] = __uint_as_float(xv.x & 0xffff0000u);
-            xr[i][2] = __uint_as_float(xv.y << 16); xr[i][3] = __uint_as_float(xv.y & 0xffff0000u);
-        } else {
-            xr[i][0] = xr[i][1] = xr[i][2] = xr[i][3] = 0.f;
+    for (int j = 0; j < TOK; j++)
+#pragma unroll
+        for (int i = 0; i < ITERS; i++) {
+            const int k = lane * 4 + 128 * i;
+            if (t0 + j < T && k < H) {
+                uint2 xv = *reinterpret_cast<const uint2*>(x + (size_t)(t0 + j) * H + k);
+                xr[j][i][0] = __uint_as_float(xv.x << 16); xr[j][i][1] = __uint_as_float(xv.x & 0xffff0000u);
+                xr[j][i][2] = __uint_as_float(xv.y << 16); xr[j][i][3] = __uint_as_float(xv.y & 0xffff0000u);
+            } else {
+                xr[j][i][0] = xr[j][i][1] = xr[j][i][2] = xr[j][i][3] = 0.f;
+            }
         }
-    }
     const int chunks = H / 4;                                       // 16-byte chunks per router row
     const int e_begin = (int)(((long long)blockIdx.y * E) / gridDim.y), e_end = (int)(((long long)(blockIdx.y + 1) * E) / gridDim.y);
-    auto issue = [&](int e) {
+    // Two router rows per step: a stage of the ring holds rows e, e + 1 (three stages), so that each
+    // lane runs eight independent FMA chains per token between two barriers.
+    auto issue = [&](int p) {                                       // pair p: rows e_begin + 2p, + 2p + 1
+        const int e = e_begin + 2 * p;
         if (e < e_end) {
+            const int nrows = min(2, e_end - e);
             const float* src = w + (size_t)e * H;
-            const uint32_t dst = smem_u32(ring + (size_t)(e & 3) * H);
-            for (int c = threadIdx.x; c < chunks; c += 256) cp_async16(dst + 16u * c, src + 4 * c);
+            const uint32_t dst = smem_u32(ring + (size_t)(p % 3) * 2 * H);
+            for (int c = threadIdx.x; c < nrows * chunks; c += 256) cp_async16(dst + 16u * c, src + 4 * c);
         }
         cp_async_commit();
     };
-    issue(e_begin); issue(e_begin + 1); issue(e_begin + 2);
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int e = e_begin; e < e_end; e++) {
-        cp_async_wait<2>();
-        __syncthreads();            // row e has landed for everyone; row e - 1 is no longer read
-        issue(e + 3);               // into the buffer row e - 1 used
-        const float* wr = ring + (size_t)(e & 3) * H;
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    issue(0); issue(1);
+    float v[TOK][4];
+#pragma unroll
+    for (int j = 0; j < TOK; j++) v[j][0] = v[j][1] = v[j][2] = v[j][3] = 0.f;
+    const int pairs = (e_end - e_begin + 1) / 2;
+    for (int p = 0; p < pairs; p++) {
+        cp_async_wait<1>();
+        __syncthreads();            // pair p has landed for everyone; pair p - 1 is no longer read
+        issue(p + 2);               // into the stage pair p - 1 used
+        const int e = e_begin + 2 * p;
+        const bool two = e + 1 < e_end;
+        const float* wr = ring + (size_t)(p % 3) * 2 * H;
+        float a[TOK][4], c2[TOK][4];
+#pragma unroll
+        for (int j = 0; j < TOK; j++) {
+            a[j][0] = a[j][1] = a[j][2] = a[j][3] = 0.f;
+            c2[j][0] = c2[j][1] = c2[j][2] = c2[j][3] = 0.f;
+        }
 #pragma unroll
         for (int i = 0; i < ITERS; i++) {
             const int k = lane * 4 + 128 * i;
             if (k < H) {
-                float4 wv = *reinterpret_cast<const float4*>(wr + k);
-                a0 = __fmaf_rn(xr[i][0], wv.x, a0);
-                a1 = __fmaf_rn(xr[i][1], wv.y, a1);
-                a2 = __fmaf_rn(xr[i][2], wv.z, a2);
-                a3 = __fmaf_rn(xr[i][3], wv.w, a3);
+                const float4 wv = *reinterpret_cast<const float4*>(wr + k);
+                const float4 wu = *reinterpret_cast<const float4*>(wr + H + k);   // stale bytes when the pair is single: unused
+#pragma unroll
+                for (int j = 0; j < TOK; j++) {
+                    a[j][0] = __fmaf_rn(xr[j][i][0], wv.x, a[j][0]);
+                    a[j][1] = __fmaf_rn(xr[j][i][1], wv.y, a[j][1]);
+                    a[j][2] = __fmaf_rn(xr[j][i][2], wv.z, a[j][2]);
+                    a[j][3] = __fmaf_rn(xr[j][i][3], wv.w, a[j][3]);
+                    c2[j][0] = __fmaf_rn(xr[j][i][0], wu.x, c2[j][0]);
+                    c2[j][1] = __fmaf_rn(xr[j][i][1], wu.y, c2[j][1]);
+                    c2[j][2] = __fmaf_rn(xr[j][i][2], wu.z, c2[j][2]);
+                    c2[j][3] = __fmaf_rn(xr[j][i][3], wu.w, c2[j][3]);
+                }
             }
         }
-        float sres = warp_butterfly_sum(__fadd_rn(__fadd_rn(a0, a1), __fadd_rn(a2, a3)));
-        if (ARCH == OCO_ARCH_GPT_OSS) sres = __fadd_rn(sres, bf16_round(bias[e]));
 #pragma unroll
-        for (int j = 0; j < 4; j++)
-            if ((e >> 5) == j && (e & 31) == lane) v[j] = sres;
-    }
-    cp_async_wait<0>();
-    if (!live) return;
-    if (logits) {
+        for (int j = 0; j < TOK; j++) {
+            float s0 = warp_butterfly_sum(__fadd_rn(__fadd_rn(a[j][0], a[j][1]), __fadd_rn(a[j][2], a[j][3])));
+            float s1 = warp_butterfly_sum(__fadd_rn(__fadd_rn(c2[j][0], c2[j][1]), __fadd_rn(c2[j][2], c2[j][3])));
+            if (ARCH == OCO_ARCH_GPT_OSS) {
+                s0 = __fadd_rn(s0, bf16_round(bias[e]));
+                if (two) s1 = __fadd_rn(s1, bf16_round(bias[e + 1]));
+            }
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int e = lane + 32 * j;
-            if (e >= e_begin && e < e_end) logits[(size_t)t * E + e] = v[j];
+            for (int q = 0; q < 4; q++) {
+                if ((e >> 5) == q && (e & 31) == lane) v[j][q] = s0;
+                if (two && ((e + 1) >> 5) == q && ((e + 1) & 31) == lane) v[j][q] = s1;
+            }
         }
     }
-    if (gridDim.y > 1) return;
-    uint32_t id[kMaxTopK];
-    float pr[kMaxTopK];
-    select_experts<ARCH>(v, E, K, ARCH == OCO_ARCH_NEMOTRON ? bias : nullptr, normalize, scale, lane, id, pr);
+    cp_async_wait<0>();
 #pragma unroll
-    for (int r = 0; r < kMaxTopK; r++)
-        if (r < K && lane == r) { ids[(size_t)t * K + r] = id[r]; probs[(size_t)t * K + r] = pr[r]; }
+    for (int j = 0; j < TOK; j++) {
+        const int t = t0 + j;
+        if (t >= T) continue;
+        if (logits) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int e = lane + 32 * q;
+                if (e >= e_begin && e < e_end) logits[(size_t)t * E + e] = v[j][q];
+            }
+        }
+        if (gridDim.y > 1) continue;
+        uint32_t id[kMaxTopK];
+        float pr[kMaxTopK];
+        select_experts<ARCH>(v[j], E, K, ARCH == OCO_ARCH_NEMOTRON ? bias : nullptr, normalize, scale, lane, id, pr);
+#pragma unroll
+        for (int r = 0; r < kMaxTopK; r++)
+            if (r < K && lane == r) { ids[(size_t)t * K + r] = id[r]; probs[(size_t)t * K + r] = pr[r]; }
+    }
 }
 
 }  // namespace oco
