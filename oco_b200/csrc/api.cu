@@ -474,11 +474,11 @@ int stage_experts(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, in
     const oco_moe_desc& d = plan->d;
     Workspace& ws = plan->ws;
     const int H = d.hidden, F = d.ffn, E = d.experts;
-    if (FMT != OCO_FMT_Q4_K && R <= plan->batch_max_avg * E && !plan->no_batch_path) {
+    if (FMT != OCO_FMT_Q4_K && R <= plan->batch_max_avg * E && !plan->no_batch_path &&
+        batch_smem_bytes(H / 32) <= kMaxDynamicSmem && batch_smem_bytes(F / 32) <= kMaxDynamicSmem) {
         // A few routes per expert: memory-bound, streamed with up to eight routes per MMA (batch.cuh).
+        // (Layers too wide for the fragments to sit in shared memory take the tiles.)
         if constexpr (FMT != OCO_FMT_Q4_K) {
-            if (batch_smem_bytes(H / 32) > kMaxDynamicSmem || batch_smem_bytes(F / 32) > kMaxDynamicSmem)
-                return fail(plan, OCO_UNSUPPORTED_SHAPE, "layer too wide for the few-token kernels");
             plan->last_tile_rows = kBatchCols;
             mark(plan, st, "route_plan");
             route_plan_kernel<<<1, 1024, 0, st>>>(ids, (uint32_t)R, (uint32_t)E, (uint32_t)kBatchCols, ws.offsets,
@@ -612,7 +612,11 @@ template <int ARCH>
 int forward_family(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int rows, cudaStream_t st,
                    cudaEvent_t residual_ready = nullptr) {
     constexpr int FMT = Family<ARCH>::kFmt;
-    if (rows == 1) {
+    const oco_moe_desc& d = plan->d;
+    // The single-token kernels keep the token's (and each route's) MMA fragments in shared memory beside
+    // their rings; layers too wide for that take the tile kernels, which have no such limit.
+    const int widest = std::max(d.hidden, std::max(d.ffn, d.shared_ffn));
+    if (rows == 1 && token_smem_bytes(FMT, widest / 32, 2) <= kMaxDynamicSmem) {
         if (residual_ready) CK(cudaStreamWaitEvent(st, residual_ready, 0));
         return forward_single<ARCH>(plan, x, residual, st);
     }

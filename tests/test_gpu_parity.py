@@ -288,6 +288,20 @@ def test_nemotron_few_tokens_streamed(moe, oracle, tokens):
     check_layer(moe, oracle, layer, tokens, seed=tokens)
 
 
+@pytest.mark.parametrize("tokens", [1, 3])
+def test_wide_layer_falls_back_to_tiles(moe, oracle, tokens):
+    """hidden = 8192 is too wide for the token's fragments to share the SM with the streaming rings:
+    single tokens and small batches then take the tile kernels (tile numerics, also for one token)."""
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, 8192, 128, 8, 2, synth.FMT_MXFP4, seed=61)
+    check_layer(moe, oracle, layer, tokens, seed=tokens, mode=2)
+
+
+def test_hidden_4096_single_token(moe, oracle):
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, 4096, 256, 8, 2, synth.FMT_MXFP4, seed=62)
+    check_layer(moe, oracle, layer, 1, seed=4)
+    check_layer(moe, oracle, layer, 5, seed=5)
+
+
 def test_few_tokens_tile_kernels(moe, oracle, monkeypatch):
     """The same small batches through the tile kernels (the path they took before the streamed one)."""
     monkeypatch.setenv("OCO_MOE_NO_BATCH", "1")
