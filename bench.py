@@ -308,6 +308,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="single-token workloads: launch kernels directly instead of replaying CUDA graphs")
     ap.add_argument("--layers", type=int, default=0, help="distinct weight copies rotated per step (0 = auto)")
+    ap.add_argument("--with-norm", action="store_true",
+                    help="time the fused entry point: residual add + RMS norm + layer (the step either side of the layer)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -351,6 +353,7 @@ def main():
     x = torch.from_numpy(x_bits.view(np.int16)).cuda()
     res = torch.from_numpy(res_bits.view(np.int16).copy()).cuda()
     stream = torch.cuda.current_stream()
+    norm_w = torch.ones(layer.hidden, dtype=torch.float32, device="cuda")
 
     graphs = [None] * copies
 
@@ -360,7 +363,10 @@ def main():
             graphs[i % copies].replay()       # launch-bound single-token step: one graph launch
             return p
         p.set_profiling(profile)
-        p.forward(x, res, tokens)
+        if args.with_norm:
+            p.add_norm_forward(res, x, norm_w, 1e-5, layer.arch == synth.ARCH_GPT_OSS, tokens)   # x stands in for the mixer's output
+        else:
+            p.forward(x, res, tokens)
         return p
 
     for i in range(max(args.warmup, copies if decode else 0)):
@@ -377,7 +383,8 @@ def main():
                 plans[c].set_profiling(False)
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g, stream=side):
-                    plans[c].forward(x, res, tokens)
+                    step_plain = plans[c].add_norm_forward(res, x, norm_w, 1e-5, layer.arch == synth.ARCH_GPT_OSS, tokens) \
+                        if args.with_norm else plans[c].forward(x, res, tokens)
                 graphs[c] = g
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
@@ -508,7 +515,7 @@ def main():
                     experts_touched=touched, weight_copies=copies,
                     cache="every step reads all expert weights (%.0f MB), more than the 126 MB L2" % (per_step_bytes / 1e6)
                     if not decode else "%d weight copies rotated per step (%.0f MB between reuses)" % (copies, copies * per_step_bytes / 1e6),
-                    cuda_graph=graphs[0] is not None,
+                    cuda_graph=graphs[0] is not None, fused_add_norm=bool(args.with_norm),
                     parallelism="replicas" if world > 1 else "single"),
         clocks=clocks, e2e=e2e, gpu_launches=launches, phases_ms=phases, roofline=roofline, cpu_baseline=base,
         step_ms_min=min(step_ms), step_ms_max=max(step_ms))

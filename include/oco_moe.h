@@ -110,6 +110,7 @@ typedef struct {
                                      (64 for Q4_K) element j sits at 2*(j mod h) + j div h, h = 16 (32 for Q4_K),
                                      the order in which the packed code bytes hold their two nibbles. */
     const uint16_t* y;            /* bf16 [routes, hidden] expert outputs in route order */
+    const uint16_t* norm;         /* bf16 [rows, hidden] normalised rows of the last oco_moe_add_norm_forward */
 } oco_moe_routing_view;
 
 typedef struct oco_moe_plan oco_moe_plan;
@@ -155,6 +156,18 @@ int oco_moe_experts(oco_moe_plan* plan, const uint16_t* rows_bf16, const uint32_
                     uint16_t* y_bf16, void* cuda_stream);
 int oco_moe_combine(oco_moe_plan* plan, const uint16_t* y_bf16, const float* probs, uint16_t* residual_bf16,
                     int rows, void* cuda_stream);
+
+/* The step either side of the layer, in one call (reference Bindings::add_norm followed by
+ * Bindings::experts, src/weights/compute.rs:100-117 and src/weights/gpt_oss.rs:122-123; kernels
+ * add_norm / norm, shaders/elementwise.metal:5-60):
+ *     hidden += projected            bf16 rows [rows, hidden]; projected may be NULL (plain norm)
+ *     x = rmsnorm(hidden) * norm_weight   f32 weight [hidden]; full_layer = 1 scales in f32 and rounds
+ *                                    once (gpt-oss), 0 rounds the normalised value and the weight to bf16
+ *                                    first (Qwen)
+ *     hidden += MoE(x)
+ * The normalised rows stay in the workspace (oco_moe_routing gives their address). */
+int oco_moe_add_norm_forward(oco_moe_plan* plan, uint16_t* hidden_bf16, const uint16_t* projected_bf16,
+                             const float* norm_weight, float epsilon, int full_layer, int rows, void* cuda_stream);
 
 /* The same call for host buffers: copies x to the device on `cuda_stream`, the residual rows on a
  * second stream the plan owns (they are needed by the last kernel only, so their copy overlaps the

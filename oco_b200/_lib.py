@@ -27,7 +27,7 @@ class Weights(C.Structure):
 
 class RoutingView(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("logits", "ids", "probs", "offsets", "row_of_route", "route_of_row",
-                                          "tiles", "tile_count", "act", "y")]
+                                          "tiles", "tile_count", "act", "y", "norm")]
 
 
 # Every symbol include/oco_moe.h declares, with its signature.
@@ -38,6 +38,7 @@ SIGNATURES = {
     "oco_moe_bind_workspace": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]),
     "oco_moe_bind_weights": (C.c_int, [C.c_void_p, C.POINTER(Weights)]),
     "oco_moe_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "oco_moe_add_norm_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_int, C.c_void_p]),
     "oco_moe_route": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "oco_moe_experts": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "oco_moe_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),

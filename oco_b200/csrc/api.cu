@@ -50,6 +50,7 @@ struct Workspace {
     float* sh_act1 = nullptr;
     __half* sh_actfrag = nullptr;
     uint32_t* sh_ids = nullptr;
+    uint16_t* norm = nullptr;     // bf16 [T, H] normalised rows of oco_moe_add_norm_forward
     uint16_t* host_x = nullptr;   // staging for the host-buffer entry point
     uint16_t* host_res = nullptr;
     size_t total = 0;
@@ -170,6 +171,7 @@ Workspace carve(const oco_moe_desc& d, int max_rows, unsigned char* base) {
         w.sh_actfrag = (__half*)take((S / 32) * 128 * 2);
         w.sh_ids = (uint32_t*)take(256);
     }
+    w.norm = (uint16_t*)take(T * H * 2);
     w.host_x = (uint16_t*)take(T * H * 2);
     w.host_res = (uint16_t*)take(T * H * 2);
     w.total = off;
@@ -790,6 +792,30 @@ int oco_moe_forward(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, i
 }
 
 // ---- stages as entry points (expert parallelism puts an all-to-all between them) ---------------
+int oco_moe_add_norm_forward(oco_moe_plan* plan, uint16_t* hidden, const uint16_t* projected, const float* norm_weight,
+                             float epsilon, int full_layer, int rows, void* cuda_stream) {
+    if (!plan) return OCO_INVALID_ARGUMENT;
+    if (!plan->have_ws || !plan->have_w) return fail(plan, OCO_INVALID_ARGUMENT, "bind a workspace and weights first");
+    if (!hidden || !norm_weight) return fail(plan, OCO_INVALID_ARGUMENT, "null hidden rows or norm weight");
+    if (rows < 1 || rows > plan->max_rows) return fail(plan, OCO_INVALID_ARGUMENT, "rows %d outside 1..%d", rows, plan->max_rows);
+    if (((uintptr_t)hidden & 15u) || ((uintptr_t)projected & 15u)) return fail(plan, OCO_INVALID_ARGUMENT, "rows must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    plan->launches = 0;
+    plan->n_marks = 0;
+    mark(plan, st, "add_norm");
+    add_norm_kernel<<<rows, 256, 0, st>>>(hidden, projected, norm_weight, plan->ws.norm, plan->d.hidden, epsilon, full_layer);
+    CK(cudaGetLastError());
+    int launches = 1;
+    int rc;
+    switch (plan->d.arch) {   // the layer itself; its own launch count is added to the norm's
+        case OCO_ARCH_GPT_OSS: rc = forward_family<OCO_ARCH_GPT_OSS>(plan, plan->ws.norm, hidden, rows, st); break;
+        case OCO_ARCH_NEMOTRON: rc = forward_family<OCO_ARCH_NEMOTRON>(plan, plan->ws.norm, hidden, rows, st); break;
+        default: rc = forward_family<OCO_ARCH_QWEN>(plan, plan->ws.norm, hidden, rows, st); break;
+    }
+    plan->launches += launches;
+    return rc;
+}
+
 int oco_moe_route(oco_moe_plan* plan, const uint16_t* x, int rows, void* cuda_stream) {
     if (!plan) return OCO_INVALID_ARGUMENT;
     if (!plan->have_ws || !plan->w.router_w) return fail(plan, OCO_INVALID_ARGUMENT, "bind a workspace and router weights first");
@@ -890,7 +916,7 @@ int oco_moe_routing(const oco_moe_plan* plan, oco_moe_routing_view* out) {
     const Workspace& ws = plan->ws;
     out->logits = ws.logits; out->ids = ws.ids; out->probs = ws.probs; out->offsets = ws.offsets;
     out->row_of_route = ws.row_of_route; out->route_of_row = ws.route_of_row; out->tiles = ws.tiles;
-    out->tile_count = ws.tile_count; out->act = ws.act; out->y = ws.y;
+    out->tile_count = ws.tile_count; out->act = ws.act; out->y = ws.y; out->norm = ws.norm;
     return OCO_OK;
 }
 

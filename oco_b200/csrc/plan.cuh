@@ -97,6 +97,52 @@ __global__ void __launch_bounds__(256) permute_rows_kernel(const uint16_t* __res
     }
 }
 
+// Residual add and RMS normalisation in one pass (reference add_norm and norm,
+// shaders/elementwise.metal:5-30,32-60; call sites src/weights/compute.rs:86-117,
+// src/weights/gpt_oss.rs:122): hidden += delta (bf16 add; delta null = plain norm), then
+// out = hidden * rsqrt(mean(hidden^2) + eps) * w, rounded as the model family asks: full_layer
+// scales the f32 value and rounds once (gpt-oss); otherwise the normalised value and the weight
+// are rounded to bf16 before the product (Qwen). The reference leaves the order of its simd_sum
+// open; the order fixed here (per thread i = tid, tid + 256, ... with FMA, xor butterfly inside
+// the warp, then the same butterfly over the eight warp sums) is carried by the CPU checker too.
+// One CTA of 256 threads per row.
+__global__ void __launch_bounds__(256) add_norm_kernel(uint16_t* __restrict__ hidden, const uint16_t* __restrict__ delta,
+                                                       const float* __restrict__ w, uint16_t* __restrict__ out, int n,
+                                                       float eps, int full_layer) {
+    __shared__ float warp_sum[8];
+    __shared__ float inv_s;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    uint16_t* row = hidden + (size_t)blockIdx.x * n;
+    const uint16_t* drow = delta ? delta + (size_t)blockIdx.x * n : nullptr;
+    float s = 0.f;
+    for (int i = tid; i < n; i += 256) {
+        float v = bf16_bits_to_f32(row[i]);
+        if (drow) {
+            v = bf16_round(__fadd_rn(v, bf16_bits_to_f32(drow[i])));
+            row[i] = f32_to_bf16_bits(v);
+        }
+        s = __fmaf_rn(v, v, s);
+    }
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, d));
+    if (lane == 0) warp_sum[warp] = s;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < 8 ? warp_sum[lane] : 0.f;
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) t = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, d));
+        if (lane == 0) inv_s = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)n), eps)));
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    uint16_t* orow = out + (size_t)blockIdx.x * n;
+    for (int i = tid; i < n; i += 256) {
+        const float normalized = __fmul_rn(bf16_bits_to_f32(row[i]), inv);
+        const float v = full_layer ? __fmul_rn(normalized, w[i]) : __fmul_rn(bf16_round(normalized), bf16_round(w[i]));
+        orow[i] = f32_to_bf16_bits(v);
+    }
+}
+
 // gpt-oss rounds every router weight to bf16 when it is used (routing.metal:108-109). The rounded
 // copy is made once per bound weight set so the per-token kernels read plain f32.
 __global__ void __launch_bounds__(256) round_router_kernel(const float* __restrict__ w, float* __restrict__ out, size_t n) {

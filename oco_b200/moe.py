@@ -99,6 +99,14 @@ class _Plan:
     def forward(self, x: torch.Tensor, residual: torch.Tensor, rows: int):
         self._check(_lib.lib().oco_moe_forward(self.handle, _ptr(x), _ptr(residual), rows, _stream_ptr()))
 
+    def add_norm_forward(self, hidden: torch.Tensor, projected: Optional[torch.Tensor], norm_weight: torch.Tensor,
+                         epsilon: float, full_layer: bool, rows: int):
+        """hidden += projected; x = rmsnorm(hidden) * norm_weight; hidden += MoE(x) (reference
+        `Bindings::add_norm` + `Bindings::experts`, src/weights/compute.rs:100-117, gpt_oss.rs:122-123)."""
+        self._check(_lib.lib().oco_moe_add_norm_forward(self.handle, _ptr(hidden), _ptr(projected) if projected is not None else None,
+                                                        _ptr(norm_weight), C.c_float(epsilon), int(bool(full_layer)), rows,
+                                                        _stream_ptr()))
+
     def forward_host(self, x: np.ndarray, residual: np.ndarray, rows: int):
         self._check(_lib.lib().oco_moe_forward_host(self.handle, x.ctypes.data_as(C.c_void_p),
                                                     residual.ctypes.data_as(C.c_void_p), rows, _stream_ptr()))
@@ -239,7 +247,8 @@ class Routing:
         out = dict(ids=self._read(v.ids, R, np.uint32).reshape(self.rows, d.top_k),
                    prob=self._read(v.probs, R, np.float32).reshape(self.rows, d.top_k),
                    logits=self._read(v.logits, self.rows * d.experts, np.float32).reshape(self.rows, d.experts),
-                   y=self._read(v.y, R * d.hidden, np.uint16).reshape(R, d.hidden))
+                   y=self._read(v.y, R * d.hidden, np.uint16).reshape(R, d.hidden),
+                   norm=self._read(v.norm, self.rows * d.hidden, np.uint16).reshape(self.rows, d.hidden))
         if self.rows > 1:
             out["offsets"] = self._read(v.offsets, d.experts + 1, np.uint32)
             out["row_of_route"] = self._read(v.row_of_route, R, np.uint32)

@@ -233,6 +233,17 @@ def moe_activate(g, u):
     return out
 
 
+def add_norm(hidden_bf16, delta_bf16, weight, eps, full_layer):
+    """Returns (hidden after the add, normalised rows), both bf16 bit patterns [rows, n]."""
+    hidden = _c(hidden_bf16, np.uint16).copy()
+    delta = None if delta_bf16 is None else _c(delta_bf16, np.uint16)
+    weight = _c(weight, np.float32)
+    rows, n = hidden.shape
+    out = np.empty_like(hidden)
+    lib().orc_add_norm(_p(hidden), _p(delta), _p(weight), rows, n, C.c_float(eps), int(full_layer), _p(out))
+    return hidden, out
+
+
 def moe_sum(routes_bf16, weights, out_bf16, k):
     routes_bf16 = _c(routes_bf16, np.uint16); weights = _c(weights, np.float32)
     out = _c(out_bf16, np.uint16).copy()

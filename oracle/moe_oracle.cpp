@@ -592,6 +592,58 @@ void orc_moe_activate(const float* g, const float* u, size_t count, uint16_t* ou
 }
 
 // moe_sum (routing.metal:154-168).
+// Residual add + RMS normalisation (shaders/elementwise.metal:5-30 norm, :32-60 add_norm; call
+// sites src/weights/compute.rs:86-117, src/weights/gpt_oss.rs:122). hidden += delta as a bf16 add
+// (delta may be null: plain norm), out = hidden * rsqrt(mean(hidden^2) + eps) * w with the
+// family's rounding (full_layer: scale in f32, round once; else round the normalised value and
+// the weight to bf16 first). The reference's simd_sum order is unspecified; the order fixed here
+// (256 strided partial sums with FMA, xor butterfly 16..1 inside each group of 32, then the same
+// butterfly over the eight group sums padded with zeros) is this build's definition and the CUDA
+// kernel carries the same one. rsqrt is taken as 1 / sqrt with IEEE division and square root.
+void orc_add_norm(uint16_t* hidden, const uint16_t* delta, const float* w, int rows, int n, float eps,
+                  int full_layer, uint16_t* out) {
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; r++) {
+        uint16_t* row = hidden + (size_t)r * n;
+        float part[256];
+        for (int t = 0; t < 256; t++) {
+            float s = 0.f;
+            for (int i = t; i < n; i += 256) {
+                float v = orc_bf16_to_f32(row[i]);
+                if (delta) {
+                    v = bf16r(v + orc_bf16_to_f32(delta[(size_t)r * n + i]));
+                    row[i] = orc_f32_to_bf16(v);
+                }
+                s = fmaf(v, v, s);
+            }
+            part[t] = s;
+        }
+        float group[32];
+        for (int g = 0; g < 32; g++) group[g] = 0.f;
+        for (int g = 0; g < 8; g++) {
+            float lane[32];
+            for (int l = 0; l < 32; l++) lane[l] = part[g * 32 + l];
+            for (int off = 16; off >= 1; off >>= 1) {
+                float next[32];
+                for (int l = 0; l < 32; l++) next[l] = lane[l] + lane[l ^ off];
+                std::memcpy(lane, next, sizeof(next));
+            }
+            group[g] = lane[0];
+        }
+        for (int off = 16; off >= 1; off >>= 1) {
+            float next[32];
+            for (int l = 0; l < 32; l++) next[l] = group[l] + group[l ^ off];
+            std::memcpy(group, next, sizeof(next));
+        }
+        const float inv = 1.0f / sqrtf(group[0] / (float)n + eps);
+        for (int i = 0; i < n; i++) {
+            const float normalized = orc_bf16_to_f32(row[i]) * inv;
+            const float v = full_layer ? normalized * w[i] : bf16r(normalized) * bf16r(w[i]);
+            out[(size_t)r * n + i] = orc_f32_to_bf16(v);
+        }
+    }
+}
+
 void orc_moe_sum(const uint16_t* routes_bf16, const float* weights, uint16_t* out_bf16, int hidden,
                  int batch, int k) {
     for (int t = 0; t < batch; t++)

@@ -302,6 +302,38 @@ def test_hidden_4096_single_token(moe, oracle):
     check_layer(moe, oracle, layer, 5, seed=5)
 
 
+@pytest.mark.parametrize("arch,full_layer", [(synth.ARCH_GPT_OSS, True), (synth.ARCH_QWEN, False)], ids=["gpt-oss", "qwen"])
+@pytest.mark.parametrize("rows", [1, 40])
+def test_add_norm_forward(moe, oracle, arch, full_layer, rows):
+    """Residual add + RMS norm + layer in one call: the summed rows and the normalised rows are
+    bit-exact against the checker, the layer output meets the usual bar."""
+    import torch
+    fmt = synth.FMT_MXFP4 if arch == synth.ARCH_GPT_OSS else synth.FMT_Q4_K
+    H = 512
+    layer = synth.make_layer(arch, H, 256, 16, 4, fmt, seed=71)
+    rng = np.random.default_rng(rows)
+    hidden, projected = synth.make_tokens(H, rows, 11, "normal")
+    weight = rng.normal(1.0, 0.2, size=H).astype(np.float32)
+    eps = 1e-5
+    for delta in (projected, None):
+        summed, normed = oracle.add_norm(hidden, delta, weight, eps, full_layer)
+        ref = oracle.moe_forward(layer, normed, summed)
+        plan = moe.plan_for(layer)
+        w = moe._Weights.from_layer(layer)
+        plan.reserve(rows); plan.bind(w)
+        h = torch.from_numpy(hidden.view(np.int16).copy()).cuda()
+        d = None if delta is None else torch.from_numpy(delta.view(np.int16).copy()).cuda()
+        nw = torch.from_numpy(weight).cuda()
+        plan.add_norm_forward(h, d, nw, eps, full_layer, rows)
+        plan.poll()
+        routing = moe.Routing(); routing.plan, routing.rows = plan, rows
+        view = routing.read()
+        assert np.array_equal(view["norm"], normed), "normalised rows differ"
+        assert np.array_equal(view["ids"], ref.ids)
+        out = h.cpu().numpy().view(np.uint16)
+        assert rel_l2(out, ref.out) <= REL_L2
+
+
 def test_few_tokens_tile_kernels(moe, oracle, monkeypatch):
     """The same small batches through the tile kernels (the path they took before the streamed one)."""
     monkeypatch.setenv("OCO_MOE_NO_BATCH", "1")

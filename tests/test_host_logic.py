@@ -94,3 +94,28 @@ def test_algorithmic_byte_counts_match_the_benchmark_description():
     N = synth.Layer(arch=synth.ARCH_NEMOTRON, hidden=2688, ffn=1856, experts=128, top_k=6, fmt=synth.FMT_Q4_0,
                     shared_ffn=3712)
     assert N.expert_bytes() == 5_612_544 and N.shared_bytes() == 11_225_088
+
+
+def test_add_norm_oracle_against_float64(oracle):
+    """The checker's residual add + RMS norm against a float64 restatement of the shader
+    (elementwise.metal:32-60), within the bf16 roundings the shader makes."""
+    from oco_b200 import synth
+    rng = np.random.default_rng(3)
+    rows, n, eps = 5, 2880, 1e-5
+    hidden, delta = synth.make_tokens(n, rows, 21, "normal")
+    w = rng.normal(1.0, 0.3, size=n).astype(np.float32)
+    for full_layer in (True, False):
+        for d in (delta, None):
+            summed, normed = oracle.add_norm(hidden, d, w, eps, full_layer)
+            h = synth.bf16_bits_to_f32(hidden).astype(np.float64)
+            if d is not None:
+                h = synth.bf16_bits_to_f32(synth.f32_to_bf16_bits((h + synth.bf16_bits_to_f32(d)).astype(np.float32))).astype(np.float64)
+                assert np.array_equal(synth.f32_to_bf16_bits(h.astype(np.float32)), summed)
+            else:
+                assert np.array_equal(summed, hidden)
+            inv = 1.0 / np.sqrt((h * h).mean(axis=1, keepdims=True) + eps)
+            want = h * inv * w
+            got = synth.bf16_bits_to_f32(normed).astype(np.float64)
+            # one bf16 rounding (2^-9) when the scale is applied in f32, three when both factors are rounded first
+            bound = 2.0 ** -8 if full_layer else 2.0 ** -6
+            assert np.all(np.abs(got - want) <= np.abs(want) * bound + 1e-30)
