@@ -19,6 +19,7 @@ streams; every computation happens inside liboco_moe.so.
 from __future__ import annotations
 
 import ctypes as C
+import warnings
 from dataclasses import dataclass
 from typing import Optional
 
@@ -47,7 +48,10 @@ def _dev_bytes(a: Optional[np.ndarray], device, misalign: int = 0) -> Optional[t
     if a is None:
         return None
     a = np.ascontiguousarray(a)
-    flat = torch.from_numpy(a.view(np.uint8).reshape(-1))
+    with warnings.catch_warnings():
+        # views of a read-only file map are only read here (copied to the device)
+        warnings.simplefilter("ignore", UserWarning)
+        flat = torch.from_numpy(a.view(np.uint8).reshape(-1))
     if not misalign:
         return flat.to(device)
     buf = torch.full((flat.numel() + misalign + 64,), 0xA5, dtype=torch.uint8, device=device)
