@@ -28,9 +28,9 @@ struct WideShape {
     static constexpr int kThreads = 18 * 32;
     static constexpr int kATile = 128 * 128;          // one A tile: 128 rows x 64 halves
     static constexpr int kAStage = 2 * kATile;        // both A tiles
-    static constexpr int kAStages = 2;
+    static constexpr int kAStages = 3;
     static constexpr int kBStage = kNT * 128;
-    static constexpr int kBStages = 3;
+    static constexpr int kBStages = 2;
     static constexpr int kChunkSlices = 2;            // K slices per raw-ring buffer
     static constexpr int kPitch = 112;                // ring bytes per row: 2 slices (<= 72 B) + 15 alignment, 16-byte chunks
     static constexpr int kRowChunks = 6;              // 16-byte chunks fetched per row per buffer
@@ -83,11 +83,11 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
     const uint32_t ctrl = ring_base + S::kRing;
     unsigned char* ctrl_gen = gen_base + (ctrl - base);
     auto full_a = [&](int s) { return ctrl + 8u * s; };
-    auto empty_a = [&](int s) { return ctrl + 8u * (2 + s); };
-    auto full_b = [&](int s) { return ctrl + 8u * (4 + s); };
-    auto empty_b = [&](int s) { return ctrl + 8u * (7 + s); };
-    const uint32_t accum_bar = ctrl + 8u * 10;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl_gen + 96);
+    auto empty_a = [&](int s) { return ctrl + 8u * (S::kAStages + s); };
+    auto full_b = [&](int s) { return ctrl + 8u * (2 * S::kAStages + s); };
+    auto empty_b = [&](int s) { return ctrl + 8u * (2 * S::kAStages + S::kBStages + s); };
+    const uint32_t accum_bar = ctrl + 8u * (2 * S::kAStages + 2 * S::kBStages);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl_gen + 128);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     uint32_t* out_rows = reinterpret_cast<uint32_t*>(ctrl_gen + 512);
     for (uint32_t i = tid; i < nv; i += S::kThreads)
