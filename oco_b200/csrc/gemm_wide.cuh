@@ -43,35 +43,49 @@ struct WideShape {
 };
 
 // FMT: MXFP4 or Q4_0 (32-element blocks of 17 / 18 bytes). EPI as in gemm.cuh.
-// grid: (ceil(n / (gated ? 128 : 256)), max_tiles). `w_end`: first byte past the 16-byte-aligned
-// envelope of the weight tensors (no copy starts at or beyond it).
+// Persistent: grid = number of SMs; CTA c takes work items c, c + grid, ... where an item is
+// (route tile, feature tile) with the feature tile running fastest, so that the CTAs running at
+// the same time share a route tile's B rows in L2. Barriers, tensor memory and rings are set up
+// once; their phases run on across items. Between two items the producers start the next item's
+// weight bytes on their way before they drain the accumulators of the finished one, and the MMA
+// warp waits for the drain (`tmem_free`) before it overwrites them. `w_end`: first byte past the
+// 16-byte-aligned envelope of the weight tensors (no copy starts at or beyond it).
 template <int FMT, int EPI>
 __global__ void __launch_bounds__(WideShape::kThreads, 1)
-grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_b) {
+grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_b32,
+                         const __grid_constant__ CUtensorMap tmap_b64, const __grid_constant__ CUtensorMap tmap_b128,
+                         const __grid_constant__ CUtensorMap tmap_b) {
     using S = WideShape;
     constexpr bool GATED = epi_gated(EPI);
     constexpr int NT = S::kNT;
     constexpr int kBlockBytes = FMT == OCO_FMT_MXFP4 ? 17 : 18;
     constexpr int kSliceBytes = 2 * kBlockBytes;
+    constexpr int kFeatPerItem = GATED ? 128 : 256;
     extern __shared__ unsigned char smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-
-    // ---- which tile ----------------------------------------------------------------------------
-    uint32_t expert, begin, count, row0;
-    if (p.tiles) {
-        if (blockIdx.y >= *p.tile_count) return;
-        expert = p.tiles[2 * blockIdx.y];
-        begin = p.tiles[2 * blockIdx.y + 1];
-        row0 = p.offsets[expert] + begin;
-        count = p.offsets[expert + 1] - p.offsets[expert];
-    } else {
-        expert = 0; begin = blockIdx.y * NT; row0 = begin; count = (uint32_t)p.dense_rows;
-        if (begin >= count) return;
-    }
     if (__syncthreads_or(tid == 0 && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u)) return;
-    const uint32_t nv = min((uint32_t)NT, count - begin);
-    const uint32_t n_mma = max(16u, (nv + 15u) & ~15u);
-    const int f0 = blockIdx.x * (GATED ? 128 : 256);     // first feature of A tile 0
+
+    // ---- the work list ---------------------------------------------------------------------------
+    const int nfeat = (p.n + kFeatPerItem - 1) / kFeatPerItem;
+    const int ntiles = p.tiles ? (int)*p.tile_count : (p.dense_rows + NT - 1) / NT;
+    const int total = nfeat * ntiles;
+    struct Item { uint32_t expert, row0, nv; int f0; };
+    auto load_item = [&](int item) {
+        Item r;
+        const int tile = item / nfeat;
+        r.f0 = (item - tile * nfeat) * kFeatPerItem;
+        uint32_t begin, count;
+        if (p.tiles) {
+            r.expert = p.tiles[2 * tile];
+            begin = p.tiles[2 * tile + 1];
+            r.row0 = p.offsets[r.expert] + begin;
+            count = p.offsets[r.expert + 1] - p.offsets[r.expert];
+        } else {
+            r.expert = 0; begin = (uint32_t)tile * NT; r.row0 = begin; count = (uint32_t)p.dense_rows;
+        }
+        r.nv = min((uint32_t)NT, count - begin);
+        return r;
+    };
     const int nkb = (p.K + 63) / 64;
     const int nblk = p.K >> 5;
 
@@ -87,16 +101,16 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
     auto full_b = [&](int s) { return ctrl + 8u * (2 * S::kAStages + s); };
     auto empty_b = [&](int s) { return ctrl + 8u * (2 * S::kAStages + S::kBStages + s); };
     const uint32_t accum_bar = ctrl + 8u * (2 * S::kAStages + 2 * S::kBStages);
+    const uint32_t tmem_free = accum_bar + 8u;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl_gen + 128);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     uint32_t* out_rows = reinterpret_cast<uint32_t*>(ctrl_gen + 512);
-    for (uint32_t i = tid; i < nv; i += S::kThreads)
-        out_rows[i] = (EPI == kEpiDownBf16 && p.route_of_row) ? p.route_of_row[row0 + i] : row0 + i;
 
     if (tid == 0) {
         for (int s = 0; s < S::kAStages; s++) { mbar_init(full_a(s), S::kProducerWarps); mbar_init(empty_a(s), 1); }
         for (int s = 0; s < S::kBStages; s++) { mbar_init(full_b(s), 1); mbar_init(empty_b(s), 1); }
         mbar_init(accum_bar, 1);
+        mbar_init(tmem_free, S::kProducerWarps);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -114,27 +128,28 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
         // Row stream rs = 16 * warp + r: A tile (rs >> 7), tile row (rs & 127).
         const int tile = warp >> 3;                                  // which A tile this warp feeds
         const uint8_t* wmat = (GATED && tile) ? p.w1 : p.w0;
-        const int feat0 = GATED ? f0 : f0 + 128 * tile;              // feature of tile row 0
         const int trow0 = (warp & 7) * 16;                           // first tile row of this warp
-        auto row_ptr = [&](int r) -> const uint8_t* {                // packed bytes of tile row trow0 + r
-            int f = min(feat0 + trow0 + r, p.n - 1);
-            return wmat + ((size_t)expert * p.n + f) * p.row_bytes;
-        };
-        // copy role: three 16-byte chunks per buffer: chunk index (lane + 32 i) -> (row, column)
+        const uint8_t* w_end = (GATED && tile) ? p.w1_end : p.w0_end;
         constexpr uint32_t kChunkBytes = S::kChunkSlices * kSliceBytes;      // packed bytes per row per buffer
         constexpr uint32_t kBufBytes = 16 * S::kPitch;
         const uint32_t ring = ring_base + (uint32_t)warp * S::kRingWarp;
-        const uint8_t* w_end = (GATED && tile) ? p.w1_end : p.w0_end;
-        const uint8_t* csrc[3];                                             // running source: row start + column
+        const int nchunks = (nkb + S::kChunkSlices - 1) / S::kChunkSlices;
+        // packed bytes of tile row trow0 + r of an item
+        auto row_ptr = [&](const Item& it, int r) -> const uint8_t* {
+            const int feat0 = GATED ? it.f0 : it.f0 + 128 * tile;
+            int f = min(feat0 + trow0 + r, p.n - 1);
+            return wmat + ((size_t)it.expert * p.n + f) * p.row_bytes;
+        };
+        // copy role: three 16-byte chunks per buffer: chunk index (lane + 32 i) -> (row, column)
         uint32_t cdst[3];
+        int crow[3];
 #pragma unroll
         for (int i = 0; i < 3; i++) {
-            int idx = lane + 32 * i, rr = idx / S::kRowChunks, c = idx % S::kRowChunks;
-            csrc[i] = row_ptr(rr);
-            cdst[i] = ring + (uint32_t)(rr * S::kPitch + c * 16);
+            int idx = lane + 32 * i;
+            crow[i] = idx / S::kRowChunks;
+            cdst[i] = ring + (uint32_t)(crow[i] * S::kPitch + (idx % S::kRowChunks) * 16);
         }
-        const int nchunks = (nkb + S::kChunkSlices - 1) / S::kChunkSlices;
-        auto issue = [&](int chunk) {                                        // K slices 2*chunk, 2*chunk + 1
+        auto issue = [&](const uint8_t* const (&csrc)[3], int chunk) {       // K slices 2*chunk, 2*chunk + 1
             if (chunk < nchunks) {
                 const uint32_t bsel = (uint32_t)(chunk & 1) * kBufBytes;
 #pragma unroll
@@ -150,7 +165,6 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
         // decode role: lane -> (row r = lane >> 1, half-slice h = lane & 1)
         const int r = lane >> 1, h = lane & 1;
         const int prow = trow0 + r;
-        const uint32_t a_lo = (uint32_t)(uintptr_t)row_ptr(r) & 15u;        // alignment of the row start
         const uint32_t ring_row = ring + (uint32_t)r * S::kPitch + (uint32_t)h * kBlockBytes;
         const uint32_t sw = (uint32_t)(prow & 7);
         const uint32_t a_row = (uint32_t)tile * S::kATile + (uint32_t)(prow >> 3) * 1024u + (uint32_t)(prow & 7) * 128u;
@@ -158,117 +172,171 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
 #pragma unroll
         for (int c = 0; c < 4; c++) st_off[c] = a_base + a_row + ((((uint32_t)(4 * h + c)) ^ sw) << 4);
         const bool ragged = (nblk & 1) != 0;                                 // K is not a multiple of 64
-        issue(0);
-        for (int chunk = 0; chunk < nchunks; chunk++) {
-            issue(chunk + 1);                                                // other buffer: decoded one chunk ago
-            cp_async_wait<1>();                                              // this chunk's copies have landed
-            __syncwarp();
-            // the row's bytes for this chunk start ((a_lo + chunk * kChunkBytes) & 15) into its ring slot
-            const uint32_t rbuf = ring_row + (uint32_t)(chunk & 1) * kBufBytes + ((a_lo + (uint32_t)chunk * kChunkBytes) & 15u);
-#pragma unroll
-            for (int kk = 0; kk < S::kChunkSlices; kk++) {
-                const int kb = chunk * S::kChunkSlices + kk;
-                if (kb < nkb) {
-                    uint32_t v[16];
-                    const uint32_t at = rbuf + (uint32_t)kk * kSliceBytes;
-                    const uint32_t a4 = at & ~3u, sh = (at & 3u) * 8u;
-                    uint32_t w[6];
-#pragma unroll
-                    for (int i = 0; i < (FMT == OCO_FMT_MXFP4 ? 5 : 6); i++)
-                        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w[i]) : "r"(a4 + 4u * i));
-                    if (FMT == OCO_FMT_MXFP4) decode_mxfp4_block(w, sh, v);
-                    else decode_q4_0_block(w, sh, v);
-                    if (ragged && h && kb == nkb - 1) {                      // the slice's second block is past K
-#pragma unroll
-                        for (int i = 0; i < 16; i++) v[i] = 0;
-                    }
-                    const int s = kb % S::kAStages;
-                    if (lane == 0) mbar_wait(empty_a(s), ((uint32_t)(kb / S::kAStages) & 1u) ^ 1u, abort_flag, p.status);
-                    __syncwarp();
-                    const uint32_t soff = (uint32_t)s * S::kAStage;
-#pragma unroll
-                    for (int c = 0; c < 4; c++)
-                        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(st_off[c] + soff), "r"(v[4 * c]),
-                                     "r"(v[4 * c + 1]), "r"(v[4 * c + 2]), "r"(v[4 * c + 3]) : "memory");
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(full_a(s));
-                }
-            }
-        }
-        cp_async_wait<0>();
-        // ===== epilogue ===========================================================================
-        if (lane == 0) mbar_wait(accum_bar, 0u, abort_flag, p.status);
-        __syncwarp();
-        tc_fence_after();
-        // warp -> tensor-memory lanes 32 * (warp & 3) (tile rows), columns [64 * (warp >> 2), +64)
+        // epilogue role: warp -> tensor-memory lanes 32 * (warp & 3) (tile rows), columns [64 * (warp >> 2), +64)
         const int erow = (warp & 3) * 32 + lane;
         const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t c_begin = (uint32_t)(warp >> 2) * 64u;
-        const uint32_t c_end = min(nv, c_begin + 64u);
-        const int fa = f0 + erow, fb = GATED ? fa : fa + 128;        // features of accumulator 0 / 1
-        float bias_a = 0.f, bias_b = 0.f;
-        if (fa < p.n && p.b0) bias_a = bf16_round(p.b0[(size_t)expert * p.n + fa]);
-        if (GATED) {
-            if (EPI == kEpiSwigluF16 && fa < p.n) bias_b = bf16_round(__fadd_rn(p.b1[(size_t)expert * p.n + fa], 1.0f));
-        } else if (fb < p.n && p.b0) {
-            bias_b = bf16_round(p.b0[(size_t)expert * p.n + fb]);
-        }
-        const int col_a = EPI == kEpiDownBf16 ? fa : operand_pos(FMT, fa);
-        const int col_b = EPI == kEpiDownBf16 ? fb : operand_pos(FMT, fb);
-        for (uint32_t c = c_begin; c < c_end; c += 16) {
-            uint32_t ra[16], rb[16];
-            tmem_ld16(taddr + c, ra);
-            tmem_ld16(taddr + NT + c, rb);
-            tmem_ld_wait();
+
+        const uint8_t* csrc[3];
+        Item cur;
+        bool started = false;                 // the first ring buffer of `cur` is already on its way
+        int seq = 0;
+        for (int item = blockIdx.x; item < total; item += gridDim.x, seq++) {
+            if (!started) {
+                cur = load_item(item);
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-                if (c + j < nv) {
-                    const size_t orow = (size_t)out_rows[c + j] * p.n;
-                    const float a = __fadd_rn(__uint_as_float(ra[j]), bias_a);
-                    const float b = __fadd_rn(__uint_as_float(rb[j]), bias_b);
-                    if (GATED) {
-                        if (fa < p.n) p.out[orow + col_a] = epilogue_value<EPI>(a, b);
-                    } else {
-                        if (fa < p.n) p.out[orow + col_a] = epilogue_value<EPI>(a, 0.f);
-                        if (fb < p.n) p.out[orow + col_b] = epilogue_value<EPI>(b, 0.f);
+                for (int i = 0; i < 3; i++) csrc[i] = row_ptr(cur, crow[i]);
+                issue(csrc, 0);
+            }
+            const uint32_t a_lo = (uint32_t)(uintptr_t)row_ptr(cur, r) & 15u;   // alignment of the row start
+            const int g0 = seq * nkb;                                           // slices of earlier items
+            for (int chunk = 0; chunk < nchunks; chunk++) {
+                issue(csrc, chunk + 1);                                          // other buffer: decoded one chunk ago
+                cp_async_wait<1>();                                              // this chunk's copies have landed
+                __syncwarp();
+                // the row's bytes for this chunk start ((a_lo + chunk * kChunkBytes) & 15) into its ring slot
+                const uint32_t rbuf = ring_row + (uint32_t)(chunk & 1) * kBufBytes + ((a_lo + (uint32_t)chunk * kChunkBytes) & 15u);
+#pragma unroll
+                for (int kk = 0; kk < S::kChunkSlices; kk++) {
+                    const int kb = chunk * S::kChunkSlices + kk;
+                    if (kb < nkb) {
+                        uint32_t v[16];
+                        const uint32_t at = rbuf + (uint32_t)kk * kSliceBytes;
+                        const uint32_t a4 = at & ~3u, sh = (at & 3u) * 8u;
+                        uint32_t w[6];
+#pragma unroll
+                        for (int i = 0; i < (FMT == OCO_FMT_MXFP4 ? 5 : 6); i++)
+                            asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w[i]) : "r"(a4 + 4u * i));
+                        if (FMT == OCO_FMT_MXFP4) decode_mxfp4_block(w, sh, v);
+                        else decode_q4_0_block(w, sh, v);
+                        if (ragged && h && kb == nkb - 1) {                      // the slice's second block is past K
+#pragma unroll
+                            for (int i = 0; i < 16; i++) v[i] = 0;
+                        }
+                        const int g = g0 + kb, s = g % S::kAStages;
+                        if (lane == 0) mbar_wait(empty_a(s), ((uint32_t)(g / S::kAStages) & 1u) ^ 1u, abort_flag, p.status);
+                        __syncwarp();
+                        const uint32_t soff = (uint32_t)s * S::kAStage;
+#pragma unroll
+                        for (int c = 0; c < 4; c++)
+                            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(st_off[c] + soff), "r"(v[4 * c]),
+                                         "r"(v[4 * c + 1]), "r"(v[4 * c + 2]), "r"(v[4 * c + 3]) : "memory");
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(full_a(s));
                     }
                 }
             }
+            cp_async_wait<0>();
+            // the next item's first bytes travel while this item's accumulators are drained
+            const Item done = cur;
+            started = item + (int)gridDim.x < total;
+            if (started) {
+                cur = load_item(item + gridDim.x);
+#pragma unroll
+                for (int i = 0; i < 3; i++) csrc[i] = row_ptr(cur, crow[i]);
+                issue(csrc, 0);
+            }
+            // ===== epilogue of `done` ================================================================
+            asm volatile("bar.sync 1, %0;" ::"n"(S::kProducerWarps * 32) : "memory");                    // nobody still reads the row map of the item before
+            for (uint32_t i = tid; i < done.nv; i += S::kProducerWarps * 32)
+                out_rows[i] = (EPI == kEpiDownBf16 && p.route_of_row) ? p.route_of_row[done.row0 + i] : done.row0 + i;
+            asm volatile("bar.sync 1, %0;" ::"n"(S::kProducerWarps * 32) : "memory");
+            if (lane == 0) mbar_wait(accum_bar, (uint32_t)seq & 1u, abort_flag, p.status);
+            __syncwarp();
+            tc_fence_after();
+            const uint32_t c_end = min(done.nv, c_begin + 64u);
+            const int fa = done.f0 + erow, fb = GATED ? fa : fa + 128;        // features of accumulator 0 / 1
+            float bias_a = 0.f, bias_b = 0.f;
+            if (fa < p.n && p.b0) bias_a = bf16_round(p.b0[(size_t)done.expert * p.n + fa]);
+            if (GATED) {
+                if (EPI == kEpiSwigluF16 && fa < p.n) bias_b = bf16_round(__fadd_rn(p.b1[(size_t)done.expert * p.n + fa], 1.0f));
+            } else if (fb < p.n && p.b0) {
+                bias_b = bf16_round(p.b0[(size_t)done.expert * p.n + fb]);
+            }
+            const int col_a = EPI == kEpiDownBf16 ? fa : operand_pos(FMT, fa);
+            const int col_b = EPI == kEpiDownBf16 ? fb : operand_pos(FMT, fb);
+            for (uint32_t c = c_begin; c < c_end; c += 16) {
+                uint32_t ra[16], rb[16];
+                tmem_ld16(taddr + c, ra);
+                tmem_ld16(taddr + NT + c, rb);
+                tmem_ld_wait();
+                if (c + 16 >= c_end) {                                        // last read of this warp's columns:
+                    tc_fence_before();                                        // the MMA warp may overwrite them while
+                    __syncwarp();                                             // the values are finished in registers
+                    if (lane == 0) mbar_arrive(tmem_free);
+                }
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    if (c + j < done.nv) {
+                        const size_t orow = (size_t)out_rows[c + j] * p.n;
+                        const float a = __fadd_rn(__uint_as_float(ra[j]), bias_a);
+                        const float b = __fadd_rn(__uint_as_float(rb[j]), bias_b);
+                        if (GATED) {
+                            if (fa < p.n) p.out[orow + col_a] = epilogue_value<EPI>(a, b);
+                        } else {
+                            if (fa < p.n) p.out[orow + col_a] = epilogue_value<EPI>(a, 0.f);
+                            if (fb < p.n) p.out[orow + col_b] = epilogue_value<EPI>(b, 0.f);
+                        }
+                    }
+                }
+            }
+            if (c_begin >= c_end) {                                           // no live column in this warp's range
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_free);
+            }
         }
-        tc_fence_before();
     } else if (warp == S::kMmaWarp) {
         if (lane == 0) {
             // ===== MMA issue ======================================================================
-            const uint32_t idesc = umma_idesc_f16(n_mma);
-            for (int kb = 0; kb < nkb; kb++) {
-                const int sa = kb % S::kAStages, sb = kb % S::kBStages;
-                mbar_wait(full_a(sa), (uint32_t)(kb / S::kAStages) & 1u, abort_flag, p.status);
-                mbar_wait(full_b(sb), (uint32_t)(kb / S::kBStages) & 1u, abort_flag, p.status);
-                tc_fence_after();
-                const uint32_t a_stage = a_base + (uint32_t)sa * S::kAStage;
-                const uint64_t a0 = umma_desc(a_stage), a1 = umma_desc(a_stage + S::kATile);
-                const uint64_t b = umma_desc(b_base + (uint32_t)sb * S::kBStage);
-#pragma unroll
-                for (int kk = 0; kk < 4; kk++) {
-                    const uint32_t acc = (kb | kk) != 0 ? 1u : 0u;
-                    umma_f16(tmem_base, a0 + 2u * kk, b + 2u * kk, idesc, acc);
-                    umma_f16(tmem_base + NT, a1 + 2u * kk, b + 2u * kk, idesc, acc);
+            int seq = 0;
+            for (int item = blockIdx.x; item < total; item += gridDim.x, seq++) {
+                const Item it = load_item(item);
+                const uint32_t n_mma = max(16u, (it.nv + 15u) & ~15u);
+                const uint32_t idesc = umma_idesc_f16(n_mma);
+                if (seq > 0) {                                                // the accumulators of the item before are drained
+                    mbar_wait(tmem_free, (uint32_t)(seq - 1) & 1u, abort_flag, p.status);
+                    tc_fence_after();
                 }
-                umma_commit(empty_a(sa));
-                umma_commit(empty_b(sb));
+                const int g0 = seq * nkb;
+                for (int kb = 0; kb < nkb; kb++) {
+                    const int g = g0 + kb, sa = g % S::kAStages, sb = g % S::kBStages;
+                    mbar_wait(full_a(sa), (uint32_t)(g / S::kAStages) & 1u, abort_flag, p.status);
+                    mbar_wait(full_b(sb), (uint32_t)(g / S::kBStages) & 1u, abort_flag, p.status);
+                    tc_fence_after();
+                    const uint32_t a_stage = a_base + (uint32_t)sa * S::kAStage;
+                    const uint64_t a0 = umma_desc(a_stage), a1 = umma_desc(a_stage + S::kATile);
+                    const uint64_t b = umma_desc(b_base + (uint32_t)sb * S::kBStage);
+#pragma unroll
+                    for (int kk = 0; kk < 4; kk++) {
+                        const uint32_t acc = (kb | kk) != 0 ? 1u : 0u;
+                        umma_f16(tmem_base, a0 + 2u * kk, b + 2u * kk, idesc, acc);
+                        umma_f16(tmem_base + NT, a1 + 2u * kk, b + 2u * kk, idesc, acc);
+                    }
+                    umma_commit(empty_a(sa));
+                    umma_commit(empty_b(sb));
+                }
+                umma_commit(accum_bar);
             }
-            umma_commit(accum_bar);
-            mbar_wait(accum_bar, 0u, abort_flag, p.status);      // every MMA has retired
+            if (seq > 0) mbar_wait(accum_bar, (uint32_t)(seq - 1) & 1u, abort_flag, p.status);   // every MMA has retired
             tc_fence_before();
         }
     } else if (lane == 0) {
         // ===== B tiles by TMA =========================================================================
-        for (int kb = 0; kb < nkb; kb++) {
-            const int sb = kb % S::kBStages;
-            mbar_wait(empty_b(sb), ((uint32_t)(kb / S::kBStages) & 1u) ^ 1u, abort_flag, p.status);
-            mbar_arrive_expect_tx(full_b(sb), (uint32_t)S::kBStage);
-            tma_load_2d(b_base + (uint32_t)sb * S::kBStage, &tmap_b, kb * 64, (int)row0, full_b(sb));
+        int seq = 0;
+        for (int item = blockIdx.x; item < total; item += gridDim.x, seq++) {
+            const Item it = load_item(item);
+            const int g0 = seq * nkb;
+            // the smallest box (32, 64, 128 or 256 rows of 64 halves) that holds the tile's live rows
+            const CUtensorMap* box = it.nv <= 32 ? &tmap_b32 : it.nv <= 64 ? &tmap_b64 : it.nv <= 128 ? &tmap_b128 : &tmap_b;
+            const uint32_t box_bytes = (it.nv <= 32 ? 32u : it.nv <= 64 ? 64u : it.nv <= 128 ? 128u : 256u) * 128u;
+            for (int kb = 0; kb < nkb; kb++) {
+                const int g = g0 + kb, sb = g % S::kBStages;
+                mbar_wait(empty_b(sb), ((uint32_t)(g / S::kBStages) & 1u) ^ 1u, abort_flag, p.status);
+                mbar_arrive_expect_tx(full_b(sb), box_bytes);
+                tma_load_2d(b_base + (uint32_t)sb * S::kBStage, box, kb * 64, (int)it.row0, full_b(sb));
+            }
         }
     }
     __syncthreads();

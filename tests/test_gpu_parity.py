@@ -115,9 +115,23 @@ def test_gpt_oss_wide_tiles(moe, oracle, hidden, ffn, tokens):
 
 
 @pytest.mark.parametrize("tokens", [100, 250], ids=["nt64", "nt128"])
-def test_gpt_oss_mid_tiles(moe, oracle, tokens):
-    """50 and 125 routes per expert on average: the 64- and 128-route tiles of the narrow tile kernel."""
+@pytest.mark.parametrize("narrow", [False, True], ids=["wide", "generic"])
+def test_gpt_oss_mid_tiles(moe, oracle, tokens, narrow, monkeypatch):
+    """50 and 125 routes per expert on average: partly filled 256-route tiles of the wide kernel (TMA
+    boxes of 64 and 128 rows), and the 64- and 128-route tiles of the generic tile kernel (the ones
+    Q4_K layers run) when the wide kernel is switched off."""
+    if narrow:
+        monkeypatch.setenv("OCO_MOE_NARROW_TILES", "1")
     layer = synth.make_layer(synth.ARCH_GPT_OSS, 320, 288, 4, 2, synth.FMT_MXFP4, seed=33)
+    check_layer(moe, oracle, layer, tokens, seed=tokens)
+
+
+@pytest.mark.parametrize("tokens", [40, 9], ids=["avg20", "avg9"])
+def test_nemotron_sparse_wide_tiles(moe, oracle, tokens):
+    """Just above the few-token limit of eight routes per expert: every expert is one thinly filled
+    256-route tile (32-row TMA boxes), shared expert as one dense tile."""
+    layer = synth.make_layer(synth.ARCH_NEMOTRON, 256, 160, 4, 2, synth.FMT_Q4_0, seed=34, shared_ffn=320,
+                             normalize=True, scale=2.5)
     check_layer(moe, oracle, layer, tokens, seed=tokens)
 
 
@@ -143,7 +157,7 @@ def test_gpt_oss_forced_routes_reference_ids(moe, oracle):
     assert np.array_equal(routing["ids"], np.tile(np.array([31, 7, 22, 30], np.uint32), (tokens, 1)))
     tiles = routing["tiles"]
     nt = int(tiles[1, 1])                      # first expert's second tile starts one tile further
-    assert nt in (32, 64, 128)
+    assert nt in (32, 64, 128, 256)
     per = -(-tokens // nt)
     assert np.array_equal(tiles[:, 0], np.repeat([7, 22, 30, 31], per))
     assert np.array_equal(tiles[:, 1], np.tile(np.arange(per) * nt, 4))
@@ -334,9 +348,12 @@ def test_add_norm_forward(moe, oracle, arch, full_layer, rows):
         assert rel_l2(out, ref.out) <= REL_L2
 
 
-def test_few_tokens_tile_kernels(moe, oracle, monkeypatch):
-    """The same small batches through the tile kernels (the path they took before the streamed one)."""
+@pytest.mark.parametrize("narrow", [False, True], ids=["wide", "generic"])
+def test_few_tokens_tile_kernels(moe, oracle, monkeypatch, narrow):
+    """The same small batches through the tile kernels instead of the streamed ones."""
     monkeypatch.setenv("OCO_MOE_NO_BATCH", "1")
+    if narrow:
+        monkeypatch.setenv("OCO_MOE_NARROW_TILES", "1")
     layer = synth.make_layer(synth.ARCH_GPT_OSS, 640, 384, 32, 4, synth.FMT_MXFP4, seed=41)
     for tokens in (2, 12):
         check_layer(moe, oracle, layer, tokens, seed=300 + tokens)
