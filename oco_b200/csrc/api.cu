@@ -78,7 +78,7 @@ struct oco_moe_plan {
     bool no_batch_path = false;  // OCO_MOE_NO_BATCH=1: few tokens take the tile kernels too
     int batch_max_avg = 8;       // routes per expert (on average) up to which the streamed few-token kernels run
                                  // (measured: they win up to 16-32 at the gpt-oss shapes; OCO_MOE_BATCH_MAX_AVG overrides)
-    int wide_min_avg = 1;        // OCO_MOE_WIDE_MIN_AVG: routes per expert from which MXFP4 / Q4_0 layers take the 256-route tiles
+    int wide_min_avg = 1;        // OCO_MOE_WIDE_MIN_AVG: routes per expert from which layers take the 256-route tiles
     bool narrow_tiles = false;   // OCO_MOE_NARROW_TILES=1: keep the generic tile kernel for 256-route tiles too
     bool profiling = false;
     int n_marks = 0;
@@ -203,11 +203,11 @@ int make_row_map(oco_moe_plan* plan, CUtensorMap* map, void* base, uint64_t rows
     return OCO_OK;
 }
 
-// Route-tile height by the average number of routes per expert. The 32-element block formats take
-// the 256-route tiles of the wide kernel from `wide_min_avg` routes per expert on (its cost per tile
-// hardly depends on the live routes, and it decodes weights several times faster than the generic
-// kernel); Q4_K picks among the generic kernel's heights: taller tiles decode an expert's weights
-// fewer times, shorter ones waste fewer MMA columns on small experts.
+// Route-tile height by the average number of routes per expert. Layers take the 256-route tiles of
+// the wide kernel from `wide_min_avg` routes per expert on (its cost per tile hardly depends on the
+// live routes, and it decodes weights several times faster than the generic kernel). The generic
+// kernel (OCO_MOE_NARROW_TILES=1, and the CUDA-core cross-check) picks among its heights: taller
+// tiles decode an expert's weights fewer times, shorter ones waste fewer MMA columns on small experts.
 int pick_tile_index(int routes, int experts, int wide_min_avg) {
     int avg = routes / (experts > 0 ? experts : 1);
     if (avg >= wide_min_avg) return 3;
@@ -246,8 +246,8 @@ int launch_gemm(oco_moe_plan* plan, const GemmParams& gp, const CUtensorMap& map
     return OCO_OK;
 }
 
-// 256-route tiles of the 32-element block formats take the wide kernel (two A tiles per CTA,
-// coalesced weight streaming); the CUDA-core cross-check and Q4_K keep the generic one.
+// 256-route tiles take the wide kernel (two A tiles per CTA, coalesced weight streaming); the
+// CUDA-core cross-check keeps the generic one.
 template <int FMT, int EPI>
 int launch_gemm_wide(oco_moe_plan* plan, GemmParams gp, const CUtensorMap* maps, int max_tiles, int experts,
                      cudaStream_t st) {
@@ -262,7 +262,7 @@ int launch_gemm_wide(oco_moe_plan* plan, GemmParams gp, const CUtensorMap* maps,
     // persistent: one CTA per SM walks the (route tile, feature tile) items; never more CTAs than items can exist
     const int feats = (gp.n + (epi_gated(EPI) ? 127 : 255)) / (epi_gated(EPI) ? 128 : 256);
     const int grid = std::min(plan->sm_count, feats * max_tiles);
-    grouped_gemm_wide_kernel<FMT, EPI><<<grid, WideShape::kThreads, WideShape::kSmemBytes, st>>>(gp, maps[0], maps[1], maps[2], maps[3]);
+    grouped_gemm_wide_kernel<FMT, EPI><<<grid, WideShapeT<FMT>::kThreads, WideShapeT<FMT>::kSmemBytes, st>>>(gp, maps[0], maps[1], maps[2], maps[3]);
     plan->launches++;
     CK(cudaGetLastError());
     return OCO_OK;
@@ -271,10 +271,8 @@ int launch_gemm_wide(oco_moe_plan* plan, GemmParams gp, const CUtensorMap* maps,
 template <int FMT, int EPI>
 int launch_gemm_nt(oco_moe_plan* plan, const GemmParams& gp, const CUtensorMap* maps, int nt_index, int max_tiles,
                    cudaStream_t st) {
-    if constexpr (FMT != OCO_FMT_Q4_K) {
-        if (nt_index == 3 && plan->d.gemm_impl == 0 && !plan->narrow_tiles)
-            return launch_gemm_wide<FMT, EPI>(plan, gp, maps, max_tiles, gp.tiles ? plan->d.experts : 1, st);
-    }
+    if (nt_index == 3 && plan->d.gemm_impl == 0 && !plan->narrow_tiles)
+        return launch_gemm_wide<FMT, EPI>(plan, gp, maps, max_tiles, gp.tiles ? plan->d.experts : 1, st);
     switch (nt_index) {
         case 0: return launch_gemm<FMT, EPI, 32>(plan, gp, maps[0], max_tiles, st);
         case 1: return launch_gemm<FMT, EPI, 64>(plan, gp, maps[1], max_tiles, st);
@@ -526,7 +524,7 @@ int stage_experts(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, in
             return OCO_OK;
         }
     }
-    const int nt_index = pick_tile_index(R, E, FMT == OCO_FMT_Q4_K || plan->narrow_tiles ? 192 : plan->wide_min_avg);
+    const int nt_index = pick_tile_index(R, E, plan->narrow_tiles ? 192 : plan->wide_min_avg);
     const int NT = kTileSizes[nt_index];
     plan->last_tile_rows = NT;
     mark(plan, st, "route_plan");
@@ -596,7 +594,7 @@ int forward_tiled(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int
         mark(plan, st, "shared_expert");
         permute_rows_kernel<<<rows, 256, 0, st>>>(x, nullptr, 1, H, FMT == OCO_FMT_Q4_K ? 32 : 16, ws.xh);  // identity gather
         plan->launches++;
-        const int snt = pick_tile_index(rows, 1, FMT == OCO_FMT_Q4_K || plan->narrow_tiles ? 192 : plan->wide_min_avg);
+        const int snt = pick_tile_index(rows, 1, plan->narrow_tiles ? 192 : plan->wide_min_avg);
         const int SNT = kTileSizes[snt];
         GemmParams su{};
         su.w0 = plan->w.shared_up_w; su.n = S; su.K = H; su.row_bytes = plan->shared_up_row_bytes;

@@ -21,28 +21,37 @@
 
 namespace oco {
 
-struct WideShape {
+// Per format: MXFP4 / Q4_0 rows are 32-element blocks of 17 / 18 bytes and a ring buffer holds two
+// K slices of a row; a Q4_K row is 144-byte super-blocks of 256 elements and a ring buffer holds one
+// super-block (four K slices), which leaves room for two A stages instead of three.
+template <int FMT>
+struct WideShapeT {
+    static constexpr bool kSuper = FMT == OCO_FMT_Q4_K;
     static constexpr int kNT = 256;                   // routes per tile (MMA N)
     static constexpr int kProducerWarps = 16;         // 256 row streams / 16 rows per warp
     static constexpr int kMmaWarp = 16, kTmaWarp = 17;
     static constexpr int kThreads = 18 * 32;
     static constexpr int kATile = 128 * 128;          // one A tile: 128 rows x 64 halves
     static constexpr int kAStage = 2 * kATile;        // both A tiles
-    static constexpr int kAStages = 3;
+    static constexpr int kAStages = kSuper ? 2 : 3;
     static constexpr int kBStage = kNT * 128;
     static constexpr int kBStages = 2;
-    static constexpr int kChunkSlices = 2;            // K slices per raw-ring buffer
-    static constexpr int kPitch = 112;                // ring bytes per row: 2 slices (<= 72 B) + 15 alignment, 16-byte chunks
-    static constexpr int kRowChunks = 6;              // 16-byte chunks fetched per row per buffer
+    static constexpr int kChunkSlices = kSuper ? 4 : 2;   // K slices per raw-ring buffer
+    static constexpr int kChunkBytes = kSuper ? 144 : 4 * (FMT == OCO_FMT_MXFP4 ? 17 : 18);   // packed bytes of them, per row
+    static constexpr int kRowChunks = (kChunkBytes + 15 + 15) / 16;   // 16-byte pieces fetched per row per buffer (any alignment)
+    static constexpr int kPitch = 16 * (kRowChunks | 1);  // ring bytes per row: an odd number of pieces spreads the rows over the banks
+    static constexpr int kCopies = 16 * kRowChunks / 32;  // pieces per lane per buffer
     static constexpr int kRingBufs = 2;
     static constexpr int kRingWarp = kRingBufs * 16 * kPitch;
     static constexpr int kRing = kProducerWarps * kRingWarp;
     static constexpr int kCtrl = 512 + kNT * 4;       // barriers, tmem slot, abort flag, row map
     static constexpr int kSmemBytes = kAStages * kAStage + kBStages * kBStage + kRing + kCtrl + 1024;
     static constexpr int kTmemCols = 512;
+    static_assert(16 * kRowChunks % 32 == 0, "pieces of a buffer divide over the lanes");
+    static_assert(kSmemBytes <= 232448, "shared memory of one CTA");
 };
 
-// FMT: MXFP4 or Q4_0 (32-element blocks of 17 / 18 bytes). EPI as in gemm.cuh.
+// FMT: MXFP4, Q4_0 or Q4_K. EPI as in gemm.cuh.
 // Persistent: grid = number of SMs; CTA c takes work items c, c + grid, ... where an item is
 // (route tile, feature tile) with the feature tile running fastest, so that the CTAs running at
 // the same time share a route tile's B rows in L2. Barriers, tensor memory and rings are set up
@@ -51,14 +60,15 @@ struct WideShape {
 // warp waits for the drain (`tmem_free`) before it overwrites them. `w_end`: first byte past the
 // 16-byte-aligned envelope of the weight tensors (no copy starts at or beyond it).
 template <int FMT, int EPI>
-__global__ void __launch_bounds__(WideShape::kThreads, 1)
+__global__ void __launch_bounds__(WideShapeT<FMT>::kThreads, 1)
 grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_b32,
                          const __grid_constant__ CUtensorMap tmap_b64, const __grid_constant__ CUtensorMap tmap_b128,
                          const __grid_constant__ CUtensorMap tmap_b) {
-    using S = WideShape;
+    using S = WideShapeT<FMT>;
     constexpr bool GATED = epi_gated(EPI);
     constexpr int NT = S::kNT;
-    constexpr int kBlockBytes = FMT == OCO_FMT_MXFP4 ? 17 : 18;
+    constexpr bool SUPER = S::kSuper;                                  // Q4_K: 144-byte super-blocks of four K slices
+    constexpr int kBlockBytes = FMT == OCO_FMT_MXFP4 ? 17 : 18;        // the 32-element formats
     constexpr int kSliceBytes = 2 * kBlockBytes;
     constexpr int kFeatPerItem = GATED ? 128 : 256;
     extern __shared__ unsigned char smem_raw[];
@@ -130,7 +140,8 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
         const uint8_t* wmat = (GATED && tile) ? p.w1 : p.w0;
         const int trow0 = (warp & 7) * 16;                           // first tile row of this warp
         const uint8_t* w_end = (GATED && tile) ? p.w1_end : p.w0_end;
-        constexpr uint32_t kChunkBytes = S::kChunkSlices * kSliceBytes;      // packed bytes per row per buffer
+        constexpr uint32_t kChunkBytes = S::kChunkBytes;                     // packed bytes per row per buffer
+        constexpr int NC = S::kCopies;
         constexpr uint32_t kBufBytes = 16 * S::kPitch;
         const uint32_t ring = ring_base + (uint32_t)warp * S::kRingWarp;
         const int nchunks = (nkb + S::kChunkSlices - 1) / S::kChunkSlices;
@@ -140,20 +151,20 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
             int f = min(feat0 + trow0 + r, p.n - 1);
             return wmat + ((size_t)it.expert * p.n + f) * p.row_bytes;
         };
-        // copy role: three 16-byte chunks per buffer: chunk index (lane + 32 i) -> (row, column)
-        uint32_t cdst[3];
-        int crow[3];
+        // copy role: NC 16-byte pieces per buffer: piece index (lane + 32 i) -> (row, column)
+        uint32_t cdst[NC];
+        int crow[NC];
 #pragma unroll
-        for (int i = 0; i < 3; i++) {
+        for (int i = 0; i < NC; i++) {
             int idx = lane + 32 * i;
             crow[i] = idx / S::kRowChunks;
             cdst[i] = ring + (uint32_t)(crow[i] * S::kPitch + (idx % S::kRowChunks) * 16);
         }
-        auto issue = [&](const uint8_t* const (&csrc)[3], int chunk) {       // K slices 2*chunk, 2*chunk + 1
+        auto issue = [&](const uint8_t* const (&csrc)[NC], int chunk) {      // the K slices of ring chunk `chunk`
             if (chunk < nchunks) {
                 const uint32_t bsel = (uint32_t)(chunk & 1) * kBufBytes;
 #pragma unroll
-                for (int i = 0; i < 3; i++) {
+                for (int i = 0; i < NC; i++) {
                     // 16-byte-aligned envelope of the row's bytes for this chunk, column (cdst offset)
                     const uint8_t* a16 = (const uint8_t*)(((uintptr_t)(csrc[i] + (size_t)chunk * kChunkBytes)) & ~(uintptr_t)15) +
                                          ((cdst[i] - ring) % S::kPitch);
@@ -165,19 +176,19 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
         // decode role: lane -> (row r = lane >> 1, half-slice h = lane & 1)
         const int r = lane >> 1, h = lane & 1;
         const int prow = trow0 + r;
-        const uint32_t ring_row = ring + (uint32_t)r * S::kPitch + (uint32_t)h * kBlockBytes;
+        const uint32_t ring_row = ring + (uint32_t)r * S::kPitch + (SUPER ? 0u : (uint32_t)h * kBlockBytes);
         const uint32_t sw = (uint32_t)(prow & 7);
         const uint32_t a_row = (uint32_t)tile * S::kATile + (uint32_t)(prow >> 3) * 1024u + (uint32_t)(prow & 7) * 128u;
         uint32_t st_off[4];
 #pragma unroll
         for (int c = 0; c < 4; c++) st_off[c] = a_base + a_row + ((((uint32_t)(4 * h + c)) ^ sw) << 4);
-        const bool ragged = (nblk & 1) != 0;                                 // K is not a multiple of 64
+        const bool ragged = !SUPER && (nblk & 1) != 0;                       // K is not a multiple of 64
         // epilogue role: warp -> tensor-memory lanes 32 * (warp & 3) (tile rows), columns [64 * (warp >> 2), +64)
         const int erow = (warp & 3) * 32 + lane;
         const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t c_begin = (uint32_t)(warp >> 2) * 64u;
 
-        const uint8_t* csrc[3];
+        const uint8_t* csrc[NC];
         Item cur;
         bool started = false;                 // the first ring buffer of `cur` is already on its way
         int seq = 0;
@@ -185,7 +196,7 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
             if (!started) {
                 cur = load_item(item);
 #pragma unroll
-                for (int i = 0; i < 3; i++) csrc[i] = row_ptr(cur, crow[i]);
+                for (int i = 0; i < NC; i++) csrc[i] = row_ptr(cur, crow[i]);
                 issue(csrc, 0);
             }
             const uint32_t a_lo = (uint32_t)(uintptr_t)row_ptr(cur, r) & 15u;   // alignment of the row start
@@ -196,19 +207,41 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
                 __syncwarp();
                 // the row's bytes for this chunk start ((a_lo + chunk * kChunkBytes) & 15) into its ring slot
                 const uint32_t rbuf = ring_row + (uint32_t)(chunk & 1) * kBufBytes + ((a_lo + (uint32_t)chunk * kChunkBytes) & 15u);
+                // Q4_K: the super-block's header (d, dmin, twelve scale bytes) serves its four slices
+                uint32_t hdr[4];
+                if (SUPER) {
+                    const uint32_t a4 = rbuf & ~3u, sh = (rbuf & 3u) * 8u;
+                    uint32_t w[5];
+#pragma unroll
+                    for (int i = 0; i < 5; i++) asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w[i]) : "r"(a4 + 4u * i));
+#pragma unroll
+                    for (int i = 0; i < 4; i++) hdr[i] = __funnelshift_r(w[i], w[i + 1], sh);
+                }
 #pragma unroll
                 for (int kk = 0; kk < S::kChunkSlices; kk++) {
                     const int kb = chunk * S::kChunkSlices + kk;
                     if (kb < nkb) {
                         uint32_t v[16];
-                        const uint32_t at = rbuf + (uint32_t)kk * kSliceBytes;
-                        const uint32_t a4 = at & ~3u, sh = (at & 3u) * 8u;
-                        uint32_t w[6];
+                        if (SUPER) {
+                            // code bytes 16 h .. 16 h + 15 of the slice's sub-block pair
+                            const uint32_t at = rbuf + 16u + 32u * (uint32_t)kk + 16u * (uint32_t)h;
+                            const uint32_t a4 = at & ~3u, sh = (at & 3u) * 8u;
+                            uint32_t w[5], codes[4];
 #pragma unroll
-                        for (int i = 0; i < (FMT == OCO_FMT_MXFP4 ? 5 : 6); i++)
-                            asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w[i]) : "r"(a4 + 4u * i));
-                        if (FMT == OCO_FMT_MXFP4) decode_mxfp4_block(w, sh, v);
-                        else decode_q4_0_block(w, sh, v);
+                            for (int i = 0; i < 5; i++) asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w[i]) : "r"(a4 + 4u * i));
+#pragma unroll
+                            for (int i = 0; i < 4; i++) codes[i] = __funnelshift_r(w[i], w[i + 1], sh);
+                            decode_q4_k_half(hdr, codes, kk, v);
+                        } else {
+                            const uint32_t at = rbuf + (uint32_t)kk * kSliceBytes;
+                            const uint32_t a4 = at & ~3u, sh = (at & 3u) * 8u;
+                            uint32_t w[6];
+#pragma unroll
+                            for (int i = 0; i < (FMT == OCO_FMT_MXFP4 ? 5 : 6); i++)
+                                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w[i]) : "r"(a4 + 4u * i));
+                            if (FMT == OCO_FMT_MXFP4) decode_mxfp4_block(w, sh, v);
+                            else decode_q4_0_block(w, sh, v);
+                        }
                         if (ragged && h && kb == nkb - 1) {                      // the slice's second block is past K
 #pragma unroll
                             for (int i = 0; i < 16; i++) v[i] = 0;
@@ -234,7 +267,7 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
             if (started) {
                 cur = load_item(item + gridDim.x);
 #pragma unroll
-                for (int i = 0; i < 3; i++) csrc[i] = row_ptr(cur, crow[i]);
+                for (int i = 0; i < NC; i++) csrc[i] = row_ptr(cur, crow[i]);
                 issue(csrc, 0);
             }
             // ===== epilogue of `done` ================================================================

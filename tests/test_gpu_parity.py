@@ -34,8 +34,10 @@ def rel_l2(got_bits, ref_bits):
     return d / max(np.linalg.norm(r[fin]), 1e-30)
 
 
-def check_layer(moe, oracle, layer, tokens, seed, residual="normal", gemm_impl=0, mode=0, misalign=0):
+def check_layer(moe, oracle, layer, tokens, seed, residual="normal", gemm_impl=0, mode=0, misalign=0, x_scale=1.0):
     x, res = synth.make_tokens(layer.hidden, tokens, seed, residual)
+    if x_scale != 1.0:      # a power of two: keeps the half activations of wide synthetic layers finite
+        x = synth.f32_to_bf16_bits(synth.bf16_bits_to_f32(x) * np.float32(x_scale))
     ref = oracle.moe_forward(layer, x, res, mode=mode)
     out, routing = moe.run_layer(layer, x, res, gemm_impl=gemm_impl, misalign=misalign)
     assert np.array_equal(routing["ids"], ref.ids), "expert ids differ"
@@ -232,9 +234,23 @@ def test_sigmoid_router_reference_case(moe, oracle):
 
 
 @pytest.mark.parametrize("tokens", [1, 24, 200])
-def test_qwen_small(moe, oracle, tokens):
+@pytest.mark.parametrize("narrow", [False, True], ids=["wide", "generic"])
+def test_qwen_small(moe, oracle, tokens, narrow, monkeypatch):
+    if narrow:
+        if tokens == 1:
+            pytest.skip("single-token path has one implementation")
+        monkeypatch.setenv("OCO_MOE_NARROW_TILES", "1")
     layer = synth.make_layer(synth.ARCH_QWEN, 512, 256, 128, 8, synth.FMT_Q4_K, seed=13)
     check_layer(moe, oracle, layer, tokens, seed=tokens)
+
+
+@pytest.mark.parametrize("hidden,ffn,tokens", [(768, 512, 1300), (512, 768, 900), (256, 1280, 700)],
+                         ids=["k768", "k512", "k256"])
+def test_qwen_wide_tiles(moe, oracle, hidden, ffn, tokens):
+    """Q4_K through the 256-route tiles: experts spanning several route tiles, one and several
+    super-blocks per row, partial 128- and 256-row feature tiles."""
+    layer = synth.make_layer(synth.ARCH_QWEN, hidden, ffn, 8, 2, synth.FMT_Q4_K, seed=52)
+    check_layer(moe, oracle, layer, tokens, seed=tokens, x_scale=0.125)
 
 
 def test_host_buffer_entry_point(moe, oracle):
