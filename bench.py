@@ -46,10 +46,13 @@ WORKLOADS = {
 EXPERT_PARALLEL = {"gpt-oss-120b-prefill", "gpt-oss-120b-decode64"}
 # DRAM bytes (read + write) of one launch of the dominant kernels, from the ncu captures that are
 # summarised under profiles/ (grouped_gemm_wide_gpt-oss-20b-prefill.md,
-# token_kernels_gpt-oss-20b-decode.md); a profiler is never attached to a timed run.
+# grouped_gemm_wide_qwen3-30b-a3b-prefill.md, token_kernels_gpt-oss-20b-decode.md); a profiler is
+# never attached to a timed run.
 NCU_TRAFFIC = {
-    ("gpt-oss-20b-prefill", "up_tiles"): 330.0e6 + 40.9e6,
-    ("gpt-oss-20b-prefill", "down_tiles"): 188.9e6 + 29.4e6,
+    ("gpt-oss-20b-prefill", "up_tiles"): 334.5e6 + 38.7e6,
+    ("gpt-oss-20b-prefill", "down_tiles"): 190.6e6 + 28.9e6,
+    ("qwen3-30b-a3b-prefill", "up_tiles"): 243.4e6 + 7.2e6,
+    ("qwen3-30b-a3b-prefill", "down_tiles"): 119.6e6 + 8.1e6,
     ("gpt-oss-20b-decode", "expand"): 35.39e6,
     ("gpt-oss-20b-decode", "down_combine"): 17.76e6,
 }
