@@ -1,4 +1,4 @@
-// Wide grouped tile kernel for large experts: 256 routes x 256 weight rows per CTA.
+// Wide grouped tile kernel: 256 routes x 256 weight rows per work item.
 //
 // Same product as grouped_gemm_tc_kernel (D[feature, route] = sum_k W[feature, k] * X[row, k], half
 // operands, fp32 accumulators in tensor memory), reorganised around what limits it on B200:
@@ -11,9 +11,10 @@
 //     owns 16 consecutive weight rows and streams their packed bytes through a private
 //     shared-memory ring with 16-byte cp.async copies, consecutive lanes taking consecutive chunks
 //     of a row; each lane then decodes one 32-element block per 64-wide K slice from the ring.
-//   * A and B stages are separate rings: A tiles are produced in the SM just in time (2 stages),
-//     B tiles travel from L2 by TMA and get 3 stages. A dedicated warp issues the TMA loads, one
-//     thread issues the MMAs, each barrier has one arrival per warp.
+//   * A and B stages are separate rings: A tiles are produced in the SM just in time, B tiles travel
+//     from L2 by TMA (the smallest box that holds the tile's live routes). A dedicated warp issues
+//     the TMA loads, one thread issues the MMAs, each barrier has one arrival per warp.
+//   * The grid is persistent: one CTA per SM walks the list of (route tile, feature tile) items.
 //
 // All waits are bounded (see mbar_wait); a wait that gives up sets the status word.
 #pragma once
