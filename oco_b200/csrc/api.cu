@@ -13,6 +13,7 @@
 #include "batch.cuh"
 #include "gemm.cuh"
 #include "gemm_wide.cuh"
+#include <cmath>
 #include "plan.cuh"
 #include "router.cuh"
 
@@ -79,6 +80,7 @@ struct oco_moe_plan {
     int batch_max_avg = 8;       // routes per expert (on average) up to which the streamed few-token kernels run
                                  // (measured: they win up to 16-32 at the gpt-oss shapes; OCO_MOE_BATCH_MAX_AVG overrides)
     int wide_min_avg = 1;        // OCO_MOE_WIDE_MIN_AVG: routes per expert from which layers take the 256-route tiles
+    int router_block_min = 512;  // OCO_MOE_ROUTER_BLOCK_MIN: rows from which the register-blocked router kernel runs
     bool narrow_tiles = false;   // OCO_MOE_NARROW_TILES=1: keep the generic tile kernel for 256-route tiles too
     bool profiling = false;
     int n_marks = 0;
@@ -442,7 +444,32 @@ int stage_route(oco_moe_plan* plan, const uint16_t* x, int rows, cudaStream_t st
             CK(allow_smem(router_stream_kernel<ARCH, 24, 1>));
             stream_attr = true;
         }
-        {
+        if (rows >= plan->router_block_min && H % 8 == 0) {
+            // many tokens: four tokens x four experts per warp (router_block_kernel)
+            static bool block_attr = false;
+            if (!block_attr) {
+                CK(allow_smem(router_block_kernel<ARCH>));
+                block_attr = true;
+            }
+            const int ctas = (rows + kRouterBlockTokens - 1) / kRouterBlockTokens;
+            // one CTA per SM at a time: split the experts over 1, 2, 4 or 8 CTAs per token group so that the
+            // last round of CTAs is nearly full (the fewest splits that waste under 5 % of it, else the best)
+            int splits = 1;
+            double best = 1e9;
+            for (int sp = 1; sp <= 8 && E / sp >= 4 && E % (4 * sp) == 0; sp *= 2) {
+                const double rounds = (double)ctas * sp / plan->sm_count;
+                const double waste = std::ceil(rounds) / rounds;
+                if (waste < best - 1e-9) { best = waste; splits = sp; }
+                if (waste < 1.05) break;
+            }
+            router_block_kernel<ARCH><<<dim3(ctas, splits), 256, router_block_smem_bytes(H), st>>>(
+                x, rw, plan->w.router_b, rows, H, E, K, d.normalize, d.scale, ws.logits, ws.ids, ws.probs);
+            if (splits > 1) {
+                router_select_kernel<ARCH><<<rows, 32, 0, st>>>(ws.logits, ARCH == OCO_ARCH_NEMOTRON ? plan->w.router_b : nullptr, E, K,
+                                                               d.normalize, d.scale, ws.ids, ws.probs);
+                plan->launches++;
+            }
+        } else {
             // few tokens: split the experts over several CTAs per token group so that the grid fills the GPU
             const int ctas = (rows + 7) / 8;
             int splits = 1;
@@ -676,6 +703,7 @@ int oco_moe_plan_create(const oco_moe_desc* desc, oco_moe_plan** out) {
     }
     { const char* e = getenv("OCO_MOE_NARROW_TILES"); plan->narrow_tiles = e && e[0] == '1'; }
     { const char* e = getenv("OCO_MOE_WIDE_MIN_AVG"); if (e && atoi(e) > 0) plan->wide_min_avg = atoi(e); }
+    { const char* e = getenv("OCO_MOE_ROUTER_BLOCK_MIN"); if (e && atoi(e) > 0) plan->router_block_min = atoi(e); }
     { const char* e = getenv("OCO_MOE_NO_BATCH"); plan->no_batch_path = e && e[0] == '1'; }
     { const char* e = getenv("OCO_MOE_BATCH_MAX_AVG"); if (e && atoi(e) > 0) plan->batch_max_avg = atoi(e) < 64 ? atoi(e) : 64; }
     int dev = 0, sms = 0;

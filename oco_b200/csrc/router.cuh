@@ -404,4 +404,140 @@ __global__ void __launch_bounds__(256, TOK == 1 ? 2 : 1) router_stream_kernel(co
     }
 }
 
+
+// Many tokens, register-blocked: a warp takes FOUR tokens against FOUR experts at a time, so that
+// every shared-memory load feeds four FMAs per lane instead of one (router_stream_kernel reads one
+// router-row float4 per four FMAs and is bound by shared-memory bandwidth). The CTA's 32 token rows
+// stay in shared memory as bf16 (2 * H bytes each); the router rows stream through a ring of three
+// stages of 4 experts x 640 columns filled with cp.async. Lane l still owns columns 4 l + 128 i with
+// its four FMA chains in ascending i, the chains are joined as (a0 + a1) + (a2 + a3) and the lanes by
+// the same butterfly, so the logits are bit-identical to canonical_logit.
+// grid (ceil(T / 32), splits) as router_stream_kernel; hidden <= 3072 and a multiple of 8.
+// Dynamic shared memory: router_block_smem_bytes(H).
+constexpr int kRouterBlockTokens = 32, kRouterBlockCols = 640, kRouterBlockStages = 3;
+__host__ __device__ inline size_t router_block_smem_bytes(int H) {
+    return (size_t)kRouterBlockTokens * H * 2 + (size_t)kRouterBlockStages * 4 * kRouterBlockCols * 4;
+}
+
+template <int ARCH>
+__global__ void __launch_bounds__(256, 1) router_block_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w,
+                                                              const float* __restrict__ bias, int T, int H, int E, int K,
+                                                              int normalize, float scale, float* __restrict__ logits,
+                                                              uint32_t* __restrict__ ids, float* __restrict__ probs) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    constexpr int KC = kRouterBlockCols, STEPS = KC / 128;
+    uint16_t* xs = reinterpret_cast<uint16_t*>(smem);                                   // [32][H] bf16
+    float* ring = reinterpret_cast<float*>(smem + (size_t)kRouterBlockTokens * H * 2);  // [3][4][KC]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = blockIdx.x * kRouterBlockTokens;
+    const int e_begin = (int)(((long long)blockIdx.y * E) / gridDim.y), e_end = (int)(((long long)(blockIdx.y + 1) * E) / gridDim.y);
+    const int nblocks = (e_end - e_begin + 3) / 4;          // expert blocks of this CTA
+    const int nkc = (H + KC - 1) / KC;                      // column chunks of a router row
+    const int steps = nblocks * nkc;
+
+    // the token rows (rows past T are zero)
+    {
+        const int per_row = H / 8;                          // 16-byte pieces
+        for (int c = threadIdx.x; c < kRouterBlockTokens * per_row; c += 256) {
+            const int r = c / per_row, j = c - r * per_row;
+            if (t0 + r < T) cp_async16(smem_u32(xs + (size_t)r * H + 8 * j), x + (size_t)(t0 + r) * H + 8 * j);
+            else *reinterpret_cast<uint4*>(xs + (size_t)r * H + 8 * j) = make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+    auto issue = [&](int s) {                               // step s: expert block s / nkc, column chunk s % nkc
+        if (s < steps) {
+            const int eb = s / nkc, kc = s - eb * nkc;
+            const int e0 = e_begin + 4 * eb, rows = min(4, e_end - e0);
+            const int cols = min(KC, H - kc * KC), pieces = cols / 4;
+            const uint32_t dst = smem_u32(ring + (size_t)(s % kRouterBlockStages) * 4 * KC);
+            for (int c = threadIdx.x; c < rows * pieces; c += 256) {
+                const int r = c / pieces, j = c - r * pieces;
+                cp_async16(dst + (uint32_t)(r * KC + 4 * j) * 4u, w + (size_t)(e0 + r) * H + kc * KC + 4 * j);
+            }
+        }
+        cp_async_commit();
+    };
+    issue(0); issue(1);                                     // the token rows travel in the first group
+    float v[4][4];                                          // token j: logit of expert lane + 32 q
+#pragma unroll
+    for (int j = 0; j < 4; j++) v[j][0] = v[j][1] = v[j][2] = v[j][3] = 0.f;
+    float acc[4][4][4];                                     // [token][expert][chain]
+    const uint16_t* xw = xs + (size_t)(4 * warp) * H;
+    for (int s = 0; s < steps; s++) {
+        cp_async_wait<1>();
+        __syncthreads();                                    // step s has landed for everyone; step s - 1 is no longer read
+        issue(s + 2);
+        const int eb = s / nkc, kc = s - eb * nkc;
+        const float* wr = ring + (size_t)(s % kRouterBlockStages) * 4 * KC;
+        if (kc == 0) {
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+#pragma unroll
+                for (int q = 0; q < 4; q++) acc[j][q][0] = acc[j][q][1] = acc[j][q][2] = acc[j][q][3] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < STEPS; i++) {
+            const int kl = lane * 4 + 128 * i, k = kc * KC + kl;
+            if (k < H) {
+                float xv[4][4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint2 b = *reinterpret_cast<const uint2*>(xw + (size_t)j * H + k);
+                    xv[j][0] = __uint_as_float(b.x << 16); xv[j][1] = __uint_as_float(b.x & 0xffff0000u);
+                    xv[j][2] = __uint_as_float(b.y << 16); xv[j][3] = __uint_as_float(b.y & 0xffff0000u);
+                }
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const float4 wv = *reinterpret_cast<const float4*>(wr + q * KC + kl);   // stale past the range's last expert: unused
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        acc[j][q][0] = __fmaf_rn(xv[j][0], wv.x, acc[j][q][0]);
+                        acc[j][q][1] = __fmaf_rn(xv[j][1], wv.y, acc[j][q][1]);
+                        acc[j][q][2] = __fmaf_rn(xv[j][2], wv.z, acc[j][q][2]);
+                        acc[j][q][3] = __fmaf_rn(xv[j][3], wv.w, acc[j][q][3]);
+                    }
+                }
+            }
+        }
+        if (kc == nkc - 1) {
+            const int e0 = e_begin + 4 * eb;
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int e = e0 + q;
+                if (e < e_end) {                            // the same in every lane
+                    const float be = ARCH == OCO_ARCH_GPT_OSS ? bf16_round(bias[e]) : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        float sum = warp_butterfly_sum(__fadd_rn(__fadd_rn(acc[j][q][0], acc[j][q][1]), __fadd_rn(acc[j][q][2], acc[j][q][3])));
+                        if (ARCH == OCO_ARCH_GPT_OSS) sum = __fadd_rn(sum, be);
+#pragma unroll
+                        for (int u = 0; u < 4; u++)
+                            if ((e >> 5) == u && (e & 31) == lane) v[j][u] = sum;
+                    }
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int t = t0 + 4 * warp + j;
+        if (t >= T) continue;
+        if (logits) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int e = lane + 32 * q;
+                if (e >= e_begin && e < e_end) logits[(size_t)t * E + e] = v[j][q];
+            }
+        }
+        if (gridDim.y > 1) continue;
+        uint32_t id[kMaxTopK];
+        float pr[kMaxTopK];
+        select_experts<ARCH>(v[j], E, K, ARCH == OCO_ARCH_NEMOTRON ? bias : nullptr, normalize, scale, lane, id, pr);
+#pragma unroll
+        for (int r = 0; r < kMaxTopK; r++)
+            if (r < K && lane == r) { ids[(size_t)t * K + r] = id[r]; probs[(size_t)t * K + r] = pr[r]; }
+    }
+}
+
 }  // namespace oco

@@ -253,6 +253,23 @@ def test_qwen_wide_tiles(moe, oracle, hidden, ffn, tokens):
     check_layer(moe, oracle, layer, tokens, seed=tokens, x_scale=0.125)
 
 
+@pytest.mark.parametrize("arch", ["gpt-oss", "nemotron", "qwen"])
+def test_register_blocked_router(moe, oracle, arch, monkeypatch):
+    """The many-token router kernel (four tokens x four experts per warp) from 33 rows on: ragged last
+    token group, expert ranges split over CTAs, a partial last column chunk; ids, logits and weights
+    stay bit-exact."""
+    monkeypatch.setenv("OCO_MOE_ROUTER_BLOCK_MIN", "33")
+    if arch == "gpt-oss":
+        layer = synth.make_layer(synth.ARCH_GPT_OSS, 736, 384, 32, 4, synth.FMT_MXFP4, seed=61)
+    elif arch == "nemotron":
+        layer = synth.make_layer(synth.ARCH_NEMOTRON, 256, 160, 20, 3, synth.FMT_Q4_0, seed=62, shared_ffn=320,
+                                 normalize=True, scale=2.5)
+    else:
+        layer = synth.make_layer(synth.ARCH_QWEN, 512, 256, 128, 8, synth.FMT_Q4_K, seed=63)
+    for tokens in (45, 333):
+        check_layer(moe, oracle, layer, tokens, seed=700 + tokens, x_scale=0.125 if arch == "qwen" else 1.0)
+
+
 def test_host_buffer_entry_point(moe, oracle):
     layer = synth.make_layer(synth.ARCH_GPT_OSS, 128, 128, 32, 4, synth.FMT_MXFP4, seed=6)
     x, res = synth.make_tokens(128, 50, 3, "normal")
