@@ -457,12 +457,12 @@ int stage_route(oco_moe_plan* plan, const uint16_t* x, int rows, cudaStream_t st
             int splits = 1;
             double best = 1e9;
             for (int sp = 1; sp <= 8 && E / sp >= 4 && E % (4 * sp) == 0; sp *= 2) {
-                const double rounds = (double)ctas * sp / plan->sm_count;
+                const double rounds = (double)ctas * sp / (plan->sm_count * (256 / kRouterBlockThreads));
                 const double waste = std::ceil(rounds) / rounds;
                 if (waste < best - 1e-9) { best = waste; splits = sp; }
                 if (waste < 1.05) break;
             }
-            router_block_kernel<ARCH><<<dim3(ctas, splits), 256, router_block_smem_bytes(H), st>>>(
+            router_block_kernel<ARCH><<<dim3(ctas, splits), kRouterBlockThreads, router_block_smem_bytes(H), st>>>(
                 x, rw, plan->w.router_b, rows, H, E, K, d.normalize, d.scale, ws.logits, ws.ids, ws.probs);
             if (splits > 1) {
                 router_select_kernel<ARCH><<<rows, 32, 0, st>>>(ws.logits, ARCH == OCO_ARCH_NEMOTRON ? plan->w.router_b : nullptr, E, K,

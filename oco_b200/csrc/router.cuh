@@ -415,12 +415,13 @@ __global__ void __launch_bounds__(256, TOK == 1 ? 2 : 1) router_stream_kernel(co
 // grid (ceil(T / 32), splits) as router_stream_kernel; hidden <= 3072 and a multiple of 8.
 // Dynamic shared memory: router_block_smem_bytes(H).
 constexpr int kRouterBlockTokens = 32, kRouterBlockCols = 640, kRouterBlockStages = 3;
+constexpr int kRouterBlockThreads = kRouterBlockTokens * 8;
 __host__ __device__ inline size_t router_block_smem_bytes(int H) {
     return (size_t)kRouterBlockTokens * H * 2 + (size_t)kRouterBlockStages * 4 * kRouterBlockCols * 4;
 }
 
 template <int ARCH>
-__global__ void __launch_bounds__(256, 1) router_block_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w,
+__global__ void __launch_bounds__(kRouterBlockThreads, 256 / kRouterBlockThreads) router_block_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w,
                                                               const float* __restrict__ bias, int T, int H, int E, int K,
                                                               int normalize, float scale, float* __restrict__ logits,
                                                               uint32_t* __restrict__ ids, float* __restrict__ probs) {
@@ -438,7 +439,7 @@ __global__ void __launch_bounds__(256, 1) router_block_kernel(const uint16_t* __
     // the token rows (rows past T are zero)
     {
         const int per_row = H / 8;                          // 16-byte pieces
-        for (int c = threadIdx.x; c < kRouterBlockTokens * per_row; c += 256) {
+        for (int c = threadIdx.x; c < kRouterBlockTokens * per_row; c += kRouterBlockThreads) {
             const int r = c / per_row, j = c - r * per_row;
             if (t0 + r < T) cp_async16(smem_u32(xs + (size_t)r * H + 8 * j), x + (size_t)(t0 + r) * H + 8 * j);
             else *reinterpret_cast<uint4*>(xs + (size_t)r * H + 8 * j) = make_uint4(0u, 0u, 0u, 0u);
@@ -450,7 +451,7 @@ __global__ void __launch_bounds__(256, 1) router_block_kernel(const uint16_t* __
             const int e0 = e_begin + 4 * eb, rows = min(4, e_end - e0);
             const int cols = min(KC, H - kc * KC), pieces = cols / 4;
             const uint32_t dst = smem_u32(ring + (size_t)(s % kRouterBlockStages) * 4 * KC);
-            for (int c = threadIdx.x; c < rows * pieces; c += 256) {
+            for (int c = threadIdx.x; c < rows * pieces; c += kRouterBlockThreads) {
                 const int r = c / pieces, j = c - r * pieces;
                 cp_async16(dst + (uint32_t)(r * KC + 4 * j) * 4u, w + (size_t)(e0 + r) * H + kc * KC + 4 * j);
             }
