@@ -88,6 +88,14 @@ typedef struct {
     const float* down_b;          /* GPT_OSS f32 [experts, hidden] */
     const uint8_t* shared_up_w;   /* NEMOTRON [shared_ffn][hidden packed] */
     const uint8_t* shared_down_w; /* NEMOTRON [hidden][shared_ffn packed] */
+    /* Gate and up projections as ONE tensor with interleaved rows, [experts][2 * ffn][hidden packed]:
+     * row 2c is gate row c, row 2c + 1 is up row c (the layout checkpoints of the gpt-oss family
+     * ship as `gate_up_proj`; the reference reads the two-tensor GGUF form, src/weights/gpt_oss/load.rs:131-133).
+     * Give either this member (with gate_w and up_w NULL) or gate_w + up_w. gate_up_b: f32
+     * [experts, 2 * ffn] with the same interleave (GPT_OSS). Results are bit-identical to the
+     * two-tensor layout. */
+    const uint8_t* gate_up_w;
+    const float* gate_up_b;
 } oco_moe_weights;
 
 /* Addresses of the routing side-outputs inside the bound workspace, valid after a forward call
@@ -127,10 +135,15 @@ void oco_moe_plan_destroy(oco_moe_plan* plan);
 size_t oco_moe_workspace_bytes(const oco_moe_plan* plan, int max_rows);
 
 /* Hands the plan a caller-owned device workspace of at least oco_moe_workspace_bytes(max_rows)
- * bytes. Must be called with the owning device current; builds the TMA descriptors over it. */
+ * bytes. Must be called with the owning device current; builds the TMA descriptors over it. A set-up
+ * call: it clears control words and waits for the device. The plan remembers the device; every
+ * later call on the plan must be made with that device current (OCO_INVALID_ARGUMENT otherwise).
+ * Kernel attributes are set per device, so plans on several GPUs may live in one process. */
 int oco_moe_bind_workspace(oco_moe_plan* plan, void* workspace, size_t bytes, int max_rows);
 
-/* Replaces binding `w: &Experts` / `w: &ReluExperts` at the call site. */
+/* Replaces binding `w: &Experts` / `w: &ReluExperts` at the call site. A set-up call: once both the
+ * workspace and GPT_OSS router weights are bound it makes the bf16-rounded router copy and waits for
+ * it, so the first forward call may already be inside a stream capture or on any stream. */
 int oco_moe_bind_weights(oco_moe_plan* plan, const oco_moe_weights* weights);
 
 /* Replaces Bindings::experts (feed_forward.rs:107-114) and Bindings::relu_experts
@@ -233,6 +246,20 @@ int oco_cuda_download(void* dst_host, const void* src_device, size_t bytes, void
 int oco_cuda_stream_create(void** out);
 int oco_cuda_stream_destroy(void* cuda_stream);
 int oco_cuda_stream_sync(void* cuda_stream);
+/* Device timestamps: what the reference's dispatch encoder samples into its counter heap around each
+ * dispatch (src/gpu/dispatch.rs:189-208, src/gpu/profile.rs:1-31). */
+int oco_cuda_event_create(void** out);
+int oco_cuda_event_destroy(void* event);
+int oco_cuda_event_record(void* event, void* cuda_stream);
+int oco_cuda_event_sync(void* event);
+int oco_cuda_event_elapsed_ms(void* start_event, void* end_event, float* ms);
+
+/* Self-test of the bounded-wait path, safe to run anywhere: enqueues a one-warp kernel that waits
+ * `wait_cycles` clock cycles (1 .. 400 000 000) on a barrier nobody arrives at, gives up, sets the
+ * workspace status word and returns normally. Afterwards oco_moe_poll reports OCO_DEVICE_TIMEOUT once
+ * and clears the word; forward calls enqueued while the word is set leave the residual rows
+ * untouched. No counterpart in the reference (Metal has no device-side waits on this path). */
+int oco_moe_selftest_wait_timeout(oco_moe_plan* plan, long long wait_cycles, void* cuda_stream);
 
 const char* oco_moe_version(void);
 

@@ -22,7 +22,7 @@ class Desc(C.Structure):
 
 class Weights(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("router_w", "router_b", "gate_w", "up_w", "down_w", "gate_b", "up_b",
-                                          "down_b", "shared_up_w", "shared_down_w")]
+                                          "down_b", "shared_up_w", "shared_down_w", "gate_up_w", "gate_up_b")]
 
 
 class RoutingView(C.Structure):
@@ -62,6 +62,12 @@ SIGNATURES = {
     "oco_cuda_stream_create": (C.c_int, [C.POINTER(C.c_void_p)]),
     "oco_cuda_stream_destroy": (C.c_int, [C.c_void_p]),
     "oco_cuda_stream_sync": (C.c_int, [C.c_void_p]),
+    "oco_cuda_event_create": (C.c_int, [C.POINTER(C.c_void_p)]),
+    "oco_cuda_event_destroy": (C.c_int, [C.c_void_p]),
+    "oco_cuda_event_record": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "oco_cuda_event_sync": (C.c_int, [C.c_void_p]),
+    "oco_cuda_event_elapsed_ms": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_float)]),
+    "oco_moe_selftest_wait_timeout": (C.c_int, [C.c_void_p, C.c_longlong, C.c_void_p]),
     "oco_moe_version": (C.c_char_p, []),
 }
 

@@ -9,7 +9,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "liboco_moe.so")
 SOURCES = ["api.cu", "route_static.cu"]
-HEADERS = ["common.cuh", "router.cuh", "plan.cuh", "decode.cuh", "batch.cuh", "gemm.cuh", "gemm_wide.cuh", "../../include/oco_moe.h"]
+HEADERS = ["common.cuh", "router.cuh", "plan.cuh", "decode.cuh", "batch.cuh", "gemm.cuh", "gemm_wide.cuh", "mx.cuh", "mx_pieces.cuh",
+           "../../include/oco_moe.h"]
 
 
 def nvcc() -> str:
@@ -30,7 +31,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not (force or stale()):
         return LIB
     cmd = [nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-           "--use_fast_math=false" if False else "-Xcompiler", "-fPIC", "-shared", "-Xptxas", "-v" if verbose else "-O3",
+           "-Xcompiler", "-fPIC", "-shared", "-Xptxas", "-v" if verbose else "-O3",
            "-o", LIB] + [os.path.join(CSRC, f) for f in SOURCES]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:

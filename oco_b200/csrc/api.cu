@@ -2,6 +2,7 @@
 // The sequencing mirrors the reference operators it replaces:
 //   Bindings::experts        src/weights/compute/feed_forward.rs:107-275
 //   Bindings::relu_experts   src/weights/compute/nemotron.rs:286-545
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -13,6 +14,7 @@
 #include "batch.cuh"
 #include "gemm.cuh"
 #include "gemm_wide.cuh"
+#include "mx.cuh"
 #include <cmath>
 #include "plan.cuh"
 #include "router.cuh"
@@ -44,7 +46,7 @@ struct Workspace {
     __half* xfrag = nullptr;      // single-token B fragments of the token itself
     __half* bfrag_in = nullptr;   // few-token path: B fragments of each route group, input rows
     __half* bfrag_out = nullptr;  //                 and activations
-    uint32_t* arrivals = nullptr; // single-token combine: one counter per eight output rows
+    uint32_t* arrivals = nullptr; // single-token combine: one counter per output row (or row block), then the router's
     uint16_t* xh = nullptr;       // half [T, H] token-order input rows (shared expert)
     uint16_t* mid = nullptr;      // half [T, S] shared expert intermediate
     uint16_t* shared_out = nullptr;  // bf16 [T, H]
@@ -52,6 +54,9 @@ struct Workspace {
     __half* sh_actfrag = nullptr;
     uint32_t* sh_ids = nullptr;
     uint16_t* norm = nullptr;     // bf16 [T, H] normalised rows of oco_moe_add_norm_forward
+    CUtensorMap* mx_maps = nullptr;   // block-scaled single-token path: tensor maps over the packed rows
+    unsigned char* mx_xb = nullptr;   //   the token as e2m1 pieces
+    unsigned char* mx_xsfb = nullptr; //   and their scales
     uint16_t* host_x = nullptr;   // staging for the host-buffer entry point
     uint16_t* host_res = nullptr;
     size_t total = 0;
@@ -67,10 +72,22 @@ struct oco_moe_plan {
     bool have_experts = false;   // expert banks bound (enough for oco_moe_experts)
     bool router_ready = false;   // the rounded router copy matches the bound weights and workspace
     int max_rows = 0;
+    int device = -1;             // the device that was current when the workspace was bound
     int sm_count = 148;
     int launches = 0;
     int last_tile_rows = 0;
     uint32_t up_row_bytes = 0, down_row_bytes = 0, shared_up_row_bytes = 0, shared_down_row_bytes = 0;
+    // Resolved gate / up operands: two tensors, or the rows of one interleaved tensor (row 2c = gate c,
+    // row 2c + 1 = up c), in which case consecutive rows of either matrix lie two packed rows apart.
+    const uint8_t* gate_rows = nullptr;
+    const uint8_t* up_rows = nullptr;
+    const float* gate_bias = nullptr;
+    const float* up_bias = nullptr;
+    uint32_t up_row_stride = 0;  // bytes between consecutive gate (or up) rows
+    int up_bias_stride = 1;      // floats between consecutive gate (or up) biases
+    // block-scaled single-token path (mx.cuh): usable once prepare_mx has built the tensor maps
+    bool mx_ready = false, mx_off = false;   // OCO_MOE_TOKEN_MX=0 keeps the mma.sync kernels
+    int mx_pr_up = 8, mx_pr_down = 8;
     CUtensorMap map_xs[kTileKinds], map_act[kTileKinds], map_xh[kTileKinds], map_mid[kTileKinds];
     // Per-phase timestamps (the counterpart of the reference's OCO_PROFILE counter heap,
     // src/gpu/profile.rs:1-31, src/gpu/dispatch.rs:189-208): one event before each kernel.
@@ -105,6 +122,23 @@ int fail(oco_moe_plan* p, int code, const char* fmt, ...) {
     do {                                                                                             \
         cudaError_t e_ = (call);                                                                     \
         if (e_ != cudaSuccess) return fail(plan, OCO_CUDA_ERROR, "%s: %s", #call, cudaGetErrorString(e_)); \
+    } while (0)
+
+// A kernel's opt-in to large dynamic shared memory is a per-device attribute: this remembers, per
+// launch site, on which devices it has been set (bit d = device d). Two threads may both find the
+// bit clear and set the attribute twice, which is harmless; a set bit is never lost.
+struct DeviceOnce {
+    std::atomic<uint64_t> done{0};
+    bool need(int dev) const { return dev < 0 || dev >= 64 || !((done.load(std::memory_order_acquire) >> dev) & 1u); }
+    void mark(int dev) { if (dev >= 0 && dev < 64) done.fetch_or(1ull << dev, std::memory_order_release); }
+};
+#define ALLOW_SMEM_ONCE(kernel)                                   \
+    do {                                                          \
+        static DeviceOnce once_;                                  \
+        if (once_.need(plan->device)) {                           \
+            CK(allow_smem(kernel));                               \
+            once_.mark(plan->device);                             \
+        }                                                         \
     } while (0)
 
 // Stamps the stream ahead of the phase called `name`; "end" closes the last phase.
@@ -165,7 +199,7 @@ Workspace carve(const oco_moe_desc& d, int max_rows, unsigned char* base) {
         w.bfrag_in = (__half*)take(groups * (H / 32) * kBatchFragBlock);
         w.bfrag_out = (__half*)take(groups * (F / 32) * kBatchFragBlock);
     }
-    w.arrivals = (uint32_t*)take((H / 8 + 1) * 4);
+    w.arrivals = (uint32_t*)take((H + 1) * 4);
     if (S) {
         w.xh = (uint16_t*)take(T * H * 2);
         w.mid = (uint16_t*)take(T * S * 2);
@@ -175,6 +209,11 @@ Workspace carve(const oco_moe_desc& d, int max_rows, unsigned char* base) {
         w.sh_ids = (uint32_t*)take(256);
     }
     w.norm = (uint16_t*)take(T * H * 2);
+    if (d.weight_format == OCO_FMT_MXFP4) {
+        w.mx_maps = (CUtensorMap*)take((size_t)3 * kMxMaxResidues * kMxMapSizes * sizeof(CUtensorMap));
+        w.mx_xb = (unsigned char*)take(mx_b_bytes(8, (uint32_t)(H / 32)));
+        w.mx_xsfb = (unsigned char*)take(mx_sfb_bytes((uint32_t)(H / 32)));
+    }
     w.host_x = (uint16_t*)take(T * H * 2);
     w.host_res = (uint16_t*)take(T * H * 2);
     w.total = off;
@@ -186,14 +225,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 int make_row_map(oco_moe_plan* plan, CUtensorMap* map, void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-    static EncodeTiledFn encode = nullptr;
-    if (!encode) {
+    // looked up once per process (initialisation of a function-local static is thread-safe)
+    static const EncodeTiledFn encode = [] {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult q;
-        CK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
-        if (q != cudaDriverEntryPointSuccess || !fn) return fail(plan, OCO_CUDA_ERROR, "cuTensorMapEncodeTiled unavailable");
-        encode = (EncodeTiledFn)fn;
-    }
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            fn = nullptr;
+        return (EncodeTiledFn)fn;
+    }();
+    if (!encode) return fail(plan, OCO_CUDA_ERROR, "cuTensorMapEncodeTiled unavailable");
     cuuint64_t dims[2] = {cols, rows};
     cuuint64_t strides[1] = {cols * 2};
     cuuint32_t box[2] = {64, box_rows};
@@ -236,11 +277,7 @@ int launch_gemm(oco_moe_plan* plan, const GemmParams& gp, const CUtensorMap& map
     if (plan->d.gemm_impl == 1) {
         grouped_gemm_simt_kernel<FMT, EPI, NT><<<grid, 128, 0, st>>>(gp);
     } else {
-        static bool attr_set = false;
-        if (!attr_set) {
-            CK(allow_smem(grouped_gemm_tc_kernel<FMT, EPI, NT>));
-            attr_set = true;
-        }
+        ALLOW_SMEM_ONCE((grouped_gemm_tc_kernel<FMT, EPI, NT>));
         grouped_gemm_tc_kernel<FMT, EPI, NT><<<grid, S::kThreads, S::kSmemBytes, st>>>(gp, map);
     }
     plan->launches++;
@@ -253,14 +290,11 @@ int launch_gemm(oco_moe_plan* plan, const GemmParams& gp, const CUtensorMap& map
 template <int FMT, int EPI>
 int launch_gemm_wide(oco_moe_plan* plan, GemmParams gp, const CUtensorMap* maps, int max_tiles, int experts,
                      cudaStream_t st) {
-    const size_t bytes = (size_t)experts * gp.n * gp.row_bytes;
+    // last row of the matrix ends (rows * stride - (stride - packed length)) bytes past its first row
+    const size_t bytes = (size_t)experts * gp.n * gp.row_bytes - (gp.row_bytes - packed_row_bytes(FMT, gp.K));
     gp.w0_end = (const uint8_t*)(((uintptr_t)gp.w0 + bytes + 15) & ~(uintptr_t)15);
     gp.w1_end = gp.w1 ? (const uint8_t*)(((uintptr_t)gp.w1 + bytes + 15) & ~(uintptr_t)15) : nullptr;
-    static bool attr_set = false;
-    if (!attr_set) {
-        CK(allow_smem(grouped_gemm_wide_kernel<FMT, EPI>));
-        attr_set = true;
-    }
+    ALLOW_SMEM_ONCE((grouped_gemm_wide_kernel<FMT, EPI>));
     // persistent: one CTA per SM walks the (route tile, feature tile) items; never more CTAs than items can exist
     const int feats = (gp.n + (epi_gated(EPI) ? 127 : 255)) / (epi_gated(EPI) ? 128 : 256);
     const int grid = std::min(plan->sm_count, feats * max_tiles);
@@ -310,11 +344,7 @@ int launch_expand(oco_moe_plan* plan, DecodeExpandParams ep, cudaStream_t st) {
     const int grid = plan->sm_count;
     if (token_smem_bytes(FMT, ep.H / 32, 2) > kMaxDynamicSmem) return fail(plan, OCO_UNSUPPORTED_SHAPE, "hidden %d too large for the single-token kernels", ep.H);
     ep.ksplit = pick_ksplit(ep.K * (ep.F / (ARCH == OCO_ARCH_NEMOTRON ? 16 : 8)), grid, tok_warps(FMT));
-    static bool attr_set = false;
-    if (!attr_set) {
-        CK(allow_smem(decode_expand_kernel<ARCH, FMT, 2>));
-        attr_set = true;
-    }
+    ALLOW_SMEM_ONCE((decode_expand_kernel<ARCH, FMT, 2>));
     CK(launch_dependent(decode_expand_kernel<ARCH, FMT, 2>, dim3(grid), dim3(tok_warps(FMT) * 32), token_smem_bytes(FMT, ep.H / 32, 2), st, ep));
     plan->launches++;
     CK(cudaGetLastError());
@@ -327,12 +357,102 @@ int launch_down(oco_moe_plan* plan, DecodeDownParams dp, cudaStream_t st) {
     if (token_smem_bytes(FMT, dp.F / 32, 2) > kMaxDynamicSmem) return fail(plan, OCO_UNSUPPORTED_SHAPE, "expert width %d too large for the single-token kernels", dp.F);
     if (dp.K > grid) return fail(plan, OCO_UNSUPPORTED_SHAPE, "more routes than multiprocessors");
     dp.ksplit = pick_ksplit(dp.H / 16, grid / dp.K, tok_warps(FMT));
-    static bool attr_set = false;
-    if (!attr_set) {
-        CK(allow_smem(decode_down_kernel<FMT, 2>));
-        attr_set = true;
-    }
+    ALLOW_SMEM_ONCE((decode_down_kernel<FMT, 2>));
     CK(launch_dependent(decode_down_kernel<FMT, 2>, dim3(grid), dim3(tok_warps(FMT) * 32), token_smem_bytes(FMT, dp.F / 32, 2), st, dp));
+    plan->launches++;
+    CK(cudaGetLastError());
+    return OCO_OK;
+}
+
+// ---- block-scaled single-token path (mx.cuh) --------------------------------------------------------
+// One 2-D tensor map per (tensor, row residue, box height): rows `pr` apart share their offset within a
+// 16-byte word, so [row / pr][16-byte envelope of a row] with pitch pr * stride is a legal TMA view.
+int encode_mx_map(oco_moe_plan* plan, CUtensorMap* map, const uint8_t* row0, uint32_t row_len, uint64_t pitch, uint64_t periods, uint32_t box_rows) {
+    static const EncodeTiledFn encode = [] {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            fn = nullptr;
+        return (EncodeTiledFn)fn;
+    }();
+    if (!encode) return fail(plan, OCO_CUDA_ERROR, "cuTensorMapEncodeTiled unavailable");
+    const uintptr_t a = (uintptr_t)row0;
+    const uint32_t off = (uint32_t)(a & 15u);
+    cuuint64_t dims[2] = {(cuuint64_t)((off + row_len + 15u) / 16u * 2u), periods};   // 8-byte elements
+    cuuint64_t strides[1] = {pitch};
+    cuuint32_t box[2] = {kMxSlot / 8, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, (void*)(a & ~(uintptr_t)15), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(plan, OCO_CUDA_ERROR, "cuTensorMapEncodeTiled (packed rows) failed (%d)", (int)r);
+    return OCO_OK;
+}
+
+int mx_period_rows(uint32_t stride) { return (8u * stride) % 16u == 0 ? 8 : 16; }
+
+// Builds the maps once weights and workspace are both bound (GPT_OSS / MXFP4 only). Shapes the path
+// cannot take simply leave mx_ready false and the mma.sync token kernels run.
+int prepare_mx(oco_moe_plan* plan) {
+    plan->mx_ready = false;
+    const oco_moe_desc& d = plan->d;
+    if (plan->mx_off || d.arch != OCO_ARCH_GPT_OSS || !plan->have_ws || !plan->have_w || !plan->ws.mx_maps) return OCO_OK;
+    const int H = d.hidden, F = d.ffn, E = d.experts;
+    const int pr_up = mx_period_rows(plan->up_row_stride), pr_dn = mx_period_rows(plan->down_row_bytes);
+    if (F % pr_up || H % pr_dn || H > 12288 || F > 12288) return OCO_OK;   // 384 tensor-memory columns of operand scales
+    // shared memory: at least two raw stages beside the fixed part
+    const uint32_t fix_up = mx_fixed_smem(2, 8, (uint32_t)(H / 32)), fix_dn = mx_fixed_smem(1, 16, (uint32_t)(F / 32));
+    if (fix_up + 2 * mx_raw_stage_bytes(2, pr_up, (128 / pr_up) * kMxSlot + 1024) > kMaxDynamicSmem ||
+        fix_dn + 2 * mx_raw_stage_bytes(1, pr_dn, (128 / pr_dn) * kMxSlot + 1024) > kMaxDynamicSmem)
+        return OCO_OK;
+    const size_t n = (size_t)3 * kMxMaxResidues * kMxMapSizes;
+    CUtensorMap* host = new (std::nothrow) CUtensorMap[n];
+    if (!host) return fail(plan, OCO_CUDA_ERROR, "out of host memory");
+    memset(host, 0, n * sizeof(CUtensorMap));
+    struct T { const uint8_t* w; uint32_t stride, len; int pr, rows; } t[3] = {
+        {plan->gate_rows, plan->up_row_stride, plan->up_row_bytes, pr_up, E * F},
+        {plan->up_rows, plan->up_row_stride, plan->up_row_bytes, pr_up, E * F},
+        {plan->w.down_w, plan->down_row_bytes, plan->down_row_bytes, pr_dn, E * H}};
+    int rc = OCO_OK;
+    for (int k = 0; k < 3 && rc == OCO_OK; k++)
+        for (int j = 0; j < t[k].pr && rc == OCO_OK; j++)
+            for (int lg = 0; lg < kMxMapSizes && rc == OCO_OK; lg++)
+                rc = encode_mx_map(plan, host + ((size_t)k * kMxMaxResidues + j) * kMxMapSizes + lg, t[k].w + (size_t)j * t[k].stride,
+                                   t[k].len, (uint64_t)t[k].pr * t[k].stride, (uint64_t)(t[k].rows / t[k].pr), 1u << lg);
+    if (rc == OCO_OK) {
+        cudaError_t e = cudaMemcpy(plan->ws.mx_maps, host, n * sizeof(CUtensorMap), cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) rc = fail(plan, OCO_CUDA_ERROR, "tensor map upload: %s", cudaGetErrorString(e));
+    }
+    delete[] host;
+    if (rc) return rc;
+    plan->mx_pr_up = pr_up; plan->mx_pr_down = pr_dn;
+    plan->mx_ready = true;
+    return OCO_OK;
+}
+
+template <bool EXPAND>
+int launch_mx(oco_moe_plan* plan, MxParams mp, cudaStream_t st) {
+    const int n_mat = EXPAND ? 2 : 1;
+    const int upr = mp.rows_per_route / mp.PR, units_total = mp.routes * upr;
+    const int grid = std::min(plan->sm_count, units_total);
+    // the largest raw region any pass of any CTA needs (the cut into boxes does not depend on the ids)
+    uint32_t region = 128;
+    for (int c = 0; c < grid; c++) {
+        const int u_end = (int)((long long)(c + 1) * units_total / grid);
+        for (int u0 = (int)((long long)c * units_total / grid); u0 < u_end;) {
+            const int u1 = mx_pass_end(u0, u_end, upr, mp.PR, !EXPAND);
+            region = std::max(region, mx_plan_copies(u0, u1, upr, [](int, int, int, uint32_t) {}, [](int, uint32_t) {}));
+            u0 = u1;
+        }
+    }
+    mp.region = (int)region;
+    const uint32_t fixed = mx_fixed_smem(n_mat, EXPAND ? 8 : 16, (uint32_t)(mp.K / 32));
+    const uint32_t stage = mx_raw_stage_bytes(n_mat, mp.PR, mp.region);
+    mp.raw_stages = (int)std::min<size_t>(12, (kMaxDynamicSmem - fixed) / stage);
+    if (mp.raw_stages < 2) return fail(plan, OCO_UNSUPPORTED_SHAPE, "shape too large for the block-scaled token kernels");
+    ALLOW_SMEM_ONCE((mx_rows_kernel<EXPAND>));
+    CK(launch_dependent(mx_rows_kernel<EXPAND>, dim3(grid), dim3(kMxThreads), fixed + (size_t)mp.raw_stages * stage, st, mp));
     plan->launches++;
     CK(cudaGetLastError());
     return OCO_OK;
@@ -363,15 +483,40 @@ int forward_single(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, cu
     Workspace& ws = plan->ws;
     const int H = d.hidden, F = d.ffn, E = d.experts, K = d.top_k;
     // logits, then (in the CTA that finishes last) the token's experts and weights
+    const bool mx = ARCH == OCO_ARCH_GPT_OSS && plan->mx_ready;
     mark(plan, st, "router_logits");
     CK(launch_dependent(router_token_kernel<ARCH>, dim3((E + 7) / 8), dim3(256), 0, st, x, plan->w.router_w, plan->w.router_b, H, E, K,
-                        d.normalize, d.scale, ws.logits, ws.ids, ws.probs, ws.xfrag, (int)FMT, ws.arrivals + H / 8));
+                        d.normalize, d.scale, ws.logits, ws.ids, ws.probs, ws.xfrag, (int)FMT, ws.arrivals + H,
+                        mx ? ws.mx_xb : nullptr, mx ? ws.mx_xsfb : nullptr));
     plan->launches++;
+    if (mx) {
+        // MXFP4 rows straight into the block-scaled MMA (mx.cuh): expand with the activation fused, then
+        // down with the weighted sum onto the residual by whoever finishes an output-row block last
+        MxParams ex{};
+        ex.maps = ws.mx_maps; ex.w[0] = plan->gate_rows; ex.w[1] = plan->up_rows; ex.tensor[0] = 0; ex.tensor[1] = 1; ex.n_mat = 2;
+        ex.row_stride = plan->up_row_stride; ex.PR = plan->mx_pr_up; ex.K = H; ex.rows_per_route = F; ex.routes = K; ex.ids = ws.ids;
+        ex.b_img = ws.mx_xb; ex.sfb_img = ws.mx_xsfb; ex.b0 = plan->gate_bias; ex.b1 = plan->up_bias; ex.bias_stride = plan->up_bias_stride;
+        ex.act_out = ws.act1; ex.status = ws.status;
+        mark(plan, st, "expand");
+        int rc = launch_mx<true>(plan, ex, st);
+        if (rc) return rc;
+        MxParams dn{};
+        dn.maps = ws.mx_maps; dn.w[0] = plan->w.down_w; dn.tensor[0] = 2; dn.n_mat = 1; dn.row_stride = plan->down_row_bytes;
+        dn.PR = plan->mx_pr_down; dn.K = F; dn.rows_per_route = H; dn.routes = K; dn.ids = ws.ids; dn.act = ws.act1;
+        dn.b0 = plan->w.down_b; dn.bias_stride = 1; dn.y = ws.y; dn.arrivals = ws.arrivals; dn.probs = ws.probs; dn.residual = residual;
+        dn.round_sum = 1; dn.status = ws.status;
+        mark(plan, st, "down_combine");
+        rc = launch_mx<false>(plan, dn, st);
+        if (rc) return rc;
+        mark(plan, st, "end");
+        return OCO_OK;
+    }
     {
         auto expand = [&](const uint8_t* gate_w, const uint8_t* up_w, const uint32_t* ids, int k, int f, float* act1,
                           __half* actfrag, uint32_t row_bytes) -> int {
             DecodeExpandParams ep{};
-            ep.gate_w = gate_w; ep.up_w = up_w; ep.gate_b = plan->w.gate_b; ep.up_b = plan->w.up_b;
+            ep.gate_w = gate_w; ep.up_w = up_w; ep.gate_b = plan->gate_bias; ep.up_b = plan->up_bias;
+            ep.bias_stride = plan->up_bias_stride;
             ep.xfrag = ws.xfrag; ep.ids = ids; ep.act = act1; ep.actfrag = actfrag;
             ep.H = H; ep.F = f; ep.K = k; ep.row_bytes = row_bytes; ep.status = ws.status;
             return launch_expand<ARCH, FMT>(plan, ep, st);
@@ -388,7 +533,7 @@ int forward_single(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, cu
             return launch_down<FMT>(plan, dp, st);
         };
         mark(plan, st, "expand");
-        int rc = expand(plan->w.gate_w, plan->w.up_w, ws.ids, K, F, ws.act1, ws.actfrag, plan->up_row_bytes);
+        int rc = expand(plan->gate_rows, plan->up_rows, ws.ids, K, F, ws.act1, ws.actfrag, plan->up_row_stride);
         if (rc) return rc;
         const uint16_t* shared = nullptr;
         if (ARCH == OCO_ARCH_NEMOTRON && d.shared_ffn) {
@@ -430,27 +575,11 @@ int stage_route(oco_moe_plan* plan, const uint16_t* x, int rows, cudaStream_t st
     mark(plan, st, "router");
     if (H <= 3072 && H % 4 == 0) {
         const float* rw = plan->w.router_w;
-        if (ARCH == OCO_ARCH_GPT_OSS) {
-            if (!plan->router_ready) {   // once per bound weight set
-                const size_t n = (size_t)E * H;
-                round_router_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(rw, ws.router_rounded, n);
-                plan->launches++;
-                plan->router_ready = true;
-            }
-            rw = ws.router_rounded;
-        }
-        static bool stream_attr = false;
-        if (!stream_attr) {
-            CK(allow_smem(router_stream_kernel<ARCH, 24, 1>));
-            stream_attr = true;
-        }
+        if (ARCH == OCO_ARCH_GPT_OSS) rw = ws.router_rounded;   // made when the weights were bound (prepare_router)
+        ALLOW_SMEM_ONCE((router_stream_kernel<ARCH, 24, 1>));
         if (rows >= plan->router_block_min && H % 8 == 0) {
             // many tokens: four tokens x four experts per warp (router_block_kernel)
-            static bool block_attr = false;
-            if (!block_attr) {
-                CK(allow_smem(router_block_kernel<ARCH>));
-                block_attr = true;
-            }
+            ALLOW_SMEM_ONCE((router_block_kernel<ARCH>));
             const int ctas = (rows + kRouterBlockTokens - 1) / kRouterBlockTokens;
             // one CTA per SM at a time: split the experts over 1, 2, 4 or 8 CTAs per token group so that the
             // last round of CTAs is nearly full (the fewest splits that waste under 5 % of it, else the best)
@@ -484,11 +613,7 @@ int stage_route(oco_moe_plan* plan, const uint16_t* x, int rows, cudaStream_t st
         }
     } else {
         size_t rsmem = (size_t)H * 4 + (size_t)8 * H * 2;
-        static bool router_attr = false;
-        if (!router_attr) {
-            CK(allow_smem(router_batched_kernel<ARCH>));
-            router_attr = true;
-        }
+        ALLOW_SMEM_ONCE((router_batched_kernel<ARCH>));
         router_batched_kernel<ARCH><<<(rows + 7) / 8, 256, rsmem, st>>>(x, plan->w.router_w, plan->w.router_b, rows, H,
                                                                       E, K, d.normalize, d.scale, ws.logits, ws.ids,
                                                                       ws.probs);
@@ -523,27 +648,23 @@ int stage_experts(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, in
                                                            H, reinterpret_cast<uint4*>(ws.bfrag_in));
             plan->launches += 2;
             const int parts = std::max(1, std::min(8, (4 * plan->sm_count + groups - 1) / groups));
-            static bool attr_set = false;
-            if (!attr_set) {
-                CK(allow_smem(batch_rows_kernel<FMT, EPI_UP>));
-                CK(allow_smem(batch_rows_kernel<FMT, kEpiDownBf16>));
-                attr_set = true;
-            }
+            ALLOW_SMEM_ONCE((batch_rows_kernel<FMT, EPI_UP>));
+            ALLOW_SMEM_ONCE((batch_rows_kernel<FMT, kEpiDownBf16>));
             BatchParams bp{};
             bp.tiles = ws.tiles; bp.tile_count = ws.tile_count; bp.offsets = ws.offsets; bp.route_of_row = ws.route_of_row;
             bp.parts = parts; bp.status = ws.status;
-            bp.w0 = ARCH == OCO_ARCH_NEMOTRON ? plan->w.up_w : plan->w.gate_w;
-            bp.w1 = ARCH == OCO_ARCH_NEMOTRON ? nullptr : plan->w.up_w;
-            bp.b0 = ARCH == OCO_ARCH_GPT_OSS ? plan->w.gate_b : nullptr;
-            bp.b1 = ARCH == OCO_ARCH_GPT_OSS ? plan->w.up_b : nullptr;
+            bp.w0 = ARCH == OCO_ARCH_NEMOTRON ? plan->up_rows : plan->gate_rows;
+            bp.w1 = ARCH == OCO_ARCH_NEMOTRON ? nullptr : plan->up_rows;
+            bp.b0 = ARCH == OCO_ARCH_GPT_OSS ? plan->gate_bias : nullptr;
+            bp.b1 = ARCH == OCO_ARCH_GPT_OSS ? plan->up_bias : nullptr;
             bp.frag_in = ws.bfrag_in; bp.frag_out = ws.bfrag_out; bp.out = ws.act;
-            bp.n_in = H; bp.n_out = F; bp.row_bytes = plan->up_row_bytes;
+            bp.n_in = H; bp.n_out = F; bp.row_bytes = plan->up_row_stride; bp.bias_stride = plan->up_bias_stride;
             mark(plan, st, "up_rows");
             batch_rows_kernel<FMT, EPI_UP><<<groups * parts, kBatchThreads, batch_smem_bytes(H / 32), st>>>(bp);
             bp.w0 = plan->w.down_w; bp.w1 = nullptr;
             bp.b0 = ARCH == OCO_ARCH_GPT_OSS ? plan->w.down_b : nullptr; bp.b1 = nullptr;
             bp.frag_in = ws.bfrag_out; bp.frag_out = nullptr; bp.out = y;
-            bp.n_in = F; bp.n_out = H; bp.row_bytes = plan->down_row_bytes;
+            bp.n_in = F; bp.n_out = H; bp.row_bytes = plan->down_row_bytes; bp.bias_stride = 1;
             mark(plan, st, "down_rows");
             batch_rows_kernel<FMT, kEpiDownBf16><<<groups * parts, kBatchThreads, batch_smem_bytes(F / 32), st>>>(bp);
             plan->launches += 2;
@@ -565,11 +686,11 @@ int stage_experts(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, in
     const int max_tiles = R / NT + (E < R ? E : R);
 
     GemmParams up{};
-    up.w0 = ARCH == OCO_ARCH_NEMOTRON ? plan->w.up_w : plan->w.gate_w;
-    up.w1 = ARCH == OCO_ARCH_NEMOTRON ? nullptr : plan->w.up_w;
-    up.b0 = ARCH == OCO_ARCH_GPT_OSS ? plan->w.gate_b : nullptr;
-    up.b1 = ARCH == OCO_ARCH_GPT_OSS ? plan->w.up_b : nullptr;
-    up.n = F; up.K = H; up.row_bytes = plan->up_row_bytes;
+    up.w0 = ARCH == OCO_ARCH_NEMOTRON ? plan->up_rows : plan->gate_rows;
+    up.w1 = ARCH == OCO_ARCH_NEMOTRON ? nullptr : plan->up_rows;
+    up.b0 = ARCH == OCO_ARCH_GPT_OSS ? plan->gate_bias : nullptr;
+    up.b1 = ARCH == OCO_ARCH_GPT_OSS ? plan->up_bias : nullptr;
+    up.n = F; up.K = H; up.row_bytes = plan->up_row_stride; up.bias_stride = plan->up_bias_stride;
     up.tiles = ws.tiles; up.tile_count = ws.tile_count; up.offsets = ws.offsets; up.route_of_row = nullptr;
     up.xs = ws.xs; up.out = ws.act; up.status = ws.status; up.dense_rows = 0; up.tile_rows = NT;
     mark(plan, st, "up_tiles");
@@ -579,7 +700,7 @@ int stage_experts(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, in
     GemmParams dn{};
     dn.w0 = plan->w.down_w; dn.w1 = nullptr;
     dn.b0 = ARCH == OCO_ARCH_GPT_OSS ? plan->w.down_b : nullptr; dn.b1 = nullptr;
-    dn.n = H; dn.K = F; dn.row_bytes = plan->down_row_bytes;
+    dn.n = H; dn.K = F; dn.row_bytes = plan->down_row_bytes; dn.bias_stride = 1;
     dn.tiles = ws.tiles; dn.tile_count = ws.tile_count; dn.offsets = ws.offsets; dn.route_of_row = ws.route_of_row;
     dn.xs = ws.act; dn.out = y; dn.status = ws.status; dn.dense_rows = 0; dn.tile_rows = NT;
     mark(plan, st, "down_tiles");
@@ -595,7 +716,8 @@ int stage_combine(oco_moe_plan* plan, const uint16_t* y, const float* probs, uin
     mark(plan, st, "combine");
     moe_combine_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, st>>>(y, probs, residual, plan->ws.shared_out,
                                                                         d.hidden, rows, d.top_k,
-                                                                        ARCH == OCO_ARCH_GPT_OSS ? 1 : 0, shared_mode);
+                                                                        ARCH == OCO_ARCH_GPT_OSS ? 1 : 0, shared_mode,
+                                                                        plan->have_ws ? plan->ws.status : nullptr);
     plan->launches++;
     CK(cudaGetLastError());
     return OCO_OK;
@@ -624,12 +746,12 @@ int forward_tiled(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int
         const int snt = pick_tile_index(rows, 1, plan->narrow_tiles ? 192 : plan->wide_min_avg);
         const int SNT = kTileSizes[snt];
         GemmParams su{};
-        su.w0 = plan->w.shared_up_w; su.n = S; su.K = H; su.row_bytes = plan->shared_up_row_bytes;
+        su.w0 = plan->w.shared_up_w; su.n = S; su.K = H; su.row_bytes = plan->shared_up_row_bytes; su.bias_stride = 1;
         su.xs = ws.xh; su.out = ws.mid; su.status = ws.status; su.dense_rows = rows; su.tile_rows = SNT;
         rc = launch_gemm_nt<FMT, kEpiRelu2Bf16F16>(plan, su, plan->map_xh, snt, (rows + SNT - 1) / SNT, st);
         if (rc) return rc;
         GemmParams sd{};
-        sd.w0 = plan->w.shared_down_w; sd.n = H; sd.K = S; sd.row_bytes = plan->shared_down_row_bytes;
+        sd.w0 = plan->w.shared_down_w; sd.n = H; sd.K = S; sd.row_bytes = plan->shared_down_row_bytes; sd.bias_stride = 1;
         sd.xs = ws.mid; sd.out = ws.shared_out; sd.status = ws.status; sd.dense_rows = rows; sd.tile_rows = SNT;
         rc = launch_gemm_nt<FMT, kEpiDownBf16>(plan, sd, plan->map_mid, snt, (rows + SNT - 1) / SNT, st);
         if (rc) return rc;
@@ -655,6 +777,30 @@ int forward_family(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, in
         return forward_single<ARCH>(plan, x, residual, st);
     }
     return forward_tiled<ARCH>(plan, x, residual, rows, st, residual_ready);
+}
+
+// The gpt-oss router multiplies with its weights rounded to bf16 (reference routing.metal:131-146 reads
+// bf16 router rows). The rounded copy is made here, as soon as both the router weights and the
+// workspace are bound, and waited for, so that no later call, captured or on whatever stream, can
+// meet a half-made copy.
+int prepare_router(oco_moe_plan* plan) {
+    if (plan->router_ready || !plan->have_ws || !plan->w.router_w) return OCO_OK;
+    if (plan->d.arch == OCO_ARCH_GPT_OSS && plan->d.hidden <= 3072 && plan->d.hidden % 4 == 0) {
+        const size_t n = (size_t)plan->d.experts * plan->d.hidden;
+        round_router_kernel<<<(unsigned)((n + 255) / 256), 256, 0, cudaStreamPerThread>>>(plan->w.router_w, plan->ws.router_rounded, n);
+        CK(cudaGetLastError());
+        CK(cudaStreamSynchronize(cudaStreamPerThread));
+    }
+    plan->router_ready = true;
+    return OCO_OK;
+}
+
+// Calls must be made with the device current on which the workspace was bound.
+int check_device(oco_moe_plan* plan) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev != plan->device)
+        return fail(plan, OCO_INVALID_ARGUMENT, "the plan's workspace was bound on device %d, the current device is %d", plan->device, dev);
+    return OCO_OK;
 }
 
 int forward_any(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int rows, cudaStream_t st,
@@ -705,6 +851,7 @@ int oco_moe_plan_create(const oco_moe_desc* desc, oco_moe_plan** out) {
     { const char* e = getenv("OCO_MOE_WIDE_MIN_AVG"); if (e && atoi(e) > 0) plan->wide_min_avg = atoi(e); }
     { const char* e = getenv("OCO_MOE_ROUTER_BLOCK_MIN"); if (e && atoi(e) > 0) plan->router_block_min = atoi(e); }
     { const char* e = getenv("OCO_MOE_NO_BATCH"); plan->no_batch_path = e && e[0] == '1'; }
+    { const char* e = getenv("OCO_MOE_TOKEN_MX"); plan->mx_off = e && e[0] == '0'; }
     { const char* e = getenv("OCO_MOE_BATCH_MAX_AVG"); if (e && atoi(e) > 0) plan->batch_max_avg = atoi(e) < 64 ? atoi(e) : 64; }
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) == cudaSuccess &&
@@ -757,7 +904,7 @@ int oco_moe_bind_workspace(oco_moe_plan* plan, void* workspace, size_t bytes, in
     // Control words and the never-written columns of the single-token fragments start at zero.
     CK(cudaMemset(ws.status, 0, 256));
     CK(cudaMemset(ws.actfrag, 0, (size_t)((d.top_k + 1) / 2) * (d.ffn / 32) * 128 * 2));
-    CK(cudaMemset(ws.arrivals, 0, (size_t)(d.hidden / 8 + 1) * 4));
+    CK(cudaMemset(ws.arrivals, 0, (size_t)(d.hidden + 1) * 4));
     if (d.shared_ffn) {
         CK(cudaMemset(ws.sh_actfrag, 0, (size_t)(d.shared_ffn / 32) * 128 * 2));
         CK(cudaMemset(ws.sh_ids, 0, 256));
@@ -776,11 +923,16 @@ int oco_moe_bind_workspace(oco_moe_plan* plan, void* workspace, size_t bytes, in
         }
     }
     CK(cudaDeviceSynchronize());
+    int dev = 0, sms = 0;
+    CK(cudaGetDevice(&dev));
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) plan->sm_count = sms;
+    plan->device = dev;
     plan->ws = ws;
     plan->max_rows = max_rows;
     plan->have_ws = true;
     plan->router_ready = false;
-    return OCO_OK;
+    if (int rc_r = prepare_router(plan)) return rc_r;
+    return prepare_mx(plan);
 }
 
 int oco_moe_bind_weights(oco_moe_plan* plan, const oco_moe_weights* w) {
@@ -789,13 +941,22 @@ int oco_moe_bind_weights(oco_moe_plan* plan, const oco_moe_weights* w) {
     // A plan may hold only a router (it then serves oco_moe_route), only experts (oco_moe_experts),
     // or both (oco_moe_forward needs both).
     const bool has_router = w->router_w != nullptr;
-    const bool has_experts = w->up_w != nullptr || w->down_w != nullptr || w->gate_w != nullptr;
+    const bool interleaved = w->gate_up_w != nullptr;
+    const bool has_experts = w->up_w != nullptr || w->down_w != nullptr || w->gate_w != nullptr || interleaved;
     if (!has_router && !has_experts) return fail(plan, OCO_INVALID_ARGUMENT, "no weights given");
     if (has_experts) {
-        if (!w->up_w || !w->down_w) return fail(plan, OCO_INVALID_ARGUMENT, "up_w and down_w are required");
-        if (d.arch != OCO_ARCH_NEMOTRON && !w->gate_w) return fail(plan, OCO_INVALID_ARGUMENT, "gate_w is required for gated experts");
-        if (d.arch == OCO_ARCH_GPT_OSS && (!w->gate_b || !w->up_b || !w->down_b))
-            return fail(plan, OCO_INVALID_ARGUMENT, "GPT_OSS needs gate, up and down biases");
+        if (interleaved) {
+            if (d.arch == OCO_ARCH_NEMOTRON) return fail(plan, OCO_INVALID_ARGUMENT, "gate_up_w given for a family without a gate");
+            if (w->gate_w || w->up_w) return fail(plan, OCO_INVALID_ARGUMENT, "give gate_up_w or gate_w + up_w, not both");
+            if (!w->down_w) return fail(plan, OCO_INVALID_ARGUMENT, "down_w is required");
+            if (d.arch == OCO_ARCH_GPT_OSS && (!w->gate_up_b || !w->down_b))
+                return fail(plan, OCO_INVALID_ARGUMENT, "GPT_OSS with gate_up_w needs gate_up_b and down_b");
+        } else {
+            if (!w->up_w || !w->down_w) return fail(plan, OCO_INVALID_ARGUMENT, "up_w and down_w are required");
+            if (d.arch != OCO_ARCH_NEMOTRON && !w->gate_w) return fail(plan, OCO_INVALID_ARGUMENT, "gate_w is required for gated experts");
+            if (d.arch == OCO_ARCH_GPT_OSS && (!w->gate_b || !w->up_b || !w->down_b))
+                return fail(plan, OCO_INVALID_ARGUMENT, "GPT_OSS needs gate, up and down biases");
+        }
         if (d.shared_ffn && (!w->shared_up_w || !w->shared_down_w)) return fail(plan, OCO_INVALID_ARGUMENT, "shared expert weights missing");
     }
     if (has_router) {
@@ -803,15 +964,33 @@ int oco_moe_bind_weights(oco_moe_plan* plan, const oco_moe_weights* w) {
         if (((uintptr_t)w->router_w & 15u) != 0) return fail(plan, OCO_INVALID_ARGUMENT, "router_w must be 16-byte aligned");
     }
     plan->w = *w;
+    if (interleaved) {
+        // row 2c = gate row c, row 2c + 1 = up row c; the biases likewise
+        plan->gate_rows = w->gate_up_w;
+        plan->up_rows = w->gate_up_w + plan->up_row_bytes;
+        plan->up_row_stride = 2 * plan->up_row_bytes;
+        plan->gate_bias = w->gate_up_b;
+        plan->up_bias = w->gate_up_b ? w->gate_up_b + 1 : nullptr;
+        plan->up_bias_stride = 2;
+    } else {
+        plan->gate_rows = w->gate_w;
+        plan->up_rows = w->up_w;
+        plan->up_row_stride = plan->up_row_bytes;
+        plan->gate_bias = w->gate_b;
+        plan->up_bias = w->up_b;
+        plan->up_bias_stride = 1;
+    }
     plan->have_w = has_router && has_experts;
     plan->have_experts = has_experts;
     plan->router_ready = false;
-    return OCO_OK;
+    if (int rc_r = prepare_router(plan)) return rc_r;
+    return prepare_mx(plan);
 }
 
 int oco_moe_forward(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int rows, void* cuda_stream) {
     if (!plan) return OCO_INVALID_ARGUMENT;
     if (!plan->have_ws || !plan->have_w) return fail(plan, OCO_INVALID_ARGUMENT, "bind a workspace and weights first");
+    if (int rc_dev = check_device(plan)) return rc_dev;
     if (!x || !residual) return fail(plan, OCO_INVALID_ARGUMENT, "null x or residual");
     if (rows < 1 || rows > plan->max_rows) return fail(plan, OCO_INVALID_ARGUMENT, "rows %d outside 1..%d", rows, plan->max_rows);
     if (((uintptr_t)x & 15u) || ((uintptr_t)residual & 15u)) return fail(plan, OCO_INVALID_ARGUMENT, "x and residual must be 16-byte aligned");
@@ -830,6 +1009,7 @@ int oco_moe_add_norm_forward(oco_moe_plan* plan, uint16_t* hidden, const uint16_
                              float epsilon, int full_layer, int rows, void* cuda_stream) {
     if (!plan) return OCO_INVALID_ARGUMENT;
     if (!plan->have_ws || !plan->have_w) return fail(plan, OCO_INVALID_ARGUMENT, "bind a workspace and weights first");
+    if (int rc_dev = check_device(plan)) return rc_dev;
     if (!hidden || !norm_weight) return fail(plan, OCO_INVALID_ARGUMENT, "null hidden rows or norm weight");
     if (rows < 1 || rows > plan->max_rows) return fail(plan, OCO_INVALID_ARGUMENT, "rows %d outside 1..%d", rows, plan->max_rows);
     if (((uintptr_t)hidden & 15u) || ((uintptr_t)projected & 15u)) return fail(plan, OCO_INVALID_ARGUMENT, "rows must be 16-byte aligned");
@@ -853,6 +1033,7 @@ int oco_moe_add_norm_forward(oco_moe_plan* plan, uint16_t* hidden, const uint16_
 int oco_moe_route(oco_moe_plan* plan, const uint16_t* x, int rows, void* cuda_stream) {
     if (!plan) return OCO_INVALID_ARGUMENT;
     if (!plan->have_ws || !plan->w.router_w) return fail(plan, OCO_INVALID_ARGUMENT, "bind a workspace and router weights first");
+    if (int rc_dev = check_device(plan)) return rc_dev;
     if (!x || rows < 1 || rows > plan->max_rows) return fail(plan, OCO_INVALID_ARGUMENT, "bad x or rows");
     cudaStream_t st = (cudaStream_t)cuda_stream;
     plan->launches = 0;
@@ -871,6 +1052,7 @@ int oco_moe_experts(oco_moe_plan* plan, const uint16_t* rows_bf16, const uint32_
                     uint16_t* y_bf16, void* cuda_stream) {
     if (!plan) return OCO_INVALID_ARGUMENT;
     if (!plan->have_ws || !plan->have_experts) return fail(plan, OCO_INVALID_ARGUMENT, "bind a workspace and expert weights first");
+    if (int rc_dev = check_device(plan)) return rc_dev;
     if (routes == 0) return OCO_OK;
     if (!rows_bf16 || !expert_ids || !y_bf16 || routes < 0 || routes > plan->max_rows * plan->d.top_k)
         return fail(plan, OCO_INVALID_ARGUMENT, "bad buffers, or more routes than max_rows * top_k");
@@ -908,6 +1090,7 @@ int oco_moe_forward_host(oco_moe_plan* plan, const uint16_t* x_host, uint16_t* r
                          void* cuda_stream) {
     if (!plan) return OCO_INVALID_ARGUMENT;
     if (!plan->have_ws) return fail(plan, OCO_INVALID_ARGUMENT, "bind a workspace first");
+    if (int rc_dev = check_device(plan)) return rc_dev;
     if (!x_host || !residual_host || rows < 1 || rows > plan->max_rows) return fail(plan, OCO_INVALID_ARGUMENT, "bad host buffers or rows");
     cudaStream_t st = (cudaStream_t)cuda_stream;
     const size_t bytes = (size_t)rows * plan->d.hidden * 2;
@@ -997,6 +1180,29 @@ int oco_cuda_stream_create(void** out) {
 }
 int oco_cuda_stream_destroy(void* stream) { return cu(cudaStreamDestroy((cudaStream_t)stream)); }
 int oco_cuda_stream_sync(void* stream) { return cu(cudaStreamSynchronize((cudaStream_t)stream)); }
+int oco_cuda_event_create(void** out) {
+    if (!out) return OCO_INVALID_ARGUMENT;
+    cudaEvent_t e;
+    cudaError_t r = cudaEventCreate(&e);
+    *out = (void*)e;
+    return cu(r);
+}
+int oco_cuda_event_destroy(void* event) { return cu(cudaEventDestroy((cudaEvent_t)event)); }
+int oco_cuda_event_record(void* event, void* stream) { return cu(cudaEventRecord((cudaEvent_t)event, (cudaStream_t)stream)); }
+int oco_cuda_event_sync(void* event) { return cu(cudaEventSynchronize((cudaEvent_t)event)); }
+int oco_cuda_event_elapsed_ms(void* start, void* end, float* ms) {
+    if (!ms) return OCO_INVALID_ARGUMENT;
+    return cu(cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)end));
+}
+
+int oco_moe_selftest_wait_timeout(oco_moe_plan* plan, long long wait_cycles, void* cuda_stream) {
+    if (!plan || !plan->have_ws) return OCO_INVALID_ARGUMENT;
+    if (wait_cycles < 1 || wait_cycles > kWaitCycles) return fail(plan, OCO_INVALID_ARGUMENT, "wait_cycles outside 1..%lld", kWaitCycles);
+    if (int rc_dev = check_device(plan)) return rc_dev;
+    wait_timeout_kernel<<<1, 32, 0, (cudaStream_t)cuda_stream>>>(plan->ws.status, wait_cycles);
+    CK(cudaGetLastError());
+    return OCO_OK;
+}
 
 }  // extern "C"
 

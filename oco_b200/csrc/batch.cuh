@@ -81,7 +81,8 @@ struct BatchParams {
     uint16_t* out;            // expand: half [R, n_out] expert-sorted, operand order; down: bf16 [R, n_out] route order
     int n_in, n_out;          // contraction length, output features
     int parts;                // CTAs per group
-    uint32_t row_bytes;
+    uint32_t row_bytes;       // bytes from one weight row of a matrix to its next row
+    int bias_stride;          // floats from one feature's bias to the next
     uint32_t* status;
 };
 
@@ -133,11 +134,11 @@ __global__ void __launch_bounds__(kBatchThreads, 1) batch_rows_kernel(const Batc
         // biases travel while the rows stream: accumulator rows g (span A) and g (span B)
         const int fa = f0 + g, fb = GATED ? fa : fa + 8;
         float bias_a = 0.f, bias_b = 0.f;
-        if (p.b0) bias_a = bf16_round(__ldg(p.b0 + (size_t)expert * p.n_out + fa));
+        if (p.b0) bias_a = bf16_round(__ldg(p.b0 + ((size_t)expert * p.n_out + fa) * p.bias_stride));
         if (GATED) {
-            if (EPI == kEpiSwigluF16) bias_b = bf16_round(__fadd_rn(__ldg(p.b1 + (size_t)expert * p.n_out + fa), 1.0f));
+            if (EPI == kEpiSwigluF16) bias_b = bf16_round(__fadd_rn(__ldg(p.b1 + ((size_t)expert * p.n_out + fa) * p.bias_stride), 1.0f));
         } else if (p.b0) {
-            bias_b = bf16_round(__ldg(p.b0 + (size_t)expert * p.n_out + fb));
+            bias_b = bf16_round(__ldg(p.b0 + ((size_t)expert * p.n_out + fb) * p.bias_stride));
         }
         float sum[4] = {0.f, 0.f, 0.f, 0.f};
         if (!fetched) { mbar_wait(xbar, 0u, give_up, p.status); fetched = true; }

@@ -137,22 +137,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Waits for the phase with the given parity. Gives up after `kWaitCycles` clock cycles, or at once
-// when another thread of the CTA has already given up (`*abort_flag` set): the caller carries on
-// with whatever is in memory, the kernel runs to its normal end and the host sees the status word.
+// Waits for the phase with the given parity. Gives up after `limit` clock cycles, or at once when
+// another thread of the CTA has already given up (`*abort_flag` set): the caller carries on with
+// whatever is in memory, the kernel runs to its normal end and the host sees the status word.
 constexpr long long kWaitCycles = 400000000LL;  // about 0.2 s at B200 clocks
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t* status_word) {
+__device__ __forceinline__ void mbar_wait_for(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                              uint32_t* status_word, long long limit) {
     if (mbar_try_wait(bar, parity)) return;
     long long start = clock64();
     while (!mbar_try_wait(bar, parity)) {
         if (*abort_flag) return;
-        if (clock64() - start > kWaitCycles) {
+        if (clock64() - start > limit) {
             *abort_flag = 1u;
             atomicExch(status_word, (uint32_t)kDevBarrierTimeout);
             return;
         }
     }
+}
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint32_t* status_word) {
+    mbar_wait_for(bar, parity, abort_flag, status_word, kWaitCycles);
 }
 
 // Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may

@@ -19,6 +19,7 @@
 // on the tensor pipe even though the kernel is bandwidth-bound.
 #pragma once
 #include "common.cuh"
+#include "mx_pieces.cuh"
 #include "router.cuh"
 
 namespace oco {
@@ -494,7 +495,9 @@ struct DecodeExpandParams {
     __half* actfrag;         // out: B fragments of the down projection, [K][F/32] blocks of 128 bytes
     int H, F, K;
     int ksplit;              // warps per unit: a divisor of the warps per CTA
-    uint32_t row_bytes;      // bytes of one packed row of length H
+    uint32_t row_bytes;      // bytes from one gate (or up) row to the next: the packed length of a row of H
+                             // elements, or twice that when gate and up rows are interleaved in one tensor
+    int bias_stride;         // floats from one feature's bias to the next (1, or 2 when interleaved)
     uint32_t* status;        // device status word: a copy that never arrives is reported here
 };
 
@@ -549,8 +552,8 @@ __global__ void __launch_bounds__(tok_warps(FMT) * 32, 1) decode_expand_kernel(c
         else rs.begin(p.up_w + off, p.up_w + off + (size_t)8 * p.row_bytes, p.row_bytes, kb0, nb);
         float b0 = 0.f, b1 = 0.f;
         if (ARCH == OCO_ARCH_GPT_OSS && s == 0 && tig == 0) {   // biases travel while the rows stream
-            b0 = __ldg(p.gate_b + (size_t)e * p.F + c0 + g);
-            b1 = __ldg(p.up_b + (size_t)e * p.F + c0 + g);
+            b0 = __ldg(p.gate_b + ((size_t)e * p.F + c0 + g) * p.bias_stride);
+            b1 = __ldg(p.up_b + ((size_t)e * p.F + c0 + g) * p.bias_stride);
         }
         float sum[4] = {0.f, 0.f, 0.f, 0.f};
         if (!fetched) { mbar_wait(xbar, 0u, give_up, p.status); fetched = true; }
@@ -672,7 +675,8 @@ __global__ void __launch_bounds__(tok_warps(FMT) * 32, 1) decode_down_kernel(con
                 if (seen == (uint32_t)(p.K - 1)) p.arrivals[rb] = 0;   // ready for the next call on this stream
             }
             seen = __shfl_sync(0xffffffffu, seen, 0);
-            if (seen == (uint32_t)(p.K - 1) && lane < 16) {
+            // (a step during which a bounded wait gave up leaves the residual as it was)
+            if (seen == (uint32_t)(p.K - 1) && lane < 16 && *reinterpret_cast<volatile uint32_t*>(p.status) == 0u) {
                 __threadfence();
                 const int row = d0 + lane;
                 float sres = p.shared ? bf16_bits_to_f32(p.shared[row]) : 0.0f;
@@ -688,13 +692,15 @@ __global__ void __launch_bounds__(tok_warps(FMT) * 32, 1) decode_down_kernel(con
 // Router of one token: logits (one warp per expert, reference router_logits, routing.metal:131-146),
 // then the CTA that finishes last selects the experts and their weights for the whole token
 // (routing.metal:71-94; nemotron.metal:167-211). On the side, the CTAs turn the token into the B
-// fragments the expert kernels multiply with. grid ceil(E/8), 256 threads.
+// fragments the expert kernels multiply with (or, for the block-scaled kernels, into e2m1 pieces).
+// grid ceil(E/8), 256 threads.
 template <int ARCH>
 __global__ void __launch_bounds__(256) router_token_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w,
                                                            const float* __restrict__ bias, int H, int E, int K,
                                                            int normalize, float scale, float* __restrict__ logits,
                                                            uint32_t* __restrict__ ids, float* __restrict__ probs,
-                                                           __half* __restrict__ xfrag, int fmt, uint32_t* __restrict__ arrival) {
+                                                           __half* __restrict__ xfrag, int fmt, uint32_t* __restrict__ arrival,
+                                                           unsigned char* __restrict__ mx_b, unsigned char* __restrict__ mx_sfb) {
     __shared__ int is_last;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int e = blockIdx.x * 8 + warp;
@@ -706,7 +712,17 @@ __global__ void __launch_bounds__(256) router_token_kernel(const uint16_t* __res
         if (ARCH == OCO_ARCH_GPT_OSS) s = __fadd_rn(s, bf16_round(bias[e]));
         if (lane == 0) logits[e] = s;
     }
-    for (int k = blockIdx.x * 256 + threadIdx.x; k < H; k += gridDim.x * 256) frag_store(xfrag, k, bf16_bits_to_f32(x[k]), fmt);
+    if (mx_b) {
+        // the token as e2m1 pieces for the block-scaled expert kernels: one warp per 32-element block,
+        // zero blocks up to the end of the last K group
+        const int nkb = H >> 5, nblk = ((nkb + 7) >> 3) << 3;
+        for (int blk = blockIdx.x * 8 + warp; blk < nblk; blk += gridDim.x * 8) {
+            const float v = blk < nkb ? bf16_bits_to_f32(x[blk * 32 + (lane >> 1) + 16 * (lane & 1)]) : 0.0f;
+            mx_split_block(v, lane, mx_b, mx_sfb, 8u, 0u, (uint32_t)blk);
+        }
+    } else {
+        for (int k = blockIdx.x * 256 + threadIdx.x; k < H; k += gridDim.x * 256) frag_store(xfrag, k, bf16_bits_to_f32(x[k]), fmt);
+    }
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {

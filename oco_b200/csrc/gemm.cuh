@@ -42,7 +42,9 @@ struct GemmParams {
     const float* b1;     // bias of w1
     int n;               // output features per expert
     int K;               // contraction length
-    uint32_t row_bytes;  // packed bytes of one weight row
+    uint32_t row_bytes;  // bytes from one weight row of a matrix to its next row (the packed row length, or twice
+                         // that when gate and up rows are interleaved in one tensor)
+    int bias_stride;     // floats from one feature's bias to the next (1, or 2 when interleaved)
     const uint32_t* tiles;       // (expert, first row within expert) pairs; null = dense
     const uint32_t* tile_count;
     const uint32_t* offsets;     // exclusive expert offsets into the sorted rows
@@ -512,8 +514,8 @@ grouped_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
         const bool live = f < p.n;
         float bias0 = 0.f, bias1 = 0.f;
         if (live) {
-            if (p.b0) bias0 = bf16_round(p.b0[(size_t)expert * p.n + f]);
-            if (EPI == kEpiSwigluF16) bias1 = bf16_round(__fadd_rn(p.b1[(size_t)expert * p.n + f], 1.0f));
+            if (p.b0) bias0 = bf16_round(p.b0[((size_t)expert * p.n + f) * p.bias_stride]);
+            if (EPI == kEpiSwigluF16) bias1 = bf16_round(__fadd_rn(p.b1[((size_t)expert * p.n + f) * p.bias_stride], 1.0f));
         }
         // Rows written for a later tile kernel keep the operand order within each block.
         const int fcol = EPI == kEpiDownBf16 ? f : operand_pos(FMT, f);
@@ -600,8 +602,8 @@ __global__ void __launch_bounds__(128) grouped_gemm_simt_kernel(const GemmParams
     const uint8_t* r1 = GATED ? p.w1 + ((size_t)expert * p.n + frow) * p.row_bytes : nullptr;
     const int nkb = (p.K + 63) / 64;
     float bias0 = 0.f, bias1 = 0.f;
-    if (p.b0) bias0 = bf16_round(p.b0[(size_t)expert * p.n + frow]);
-    if (EPI == kEpiSwigluF16) bias1 = bf16_round(__fadd_rn(p.b1[(size_t)expert * p.n + frow], 1.0f));
+    if (p.b0) bias0 = bf16_round(p.b0[((size_t)expert * p.n + frow) * p.bias_stride]);
+    if (EPI == kEpiSwigluF16) bias1 = bf16_round(__fadd_rn(p.b1[((size_t)expert * p.n + frow) * p.bias_stride], 1.0f));
     for (uint32_t c = 0; c < nv; c += 8) {
         float acc0[8], acc1[8];
 #pragma unroll

@@ -282,11 +282,11 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
             const uint32_t c_end = min(done.nv, c_begin + 64u);
             const int fa = done.f0 + erow, fb = GATED ? fa : fa + 128;        // features of accumulator 0 / 1
             float bias_a = 0.f, bias_b = 0.f;
-            if (fa < p.n && p.b0) bias_a = bf16_round(p.b0[(size_t)done.expert * p.n + fa]);
+            if (fa < p.n && p.b0) bias_a = bf16_round(p.b0[((size_t)done.expert * p.n + fa) * p.bias_stride]);
             if (GATED) {
-                if (EPI == kEpiSwigluF16 && fa < p.n) bias_b = bf16_round(__fadd_rn(p.b1[(size_t)done.expert * p.n + fa], 1.0f));
+                if (EPI == kEpiSwigluF16 && fa < p.n) bias_b = bf16_round(__fadd_rn(p.b1[((size_t)done.expert * p.n + fa) * p.bias_stride], 1.0f));
             } else if (fb < p.n && p.b0) {
-                bias_b = bf16_round(p.b0[(size_t)done.expert * p.n + fb]);
+                bias_b = bf16_round(p.b0[((size_t)done.expert * p.n + fb) * p.bias_stride]);
             }
             const int col_a = EPI == kEpiDownBf16 ? fa : operand_pos(FMT, fa);
             const int col_b = EPI == kEpiDownBf16 ? fb : operand_pos(FMT, fb);

@@ -159,10 +159,13 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __rest
                                                           const float* __restrict__ probs,
                                                           uint16_t* __restrict__ out,
                                                           const uint16_t* __restrict__ shared, int H, int T, int K,
-                                                          int round_sum, int shared_mode) {
+                                                          int round_sum, int shared_mode,
+                                                          const uint32_t* __restrict__ status) {
     size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     size_t pairs = (size_t)T * H / 2;
     if (i >= pairs) return;
+    // a step during which a bounded wait gave up leaves the residual rows as they were
+    if (status && *reinterpret_cast<const volatile uint32_t*>(status) != 0u) return;
     int t = (int)(i / (H / 2)), d = (int)(i % (H / 2)) * 2;
     float s0 = 0.f, s1 = 0.f;
     uint32_t resw = *reinterpret_cast<const uint32_t*>(out + (size_t)t * H + d);
@@ -182,6 +185,23 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __rest
     if (round_sum) { s0 = bf16_round(s0); s1 = bf16_round(s1); }
     uint32_t o = (uint32_t)f32_to_bf16_bits(__fadd_rn(r0, s0)) | ((uint32_t)f32_to_bf16_bits(__fadd_rn(r1, s1)) << 16);
     *reinterpret_cast<uint32_t*>(out + (size_t)t * H + d) = o;
+}
+
+// The bounded wait, run on a barrier that nobody arrives at: one warp waits `limit` clock cycles, gives
+// up, sets the status word and returns normally. Lets a host test see the whole give-up path
+// (status word -> oco_moe_poll -> OCO_DEVICE_TIMEOUT) without any fault on the device.
+__global__ void __launch_bounds__(32) wait_timeout_kernel(uint32_t* status, long long limit) {
+    __shared__ __align__(8) unsigned long long bar_storage;
+    __shared__ volatile uint32_t give_up;
+    const uint32_t bar = smem_u32(&bar_storage);
+    if (threadIdx.x == 0) {
+        give_up = 0u;
+        mbar_init(bar, 1);
+        fence_barrier_init();
+    }
+    __syncwarp();
+    if (threadIdx.x == 0) mbar_wait_for(bar, 0u, &give_up, status, limit);
+    __syncwarp();
 }
 
 }  // namespace oco

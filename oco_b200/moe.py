@@ -191,16 +191,30 @@ class _Weights:
     down_b: Optional[torch.Tensor] = None
     shared_up_w: Optional[torch.Tensor] = None
     shared_down_w: Optional[torch.Tensor] = None
+    gate_up_w: Optional[torch.Tensor] = None   # one tensor, rows interleaved: 2c = gate row c, 2c + 1 = up row c
+    gate_up_b: Optional[torch.Tensor] = None
 
     @classmethod
-    def from_layer(cls, layer: synth.Layer, device="cuda", misalign: int = 0):
+    def from_layer(cls, layer: synth.Layer, device="cuda", misalign: int = 0, interleaved: bool = False):
         """Uploads a host layer unchanged (reference `import()` / `MappedRegions::new`,
         src/gpu/buffer.rs:151-194: the GGUF bytes are registered, never repacked). `misalign`
-        applies to the packed expert banks only; f32 tensors keep their natural alignment."""
+        applies to the packed expert banks only; f32 tensors keep their natural alignment.
+        `interleaved` stages gate and up as one tensor with alternating rows (and biases)."""
         packed = ("gate_w", "up_w", "down_w", "shared_up_w", "shared_down_w")
-        return cls(**{k: _dev_bytes(getattr(layer, k), device, misalign if k in packed else 0) for k in
-                      ("router_w", "router_b", "gate_w", "up_w", "down_w", "gate_b", "up_b", "down_b",
-                       "shared_up_w", "shared_down_w")})
+        names = ["router_w", "router_b", "gate_w", "up_w", "down_w", "gate_b", "up_b", "down_b", "shared_up_w", "shared_down_w"]
+        if interleaved and layer.gate_w is not None:
+            E, F, rb = layer.gate_w.shape
+            both = np.empty((E, 2 * F, rb), np.uint8)
+            both[:, 0::2], both[:, 1::2] = layer.gate_w, layer.up_w
+            out = cls(**{k: _dev_bytes(getattr(layer, k), device, misalign if k in packed else 0)
+                         for k in names if k not in ("gate_w", "up_w", "gate_b", "up_b")})
+            out.gate_up_w = _dev_bytes(both, device, misalign)
+            if layer.gate_b is not None:
+                bias = np.empty((E, 2 * F), np.float32)
+                bias[:, 0::2], bias[:, 1::2] = layer.gate_b, layer.up_b
+                out.gate_up_b = _dev_bytes(bias, device)
+            return out
+        return cls(**{k: _dev_bytes(getattr(layer, k), device, misalign if k in packed else 0) for k in names})
 
 
 class Experts(_Weights):
@@ -312,13 +326,13 @@ def plan_for(layer: synth.Layer, gemm_impl: int = 0) -> _Plan:
 
 
 def run_layer(layer: synth.Layer, x_bits: np.ndarray, residual_bits: np.ndarray, gemm_impl: int = 0,
-              device="cuda", state: Optional[dict] = None, misalign: int = 0):
+              device="cuda", state: Optional[dict] = None, misalign: int = 0, interleaved: bool = False):
     """Convenience used by tests and the benchmark: uploads (or reuses) a layer, runs it on bf16
     bit patterns given as uint16 arrays and returns (residual bits, routing dict)."""
     state = state if state is not None else {}
     if "plan" not in state:
         state["plan"] = plan_for(layer, gemm_impl)
-        state["weights"] = _Weights.from_layer(layer, device, misalign)
+        state["weights"] = _Weights.from_layer(layer, device, misalign, interleaved)
     plan, w = state["plan"], state["weights"]
     rows = x_bits.shape[0]
     x = torch.from_numpy(np.ascontiguousarray(x_bits).view(np.int16)).to(device)
