@@ -54,9 +54,11 @@ struct Workspace {
     __half* sh_actfrag = nullptr;
     uint32_t* sh_ids = nullptr;
     uint16_t* norm = nullptr;     // bf16 [T, H] normalised rows of oco_moe_add_norm_forward
-    CUtensorMap* mx_maps = nullptr;   // block-scaled single-token path: tensor maps over the packed rows
-    unsigned char* mx_xb = nullptr;   //   the token as e2m1 pieces
+    unsigned char* mx_xb = nullptr;   // block-scaled single-token path: the token as e2m1 pieces
     unsigned char* mx_xsfb = nullptr; //   and their scales
+    unsigned char* mx_actb = nullptr; //   each route's activations as e2m1 pieces [top_k][..], their scales,
+    unsigned char* mx_actsfb = nullptr;
+    uint32_t* mx_blk_arrivals = nullptr;   // and one counter per route and block of 32 activations
     uint16_t* host_x = nullptr;   // staging for the host-buffer entry point
     uint16_t* host_res = nullptr;
     size_t total = 0;
@@ -86,8 +88,7 @@ struct oco_moe_plan {
     uint32_t up_row_stride = 0;  // bytes between consecutive gate (or up) rows
     int up_bias_stride = 1;      // floats between consecutive gate (or up) biases
     // block-scaled single-token path (mx.cuh): usable once prepare_mx has built the tensor maps
-    bool mx_ready = false, mx_off = false;   // OCO_MOE_TOKEN_MX=0 keeps the mma.sync kernels
-    int mx_pr_up = 8, mx_pr_down = 8;
+    bool mx_ready = false, mx_on = false;    // OCO_MOE_TOKEN_MX=1 selects them (measured slower than the mma.sync kernels so far)
     CUtensorMap map_xs[kTileKinds], map_act[kTileKinds], map_xh[kTileKinds], map_mid[kTileKinds];
     // Per-phase timestamps (the counterpart of the reference's OCO_PROFILE counter heap,
     // src/gpu/profile.rs:1-31, src/gpu/dispatch.rs:189-208): one event before each kernel.
@@ -210,9 +211,11 @@ Workspace carve(const oco_moe_desc& d, int max_rows, unsigned char* base) {
     }
     w.norm = (uint16_t*)take(T * H * 2);
     if (d.weight_format == OCO_FMT_MXFP4) {
-        w.mx_maps = (CUtensorMap*)take((size_t)3 * kMxMaxResidues * kMxMapSizes * sizeof(CUtensorMap));
         w.mx_xb = (unsigned char*)take(mx_b_bytes(8, (uint32_t)(H / 32)));
         w.mx_xsfb = (unsigned char*)take(mx_sfb_bytes((uint32_t)(H / 32)));
+        w.mx_actb = (unsigned char*)take(K * mx_b_bytes(8, (uint32_t)(F / 32)));
+        w.mx_actsfb = (unsigned char*)take(K * mx_sfb_bytes((uint32_t)(F / 32)));
+        w.mx_blk_arrivals = (uint32_t*)take(K * (F / 32) * 4);
     }
     w.host_x = (uint16_t*)take(T * H * 2);
     w.host_res = (uint16_t*)take(T * H * 2);
@@ -365,68 +368,19 @@ int launch_down(oco_moe_plan* plan, DecodeDownParams dp, cudaStream_t st) {
 }
 
 // ---- block-scaled single-token path (mx.cuh) --------------------------------------------------------
-// One 2-D tensor map per (tensor, row residue, box height): rows `pr` apart share their offset within a
-// 16-byte word, so [row / pr][16-byte envelope of a row] with pitch pr * stride is a legal TMA view.
-int encode_mx_map(oco_moe_plan* plan, CUtensorMap* map, const uint8_t* row0, uint32_t row_len, uint64_t pitch, uint64_t periods, uint32_t box_rows) {
-    static const EncodeTiledFn encode = [] {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            fn = nullptr;
-        return (EncodeTiledFn)fn;
-    }();
-    if (!encode) return fail(plan, OCO_CUDA_ERROR, "cuTensorMapEncodeTiled unavailable");
-    const uintptr_t a = (uintptr_t)row0;
-    const uint32_t off = (uint32_t)(a & 15u);
-    cuuint64_t dims[2] = {(cuuint64_t)((off + row_len + 15u) / 16u * 2u), periods};   // 8-byte elements
-    cuuint64_t strides[1] = {pitch};
-    cuuint32_t box[2] = {kMxSlot / 8, box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, (void*)(a & ~(uintptr_t)15), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(plan, OCO_CUDA_ERROR, "cuTensorMapEncodeTiled (packed rows) failed (%d)", (int)r);
-    return OCO_OK;
-}
-
-int mx_period_rows(uint32_t stride) { return (8u * stride) % 16u == 0 ? 8 : 16; }
-
-// Builds the maps once weights and workspace are both bound (GPT_OSS / MXFP4 only). Shapes the path
-// cannot take simply leave mx_ready false and the mma.sync token kernels run.
+// Shapes the path cannot take leave mx_ready false and the mma.sync token kernels run (GPT_OSS / MXFP4 only).
 int prepare_mx(oco_moe_plan* plan) {
     plan->mx_ready = false;
     const oco_moe_desc& d = plan->d;
-    if (plan->mx_off || d.arch != OCO_ARCH_GPT_OSS || !plan->have_ws || !plan->have_w || !plan->ws.mx_maps) return OCO_OK;
-    const int H = d.hidden, F = d.ffn, E = d.experts;
-    const int pr_up = mx_period_rows(plan->up_row_stride), pr_dn = mx_period_rows(plan->down_row_bytes);
-    if (F % pr_up || H % pr_dn || H > 12288 || F > 12288) return OCO_OK;   // 384 tensor-memory columns of operand scales
-    // shared memory: at least two raw stages beside the fixed part
-    const uint32_t fix_up = mx_fixed_smem(2, 8, (uint32_t)(H / 32)), fix_dn = mx_fixed_smem(1, 16, (uint32_t)(F / 32));
-    if (fix_up + 2 * mx_raw_stage_bytes(2, pr_up, (128 / pr_up) * kMxSlot + 1024) > kMaxDynamicSmem ||
-        fix_dn + 2 * mx_raw_stage_bytes(1, pr_dn, (128 / pr_dn) * kMxSlot + 1024) > kMaxDynamicSmem)
+    if (!plan->mx_on || d.arch != OCO_ARCH_GPT_OSS || !plan->have_ws || !plan->have_w || !plan->ws.mx_xb) return OCO_OK;
+    const int H = d.hidden, F = d.ffn;
+    if (F % 32 || H % 8 || H > 12288 || F > 12288) return OCO_OK;   // 384 tensor-memory columns of operand scales
+    // shared memory: the fixed part and the rings of at least one pair of producer warps per matrix
+    const int per_cta_up = std::min(16, (d.top_k * (F / 8) + plan->sm_count - 1) / plan->sm_count);
+    const int per_cta_dn = std::min(16, (d.top_k * (H / 8) + plan->sm_count - 1) / plan->sm_count);
+    if (mx_fixed_smem(2, (uint32_t)(H / 32)) + 16 * mx_ring_bytes(per_cta_up) > kMaxDynamicSmem ||
+        mx_fixed_smem(1, (uint32_t)(F / 32)) + 8 * mx_ring_bytes(per_cta_dn) > kMaxDynamicSmem)
         return OCO_OK;
-    const size_t n = (size_t)3 * kMxMaxResidues * kMxMapSizes;
-    CUtensorMap* host = new (std::nothrow) CUtensorMap[n];
-    if (!host) return fail(plan, OCO_CUDA_ERROR, "out of host memory");
-    memset(host, 0, n * sizeof(CUtensorMap));
-    struct T { const uint8_t* w; uint32_t stride, len; int pr, rows; } t[3] = {
-        {plan->gate_rows, plan->up_row_stride, plan->up_row_bytes, pr_up, E * F},
-        {plan->up_rows, plan->up_row_stride, plan->up_row_bytes, pr_up, E * F},
-        {plan->w.down_w, plan->down_row_bytes, plan->down_row_bytes, pr_dn, E * H}};
-    int rc = OCO_OK;
-    for (int k = 0; k < 3 && rc == OCO_OK; k++)
-        for (int j = 0; j < t[k].pr && rc == OCO_OK; j++)
-            for (int lg = 0; lg < kMxMapSizes && rc == OCO_OK; lg++)
-                rc = encode_mx_map(plan, host + ((size_t)k * kMxMaxResidues + j) * kMxMapSizes + lg, t[k].w + (size_t)j * t[k].stride,
-                                   t[k].len, (uint64_t)t[k].pr * t[k].stride, (uint64_t)(t[k].rows / t[k].pr), 1u << lg);
-    if (rc == OCO_OK) {
-        cudaError_t e = cudaMemcpy(plan->ws.mx_maps, host, n * sizeof(CUtensorMap), cudaMemcpyHostToDevice);
-        if (e != cudaSuccess) rc = fail(plan, OCO_CUDA_ERROR, "tensor map upload: %s", cudaGetErrorString(e));
-    }
-    delete[] host;
-    if (rc) return rc;
-    plan->mx_pr_up = pr_up; plan->mx_pr_down = pr_dn;
     plan->mx_ready = true;
     return OCO_OK;
 }
@@ -434,25 +388,15 @@ int prepare_mx(oco_moe_plan* plan) {
 template <bool EXPAND>
 int launch_mx(oco_moe_plan* plan, MxParams mp, cudaStream_t st) {
     const int n_mat = EXPAND ? 2 : 1;
-    const int upr = mp.rows_per_route / mp.PR, units_total = mp.routes * upr;
+    const int units_total = mp.routes * (mp.rows_per_route / 8);
     const int grid = std::min(plan->sm_count, units_total);
-    // the largest raw region any pass of any CTA needs (the cut into boxes does not depend on the ids)
-    uint32_t region = 128;
-    for (int c = 0; c < grid; c++) {
-        const int u_end = (int)((long long)(c + 1) * units_total / grid);
-        for (int u0 = (int)((long long)c * units_total / grid); u0 < u_end;) {
-            const int u1 = mx_pass_end(u0, u_end, upr, mp.PR, !EXPAND);
-            region = std::max(region, mx_plan_copies(u0, u1, upr, [](int, int, int, uint32_t) {}, [](int, uint32_t) {}));
-            u0 = u1;
-        }
-    }
-    mp.region = (int)region;
-    const uint32_t fixed = mx_fixed_smem(n_mat, EXPAND ? 8 : 16, (uint32_t)(mp.K / 32));
-    const uint32_t stage = mx_raw_stage_bytes(n_mat, mp.PR, mp.region);
-    mp.raw_stages = (int)std::min<size_t>(12, (kMaxDynamicSmem - fixed) / stage);
-    if (mp.raw_stages < 2) return fail(plan, OCO_UNSUPPORTED_SHAPE, "shape too large for the block-scaled token kernels");
+    const uint32_t fixed = mx_fixed_smem(n_mat, (uint32_t)(mp.K / 32));
+    // units per pass: a CTA's whole share if it fits the 128 tile rows (16 units)
+    mp.pass_units = std::min(16, (units_total + grid - 1) / grid);
+    const size_t smem = fixed + (size_t)n_mat * 8 * mx_ring_bytes(mp.pass_units);
+    if (smem > kMaxDynamicSmem) return fail(plan, OCO_UNSUPPORTED_SHAPE, "shape too large for the block-scaled token kernels");
     ALLOW_SMEM_ONCE((mx_rows_kernel<EXPAND>));
-    CK(launch_dependent(mx_rows_kernel<EXPAND>, dim3(grid), dim3(kMxThreads), fixed + (size_t)mp.raw_stages * stage, st, mp));
+    CK(launch_dependent(mx_rows_kernel<EXPAND>, dim3(grid), dim3(kMxThreads), smem, st, mp));
     plan->launches++;
     CK(cudaGetLastError());
     return OCO_OK;
@@ -492,17 +436,25 @@ int forward_single(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, cu
     if (mx) {
         // MXFP4 rows straight into the block-scaled MMA (mx.cuh): expand with the activation fused, then
         // down with the weighted sum onto the residual by whoever finishes an output-row block last
+        auto envelope_end = [](const uint8_t* w, size_t rows, uint32_t stride, uint32_t len) {
+            return (const uint8_t*)(((uintptr_t)w + (rows - 1) * stride + len + 15) & ~(uintptr_t)15);
+        };
         MxParams ex{};
-        ex.maps = ws.mx_maps; ex.w[0] = plan->gate_rows; ex.w[1] = plan->up_rows; ex.tensor[0] = 0; ex.tensor[1] = 1; ex.n_mat = 2;
-        ex.row_stride = plan->up_row_stride; ex.PR = plan->mx_pr_up; ex.K = H; ex.rows_per_route = F; ex.routes = K; ex.ids = ws.ids;
+        ex.w[0] = plan->gate_rows; ex.w[1] = plan->up_rows;
+        ex.w_end[0] = envelope_end(plan->gate_rows, (size_t)E * F, plan->up_row_stride, plan->up_row_bytes);
+        ex.w_end[1] = envelope_end(plan->up_rows, (size_t)E * F, plan->up_row_stride, plan->up_row_bytes);
+        ex.row_stride = plan->up_row_stride; ex.K = H; ex.rows_per_route = F; ex.routes = K; ex.ids = ws.ids;
         ex.b_img = ws.mx_xb; ex.sfb_img = ws.mx_xsfb; ex.b0 = plan->gate_bias; ex.b1 = plan->up_bias; ex.bias_stride = plan->up_bias_stride;
-        ex.act_out = ws.act1; ex.status = ws.status;
+        ex.act_out = ws.act1; ex.act_b = ws.mx_actb; ex.act_sfb = ws.mx_actsfb; ex.blk_arrivals = ws.mx_blk_arrivals;
+        ex.act_b_route_bytes = mx_b_bytes(8, (uint32_t)(F / 32)); ex.act_sfb_route_bytes = mx_sfb_bytes((uint32_t)(F / 32));
+        ex.status = ws.status;
         mark(plan, st, "expand");
         int rc = launch_mx<true>(plan, ex, st);
         if (rc) return rc;
         MxParams dn{};
-        dn.maps = ws.mx_maps; dn.w[0] = plan->w.down_w; dn.tensor[0] = 2; dn.n_mat = 1; dn.row_stride = plan->down_row_bytes;
-        dn.PR = plan->mx_pr_down; dn.K = F; dn.rows_per_route = H; dn.routes = K; dn.ids = ws.ids; dn.act = ws.act1;
+        dn.w[0] = plan->w.down_w; dn.w_end[0] = envelope_end(plan->w.down_w, (size_t)E * H, plan->down_row_bytes, plan->down_row_bytes);
+        dn.row_stride = plan->down_row_bytes; dn.K = F; dn.rows_per_route = H; dn.routes = K; dn.ids = ws.ids;
+        dn.b_img = ws.mx_actb; dn.sfb_img = ws.mx_actsfb; dn.b_route_bytes = ex.act_b_route_bytes; dn.sfb_route_bytes = ex.act_sfb_route_bytes;
         dn.b0 = plan->w.down_b; dn.bias_stride = 1; dn.y = ws.y; dn.arrivals = ws.arrivals; dn.probs = ws.probs; dn.residual = residual;
         dn.round_sum = 1; dn.status = ws.status;
         mark(plan, st, "down_combine");
@@ -851,7 +803,7 @@ int oco_moe_plan_create(const oco_moe_desc* desc, oco_moe_plan** out) {
     { const char* e = getenv("OCO_MOE_WIDE_MIN_AVG"); if (e && atoi(e) > 0) plan->wide_min_avg = atoi(e); }
     { const char* e = getenv("OCO_MOE_ROUTER_BLOCK_MIN"); if (e && atoi(e) > 0) plan->router_block_min = atoi(e); }
     { const char* e = getenv("OCO_MOE_NO_BATCH"); plan->no_batch_path = e && e[0] == '1'; }
-    { const char* e = getenv("OCO_MOE_TOKEN_MX"); plan->mx_off = e && e[0] == '0'; }
+    { const char* e = getenv("OCO_MOE_TOKEN_MX"); plan->mx_on = e && e[0] == '1'; }
     { const char* e = getenv("OCO_MOE_BATCH_MAX_AVG"); if (e && atoi(e) > 0) plan->batch_max_avg = atoi(e) < 64 ? atoi(e) : 64; }
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) == cudaSuccess &&
@@ -905,6 +857,12 @@ int oco_moe_bind_workspace(oco_moe_plan* plan, void* workspace, size_t bytes, in
     CK(cudaMemset(ws.status, 0, 256));
     CK(cudaMemset(ws.actfrag, 0, (size_t)((d.top_k + 1) / 2) * (d.ffn / 32) * 128 * 2));
     CK(cudaMemset(ws.arrivals, 0, (size_t)(d.hidden + 1) * 4));
+    if (ws.mx_actb) {
+        // blocks past the end of a row stay zero for good; the counters are left at zero by every call
+        CK(cudaMemset(ws.mx_actb, 0, (size_t)d.top_k * mx_b_bytes(8, (uint32_t)(d.ffn / 32))));
+        CK(cudaMemset(ws.mx_actsfb, 0, (size_t)d.top_k * mx_sfb_bytes((uint32_t)(d.ffn / 32))));
+        CK(cudaMemset(ws.mx_blk_arrivals, 0, (size_t)d.top_k * (d.ffn / 32) * 4));
+    }
     if (d.shared_ffn) {
         CK(cudaMemset(ws.sh_actfrag, 0, (size_t)(d.shared_ffn / 32) * 128 * 2));
         CK(cudaMemset(ws.sh_ids, 0, 256));

@@ -1,14 +1,14 @@
 // MXFP4 expert rows on the block-scaled tensor-core path (tcgen05.mma kind::mxf4, UE8M0 scales per 32
-// elements, fp32 accumulators in tensor memory), for one token and for a few tokens.
+// elements, fp32 accumulators in tensor memory), for one token.
 //
 // A GGUF MXFP4 block is already what this MMA kind multiplies: sixteen bytes of e2m1 pairs and one
-// E8M0 scale. Nothing is decoded: the packed rows stream from HBM into shared memory (TMA tensor
-// copies), producer warps move each block's sixteen code bytes to the 16-byte-aligned position the
-// MMA descriptor wants and its scale byte into the scale-factor tile, and one thread issues the
-// MMAs. A code byte holds elements j and j + 16 of its block while the tensor core reads a byte as
-// two consecutive contraction positions, so the activation operand is laid out in the same
-// "operand order" (position 2j = element j, position 2j + 1 = element j + 16); a dot product does
-// not care in which order k is visited.
+// E8M0 scale. Nothing is decoded: the packed rows stream from HBM into shared memory, producer warps
+// move each block's sixteen code bytes to the 16-byte-aligned position the MMA descriptor wants and
+// its scale byte into the scale-factor tile, and one thread issues the MMAs. A code byte holds
+// elements j and j + 16 of its block while the tensor core reads a byte as two consecutive
+// contraction positions, so the activation operand is laid out in the same "operand order"
+// (position 2j = element j, position 2j + 1 = element j + 16); a dot product does not care in which
+// order k is visited.
 //
 // The activations stay at full precision although the B operand is e2m1 too: a value is split into
 // pieces x = sum_p q_p * 2^(e_p), every q_p an e2m1 number, e_p a scale shared by the 32 elements of
@@ -19,12 +19,11 @@
 // accumulation is fp32, which is the reference's single-token arithmetic (f32 activations times
 // decoded weights, shaders/experts/projections.metal:78-182) up to summation order.
 //
-// The rows of a GGUF tensor are `row_bytes` apart, not a multiple of 16 bytes, so no single tensor
-// map covers them. Rows PR apart (PR = 8, or 16 when 8 rows are not a multiple of 16 bytes) start at
-// the same offset within a 16-byte word: there is one tensor map per residue j = row mod PR, a 2-D
-// view [row / PR][16-byte envelope of the row] with pitch PR * row_bytes, and one copy brings the
-// same K range of every PR-th row of a CTA's share. Reads past a row's end are out of the view's
-// bounds and come back as zeros.
+// The rows of a GGUF tensor start at any byte address and are not a multiple of 16 bytes long, so
+// they are fetched as the 16-byte pieces that cover them (cp.async, consecutive lanes taking
+// consecutive pieces of a row): every producer warp streams its own 16 rows through a private ring,
+// one K group (256 elements, 136 packed bytes) per stage, and nothing but the MMA barriers is
+// shared between warps.
 #pragma once
 #include "gemm.cuh"
 #include "mx_pieces.cuh"
@@ -33,11 +32,15 @@ namespace oco {
 
 constexpr int kMxGroupBlocks = 8;                    // blocks per K group: one 128-byte swizzle row of e2m1 codes
 constexpr int kMxGroupBytes = kMxGroupBlocks * 17;   // packed bytes of a K group in a row
-constexpr int kMxSlot = 176;                         // raw bytes per row and K group: 136 + 15 of misalignment, 16 x odd
-constexpr int kMxMapSizes = 5;                       // tensor maps with 1, 2, 4, 8, 16 rows per box
-constexpr int kMxMaxResidues = 16;
-constexpr int kMxThreads = 10 * 32;                  // 8 producer / epilogue warps, the MMA warp, the TMA warp
-constexpr int kMxMmaWarp = 8, kMxTmaWarp = 9;
+constexpr int kMxSlot = 176;                         // ring bytes per row and K group: 136 + 15 of misalignment, 16 x 11
+constexpr int kMxPiecesPerRow = 10;                  // 16-byte pieces fetched per row and K group
+constexpr int kMxWarpRows = 16;                      // tile rows of a producer warp (two units of eight rows)
+constexpr int kMxRingStages = 4;
+// ring bytes of one producer warp: a stage holds one K group of its row of every unit of a pass
+__host__ __device__ constexpr uint32_t mx_ring_bytes(int pass_units) { return (uint32_t)(kMxRingStages * pass_units * kMxSlot); }
+constexpr int kMxProducerWarps = 16;                 // 2 matrices x 128 tile rows / 16
+constexpr int kMxMmaWarp = kMxProducerWarps;
+constexpr int kMxThreads = (kMxProducerWarps + 2) * 32;   // + one MMA-issuing warp per matrix
 constexpr int kMxAStages = 2;
 constexpr int kMxTmemCols = 512;
 constexpr int kMxColD = 0, kMxColSfa = 64, kMxColSfb = 128;   // scale addresses are multiples of four columns
@@ -60,12 +63,6 @@ __device__ __forceinline__ void umma_mxf4(uint32_t d, uint64_t a, uint64_t b, ui
 __device__ __forceinline__ uint32_t mx_idesc(uint32_t n, uint32_t sf_id) {
     return (sf_id << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24) | (sf_id << 29);
 }
-__device__ __forceinline__ void tma_load_2d_gmap(uint32_t smem_dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-        : "memory");
-}
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
@@ -74,27 +71,28 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
 }
 
 struct MxParams {
-    const CUtensorMap* maps;      // device memory: [tensor][kMxMaxResidues][kMxMapSizes]
     const uint8_t* w[2];          // first packed row of each matrix (expand: gate, up; down: down)
-    int tensor[2];                // which tensor's maps each matrix uses
-    int n_mat;
+    const uint8_t* w_end[2];      // first byte past the 16-byte envelope of each matrix (no piece starts there or beyond)
     uint32_t row_stride;          // bytes between consecutive rows of a matrix
-    int PR;                       // rows per tensor-map period
     int K;                        // contraction length
     int rows_per_route;           // output rows of one expert's matrix
     int routes;
-    int region;                   // raw bytes per residue, matrix and stage (a multiple of 128, see mx_region_bytes)
-    int raw_stages;
+    int pass_units;               // units (eight rows of one route, of every matrix) a CTA takes per pass
     const uint32_t* ids;          // [routes] expert of each route; null = expert 0
-    // B operand
-    const unsigned char* b_img;   // expand: the token's pieces, mx_b_bytes(8, nkb)
-    const unsigned char* sfb_img; //         and their scales, mx_sfb_bytes(nkb)
-    const float* act;             // down: f32 [routes][K] activations, split by the kernel itself
+    // B operand: e2m1 pieces and their scales. expand: of the token (one image for all routes);
+    // down: of each route's activations, `b_route_bytes` / `sfb_route_bytes` apart
+    const unsigned char* b_img;
+    const unsigned char* sfb_img;
+    uint32_t b_route_bytes, sfb_route_bytes;
     // epilogue
     const float* b0;              // expand: gate bias; down: bias (or null)
     const float* b1;              // expand: up bias
     int bias_stride;
     float* act_out;               // expand: f32 [routes][rows_per_route]
+    unsigned char* act_b;         // expand: the down kernel's B images, one per route, and their scales, written
+    unsigned char* act_sfb;       //         by whoever completes a block of 32 activations last
+    uint32_t act_b_route_bytes, act_sfb_route_bytes;
+    uint32_t* blk_arrivals;       // expand: one zeroed counter per route and block of 32 activations
     uint16_t* y;                  // down: bf16 [routes][rows_per_route]
     uint32_t* arrivals;           // down: one zeroed counter per output row
     const float* probs;
@@ -103,95 +101,121 @@ struct MxParams {
     uint32_t* status;
 };
 
-// Shared memory: A stages | SFA atoms | B image | SFB image | down: nothing more | control | raw ring.
-constexpr uint32_t kMxCtrlBytes = 3072;             // barriers | tensor-memory slot, flags | copy list | row offsets
-__host__ __device__ inline uint32_t mx_fixed_smem(int n_mat, uint32_t n_cols, uint32_t nkb) {
-    return (uint32_t)kMxAStages * n_mat * (16384u + 1024u) + mx_b_bytes(n_cols, nkb) + mx_sfb_bytes(nkb) + kMxCtrlBytes + 1024u;
+constexpr uint32_t kMxCtrlBytes = 1024;              // barriers | tensor-memory slot, flags, queue
+// Shared memory: A stages | SFA tiles | B image | SFB tiles | control | one ring per live producer warp.
+__host__ __device__ inline uint32_t mx_fixed_smem(int n_mat, uint32_t nkb) {
+    return (uint32_t)kMxAStages * n_mat * (16384u + 1024u) + mx_b_bytes(8, nkb) + mx_sfb_bytes(nkb) + kMxCtrlBytes + 1024u;
 }
-__host__ __device__ inline uint32_t mx_raw_stage_bytes(int n_mat, int PR, int region) { return (uint32_t)n_mat * PR * region; }
-
-// The copies that bring units [u0, u1) (one row per unit and residue) into a residue's raw region: runs of
-// units inside one route are cut into boxes of 16, 8, 4, 2, 1 rows; a box holds its rows kMxSlot bytes
-// apart and starts on a 128-byte boundary, as a TMA destination must. Calls emit(y offset within the
-// route, log2 rows, byte offset) per box and row(s, byte offset) per unit; returns the bytes used.
-template <class Emit, class Row>
-__host__ __device__ inline uint32_t mx_plan_copies(int u0, int u1, int upr, Emit emit, Row row) {
-    uint32_t off = 0;
-    for (int u = u0; u < u1;) {
-        const int r = u / upr, su = u - r * upr;
-        int left = min(u1 - u, upr - su), y = su;
-        for (int lg = kMxMapSizes - 1; lg >= 0; lg--) {
-            if (left & (1 << lg)) {
-                off = (off + 127u) & ~127u;
-                emit(r, y, lg, off);
-                for (int i = 0; i < (1 << lg); i++) row(u - u0 + (y - su) + i, off + (uint32_t)i * kMxSlot);
-                off += (uint32_t)(1 << lg) * kMxSlot;
-                y += 1 << lg; left -= 1 << lg;
-            }
-        }
-        u += min(u1 - u, upr - su);
-    }
-    return (off + 127u) & ~127u;
-}
-// The units of a pass that starts at u0 for a CTA whose share ends at u_end.
-__host__ __device__ inline int mx_pass_end(int u0, int u_end, int upr, int PR, bool two_routes_at_most) {
-    int u1 = min(u_end, u0 + 128 / PR);
-    if (two_routes_at_most) u1 = min(u1, (u0 / upr + 2) * upr);
+// Units of a pass that starts at u0 for a CTA whose share ends at u_end: `pass_units` at most, and (down)
+// units of one route only, since a pass multiplies with one activation vector.
+__host__ __device__ inline int mx_pass_end(int u0, int u_end, int upr, int pass_units, bool one_route) {
+    int u1 = u0 + pass_units;
+    if (u1 > u_end) u1 = u_end;
+    if (one_route && u1 > (u0 / upr + 1) * upr) u1 = (u0 / upr + 1) * upr;
     return u1;
 }
 
-// EXPAND: two matrices (gate, up), one activation vector for all routes (8 columns), fused clipped SwiGLU,
-// f32 activations out. Otherwise: one matrix, the activations of up to two routes per pass (16 columns),
-// bf16 expert outputs and, by whoever completes an output-row block last, the weighted sum onto the residual.
-// Grid: one CTA per SM; CTA c owns the units [c U / G, (c + 1) U / G) where a unit is PR consecutive
-// rows of one route (and of both matrices), U = routes * rows_per_route / PR.
+// Moves the eight blocks of one K group of ONE raw row (this lane's) into its A tile row and scale tiles.
+// c[0..39]: the row's ring slot as 16-byte pieces; the row's data starts at byte D of the slot. With D a
+// compile-time constant every word index and shift below is static: a block's sixteen code bytes are
+// four funnel shifts away from their aligned place, its scale byte one byte permute. (A row's last K
+// group, when it is not full, takes mx_move_row_any, which zeroes the blocks past the end of the row.)
+template <int D>
+__device__ __forceinline__ void mx_move_row(const uint32_t (&c)[40], unsigned char* a_row, uint32_t sw, unsigned char* sf_dst) {
+    uint32_t sfw[2] = {0u, 0u};
+#pragma unroll
+    for (int b = 0; b < 8; b++) {
+        const int o = D + 17 * b;                  // the block's scale byte; its codes follow
+        const int q = (o + 1) >> 2, t = ((o + 1) & 3) * 8;
+        uint4 k;
+        if (t == 0) k = make_uint4(c[q], c[q + 1], c[q + 2], c[q + 3]);
+        else k = make_uint4(__funnelshift_r(c[q], c[q + 1], t), __funnelshift_r(c[q + 1], c[q + 2], t),
+                            __funnelshift_r(c[q + 2], c[q + 3], t), __funnelshift_r(c[q + 3], c[q + 4], t));
+        *reinterpret_cast<uint4*>(a_row + (((uint32_t)b << 4) ^ sw)) = k;
+        // the scale byte into byte b & 3 of its word: one byte permute
+        sfw[b >> 2] = __byte_perm(sfw[b >> 2], c[o >> 2], (0x3210u & ~(0xfu << (4 * (b & 3)))) | ((4u + (uint32_t)(o & 3)) << (4 * (b & 3))));
+    }
+    *reinterpret_cast<uint32_t*>(sf_dst) = sfw[0];
+    *reinterpret_cast<uint32_t*>(sf_dst + 512) = sfw[1];
+}
+// The same with a start byte known only at run time (rows whose pointers differ in their low four bits:
+// matrices with an odd row stride) and with blocks past `nb` zeroed (scale byte zero): the words are
+// selected with conditional moves.
+__device__ __forceinline__ void mx_move_row_any(uint32_t dl, const uint32_t (&c)[40], unsigned char* a_row, uint32_t sw, unsigned char* sf_dst, int nb) {
+    uint32_t sfw[2] = {0u, 0u};
+#pragma unroll
+    for (int b = 0; b < 8; b++) {
+        const uint32_t o = dl + (uint32_t)b;                 // block b starts at byte dl + 17 b = 16 b + o
+        const bool hi = o >= 16u;
+        const uint32_t sh = o & 15u, qw = sh >> 2, tb = (sh & 3u) * 8u;
+        uint32_t w[8], y[6], x[5];
+#pragma unroll
+        for (int i = 0; i < 8; i++) w[i] = hi ? c[4 * (b + 1) + i] : c[4 * b + i];
+#pragma unroll
+        for (int i = 0; i < 6; i++) y[i] = (qw & 2u) ? w[i + 2] : w[i];
+#pragma unroll
+        for (int i = 0; i < 5; i++) x[i] = (qw & 1u) ? y[i + 1] : y[i];
+        uint32_t scale = (x[0] >> tb) & 0xffu;
+        uint4 k = make_uint4(__funnelshift_rc(x[0], x[1], tb + 8u), __funnelshift_rc(x[1], x[2], tb + 8u),
+                             __funnelshift_rc(x[2], x[3], tb + 8u), __funnelshift_rc(x[3], x[4], tb + 8u));
+        if (b >= nb) { k = make_uint4(0u, 0u, 0u, 0u); scale = 0u; }
+        *reinterpret_cast<uint4*>(a_row + (((uint32_t)b << 4) ^ sw)) = k;
+        sfw[b >> 2] |= scale << (8 * (b & 3));
+    }
+    *reinterpret_cast<uint32_t*>(sf_dst) = sfw[0];
+    *reinterpret_cast<uint32_t*>(sf_dst + 512) = sfw[1];
+}
+
+// EXPAND: two matrices (gate, up), one activation vector for all routes, fused clipped SwiGLU, f32
+// activations out; whoever completes a block of 32 activations last also splits it into the pieces the
+// down kernel multiplies with. Otherwise: one matrix, one route per pass, bf16 expert outputs and, by
+// whoever completes an output row last, the weighted sum onto the residual.
+// Grid: one CTA per SM; CTA c owns the units [c U / G, (c + 1) U / G) where a unit is eight consecutive
+// rows of one route (of both matrices), U = routes * rows_per_route / 8. Tile row t of a pass is row j = t / 16
+// of the pass's unit t mod 16, and producer warp j of a matrix serves the rows j of all units: rows eight
+// apart start at the same byte of a 16-byte word (unless the row stride is odd), so one warp's rows
+// need the same shifts.
 template <bool EXPAND>
 __global__ void __launch_bounds__(kMxThreads, 1) mx_rows_kernel(const MxParams p) {
     constexpr int NMAT = EXPAND ? 2 : 1;
-    constexpr uint32_t NCOL = EXPAND ? 8u : 16u;
+    constexpr uint32_t NCOL = 8u;
     extern __shared__ unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
-    const int PR = p.PR;
     const int nkb = p.K >> 5, nkg = (nkb + 7) >> 3;
-    const int upr = p.rows_per_route / PR;                      // units per route
+    const int upr = p.rows_per_route >> 3;                      // units per route
     const int units_total = p.routes * upr;
     const int u_begin = (int)((long long)blockIdx.x * units_total / gridDim.x);
     const int u_end = (int)((long long)(blockIdx.x + 1) * units_total / gridDim.x);
-    const int units_pass = 128 / PR;
 
     // ---- shared memory carve-up ------------------------------------------------------------------
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* gen = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t a_base = base;                                               // [stage][mat] 16 KB tiles
-    const uint32_t sfa_base = a_base + kMxAStages * NMAT * 16384u;              // [stage][mat] two 512-byte atoms
+    const uint32_t sfa_base = a_base + kMxAStages * NMAT * 16384u;              // [stage][mat] two 512-byte tiles
     const uint32_t b_base = sfa_base + kMxAStages * NMAT * 1024u;
-    const uint32_t sfb_base = b_base + mx_b_bytes(NCOL, nkb);
-    const uint32_t ctrl = sfb_base + mx_sfb_bytes(nkb);
-    const uint32_t raw_base = ctrl + kMxCtrlBytes;
-    const uint32_t raw_stage_bytes = mx_raw_stage_bytes(NMAT, PR, p.region);
+    const uint32_t b_bytes = mx_b_bytes(NCOL, nkb), sfb_bytes = mx_sfb_bytes(nkb);
+    const uint32_t sfb_base = b_base + b_bytes;
+    const uint32_t ctrl = sfb_base + sfb_bytes;
+    const uint32_t ring_base = ctrl + kMxCtrlBytes;
     unsigned char* ctrl_gen = gen + (ctrl - base);
-    auto raw_full = [&](int s) { return ctrl + 8u * s; };
-    auto raw_empty = [&](int s) { return ctrl + 8u * (16 + s); };
-    auto a_full = [&](int s) { return ctrl + 8u * (32 + s); };
-    auto a_empty = [&](int s) { return ctrl + 8u * (34 + s); };
-    const uint32_t accum_bar = ctrl + 8u * 36, b_bar = ctrl + 8u * 37, tmem_free = ctrl + 8u * 38;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl_gen + 512);
+    auto a_full = [&](int s) { return ctrl + 8u * s; };
+    auto a_empty = [&](int s) { return ctrl + 8u * (2 + s); };
+    const uint32_t accum_bar = ctrl + 8u * 4, b_bar = ctrl + 8u * 5, tmem_free = ctrl + 8u * 6, sfb_ready = ctrl + 8u * 7;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl_gen + 64);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    // per pass: the copy list of a residue (the same for every residue and matrix) and each unit's place
-    struct Copy { int y, lg; uint32_t off, pad; };
-    Copy* copies = reinterpret_cast<Copy*>(ctrl_gen + 1024);                    // at most 64 entries
-    uint32_t* row_off = reinterpret_cast<uint32_t*>(ctrl_gen + 2048);           // [units of a pass]
-    int* ncopies = reinterpret_cast<int*>(ctrl_gen + 520);
+    uint32_t* queue_len = tmem_slot + 2;                                        // expand: completed activation blocks
+    uint32_t* queue = reinterpret_cast<uint32_t*>(ctrl_gen + 128);              //         (route << 16 | block), up to 64
 
     pdl_launch_dependents();
     if (tid == 0) {
-        for (int s = 0; s < p.raw_stages; s++) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), 4 * NMAT); }
-        for (int s = 0; s < kMxAStages; s++) { mbar_init(a_full(s), 4 * NMAT); mbar_init(a_empty(s), 1); }
-        mbar_init(accum_bar, 1);
+        for (int s = 0; s < kMxAStages; s++) { mbar_init(a_full(s), 8 * NMAT); mbar_init(a_empty(s), NMAT); }
+        mbar_init(accum_bar, NMAT);
+        mbar_init(sfb_ready, 1);
         mbar_init(b_bar, 1);
         mbar_init(tmem_free, 4);
         *abort_flag = 0;
+        *queue_len = 0;
         fence_barrier_init();
     }
     if (warp == kMxMmaWarp) {
@@ -204,242 +228,242 @@ __global__ void __launch_bounds__(kMxThreads, 1) mx_rows_kernel(const MxParams p
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();                       // ids, activations and pieces written by the kernels before are complete
 
-    if (EXPAND && u_begin < u_end) {
-        // the token's pieces and their scales, prepared by the router kernel
-        if (tid == 0) {
-            const uint32_t bb = mx_b_bytes(NCOL, nkb), sb = mx_sfb_bytes(nkb);
-            mbar_arrive_expect_tx(b_bar, bb + sb);
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(b_base), "l"(p.b_img), "r"(bb), "r"(b_bar) : "memory");
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(sfb_base), "l"(p.sfb_img), "r"(sb), "r"(b_bar) : "memory");
-        }
-    }
-
-    int step0 = 0;            // K groups of earlier passes (ring and barrier phases run on)
+    int step0 = 0;            // K groups of earlier passes (barrier phases run on)
     int pass = 0;
-    int b_routes_first = -1;  // down: the routes whose pieces are in the B image
+    int b_loads = 0;          // B images fetched so far (phase of b_bar)
+    int b_route = -1;
     for (int u0 = u_begin; u0 < u_end; pass++) {
-        // a pass: up to 128 rows, and (down) units of at most two routes
-        const int u1 = mx_pass_end(u0, u_end, upr, PR, !EXPAND);
+        const int u1 = mx_pass_end(u0, u_end, upr, p.pass_units, !EXPAND);
         const int r_first = u0 / upr;
         const int n_units = u1 - u0;
-        __syncthreads();      // the pass before is finished with the copy list and (down) the B image
-        if (tid == 0) {
-            int n = 0;
-            mx_plan_copies(u0, u1, upr,
-                           [&](int r, int y, int lg, uint32_t off) {
-                               const uint32_t e = p.ids ? p.ids[r] : 0u;
-                               if (n < 64) { copies[n].y = (int)e * upr + y; copies[n].lg = lg; copies[n].off = off; n++; }
-                           },
-                           [&](int s, uint32_t off) { row_off[s] = off; });
-            *ncopies = n;
+        __syncthreads();      // the pass before is finished with the B image
+        const bool load_b = EXPAND ? pass == 0 : r_first != b_route;
+        if (tid == 0 && load_b) {
+            // the activation vector's pieces and their scales (made by the router or the expand kernel)
+            const size_t r = EXPAND ? 0 : (size_t)r_first;
+            mbar_arrive_expect_tx(b_bar, b_bytes + sfb_bytes);
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(b_base), "l"(p.b_img + r * p.b_route_bytes), "r"(b_bytes), "r"(b_bar) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(sfb_base), "l"(p.sfb_img + r * p.sfb_route_bytes), "r"(sfb_bytes), "r"(b_bar) : "memory");
         }
-        if (!EXPAND && r_first != b_routes_first) {
-            // split the f32 activations of routes r_first, r_first + 1 into pieces (columns 0-7, 8-15)
-            unsigned char* bimg = gen + (b_base - base);
-            unsigned char* sfimg = gen + (sfb_base - base);
-            const int nwarps = kMxThreads / 32;
-            for (int i = warp; i < 2 * nkg * 8; i += nwarps) {
-                const int rr = i / (nkg * 8), blk = i - rr * (nkg * 8);
-                const int route = r_first + rr;
-                float v = 0.0f;
-                if (route < p.routes && blk < nkb) v = p.act[(size_t)route * p.K + blk * 32 + (lane >> 1) + 16 * (lane & 1)];
-                mx_split_block(v, lane, bimg, sfimg, NCOL, 8u * rr, (uint32_t)blk);
-            }
-            b_routes_first = r_first;
-            fence_proxy_async_smem();
-        }
-        __syncthreads();
+        if (load_b) { b_route = r_first; b_loads++; }
 
-        if (warp < 4 * NMAT) {
-            // ===== producers: raw slot -> A tile row + scale bytes =================================
-            const int mat = warp >> 2, q = warp & 3;
-            const int t = q * 32 + lane;                                  // tile row
-            // eight consecutive lanes hold eight consecutive units of one residue: their raw rows lie
-            // kMxSlot = 16 x 11 bytes apart, so a 16-byte load per lane has no bank conflict
-            const int j = t / units_pass, s = t - j * units_pass;
-            const bool live = s < n_units;
-            const uint32_t off0 = (uint32_t)((uintptr_t)(p.w[mat] + (size_t)j * p.row_stride) & 15u);
-            const uint32_t slot_off = (uint32_t)((mat * PR + j) * p.region) + (live ? row_off[s] : 0u);
-            const uint32_t a_row = (uint32_t)(t >> 3) * 1024u + (uint32_t)(t & 7) * 128u, sw = (uint32_t)(t & 7);
-            for (int g = 0; g < nkg; g++) {
-                const int n = step0 + g, rs = n % p.raw_stages, as = n % kMxAStages;
-                if (lane == 0) {
-                    mbar_wait(raw_full(rs), (uint32_t)(n / p.raw_stages) & 1u, abort_flag, p.status);
-                    mbar_wait(a_empty(as), ((uint32_t)(n / kMxAStages) & 1u) ^ 1u, abort_flag, p.status);
+        if (warp < kMxProducerWarps) {
+            const int mat = warp >> 3, wi = warp & 7;
+            if (mat < NMAT) {
+                // ===== producers ========================================================================
+                // Warp wi serves row wi of every unit of the pass: lane s < 16 is unit u0 + s (tile row 16 wi + s).
+                const int j = wi;
+                const uint32_t stage_bytes = (uint32_t)(p.pass_units * kMxSlot);
+                const uint32_t ring = ring_base + (uint32_t)(mat * 8 + wi) * mx_ring_bytes(p.pass_units);
+                const unsigned char* ring_gen = gen + (ring - base);
+                auto row_ptr = [&](int s) -> const uint8_t* {
+                    const int unit = u0 + s;
+                    if (unit >= u1) return nullptr;
+                    const int route = unit / upr;
+                    const uint32_t e = p.ids ? p.ids[route] : 0u;
+                    return p.w[mat] + ((size_t)e * p.rows_per_route + (size_t)(unit - route * upr) * 8 + j) * p.row_stride;
+                };
+                // fetch role: 160 pieces per stage, piece (lane + 32 k) -> row s = / 10, piece % 10
+                // (row16: the row's pointer rounded down to 16 bytes plus the piece; r15: its low four bits)
+                const uint8_t* row16[5];
+                uint32_t fdst[5], r15[5];
+                bool guard = false;         // some piece of some K group may start at or past the end of the tensor's envelope
+#pragma unroll
+                for (int k = 0; k < 5; k++) {
+                    const int idx = lane + 32 * k, sr = idx / kMxPiecesPerRow, piece = idx - sr * kMxPiecesPerRow;
+                    const uint8_t* rp = row_ptr(sr);
+                    row16[k] = rp ? (const uint8_t*)((uintptr_t)rp & ~(uintptr_t)15) + piece * 16 : nullptr;
+                    r15[k] = (uint32_t)((uintptr_t)rp & 15u);
+                    fdst[k] = (uint32_t)(sr * kMxSlot + piece * 16);
+                    if (rp && row16[k] + (size_t)nkg * kMxGroupBytes + 16 > p.w_end[mat]) guard = true;
                 }
-                __syncwarp();
-                if (live) {
-                    const uint32_t slot = raw_base + (uint32_t)rs * raw_stage_bytes + slot_off;
-                    const uint32_t dl = (off0 + 8u * (uint32_t)g) & 15u;      // where the row's bytes start in the slot
-                    uint32_t c[40];
+                guard = __any_sync(0xffffffffu, guard);
+                auto issue = [&](int g) {
+                    if (g < nkg) {
+                        const uint32_t st = ring + (uint32_t)((step0 + g) % kMxRingStages) * stage_bytes;
 #pragma unroll
-                    for (int i = 0; i < 10; i++)
-                        asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(c[4 * i]), "=r"(c[4 * i + 1]), "=r"(c[4 * i + 2]), "=r"(c[4 * i + 3]) : "r"(slot + 16u * i));
-                    const uint32_t a_dst = a_base + (uint32_t)(as * NMAT + mat) * 16384u + a_row;
-                    uint32_t sfw[2] = {0u, 0u};
-#pragma unroll
-                    for (int b = 0; b < 8; b++) {
-                        const uint32_t o = dl + (uint32_t)b;                 // block b starts at byte dl + 17 b = 16 b + o
-                        const bool hi = o >= 16u;
-                        const uint32_t sh = o & 15u, qw = sh >> 2, tb = (sh & 3u) * 8u;
-                        uint32_t w[8], y[6], x[5];
-#pragma unroll
-                        for (int i = 0; i < 8; i++) w[i] = hi ? c[4 * (b + 1) + i] : c[4 * b + i];
-#pragma unroll
-                        for (int i = 0; i < 6; i++) y[i] = (qw & 2u) ? w[i + 2] : w[i];
-#pragma unroll
-                        for (int i = 0; i < 5; i++) x[i] = (qw & 1u) ? y[i + 1] : y[i];
-                        const uint32_t scale = (x[0] >> tb) & 0xffu;
-                        const uint32_t k0 = __funnelshift_rc(x[0], x[1], tb + 8u), k1 = __funnelshift_rc(x[1], x[2], tb + 8u),
-                                       k2 = __funnelshift_rc(x[2], x[3], tb + 8u), k3 = __funnelshift_rc(x[3], x[4], tb + 8u);
-                        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a_dst + (((uint32_t)b ^ sw) << 4)), "r"(k0), "r"(k1), "r"(k2), "r"(k3) : "memory");
-                        sfw[b >> 2] |= scale << (8 * (b & 3));
+                        for (int k = 0; k < 5; k++) {
+                            if (row16[k]) {
+                                // this lane's piece of the 16-byte envelope of the row's K group g
+                                const uint8_t* a16 = row16[k] + ((r15[k] + (uint32_t)g * kMxGroupBytes) & ~15u);
+                                if (!guard || a16 < p.w_end[mat]) cp_async16(st + fdst[k], a16);
+                            }
+                        }
                     }
-                    const uint32_t sf_dst = sfa_base + (uint32_t)(as * NMAT + mat) * 1024u + (uint32_t)lane * 16u + (uint32_t)q * 4u;
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(sf_dst), "r"(sfw[0]) : "memory");
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(sf_dst + 512u), "r"(sfw[1]) : "memory");
+                    cp_async_commit();
+                };
+                // move role: lane s < 16 moves its row
+                const int t = j * 16 + (lane & 15);
+                const uint8_t* mrow = lane < 16 ? row_ptr(lane) : nullptr;
+                const uint32_t a_off = (uint32_t)(t >> 3) * 1024u + (uint32_t)(t & 7) * 128u, sw = (uint32_t)(t & 7) << 4;
+                const uint32_t sf_off = (uint32_t)(t & 31) * 16u + (uint32_t)(t >> 5) * 4u;
+#pragma unroll
+                for (int sI = 0; sI < kMxRingStages - 1; sI++) issue(sI);
+                for (int g = 0; g < nkg; g++) {
+                    const int n = step0 + g, as = n & (kMxAStages - 1);
+                    issue(g + kMxRingStages - 1);
+                    cp_async_wait<kMxRingStages - 1>();                            // K group g has landed
+                    if (lane == 0) mbar_wait(a_empty(as), ((uint32_t)(n / kMxAStages) & 1u) ^ 1u, abort_flag, p.status);
+                    __syncwarp();
+                    const uint32_t dl = (uint32_t)((uintptr_t)(mrow + (size_t)g * kMxGroupBytes) & 15u);   // where the row's data starts in its slot
+                    const uint32_t dl_first = __shfl_sync(0xffffffffu, dl, 0);              // every lane takes part in the shuffle
+                    const bool same = __all_sync(0xffffffffu, !mrow || dl == dl_first);
+                    if (mrow) {
+                        const unsigned char* slot = ring_gen + (size_t)(n % kMxRingStages) * stage_bytes + (lane & 15) * kMxSlot;
+                        unsigned char* a_row = gen + (a_base - base) + (size_t)(as * NMAT + mat) * 16384u + a_off;
+                        unsigned char* sf_dst = gen + (sfa_base - base) + (size_t)(as * NMAT + mat) * 1024u + sf_off;
+                        const int nb = min(8, nkb - g * 8);
+                        uint32_t c[40];
+#pragma unroll
+                        for (int i = 0; i < 10; i++) {
+                            const uint4 v = *reinterpret_cast<const uint4*>(slot + 16 * i);
+                            c[4 * i] = v.x; c[4 * i + 1] = v.y; c[4 * i + 2] = v.z; c[4 * i + 3] = v.w;
+                        }
+                        if (same && nb == 8) {
+                            switch (dl) {
+                                case 0: mx_move_row<0>(c, a_row, sw, sf_dst); break;
+                                case 1: mx_move_row<1>(c, a_row, sw, sf_dst); break;
+                                case 2: mx_move_row<2>(c, a_row, sw, sf_dst); break;
+                                case 3: mx_move_row<3>(c, a_row, sw, sf_dst); break;
+                                case 4: mx_move_row<4>(c, a_row, sw, sf_dst); break;
+                                case 5: mx_move_row<5>(c, a_row, sw, sf_dst); break;
+                                case 6: mx_move_row<6>(c, a_row, sw, sf_dst); break;
+                                case 7: mx_move_row<7>(c, a_row, sw, sf_dst); break;
+                                case 8: mx_move_row<8>(c, a_row, sw, sf_dst); break;
+                                case 9: mx_move_row<9>(c, a_row, sw, sf_dst); break;
+                                case 10: mx_move_row<10>(c, a_row, sw, sf_dst); break;
+                                case 11: mx_move_row<11>(c, a_row, sw, sf_dst); break;
+                                case 12: mx_move_row<12>(c, a_row, sw, sf_dst); break;
+                                case 13: mx_move_row<13>(c, a_row, sw, sf_dst); break;
+                                case 14: mx_move_row<14>(c, a_row, sw, sf_dst); break;
+                                default: mx_move_row<15>(c, a_row, sw, sf_dst); break;
+                            }
+                        } else {
+                            mx_move_row_any(dl, c, a_row, sw, sf_dst, nb);
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(a_full(as));
                 }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) { mbar_arrive(a_full(as)); mbar_arrive(raw_empty(rs)); }
+                cp_async_wait<0>();
             }
-            // ===== epilogue =============================================================================
-            if (mat == 0) {
+            // ===== epilogue (warps 0-3, one quadrant of tensor-memory lanes each) ======================
+            if (warp < 4) {
+                const int q = warp;
                 if (lane == 0) mbar_wait(accum_bar, (uint32_t)pass & 1u, abort_flag, p.status);
                 __syncwarp();
                 tc_fence_after();
+                const int t = q * 32 + lane;
+                const int unit = u0 + (t & 15);
+                const bool live = unit < u1;
+                const int route = unit / upr, row = (unit - route * upr) * 8 + (t >> 4);   // row within the route's matrix
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + kMxColD;
-                const int unit = u0 + s, route = unit / upr, row = (unit - route * upr) * PR + j;   // row within the route's matrix
+                uint32_t d0[8], d1[8];
+                tmem_ld8(taddr, d0);
+                if (EXPAND) tmem_ld8(taddr + 32u, d1);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_free);
                 if (EXPAND) {
-                    uint32_t dg[8], du[8];
-                    tmem_ld8(taddr, dg);
-                    tmem_ld8(taddr + 32u, du);
-                    tmem_ld_wait();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(tmem_free);
                     if (live) {
                         float sg = 0.f, su = 0.f;
 #pragma unroll
-                        for (int i = 7; i >= 0; i--) { sg = __fadd_rn(sg, __uint_as_float(dg[i])); su = __fadd_rn(su, __uint_as_float(du[i])); }
+                        for (int i = 7; i >= 0; i--) { sg = __fadd_rn(sg, __uint_as_float(d0[i])); su = __fadd_rn(su, __uint_as_float(d1[i])); }
                         const uint32_t e = p.ids ? p.ids[route] : 0u;
                         const size_t bi = ((size_t)e * p.rows_per_route + row) * p.bias_stride;
                         const float gate = __fadd_rn(sg, bf16_round(p.b0[bi]));
                         const float up = __fadd_rn(su, bf16_round(__fadd_rn(p.b1[bi], 1.0f)));
                         p.act_out[(size_t)route * p.rows_per_route + row] = swiglu_clipped(gate, up);
+                        // whoever writes the last of a block's 32 activations queues the block for splitting
+                        __threadfence();
+                        const uint32_t blk = (uint32_t)row >> 5;
+                        uint32_t* counter = p.blk_arrivals + (size_t)route * (p.rows_per_route >> 5) + blk;
+                        if (atomicAdd(counter, 1u) == 31u) {
+                            *counter = 0;                                                 // ready for the next call
+                            const uint32_t at = atomicAdd(queue_len, 1u);
+                            if (at < 64u) queue[at] = ((uint32_t)route << 16) | blk;
+                        }
                     }
-                } else {
-                    // both routes' columns; each lane keeps the eight of its own route
-                    uint32_t d16[16], d[8];
-                    tmem_ld16(taddr, d16);
-                    tmem_ld_wait();
-                    const bool second = live && route != r_first;
+                } else if (live) {
+                    float sy = 0.f;
 #pragma unroll
-                    for (int i = 0; i < 8; i++) d[i] = second ? d16[8 + i] : d16[i];
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(tmem_free);
-                    if (live) {
-                        float sy = 0.f;
-#pragma unroll
-                        for (int i = 7; i >= 0; i--) sy = __fadd_rn(sy, __uint_as_float(d[i]));
-                        const uint32_t e = p.ids ? p.ids[route] : 0u;
-                        if (p.b0) sy = __fadd_rn(sy, bf16_round(p.b0[((size_t)e * p.rows_per_route + row) * p.bias_stride]));
-                        p.y[(size_t)route * p.rows_per_route + row] = f32_to_bf16_bits(sy);
-                    }
+                    for (int i = 7; i >= 0; i--) sy = __fadd_rn(sy, __uint_as_float(d0[i]));
+                    const uint32_t e = p.ids ? p.ids[route] : 0u;
+                    if (p.b0) sy = __fadd_rn(sy, bf16_round(p.b0[((size_t)e * p.rows_per_route + row) * p.bias_stride]));
+                    p.y[(size_t)route * p.rows_per_route + row] = f32_to_bf16_bits(sy);
                     if (p.residual) {
                         // Whoever completes an output row last (the routes' rows are spread over CTAs) adds the
                         // weighted expert outputs to the residual (moe_sum, routing.metal:154-168). Nobody waits.
-                        if (live) {
-                            __threadfence();
-                            const uint32_t seen = atomicAdd(p.arrivals + row, 1u);
-                            if (seen == (uint32_t)(p.routes - 1)) {
-                                p.arrivals[row] = 0;                                        // ready for the next call
-                                if (*reinterpret_cast<volatile uint32_t*>(p.status) == 0u) {
-                                    __threadfence();
-                                    float sres = 0.0f;
-                                    for (int r = 0; r < p.routes; r++)
-                                        sres = __fmaf_rn(bf16_bits_to_f32(__ldcg(p.y + (size_t)r * p.rows_per_route + row)), p.probs[r], sres);
-                                    if (p.round_sum) sres = bf16_round(sres);
-                                    p.residual[row] = f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(p.residual[row]), sres));
-                                }
+                        __threadfence();
+                        const uint32_t seen = atomicAdd(p.arrivals + row, 1u);
+                        if (seen == (uint32_t)(p.routes - 1)) {
+                            p.arrivals[row] = 0;                                            // ready for the next call
+                            if (*reinterpret_cast<volatile uint32_t*>(p.status) == 0u) {
+                                __threadfence();
+                                float sres = 0.0f;
+                                for (int r = 0; r < p.routes; r++)
+                                    sres = __fmaf_rn(bf16_bits_to_f32(__ldcg(p.y + (size_t)r * p.rows_per_route + row)), p.probs[r], sres);
+                                if (p.round_sum) sres = bf16_round(sres);
+                                p.residual[row] = f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(p.residual[row]), sres));
                             }
                         }
                     }
                 }
             }
-        } else if (warp == kMxMmaWarp) {
-            if (lane == 0) {
-                // ===== MMA issue ========================================================================
-                if (pass == 0) {
-                    if (EXPAND) mbar_wait(b_bar, 0u, abort_flag, p.status);
-                } else {
-                    mbar_wait(tmem_free, (uint32_t)(pass - 1) & 1u, abort_flag, p.status);   // accumulators of the pass before are read
-                }
-                tc_fence_after();
-                if (EXPAND ? pass == 0 : true) {
-                    // scales of the B operand: four blocks per copy
-                    for (int i = 0; i < (nkb + 3) / 4; i++) mx_cp_scales(tmem_base + kMxColSfb + 4u * i, mx_sf_desc(sfb_base + 512u * i));
-                }
-                for (int g = 0; g < nkg; g++) {
-                    const int n = step0 + g, as = n % kMxAStages;
-                    mbar_wait(a_full(as), (uint32_t)(n / kMxAStages) & 1u, abort_flag, p.status);
+        } else if (lane == 0 && warp - kMxMmaWarp < NMAT) {
+            // ===== MMA issue: one thread per matrix (issuing an MMA costs tens of cycles) ================
+            const int mat = warp - kMxMmaWarp;
+            if (pass > 0) mbar_wait(tmem_free, (uint32_t)(pass - 1) & 1u, abort_flag, p.status);   // accumulators of the pass before are read
+            if (load_b) {
+                if (mat == 0) {
+                    mbar_wait(b_bar, (uint32_t)(b_loads - 1) & 1u, abort_flag, p.status);
                     tc_fence_after();
-#pragma unroll
-                    for (int mat = 0; mat < NMAT; mat++) {
-                        const uint32_t sfa_smem = sfa_base + (uint32_t)(as * NMAT + mat) * 1024u;
-                        const uint32_t sfa_t = tmem_base + kMxColSfa + (uint32_t)(as * NMAT + mat) * 8u;
-                        mx_cp_scales(sfa_t, mx_sf_desc(sfa_smem));
-                        mx_cp_scales(sfa_t + 4u, mx_sf_desc(sfa_smem + 512u));
-                        const uint64_t ad = umma_desc(a_base + (uint32_t)(as * NMAT + mat) * 16384u);
-                        const uint64_t bd = umma_desc(b_base + (uint32_t)g * (NCOL * 128u));
-#pragma unroll
-                        for (int kk = 0; kk < 4; kk++) {
-                            const uint32_t sfid = (uint32_t)(kk & 1) * 2u;
-                            umma_mxf4(tmem_base + kMxColD + 32u * mat, ad + 2u * kk, bd + 2u * kk, mx_idesc(NCOL, sfid),
-                                      sfa_t + 4u * (kk >> 1), tmem_base + kMxColSfb + 4u * (2u * g + (kk >> 1)), (g | kk) ? 1u : 0u);
-                        }
-                    }
-                    umma_commit(a_empty(as));
+                    // scales of the B operand: four blocks per copy, up to the end of the last K group (the MMAs of
+                    // a partly filled group read them too; their blocks hold zeros with a zero scale byte)
+                    for (int i = 0; i < 2 * nkg; i++) mx_cp_scales(tmem_base + kMxColSfb + 4u * i, mx_sf_desc(sfb_base + 512u * i));
+                    if (NMAT > 1) umma_commit(sfb_ready);
+                } else {
+                    mbar_wait(sfb_ready, (uint32_t)(b_loads - 1) & 1u, abort_flag, p.status);
+                    mbar_wait(b_bar, (uint32_t)(b_loads - 1) & 1u, abort_flag, p.status);
                 }
-                umma_commit(accum_bar);
             }
-        } else if (warp == kMxTmaWarp) {
-            // ===== packed rows by TMA: lane j copies the rows with residue j =======================
-            const int nc = *ncopies;
-            // the tensor maps live in global memory (written by a host copy): acquire them for the TMA unit
-            if (pass == 0 && lane < PR) {
-#pragma unroll
-                for (int mat = 0; mat < NMAT; mat++)
-                    for (int lg = 0; lg < kMxMapSizes; lg++)
-                        asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(p.maps + ((size_t)p.tensor[mat] * kMxMaxResidues + lane) * kMxMapSizes + lg) : "memory");
-            }
-            uint32_t off0[NMAT];
-#pragma unroll
-            for (int mat = 0; mat < NMAT; mat++) off0[mat] = (uint32_t)((uintptr_t)(p.w[mat] + (size_t)lane * p.row_stride) & 15u);
-            const uint32_t stage_tx = (uint32_t)(NMAT * PR * n_units * kMxSlot);
+            tc_fence_after();
             for (int g = 0; g < nkg; g++) {
-                const int n = step0 + g, rs = n % p.raw_stages;
-                if (lane == 0) {
-                    mbar_wait(raw_empty(rs), ((uint32_t)(n / p.raw_stages) & 1u) ^ 1u, abort_flag, p.status);
-                    mbar_arrive_expect_tx(raw_full(rs), stage_tx);
-                }
-                __syncwarp();
-                if (lane < PR && !*abort_flag) {
+                const int n = step0 + g, as = n & (kMxAStages - 1);
+                mbar_wait(a_full(as), (uint32_t)(n / kMxAStages) & 1u, abort_flag, p.status);
+                tc_fence_after();
+                const uint32_t sfa_smem = sfa_base + (uint32_t)(as * NMAT + mat) * 1024u;
+                const uint32_t sfa_t = tmem_base + kMxColSfa + (uint32_t)(as * NMAT + mat) * 8u;
+                mx_cp_scales(sfa_t, mx_sf_desc(sfa_smem));
+                mx_cp_scales(sfa_t + 4u, mx_sf_desc(sfa_smem + 512u));
+                const uint64_t ad = umma_desc(a_base + (uint32_t)(as * NMAT + mat) * 16384u);
+                const uint64_t bd = umma_desc(b_base + (uint32_t)g * (NCOL * 128u));
 #pragma unroll
-                    for (int mat = 0; mat < NMAT; mat++) {
-                        const int x0 = (int)(((off0[mat] + (uint32_t)g * kMxGroupBytes) >> 4) * 2u);   // 8-byte elements, 16-byte aligned
-                        const CUtensorMap* mj = p.maps + ((size_t)p.tensor[mat] * kMxMaxResidues + lane) * kMxMapSizes;
-                        const uint32_t dst = raw_base + (uint32_t)rs * raw_stage_bytes + (uint32_t)((mat * PR + lane) * p.region);
-                        for (int i = 0; i < nc; i++) tma_load_2d_gmap(dst + copies[i].off, mj + copies[i].lg, x0, copies[i].y, raw_full(rs));
-                    }
+                for (int kk = 0; kk < 4; kk++) {
+                    const uint32_t sfid = (uint32_t)(kk & 1) * 2u;
+                    umma_mxf4(tmem_base + kMxColD + 32u * mat, ad + 2u * kk, bd + 2u * kk, mx_idesc(NCOL, sfid),
+                              sfa_t + 4u * (kk >> 1), tmem_base + kMxColSfb + 4u * (2u * g + (kk >> 1)), (g | kk) ? 1u : 0u);
                 }
+                umma_commit(a_empty(as));
             }
+            umma_commit(accum_bar);
         }
         step0 += nkg;
         u0 = u1;
     }
     __syncthreads();
+    if (EXPAND) {
+        // the blocks of 32 activations this CTA completed: split them for the down kernel
+        __threadfence();
+        const uint32_t nq = min(*queue_len, 64u);
+        for (uint32_t k = (uint32_t)warp; k < nq; k += kMxThreads / 32) {
+            const uint32_t route = queue[k] >> 16, blk = queue[k] & 0xffffu;
+            const float v = __ldcg(p.act_out + (size_t)route * p.rows_per_route + blk * 32u + (uint32_t)(lane >> 1) + 16u * (uint32_t)(lane & 1));
+            mx_split_block(v, lane, p.act_b + (size_t)route * p.act_b_route_bytes, p.act_sfb + (size_t)route * p.act_sfb_route_bytes, 8u, 0u, blk);
+        }
+    }
     if (*abort_flag) {
         for (int i = 0; i < 64; i++) __nanosleep(1000);   // let copies in flight land before the CTA retires
         __syncthreads();

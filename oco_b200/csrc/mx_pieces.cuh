@@ -26,7 +26,7 @@ __host__ __device__ inline uint32_t mx_b_bytes(uint32_t N, uint32_t nkb) { retur
 // Scales of the operand rows: one 512-byte tile per four blocks, [32 rows][16 bytes] with a row's four
 // scale bytes first (the layout tcgen05.cp spreads over one scale-factor column of tensor memory; the
 // block-scaled MMA takes scale addresses in steps of four columns).
-__host__ __device__ inline uint32_t mx_sfb_bytes(uint32_t nkb) { return ((nkb + 3u) / 4u) * 512u; }
+__host__ __device__ inline uint32_t mx_sfb_bytes(uint32_t nkb) { return ((nkb + 7u) / 8u) * 1024u; }   // whole K groups of eight blocks
 
 // Splits one block of 32 activations into kMxPieces e2m1 pieces (operand rows n0 .. n0 + 7 of the B
 // image) and their UE8M0 scales. Called by a whole warp; lane l holds the value at contraction

@@ -286,9 +286,32 @@ def test_host_buffer_entry_point(moe, oracle):
         plan.forward_host(x, got, 51)      # beyond the reserved rows: a status, not a crash
 
 
+def selection_margin(layer, x_bits, logits_f32, ids):
+    """Smallest gap, over the tokens, between the last selected and the first rejected expert, measured on
+    logits recomputed in float64 from the same rounded operands (bf16 x; bf16 router weights and bias for the
+    gpt-oss family), and the largest distance of the float32 logits from them. A margin far above that
+    distance means no legal summation order could have selected other experts."""
+    x = synth.bf16_bits_to_f32(x_bits).astype(np.float64)
+    w = layer.router_w.astype(np.float64)
+    if layer.arch == synth.ARCH_GPT_OSS:
+        w = synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(layer.router_w)).astype(np.float64)
+    z = x @ w.T
+    if layer.arch == synth.ARCH_GPT_OSS:
+        z = z + synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(layer.router_b)).astype(np.float64)
+    score = z
+    if layer.arch == synth.ARCH_NEMOTRON:        # selection on sigmoid(z) + bias: monotone in z only without the bias
+        score = 1.0 / (1.0 + np.exp(-z)) + layer.router_b.astype(np.float64)
+    chosen = np.zeros(score.shape, bool)
+    np.put_along_axis(chosen, ids.astype(np.int64), True, axis=1)
+    lowest_in = np.where(chosen, score, np.inf).min(axis=1)
+    highest_out = np.where(chosen, -np.inf, score).max(axis=1)
+    return float((lowest_in - highest_out).min()), float(np.abs(logits_f32.astype(np.float64) - z).max())
+
+
 def _sampled_full_size(moe, oracle, name, tokens, sample, seed, mode):
     """Full benchmark shape on the GPU; the oracle re-computes a sample of the tokens (tokens are
-    independent in this layer) plus the router for all of them."""
+    independent in this layer) plus the router for all of them. The sample is spread over the batch and
+    always holds tokens routed to the fullest and to the emptiest expert."""
     layer = synth.make_config(name, seed=seed)
     x, res = synth.make_tokens(layer.hidden, tokens, seed, "normal")
     out, routing = moe.run_layer(layer, x, res)
@@ -300,12 +323,21 @@ def _sampled_full_size(moe, oracle, name, tokens, sample, seed, mode):
         _, ids, probs = oracle.router_softmax_topk(x, layer.router_w, layer.top_k)
     assert np.array_equal(routing["ids"], ids)
     assert np.array_equal(routing["prob"].view(np.uint32), probs.view(np.uint32))
+    margin, drift = selection_margin(layer, x, routing["logits"], ids)
+    print(f"{name} x {tokens}: smallest selection margin {margin:.3e}, largest |f32 logit - f64 logit| {drift:.3e}")
+    assert margin > 0, "the float64 logits select other experts"
+    pick = set(np.linspace(0, tokens - 1, sample).astype(int).tolist())
     if tokens > 1:
         offsets, row_of_route, route_of_row = oracle.permutation(ids, layer.experts)
         assert np.array_equal(routing["offsets"], offsets)
         assert np.array_equal(routing["row_of_route"], row_of_route)
         assert np.array_equal(routing["route_of_row"], route_of_row)
-    pick = np.unique(np.linspace(0, tokens - 1, sample).astype(int))
+        counts = np.diff(offsets.astype(np.int64))
+        fullest, emptiest = int(counts.argmax()), int(np.where(counts > 0, counts, counts.max() + 1).argmin())
+        for e in (fullest, emptiest):
+            rows = np.nonzero((ids == e).any(axis=1))[0]
+            pick.update(rows[:2].tolist())
+    pick = np.array(sorted(pick))
     ref = oracle.moe_forward(layer, x[pick], res[pick], mode=mode, trace=False)
     assert np.array_equal(ref.ids, ids[pick])
     err = rel_l2(out[pick], ref.out)
@@ -417,4 +449,148 @@ def test_gpt_oss_20b_decode_full_size(moe, oracle):
 
 
 def test_gpt_oss_20b_prefill_full_size(moe, oracle):
-    _sampled_full_size(moe, oracle, "gpt-oss-20b", 2048, 6, seed=0, mode=2)
+    _sampled_full_size(moe, oracle, "gpt-oss-20b", 2048, 32, seed=0, mode=2)
+
+
+def test_qwen3_30b_prefill_full_size(moe, oracle):
+    _sampled_full_size(moe, oracle, "qwen3-30b-a3b", 512, 12, seed=0, mode=2)
+
+
+def test_nemotron_h_prefill_full_size(moe, oracle):
+    _sampled_full_size(moe, oracle, "nemotron-h", 1024, 8, seed=0, mode=2)
+
+
+def test_gpt_oss_120b_prefill_full_size(moe, oracle):
+    _sampled_full_size(moe, oracle, "gpt-oss-120b", 8192, 12, seed=0, mode=2)
+
+
+# ---- the block-scaled single-token kernels (opt-in) --------------------------------------------------
+@pytest.mark.parametrize("hidden,ffn,experts,misalign", [(96, 96, 32, 0), (640, 384, 32, 0), (256, 160, 32, 7), (2880, 2880, 32, 0),
+                                                          (4096, 256, 8, 3)],
+                         ids=["k96", "k640", "unaligned", "20b", "k4096"])
+def test_gpt_oss_single_token_block_scaled(moe, oracle, monkeypatch, hidden, ffn, experts, misalign):
+    """MXFP4 rows fed to tcgen05 kind::mxf4 as they are, the token split into e2m1 pieces: odd and even row
+    strides (run-time and constant shifts), partial last K groups, unaligned tensors, the benchmark shape."""
+    monkeypatch.setenv("OCO_MOE_TOKEN_MX", "1")
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, hidden, ffn, experts, min(4, experts), synth.FMT_MXFP4, seed=91)
+    err = check_layer(moe, oracle, layer, 1, seed=hidden, residual="normal", misalign=misalign, mode=1)
+    assert err <= 2e-4, f"pieces should carry the activations nearly exactly, rel-L2 {err}"
+
+
+def test_block_scaled_token_path_propagates_nan(moe, oracle, monkeypatch):
+    monkeypatch.setenv("OCO_MOE_TOKEN_MX", "1")
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, 128, 128, 32, 4, synth.FMT_MXFP4, seed=8)
+    x, res = synth.make_tokens(128, 1, 77)
+    clean = oracle.moe_forward(layer, x, res)
+    bad = synth.Layer(**{**layer.__dict__})
+    bad.up_w = layer.up_w.copy()
+    bad.up_w[int(clean.ids[0, 0]), 5, 0] = 255
+    ref = oracle.moe_forward(bad, x, res)
+    out, routing = moe.run_layer(bad, x, res)
+    assert np.array_equal(routing["ids"], ref.ids)
+    assert np.array_equal(np.isnan(synth.bf16_bits_to_f32(out)), np.isnan(synth.bf16_bits_to_f32(ref.out)))
+
+
+# ---- one interleaved gate_up tensor instead of two ---------------------------------------------------
+@pytest.mark.parametrize("tokens,env", [(1, {}), (1, {"OCO_MOE_TOKEN_MX": "1"}), (6, {}), (70, {}), (70, {"OCO_MOE_NARROW_TILES": "1"}),
+                                        (300, {})], ids=["t1", "t1-mx", "t6", "t70", "t70-generic", "t300"])
+def test_interleaved_gate_up_is_bit_identical(moe, oracle, monkeypatch, tokens, env):
+    """Row 2c = gate row c, row 2c + 1 = up row c (and the biases likewise) must give the very bits the
+    two-tensor layout gives, on every kernel family."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, 320, 288, 8, 2, synth.FMT_MXFP4, seed=17)
+    x, res = synth.make_tokens(320, tokens, 5, "normal")
+    split, r0 = moe.run_layer(layer, x, res, misalign=5)
+    both, r1 = moe.run_layer(layer, x, res, misalign=5, interleaved=True)
+    assert np.array_equal(split, both)
+    assert np.array_equal(r0["ids"], r1["ids"]) and np.array_equal(r0["y"], r1["y"])
+    ref = oracle.moe_forward(layer, x, res)
+    assert rel_l2(both, ref.out) <= REL_L2
+
+
+def test_interleaved_and_split_tensors_are_exclusive(moe):
+    from oco_b200 import _lib
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, 96, 96, 4, 2, synth.FMT_MXFP4, seed=3)
+    plan = moe.plan_for(layer)
+    w = moe._Weights.from_layer(layer, interleaved=True)
+    w.gate_w = w.gate_up_w
+    with pytest.raises(moe.OcoError) as e:
+        plan.bind(w)
+    assert e.value.code == _lib.INVALID_ARGUMENT
+
+
+# ---- bounded device waits --------------------------------------------------------------------------
+def test_bounded_wait_gives_up_and_recovers(moe, oracle):
+    """A wait on a barrier nobody arrives at runs out (a few microseconds here), the kernel returns
+    normally, poll reports DEVICE_TIMEOUT once, a forward enqueued before the poll leaves the residual
+    untouched, and the first forward after the poll is correct again."""
+    import ctypes as C
+    import torch
+    from oco_b200 import _lib
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, 128, 128, 32, 4, synth.FMT_MXFP4, seed=6)
+    for tokens in (1, 40):
+        x, res = synth.make_tokens(128, tokens, 3, "normal")
+        plan = moe.plan_for(layer)
+        plan.reserve(tokens)
+        plan.bind(moe._Weights.from_layer(layer))
+        xd = torch.from_numpy(x.view(np.int16)).cuda()
+        rd = torch.from_numpy(res.view(np.int16).copy()).cuda()
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        assert _lib.lib().oco_moe_selftest_wait_timeout(plan.handle, 20000, stream) == _lib.OK
+        plan.forward(xd, rd, tokens)                       # enqueued while the status word is set
+        with pytest.raises(moe.OcoError) as e:
+            plan.poll()
+        assert e.value.code == _lib.DEVICE_TIMEOUT
+        assert np.array_equal(rd.cpu().numpy().view(np.uint16), res), "a poisoned step changed the residual"
+        plan.poll()                                        # reported once, then clear
+        plan.forward(xd, rd, tokens)
+        plan.poll()
+        ref = oracle.moe_forward(layer, x, res)
+        assert rel_l2(rd.cpu().numpy().view(np.uint16), ref.out) <= REL_L2
+    assert _lib.lib().oco_moe_selftest_wait_timeout(plan.handle, 0, stream) == _lib.INVALID_ARGUMENT
+
+
+def test_event_seam_times_a_forward(moe):
+    import ctypes as C
+    import torch
+    from oco_b200 import _lib
+    L = _lib.lib()
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, 128, 128, 8, 2, synth.FMT_MXFP4, seed=2)
+    x, res = synth.make_tokens(128, 64, 1)
+    plan = moe.plan_for(layer)
+    plan.reserve(64)
+    plan.bind(moe._Weights.from_layer(layer))
+    xd = torch.from_numpy(x.view(np.int16)).cuda()
+    rd = torch.from_numpy(res.view(np.int16).copy()).cuda()
+    a, b = C.c_void_p(), C.c_void_p()
+    assert L.oco_cuda_event_create(C.byref(a)) == _lib.OK and L.oco_cuda_event_create(C.byref(b)) == _lib.OK
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert L.oco_cuda_event_record(a, stream) == _lib.OK
+    plan.forward(xd, rd, 64)
+    assert L.oco_cuda_event_record(b, stream) == _lib.OK
+    assert L.oco_cuda_event_sync(b) == _lib.OK
+    ms = C.c_float(-1.0)
+    assert L.oco_cuda_event_elapsed_ms(a, b, C.byref(ms)) == _lib.OK and 0.0 < ms.value < 1000.0
+    assert L.oco_cuda_event_destroy(a) == _lib.OK and L.oco_cuda_event_destroy(b) == _lib.OK
+
+
+def test_plan_is_tied_to_its_device(moe):
+    """Kernel attributes and the workspace belong to one device: a call with another device current is
+    refused (needs two GPUs to show; with one, the same-device call must pass)."""
+    import torch
+    from oco_b200 import _lib
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, 128, 128, 8, 2, synth.FMT_MXFP4, seed=2)
+    x, res = synth.make_tokens(128, 1, 1)
+    plan = moe.plan_for(layer)
+    plan.reserve(1)
+    plan.bind(moe._Weights.from_layer(layer))
+    xd = torch.from_numpy(x.view(np.int16)).cuda()
+    rd = torch.from_numpy(res.view(np.int16).copy()).cuda()
+    plan.forward(xd, rd, 1)
+    plan.poll()
+    if torch.cuda.device_count() > 1:
+        with torch.cuda.device(1):
+            with pytest.raises(moe.OcoError) as e:
+                plan.forward(xd, rd, 1)
+            assert e.value.code == _lib.INVALID_ARGUMENT

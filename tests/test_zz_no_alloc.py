@@ -22,11 +22,12 @@ LAYERS = {
     "gpt_oss": dict(arch=synth.ARCH_GPT_OSS, hidden=2880, ffn=64, experts=32, top_k=4, fmt=synth.FMT_MXFP4, seed=51),
     "nemotron": dict(arch=synth.ARCH_NEMOTRON, hidden=2688, ffn=64, experts=128, top_k=6, fmt=synth.FMT_Q4_0, seed=52,
                      normalize=True, scale=2.5),
+    "qwen": dict(arch=synth.ARCH_QWEN, hidden=2048, ffn=256, experts=128, top_k=8, fmt=synth.FMT_Q4_K, seed=53),
 }
 
 
 @pytest.mark.parametrize("name", sorted(LAYERS))
-def test_static_route_matches_forward_twice(name):
+def test_static_route_matches_forward_twice(name, oracle):
     import torch
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
@@ -55,8 +56,17 @@ def test_static_route_matches_forward_twice(name):
         # ids and weights are held to bit-exactness everywhere in this suite
         assert np.array_equal(got_ids, routing["ids"][0]), f"call {call}"
         assert np.array_equal(got_probs.view(np.uint32), routing["prob"][0].view(np.uint32)), f"call {call}"
+        # and against the CPU checker directly, so that both CUDA paths cannot be wrong together
+        if layer.arch == synth.ARCH_GPT_OSS:
+            _, ref_ids, ref_probs = oracle.router_gptoss(x, layer.router_w, layer.router_b, layer.top_k)
+        elif layer.arch == synth.ARCH_NEMOTRON:
+            _, ref_ids, ref_probs = oracle.router_sigmoid(x, layer.router_w, layer.router_b, layer.top_k, layer.normalize, layer.scale)
+        else:
+            _, ref_ids, ref_probs = oracle.router_softmax_topk(x, layer.router_w, layer.top_k)
+        assert np.array_equal(got_ids, ref_ids[0].astype(np.uint32)), f"call {call}: ids differ from the checker"
+        assert np.array_equal(got_probs.view(np.uint32), ref_probs[0].view(np.uint32)), f"call {call}: weights differ from the checker"
     # sizes beyond what the static array holds are refused with a message, nothing is launched
     rc = lib.oco_moe_route_token_static(layer.arch, C.c_void_p(xd.data_ptr()), C.c_void_p(w.router_w.data_ptr()),
-                                        C.c_void_p(w.router_b.data_ptr()), layer.hidden, 129, layer.top_k, 0, 1.0,
+                                        C.c_void_p(w.router_b.data_ptr()) if w.router_b is not None else None, layer.hidden, 129, layer.top_k, 0, 1.0,
                                         C.c_void_p(ids.data_ptr()), C.c_void_p(probs.data_ptr()), None, err, 256)
     assert rc == _lib.UNSUPPORTED_SHAPE and b"128" in err.value
