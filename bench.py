@@ -44,10 +44,8 @@ WORKLOADS = {
     "gpt-oss-120b-decode64": ("gpt-oss-120b", 64),
 }
 EXPERT_PARALLEL = {"gpt-oss-120b-prefill", "gpt-oss-120b-decode64"}
-# DRAM bytes (read + write) of one launch of the dominant kernels, from the ncu captures that are
-# summarised under profiles/ (grouped_gemm_wide_gpt-oss-20b-prefill.md,
-# grouped_gemm_wide_qwen3-30b-a3b-prefill.md, token_kernels_gpt-oss-20b-decode.md); a profiler is
-# never attached to a timed run.
+# DRAM bytes (read + write) of one launch of the dominant kernels, from ncu captures of the same commands
+# (dram__bytes_read.sum + dram__bytes_write.sum of one launch); a profiler is never attached to a timed run.
 NCU_TRAFFIC = {
     ("gpt-oss-20b-prefill", "up_tiles"): 334.5e6 + 38.7e6,
     ("gpt-oss-20b-prefill", "down_tiles"): 190.6e6 + 28.9e6,
@@ -67,6 +65,24 @@ def measured_peaks():
     return dict(hbm_gbs=6650.0, tflops=1590.0, tflops_sustained=1400.0, source="fallback")
 
 
+FP4_NOMINAL_TFLOPS, FP8_NOMINAL_TFLOPS = 9000.0, 4500.0   # dense, per GPU (vendor figures)
+
+
+def tensor_peaks():
+    """Tensor-pipe ceilings measured on this GPU with the library's own issue loop (tcgen05.mma, M128 N256,
+    zero operands): what a kernel of each kind could reach at best, beside the vendor's nominal figures."""
+    import ctypes as C
+    from oco_b200 import _lib
+    out = {}
+    for kind, name in enumerate(("f16_tcgen05", "fp8_tcgen05", "mxfp8_tcgen05", "mxfp4_tcgen05")):
+        v = C.c_float(0.0)
+        rc = _lib.lib().oco_tensor_peak(kind, 4096, C.byref(v))
+        out[name + "_tflops"] = float(v.value) if rc == _lib.OK else None
+    out["fp4_nominal_tflops"], out["fp8_nominal_tflops"] = FP4_NOMINAL_TFLOPS, FP8_NOMINAL_TFLOPS
+    out["how"] = "oco_tensor_peak: 4096 x 4 back-to-back tcgen05.mma per SM, best of 3, CUDA events"
+    return out
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -81,7 +97,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -114,7 +130,7 @@ class ClockSampler:
         sm_sorted = sorted(sm)
         load = sm_sorted[len(sm_sorted) // 2:] if sm_sorted else []
         return dict(sm_mhz=float(np.median(load)) if load else None, sm_max_mhz=max(mx) if mx else None,
-                    reasons=sorted(reasons), samples=len(sm))
+                    reasons=sorted(reasons), samples=len(sm), sm_mhz_all=sm)
 
 
 def algorithmic(layer: synth.Layer, tokens: int, ids: np.ndarray):
@@ -146,17 +162,25 @@ def cpu_baseline(layer, tokens, seed, budget_tokens, threads=None):
 
 
 def run_reference(args):
-    """CPU arm: the reference's MoE arithmetic restated in C++ (oracle/), timed on the host cores."""
+    """CPU arm: the reference's MoE arithmetic restated in C++ (oracle/), timed on the host cores with all the
+    threads the process may use. A step is the whole batch when K + W of them fit in about four minutes
+    (they do for the default workload), else a bounded sample of it."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
     cfg, default_tokens = WORKLOADS[args.workload]
     tokens = args.tokens or default_tokens
     layer = synth.make_config(cfg, seed=args.seed)
-    sample = min(tokens, args.cpu_tokens)
+    probe = min(tokens, 64)
+    _, dt = cpu_baseline(layer, tokens, args.seed, probe)
+    runs = args.warmup + args.steps
+    # per-token cost falls as the batch grows (each expert's rows are decoded once per batch), so the probe's
+    # rate is a safe upper bound on the time of a larger step
+    sample = tokens if dt / probe * tokens * runs <= 240.0 else max(probe, int(240.0 / runs / (dt / probe)))
+    sample = min(sample, tokens)
     times = []
     base = None
-    for i in range(args.warmup + args.steps):
+    for i in range(runs):
         base, dt = cpu_baseline(layer, tokens, args.seed + i, sample)
         if i >= args.warmup:
             times.append(dt)
@@ -167,7 +191,8 @@ def run_reference(args):
                 warmup=args.warmup, ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None,
                 dtype="f32", data="synthetic",
                 config=dict(workload=args.workload, tokens_per_step=sample, full_batch=tokens,
-                            note="each step is a bounded sample of the batch on the host cores"),
+                            note="each step is the whole batch on the host cores" if sample == tokens else
+                                 "each step is a bounded sample of the batch on the host cores"),
                 cpu_baseline=base, e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line))
     return 0
@@ -194,12 +219,12 @@ class _Replayed:
         self.i += 1
 
 
-def run_expert_parallel(args, torch, dist, world, rank, local):
+def run_expert_parallel(args, torch, dist, world, rank, local, workload, steps, warmup, with_cpu=False):
     """Experts sharded over the ranks, the batch split evenly between them (its total is fixed as N
-    grows), dispatch and combine as all-to-all over NCCL."""
+    grows), dispatch and combine as all-to-all over NCCL. Returns rank 0's record (None elsewhere)."""
     from oco_b200 import ep
-    cfg, default_tokens = WORKLOADS[args.workload]
-    total = args.tokens or default_tokens
+    cfg, default_tokens = WORKLOADS[workload]
+    total = (args.tokens if workload == args.workload and args.tokens else default_tokens)
     if total % world:
         raise SystemExit(f"{total} tokens do not divide over {world} ranks")
     T = total // world
@@ -207,12 +232,33 @@ def run_expert_parallel(args, torch, dist, world, rank, local):
     E, K, H, F = layer.experts, layer.top_k, layer.hidden, layer.ffn
     be = ep.CudaBackend(layer, rank, world, max_rows=T)
     backend = be.backend()
-    x_bits, res_bits = synth.make_tokens(H, total, args.seed, "normal")
-    x_bits, res_bits = x_bits[rank * T:(rank + 1) * T], res_bits[rank * T:(rank + 1) * T]
+    x_all, res_all = synth.make_tokens(H, total, args.seed, "normal")
+    x_bits, res_bits = x_all[rank * T:(rank + 1) * T], res_all[rank * T:(rank + 1) * T]
     hx = torch.from_numpy(x_bits.view(np.int16).copy()).pin_memory()
     hres = torch.from_numpy(res_bits.view(np.int16).copy()).pin_memory()
     x, res = hx.cuda(), hres.cuda()
     stream = torch.cuda.current_stream()
+
+    # ---- parity of this rank's rows against the CPU checker (a token sample), before any timing ----
+    import oracle
+    ep.forward(x, res, backend, E, uniform=True)
+    torch.cuda.synchronize()
+    got = res.cpu().numpy().view(np.uint16)
+    ids_gpu, _ = be.route(x)
+    ids_gpu = ids_gpu.cpu().numpy().astype(np.uint32)
+    pick = np.unique(np.linspace(0, T - 1, 4).astype(int))
+    ref = oracle.moe_forward(layer, x_bits[pick], res_bits[pick], mode=2, trace=False)
+    _, ids_ref, _ = oracle.router_gptoss(x_bits, layer.router_w, layer.router_b, K)
+    g = synth.bf16_bits_to_f32(got[pick]).astype(np.float64)
+    r = synth.bf16_bits_to_f32(ref.out).astype(np.float64)
+    par = torch.tensor([float(np.array_equal(ids_gpu, ids_ref.astype(np.uint32))),
+                        float(np.linalg.norm(g - r) / max(np.linalg.norm(r), 1e-30))], device="cuda", dtype=torch.float64)
+    worst = par.clone()
+    dist.all_reduce(worst[1:], op=dist.ReduceOp.MAX)
+    dist.all_reduce(par[:1], op=dist.ReduceOp.MIN)
+    parity = dict(ids_exact=bool(par[0].item() == 1.0), rel_l2=float(worst[1].item()), tolerance=1e-3,
+                  sample=f"{len(pick)} tokens per rank against the CPU checker; ids of all tokens; worst rank")
+    res.copy_(hres)
 
     def timed(n, exchange=None):
         dist.barrier(); torch.cuda.synchronize()
@@ -228,22 +274,23 @@ def run_expert_parallel(args, torch, dist, world, rank, local):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()), launches
 
-    for _ in range(max(3, args.warmup)):
+    for _ in range(max(3, warmup)):
         ep.forward(x, res, backend, E, uniform=True)
     sampler = ClockSampler(local)
     if rank == 0:
-        sampler.start(); time.sleep(0.3)
-    ms_per_step, launches = timed(args.steps)
+        sampler.start(); time.sleep(0.2)
+    ms_per_step, launches = timed(steps)
     clocks = sampler.stop() if rank == 0 else {}
+    clocks.pop("sm_mhz_all", None)
     be.router_plan.poll(); be.expert_plan.poll()
     # the same step with the exchange replaced by device-local copies of what it delivered
     rec = _Recorded(dist)
     ep.forward(x, res, backend, E, exchange=rec)
-    ms_local, _ = timed(args.steps, exchange=_Replayed(rec.log))
+    ms_local, _ = timed(steps, exchange=_Replayed(rec.log))
     # per-stage times of single steps
     tm, acc = {}, {}
     be.expert_plan.set_profiling(True)
-    for _ in range(min(5, args.steps)):
+    for _ in range(min(5, steps)):
         ep.forward(x, res, backend, E, timings=tm, uniform=True)
         for k, v in tm.items():
             acc.setdefault(k, []).append(v)
@@ -253,7 +300,7 @@ def run_expert_parallel(args, torch, dist, world, rank, local):
     phases = {k: float(np.mean(v)) for k, v in acc.items()}
     routes_here = int(phases.pop("routes_received"))
     # end to end: pinned host rows in, the layer, residual rows back
-    e2e_steps = max(3, min(args.steps, 10))
+    e2e_steps = max(3, min(steps, 10))
     dist.barrier(); torch.cuda.synchronize()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
@@ -264,9 +311,10 @@ def run_expert_parallel(args, torch, dist, world, rank, local):
     t = torch.tensor([1e3 * (time.perf_counter() - t0) / e2e_steps], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item())
+    del be, backend
+    torch.cuda.empty_cache()
     if rank != 0:
-        dist.destroy_process_group()
-        return 0
+        return None
     peaks = measured_peaks()
     row_bytes = T * H * 2
     e2e = dict(value=total / (e2e_ms / 1e3), unit="tokens/s", ms_per_step=e2e_ms, h2d_bytes_per_step=2 * row_bytes,
@@ -279,72 +327,36 @@ def run_expert_parallel(args, torch, dist, world, rank, local):
                         frac=ach / peaks["tflops"], traffic=None, peak_source=f"{peaks['source']} dense bf16 cuBLAS, burst",
                         algorithmic_flops_per_launch=flops, launch_ms=phases["up_tiles"], routes_on_rank0=routes_here)
     base = None
-    if not args.no_cpu_baseline:
+    if with_cpu:
         base, _ = cpu_baseline(layer, total, args.seed, args.cpu_tokens)
-    line = dict(
-        metric=METRIC, value=total / (ms_per_step / 1e3), unit="tokens/s", n_gpus=world, steps=args.steps,
-        warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True, scaling="strong", vs_baseline=None,
-        dtype="f16", data="synthetic",
-        config=dict(workload=args.workload, tokens_total=total, tokens_per_gpu=T, hidden=H, ffn=F, experts=E, top_k=K,
+    return dict(
+        value=total / (ms_per_step / 1e3), unit="tokens/s", n_gpus=world, steps=steps, warmup=warmup, ms_per_step=ms_per_step,
+        scaling="strong", dtype="f16",
+        config=dict(workload=workload, tokens_total=total, tokens_per_gpu=T, hidden=H, ffn=F, experts=E, top_k=K,
                     weight_format="MXFP4", experts_per_gpu=E // world, parallelism=f"ep{world}",
                     cache="every step reads the rank's whole expert shard (%.0f MB), more than the 126 MB L2"
                           % (E // world * layer.expert_bytes() / 1e6)),
         all_to_all=dict(exposed_ms=ms_per_step - ms_local, ms_per_step_with_local_copies=ms_local,
                         dispatch_ms=phases.get("dispatch_ms"), combine_ms=phases.get("combine_a2a_ms"),
                         route_bytes_each_way_per_gpu=T * K * H * 2),
-        clocks=clocks, e2e=e2e, gpu_launches=launches, phases_ms=phases, roofline=roofline, cpu_baseline=base)
-    print(json.dumps(line))
-    dist.destroy_process_group()
-    return 0
+        parity=parity, clocks=clocks, e2e=e2e, gpu_launches=launches, phases_ms=phases, roofline=roofline, cpu_baseline=base)
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gpt-oss-20b-prefill", choices=sorted(WORKLOADS))
-    ap.add_argument("--tokens", type=int, default=0)
-    ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--cpu-tokens", type=int, default=32, help="tokens in the CPU baseline's bounded sample")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-graph", action="store_true", help="single-token workloads: launch kernels directly instead of replaying CUDA graphs")
-    ap.add_argument("--layers", type=int, default=0, help="distinct weight copies rotated per step (0 = auto)")
-    ap.add_argument("--with-norm", action="store_true",
-                    help="time the fused entry point: residual add + RMS norm + layer (the step either side of the layer)")
-    args = ap.parse_args()
-    if args.impl == "reference":
-        return run_reference(args)
-
-    import torch
-    import torch.distributed as dist
-    from oco_b200 import build, moe
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU path for this library")
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    if rank == 0:
-        build.build()
-    if world > 1:
-        dist.barrier()
-
-    if world > 1 and args.workload in EXPERT_PARALLEL:
-        return run_expert_parallel(args, torch, dist, world, rank, local)
-
-    cfg, default_tokens = WORKLOADS[args.workload]
-    tokens = args.tokens or default_tokens
+def measure_layer(args, ctx, workload, steps, warmup, tokens=0, graph=True, with_norm=False, layers=0, sustained_s=0.0):
+    """One workload on this rank's GPU (every rank runs the same layer on its own tokens): device-timed
+    steps, per-kernel phase times, the end-to-end call with host buffers and, on request, a seconds-long
+    loop with the SM clock sampled. Returns rank 0's record (other ranks: the timing fields only)."""
+    torch, dist, world, rank, local = ctx
+    from oco_b200 import moe
+    cfg, default_tokens = WORKLOADS[workload]
+    tokens = tokens or default_tokens
     layer = synth.make_config(cfg, seed=args.seed)
     decode = tokens == 1
     # Cold-cache protocol. Prefill reads every expert (hundreds of MB, more than the 126 MB L2) each
     # step, so the inputs themselves exceed L2. A single token touches only top_k experts (tens of
     # MB), so distinct weight copies are rotated step by step and never revisited within L2 reach.
     per_step_bytes = layer.top_k * layer.expert_bytes() if decode else layer.experts * layer.expert_bytes()
-    copies = args.layers or (max(2, int(np.ceil(600e6 / per_step_bytes))) if decode else 1)
+    copies = layers or (max(2, int(np.ceil(600e6 / per_step_bytes))) if decode else 1)
     weights = [moe._Weights.from_layer(layer) for _ in range(copies)]
     plans = []
     for w in weights:
@@ -357,7 +369,6 @@ def main():
     res = torch.from_numpy(res_bits.view(np.int16).copy()).cuda()
     stream = torch.cuda.current_stream()
     norm_w = torch.ones(layer.hidden, dtype=torch.float32, device="cuda")
-
     graphs = [None] * copies
 
     def step(i, profile=False):
@@ -366,17 +377,17 @@ def main():
             graphs[i % copies].replay()       # launch-bound single-token step: one graph launch
             return p
         p.set_profiling(profile)
-        if args.with_norm:
+        if with_norm:
             p.add_norm_forward(res, x, norm_w, 1e-5, layer.arch == synth.ARCH_GPT_OSS, tokens)   # x stands in for the mixer's output
         else:
             p.forward(x, res, tokens)
         return p
 
-    for i in range(max(args.warmup, copies if decode else 0)):
+    for i in range(max(warmup, copies if decode else 0)):
         step(i)
     torch.cuda.synchronize()
     plans[0].poll()
-    if decode and not args.no_graph:
+    if decode and graph:
         # A single token is a handful of microsecond kernels: capture each weight copy's step in a
         # CUDA graph so the timed region measures the GPU, not the host's launch rate.
         side = torch.cuda.Stream()
@@ -386,14 +397,16 @@ def main():
                 plans[c].set_profiling(False)
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g, stream=side):
-                    step_plain = plans[c].add_norm_forward(res, x, norm_w, 1e-5, layer.arch == synth.ARCH_GPT_OSS, tokens) \
-                        if args.with_norm else plans[c].forward(x, res, tokens)
+                    if with_norm:
+                        plans[c].add_norm_forward(res, x, norm_w, 1e-5, layer.arch == synth.ARCH_GPT_OSS, tokens)
+                    else:
+                        plans[c].forward(x, res, tokens)
                 graphs[c] = g
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
     # routing of this batch (for the algorithmic byte count)
-    routing = moe.Routing(); routing.plan, routing.rows = plans[(args.warmup - 1) % copies if args.warmup else 0], tokens
-    if not args.warmup:
+    routing = moe.Routing(); routing.plan, routing.rows = plans[(warmup - 1) % copies if warmup else 0], tokens
+    if not warmup:
         step(0); torch.cuda.synchronize()
     ids = routing.read()["ids"]
     alg_bytes, alg_flops, touched = algorithmic(layer, tokens, ids)
@@ -401,35 +414,38 @@ def main():
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.3)
+        time.sleep(0.2)
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     phase_acc = {}
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
     launches = 0
     t_wall = time.perf_counter()
-    for i in range(args.steps):
+    for i in range(steps):
         starts[i].record(stream)
-        p = step(args.warmup + i, profile=graphs[0] is None)
+        p = step(warmup + i, profile=False)
         ends[i].record(stream)
         launches += p.launch_count()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     wall = time.perf_counter() - t_wall
+    clocks = sampler.stop() if rank == 0 else {}
+    clocks.pop("sm_mhz_all", None)
     # Per-kernel durations: the phase events of a plan hold its last call, so a few more steps are
     # run one at a time and read back (same kernels, same inputs, still rotating weight copies).
-    for i in range(min(10, args.steps)):
-        p = step(args.warmup + args.steps + i, profile=True)
+    for i in range(min(10, steps)):
+        p = step(warmup + steps + i, profile=True)
         torch.cuda.synchronize()
         for k, v in p.phase_times().items():
             phase_acc.setdefault(k, []).append(v)
-    clocks = sampler.stop() if rank == 0 else {}
+    for p in plans:
+        p.set_profiling(False)
     step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
     total_ms = starts[0].elapsed_time(ends[-1])
-    ms_per_step = total_ms / args.steps
+    ms_per_step = total_ms / steps
     if world > 1:
         t = torch.tensor([ms_per_step], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -437,13 +453,37 @@ def main():
     plans[0].poll()
     value = world * tokens / (ms_per_step / 1e3)
 
+    # ---- a seconds-long run of the same step, the SM clock sampled every 50 ms -------------------------
+    sustained = None
+    if sustained_s > 0:
+        n = max(steps, int(sustained_s * 1e3 / max(ms_per_step, 1e-3)) + 1)
+        s2 = ClockSampler(local)
+        if rank == 0:
+            s2.start(); time.sleep(0.1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record(stream)
+        for i in range(n):
+            step(i)
+        b.record(stream)
+        torch.cuda.synchronize()
+        c2 = s2.stop() if rank == 0 else {}
+        ms_long = a.elapsed_time(b) / n
+        if rank == 0:
+            mhz = np.array(c2.pop("sm_mhz_all", []) or [0.0])
+            under = mhz[mhz >= np.median(mhz)] if len(mhz) else mhz
+            hist = {str(int(k)): int(v) for k, v in zip(*np.unique((mhz // 100) * 100, return_counts=True))}
+            sustained = dict(seconds=ms_long * n / 1e3, steps=n, ms_per_step=ms_long, tokens_per_s=tokens / (ms_long / 1e3),
+                             sm_mhz_median_under_load=float(np.median(under)), sm_mhz_histogram_100mhz_bins=hist,
+                             ms_times_median_mhz=ms_long * float(np.median(under)), reasons=c2.get("reasons"),
+                             burst_ms_per_step=ms_per_step)
+
     # ---- end to end through the host-buffer entry point -----------------------------------------
     hx = torch.from_numpy(x_bits.view(np.int16)).pin_memory()
     hres = torch.from_numpy(res_bits.view(np.int16).copy()).pin_memory()
     hx_np, hres_np = hx.numpy().view(np.uint16), hres.numpy().view(np.uint16)
-    e2e_steps = max(3, min(args.steps, 20))
+    e2e_steps = max(3, min(steps, 20))
     for i in range(2):
-        plans[i % copies].set_profiling(False)
         plans[i % copies].forward_host(hx_np, hres_np, tokens)
     if world > 1:
         dist.barrier()
@@ -460,11 +500,10 @@ def main():
     e2e = dict(value=world * tokens / (e2e_ms / 1e3), unit="tokens/s", ms_per_step=e2e_ms,
                h2d_bytes_per_step=2 * row_bytes, d2h_bytes_per_step=row_bytes,
                api="oco_moe_forward_host (pinned host buffers in, residual rows back)")
-
+    del plans, weights, graphs
+    torch.cuda.empty_cache()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return 0
+        return None
 
     # ---- roofline of the dominant kernel ---------------------------------------------------------
     peaks = measured_peaks()
@@ -488,9 +527,11 @@ def main():
             units = per.get(dominant, alg_bytes)
             achieved = units / dur_s / 1e9
             roofline = dict(bound="hbm", kernel=dominant, achieved=achieved, peak=peaks["hbm_gbs"], unit="GB/s",
-                            frac=achieved / peaks["hbm_gbs"], traffic=NCU_TRAFFIC.get((args.workload, dominant)),
+                            frac=achieved / peaks["hbm_gbs"], traffic=NCU_TRAFFIC.get((workload, dominant)),
                             peak_source=f"{peaks['source']} copy bandwidth",
                             algorithmic_bytes_per_launch=units, launch_ms=phases[dominant],
+                            per_kernel={k: dict(gbs=per[k] / (v / 1e3) / 1e9, frac=per[k] / (v / 1e3) / 1e9 / peaks["hbm_gbs"])
+                                        for k, v in expert_phases.items() if k in per},
                             whole_step=dict(bytes=alg_bytes, gbs=alg_bytes / (ms_per_step / 1e3) / 1e9,
                                             frac=alg_bytes / (ms_per_step / 1e3) / 1e9 / peaks["hbm_gbs"]))
         else:
@@ -500,29 +541,126 @@ def main():
             long_run = wall > 2.0 and peaks.get("tflops_sustained")
             peak = peaks["tflops_sustained"] if long_run else peaks["tflops"]
             roofline = dict(bound="tensor", kernel=dominant, achieved=achieved, peak=peak, unit="TFLOP/s",
-                            frac=achieved / peak, traffic=NCU_TRAFFIC.get((args.workload, dominant)) if tokens == default_tokens else None,
+                            frac=achieved / peak, traffic=NCU_TRAFFIC.get((workload, dominant)) if tokens == default_tokens else None,
                             peak_source=f"{peaks['source']} dense bf16 cuBLAS, {'sustained' if long_run else 'burst'}",
                             algorithmic_flops_per_launch=units, launch_ms=phases[dominant],
                             whole_step=dict(flops=alg_flops, tflops=alg_flops / (ms_per_step / 1e3) / 1e12,
                                             bytes=alg_bytes, gbs=alg_bytes / (ms_per_step / 1e3) / 1e9))
-    base = None
-    if not args.no_cpu_baseline:
-        base, _ = cpu_baseline(layer, tokens, args.seed, args.cpu_tokens)
-
-    line = dict(
-        metric=METRIC, value=value, unit="tokens/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
-        ms_per_step=ms_per_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f16",
-        data="synthetic",
-        config=dict(workload=args.workload, tokens_per_gpu=tokens, hidden=layer.hidden, ffn=layer.ffn,
+    return dict(
+        value=value, ms_per_step=ms_per_step, layer=layer, tokens=tokens,
+        config=dict(workload=workload, tokens_per_gpu=tokens, hidden=layer.hidden, ffn=layer.ffn,
                     experts=layer.experts, top_k=layer.top_k, weight_format={39: "MXFP4", 12: "Q4_K", 2: "Q4_0"}[layer.fmt],
                     experts_touched=touched, weight_copies=copies,
                     cache="every step reads all expert weights (%.0f MB), more than the 126 MB L2" % (per_step_bytes / 1e6)
                     if not decode else "%d weight copies rotated per step (%.0f MB between reuses)" % (copies, copies * per_step_bytes / 1e6),
-                    cuda_graph=graphs[0] is not None, fused_add_norm=bool(args.with_norm),
+                    cuda_graph=bool(decode and graph), fused_add_norm=bool(with_norm),
                     parallelism="replicas" if world > 1 else "single"),
-        clocks=clocks, e2e=e2e, gpu_launches=launches, phases_ms=phases, roofline=roofline, cpu_baseline=base,
+        clocks=clocks, e2e=e2e, gpu_launches=launches, phases_ms=phases, roofline=roofline, sustained=sustained,
         step_ms_min=min(step_ms), step_ms_max=max(step_ms))
-    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gpt-oss-20b-prefill", choices=sorted(WORKLOADS))
+    ap.add_argument("--tokens", type=int, default=0)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--cpu-tokens", type=int, default=256, help="tokens in the CPU baseline's bounded sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="only the headline workload: no decode block, tensor peaks, sustained run, CPU full batch or expert-parallel block")
+    ap.add_argument("--no-graph", action="store_true", help="single-token workloads: launch kernels directly instead of replaying CUDA graphs")
+    ap.add_argument("--layers", type=int, default=0, help="distinct weight copies rotated per step (0 = auto)")
+    ap.add_argument("--with-norm", action="store_true",
+                    help="time the fused entry point: residual add + RMS norm + layer (the step either side of the layer)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    from oco_b200 import build
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path for this library")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if rank == 0:
+        build.build()
+    if world > 1:
+        dist.barrier()
+    ctx = (torch, dist, world, rank, local)
+    default = args.workload == "gpt-oss-20b-prefill" and not args.tokens
+    extras = default and not args.no_extras
+
+    if world > 1 and args.workload in EXPERT_PARALLEL:
+        rec = run_expert_parallel(args, torch, dist, world, rank, local, args.workload, args.steps, args.warmup,
+                                  with_cpu=not args.no_cpu_baseline)
+        if rank == 0:
+            print(json.dumps(dict(metric=METRIC, higher_is_better=True, vs_baseline=None, data="synthetic", **rec)))
+        dist.destroy_process_group()
+        return 0
+
+    head = measure_layer(args, ctx, args.workload, args.steps, args.warmup, tokens=args.tokens, graph=not args.no_graph,
+                         with_norm=args.with_norm, layers=args.layers, sustained_s=2.0 if extras else 0.0)
+    line = None
+    if rank == 0:
+        layer, tokens = head.pop("layer"), head.pop("tokens")
+        line = dict(metric=METRIC, value=head.pop("value"), unit="tokens/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
+                    ms_per_step=head.pop("ms_per_step"), higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f16",
+                    data="synthetic", **head)
+        if not args.no_cpu_baseline:
+            base, _ = cpu_baseline(layer, tokens, args.seed, args.cpu_tokens)
+            base["note"] = "the port is the bit-exact checker, not a tuned CPU kernel"
+            if extras:
+                full, dt = cpu_baseline(layer, tokens, args.seed, tokens)
+                base["full_batch"] = dict(value=full["value"], unit="tokens/s", tokens=tokens, seconds=dt, cores=full["cores"])
+            line["cpu_baseline"] = base
+        else:
+            line["cpu_baseline"] = None
+    if extras:
+        # the HBM half of the metric: one token through the same layer (three launches replayed as a graph)
+        dec = measure_layer(args, ctx, "gpt-oss-20b-decode", 200, 10)
+        if rank == 0:
+            rl = dec["roofline"] or {}
+            line["decode"] = dict(workload="gpt-oss-20b-decode", us_per_token=1e3 * dec["ms_per_step"], tokens_per_s=dec["value"] / world,
+                                  whole_step_hbm_frac=(rl.get("whole_step") or {}).get("frac"),
+                                  per_kernel_hbm=rl.get("per_kernel"), phases_ms=dec["phases_ms"], gpu_launches=dec["gpu_launches"],
+                                  e2e_us_per_token=1e3 * dec["e2e"]["ms_per_step"], config=dec["config"],
+                                  hbm_peak_gbs=measured_peaks()["hbm_gbs"], hbm_nominal_gbs=8000.0)
+            # every tensor fraction against the measured and the nominal ceilings
+            pk = tensor_peaks()
+            mp = measured_peaks()
+            pk["bf16_cublas_tflops"] = mp["tflops"]
+            pk["bf16_cublas_sustained_tflops"] = mp["tflops_sustained"]
+            line["peaks"] = pk
+            r = line.get("roofline")
+            if r and r.get("bound") == "tensor":
+                a = r["achieved"]
+                r["frac_of"] = {k: (a / v if v else None) for k, v in
+                                dict(bf16_cublas_measured=mp["tflops"], f16_tcgen05_measured=pk["f16_tcgen05_tflops"],
+                                     fp4_tcgen05_measured=pk["mxfp4_tcgen05_tflops"], fp4_nominal=FP4_NOMINAL_TFLOPS).items()}
+        if world > 1:
+            # the configuration that shards: 128 experts over the ranks, all-to-all dispatch and combine; rank 0
+            # also runs it alone first, for the strong-scaling reference on the same box
+            n1 = None
+            if rank == 0:
+                solo = measure_layer(args, (torch, dist, 1, 0, local), "gpt-oss-120b-prefill", 10, 3)
+                n1 = solo["ms_per_step"]
+            dist.barrier()
+            epr = run_expert_parallel(args, torch, dist, world, rank, local, "gpt-oss-120b-prefill", 10, 3)
+            if rank == 0:
+                epr["n1_ms_per_step_same_box"] = n1
+                epr["strong_scaling_efficiency"] = n1 / (world * epr["ms_per_step"]) if n1 else None
+                line["expert_parallel"] = epr
+    if rank == 0:
+        print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
     return 0

@@ -261,6 +261,12 @@ int oco_cuda_event_elapsed_ms(void* start_event, void* end_event, float* ms);
  * untouched. No counterpart in the reference (Metal has no device-side waits on this path). */
 int oco_moe_selftest_wait_timeout(oco_moe_plan* plan, long long wait_cycles, void* cuda_stream);
 
+/* Measured tensor-pipe ceiling of the current GPU for one tcgen05.mma kind (0 = f16, 1 = f8f6f4 e4m3,
+ * 2 = mxf8f6f4 block-scaled e4m3, 3 = mxf4 block-scaled e2m1): `iters` x 4 back-to-back MMAs of shape
+ * M128 N256 on zero operands per SM, dense TFLOP/s in *tflops. Measurement support for the benchmark's
+ * roofline fractions; allocates 256 bytes for the call's duration. No counterpart in the reference. */
+int oco_tensor_peak(int kind, int iters, float* tflops);
+
 const char* oco_moe_version(void);
 
 #ifdef __cplusplus

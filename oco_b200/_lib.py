@@ -68,6 +68,7 @@ SIGNATURES = {
     "oco_cuda_event_sync": (C.c_int, [C.c_void_p]),
     "oco_cuda_event_elapsed_ms": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_float)]),
     "oco_moe_selftest_wait_timeout": (C.c_int, [C.c_void_p, C.c_longlong, C.c_void_p]),
+    "oco_tensor_peak": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_float)]),
     "oco_moe_version": (C.c_char_p, []),
 }
 

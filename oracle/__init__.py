@@ -24,7 +24,8 @@ ARCH_GPT_OSS, ARCH_NEMOTRON, ARCH_QWEN = 0, 1, 2
 def build(force: bool = False) -> str:
     """Compile the oracle with the Makefile beside it (g++ only, no external libraries)."""
     src = os.path.join(_HERE, "moe_oracle.cpp")
-    stale = (not os.path.exists(_LIB_PATH)) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src)
+    newest = max(os.path.getmtime(src), os.path.getmtime(os.path.join(_HERE, "Makefile")))
+    stale = (not os.path.exists(_LIB_PATH)) or os.path.getmtime(_LIB_PATH) < newest
     if force or stale:
         subprocess.run(["make", "-C", _HERE, "-B", "libmoe_oracle.so"], check=True,
                        stdout=subprocess.DEVNULL)
