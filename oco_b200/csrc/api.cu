@@ -786,7 +786,8 @@ int oco_moe_plan_create(const oco_moe_desc* desc, oco_moe_plan** out) {
     if (d.weight_format != want)
         return fail(plan, OCO_UNSUPPORTED_SHAPE, "arch %d is built for weight format %d, got %d", d.arch, want, d.weight_format);
     if (d.experts < 1 || d.experts > kMaxExperts) return fail(plan, OCO_UNSUPPORTED_SHAPE, "experts must be 1..128");
-    if (d.top_k < 1 || d.top_k > kMaxTopK || d.top_k > d.experts) return fail(plan, OCO_UNSUPPORTED_SHAPE, "top_k must be 1..8");
+    // (a plan over a shard of the experts may hold fewer experts than routes per token: it never routes)
+    if (d.top_k < 1 || d.top_k > kMaxTopK) return fail(plan, OCO_UNSUPPORTED_SHAPE, "top_k must be 1..8");
     const int be = block_elems(d.weight_format);
     if (d.hidden <= 0 || d.ffn <= 0 || d.hidden % be || d.ffn % be || (d.shared_ffn % be))
         return fail(plan, OCO_UNSUPPORTED_SHAPE, "hidden, ffn and shared_ffn must be multiples of the %d-element block", be);
@@ -918,6 +919,7 @@ int oco_moe_bind_weights(oco_moe_plan* plan, const oco_moe_weights* w) {
         if (d.shared_ffn && (!w->shared_up_w || !w->shared_down_w)) return fail(plan, OCO_INVALID_ARGUMENT, "shared expert weights missing");
     }
     if (has_router) {
+        if (d.top_k > d.experts) return fail(plan, OCO_UNSUPPORTED_SHAPE, "a router over %d experts cannot pick %d", d.experts, d.top_k);
         if (d.arch != OCO_ARCH_QWEN && !w->router_b) return fail(plan, OCO_INVALID_ARGUMENT, "this family needs router_b");
         if (((uintptr_t)w->router_w & 15u) != 0) return fail(plan, OCO_INVALID_ARGUMENT, "router_w must be 16-byte aligned");
     }

@@ -64,7 +64,7 @@ def forward(x: torch.Tensor, residual: torch.Tensor, backend: Backend, experts_t
     rank = dist.get_rank(group)
     epr = experts_total // world
     T, H = x.shape
-    ids, probs = backend.route(x)
+    ids, probs = backend.route(x)         # a rank without tokens still takes part in every exchange
     K = ids.shape[1]
     order, send_counts, local_ids = dispatch_layout(ids, world, epr)
     send_rows = x.index_select(0, order // K)
@@ -105,7 +105,8 @@ def forward(x: torch.Tensor, residual: torch.Tensor, backend: Backend, experts_t
         ev[3].record()
     y_routes = torch.empty_like(y_back)
     y_routes.index_copy_(0, order, y_back)           # back to route order
-    backend.combine(y_routes, probs, residual)
+    if T:
+        backend.combine(y_routes, probs, residual)
     if ev:
         torch.cuda.synchronize()
         timings["dispatch_ms"] = ev[0].elapsed_time(ev[1])
@@ -123,6 +124,10 @@ class CudaBackend:
         self._lib, self._moe = _lib, moe
         E = layer.experts
         assert E % world == 0, "experts must divide evenly over the ranks"
+        if layer.shared_ffn:
+            # the always-on expert belongs to the token-owning rank, beside the routed sum; this protocol moves
+            # routed rows only, so a layer with a shared expert is refused rather than silently losing that term
+            raise moe.OcoError(_lib.UNSUPPORTED_SHAPE, "expert parallelism does not run layers with a shared expert")
         self.epr = E // world
         lo, hi = rank * self.epr, (rank + 1) * self.epr
         self.layer = layer
@@ -154,6 +159,9 @@ class CudaBackend:
 
     def route(self, x):
         T = x.shape[0]
+        if T == 0:
+            return (torch.empty((0, self.K), dtype=torch.int32, device=x.device),
+                    torch.empty((0, self.K), dtype=torch.float32, device=x.device))
         p = self.router_plan
         p._check(self._lib.lib().oco_moe_route(p.handle, C.c_void_p(x.data_ptr()), T, self._stream()))
         v = self._lib.RoutingView()

@@ -17,7 +17,8 @@ from oco_b200 import ep, synth  # noqa: E402
 def main():
     dist.init_process_group("gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
-    for T, uniform in ((11, False), (12, True)):     # 11 tokens: ranks hold uneven shares; 12: equal shares
+    # 11 tokens: ranks hold uneven shares; 12: equal shares; 2: with four ranks some hold no token at all
+    for T, uniform in ((11, False), (12, True), (2, False)):
         run_case(rank, world, T, uniform)
     dist.barrier()
     dist.destroy_process_group()
@@ -34,6 +35,8 @@ def run_case(rank, world, T, uniform):
     e_lo = rank * epr
 
     def route(x):
+        if x.shape[0] == 0:
+            return torch.empty((0, K), dtype=torch.int32), torch.empty((0, K), dtype=torch.float32)
         _, ids, probs = oracle.router_gptoss(x.numpy().view(np.uint16), layer.router_w, layer.router_b, K)
         return torch.from_numpy(ids.astype(np.int32)), torch.from_numpy(probs)
 

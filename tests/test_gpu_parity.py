@@ -594,3 +594,39 @@ def test_plan_is_tied_to_its_device(moe):
             with pytest.raises(moe.OcoError) as e:
                 plan.forward(xd, rd, 1)
             assert e.value.code == _lib.INVALID_ARGUMENT
+
+
+
+def test_expert_shard_with_fewer_experts_than_routes_per_token(moe, oracle):
+    """A plan over a shard of the experts (expert parallelism) may hold fewer experts than the layer's
+    top_k: it never routes, it only multiplies rows that arrive with their local expert id."""
+    import ctypes as C
+    import torch
+    from oco_b200 import _lib
+    E, K, H, F, R = 4, 6, 256, 192, 50
+    layer = synth.make_layer(synth.ARCH_NEMOTRON, H, F, E, 2, synth.FMT_Q4_0, seed=23, normalize=True, scale=2.5)
+    plan = moe._Plan(synth.ARCH_NEMOTRON, H, F, E, K, synth.FMT_Q4_0, normalize=True, scale=2.5)
+    shard = synth.Layer(**{**layer.__dict__})
+    shard.router_w = shard.router_b = None
+    w = moe._Weights.from_layer(shard)
+    plan.reserve(R)
+    plan.bind(w)
+    rng = np.random.default_rng(1)
+    x, _ = synth.make_tokens(H, R, 3)
+    ids = rng.integers(0, E, size=R).astype(np.uint32)
+    xd = torch.from_numpy(x.view(np.int16)).cuda()
+    idd = torch.from_numpy(ids.view(np.int32)).cuda()
+    y = torch.zeros((R, H), dtype=torch.int16, device="cuda")
+    rc = _lib.lib().oco_moe_experts(plan.handle, C.c_void_p(xd.data_ptr()), C.c_void_p(idd.data_ptr()), R, C.c_void_p(y.data_ptr()),
+                                    C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == _lib.OK, _lib.lib().oco_moe_last_error(plan.handle)
+    plan.poll()
+    up = oracle.expert_up_tile(layer.up_w, x, None, 0.0, ids, 1, H, F, fmt=synth.FMT_Q4_0)
+    up = synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(up))          # the projection is rounded to bf16, then relu^2 in f32 -> half
+    act = (np.maximum(up, 0.0) ** 2).astype(np.float16)
+    ref = oracle.expert_down_tile(layer.down_w, act.view(np.uint16), None, ids, F, H, fmt=synth.FMT_Q4_0)
+    assert rel_l2(y.cpu().numpy().view(np.uint16), ref) <= 2e-3
+    # a router over four experts cannot pick six
+    bad = moe._Plan(synth.ARCH_NEMOTRON, H, F, E, K, synth.FMT_Q4_0, normalize=True, scale=2.5)
+    with pytest.raises(moe.OcoError):
+        bad.bind(moe._Weights.from_layer(layer))
