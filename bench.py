@@ -342,7 +342,7 @@ def run_expert_parallel(args, torch, dist, world, rank, local, workload, steps, 
         parity=parity, clocks=clocks, e2e=e2e, gpu_launches=launches, phases_ms=phases, roofline=roofline, cpu_baseline=base)
 
 
-def measure_layer(args, ctx, workload, steps, warmup, tokens=0, graph=True, with_norm=False, layers=0, sustained_s=0.0):
+def measure_layer(args, ctx, workload, steps, warmup, tokens=0, graph=True, with_norm=False, layers=0, sustained_s=0.0, numerics=0):
     """One workload on this rank's GPU (every rank runs the same layer on its own tokens): device-timed
     steps, per-kernel phase times, the end-to-end call with host buffers and, on request, a seconds-long
     loop with the SM clock sampled. Returns rank 0's record (other ranks: the timing fields only)."""
@@ -360,7 +360,7 @@ def measure_layer(args, ctx, workload, steps, warmup, tokens=0, graph=True, with
     weights = [moe._Weights.from_layer(layer) for _ in range(copies)]
     plans = []
     for w in weights:
-        p = moe.plan_for(layer)
+        p = moe.plan_for(layer, numerics=numerics)
         p.reserve(tokens)
         p.bind(w)
         plans.append(p)
@@ -540,9 +540,13 @@ def measure_layer(args, ctx, workload, steps, warmup, tokens=0, graph=True, with
             achieved = units / dur_s / 1e12
             long_run = wall > 2.0 and peaks.get("tflops_sustained")
             peak = peaks["tflops_sustained"] if long_run else peaks["tflops"]
+            source = f"{peaks['source']} dense bf16 cuBLAS, {'sustained' if long_run else 'burst'}"
+            if numerics == 2:
+                pk4 = tensor_peaks()["mxfp4_tcgen05_tflops"]
+                peak, source = (pk4 or FP4_NOMINAL_TFLOPS), ("measured tcgen05 kind::mxf4 issue loop" if pk4 else "nominal FP4")
             roofline = dict(bound="tensor", kernel=dominant, achieved=achieved, peak=peak, unit="TFLOP/s",
-                            frac=achieved / peak, traffic=NCU_TRAFFIC.get((workload, dominant)) if tokens == default_tokens else None,
-                            peak_source=f"{peaks['source']} dense bf16 cuBLAS, {'sustained' if long_run else 'burst'}",
+                            frac=achieved / peak, traffic=(NCU_TRAFFIC.get((workload, dominant)) if tokens == default_tokens and numerics == 0 else None),
+                            peak_source=source, frac_of_fp4_nominal=achieved / FP4_NOMINAL_TFLOPS,
                             algorithmic_flops_per_launch=units, launch_ms=phases[dominant],
                             whole_step=dict(flops=alg_flops, tflops=alg_flops / (ms_per_step / 1e3) / 1e12,
                                             bytes=alg_bytes, gbs=alg_bytes / (ms_per_step / 1e3) / 1e9))
@@ -553,7 +557,7 @@ def measure_layer(args, ctx, workload, steps, warmup, tokens=0, graph=True, with
                     experts_touched=touched, weight_copies=copies,
                     cache="every step reads all expert weights (%.0f MB), more than the 126 MB L2" % (per_step_bytes / 1e6)
                     if not decode else "%d weight copies rotated per step (%.0f MB between reuses)" % (copies, copies * per_step_bytes / 1e6),
-                    cuda_graph=bool(decode and graph), fused_add_norm=bool(with_norm),
+                    cuda_graph=bool(decode and graph), fused_add_norm=bool(with_norm), numerics=numerics,
                     parallelism="replicas" if world > 1 else "single"),
         clocks=clocks, e2e=e2e, gpu_launches=launches, phases_ms=phases, roofline=roofline, sustained=sustained,
         step_ms_min=min(step_ms), step_ms_max=max(step_ms))
@@ -574,6 +578,8 @@ def main():
                     help="only the headline workload: no decode block, tensor peaks, sustained run, CPU full batch or expert-parallel block")
     ap.add_argument("--no-graph", action="store_true", help="single-token workloads: launch kernels directly instead of replaying CUDA graphs")
     ap.add_argument("--layers", type=int, default=0, help="distinct weight copies rotated per step (0 = auto)")
+    ap.add_argument("--numerics", type=int, default=0, choices=[0, 2],
+                    help="2: the opt-in block-scaled mode (MXFP4 activations on tcgen05 kind::mxf4); never the headline")
     ap.add_argument("--with-norm", action="store_true",
                     help="time the fused entry point: residual add + RMS norm + layer (the step either side of the layer)")
     args = ap.parse_args()
@@ -596,7 +602,7 @@ def main():
     if world > 1:
         dist.barrier()
     ctx = (torch, dist, world, rank, local)
-    default = args.workload == "gpt-oss-20b-prefill" and not args.tokens
+    default = args.workload == "gpt-oss-20b-prefill" and not args.tokens and args.numerics == 0
     extras = default and not args.no_extras
 
     if world > 1 and args.workload in EXPERT_PARALLEL:
@@ -608,12 +614,13 @@ def main():
         return 0
 
     head = measure_layer(args, ctx, args.workload, args.steps, args.warmup, tokens=args.tokens, graph=not args.no_graph,
-                         with_norm=args.with_norm, layers=args.layers, sustained_s=2.0 if extras else 0.0)
+                         with_norm=args.with_norm, layers=args.layers, sustained_s=2.0 if extras else 0.0, numerics=args.numerics)
     line = None
     if rank == 0:
         layer, tokens = head.pop("layer"), head.pop("tokens")
         line = dict(metric=METRIC, value=head.pop("value"), unit="tokens/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
-                    ms_per_step=head.pop("ms_per_step"), higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f16",
+                    ms_per_step=head.pop("ms_per_step"), higher_is_better=True, scaling="weak", vs_baseline=None,
+                    dtype="f16" if args.numerics == 0 else "mxfp4 (opt-in numerics: not the reference's arithmetic)",
                     data="synthetic", **head)
         if not args.no_cpu_baseline:
             base, _ = cpu_baseline(layer, tokens, args.seed, args.cpu_tokens)
@@ -624,6 +631,27 @@ def main():
             line["cpu_baseline"] = base
         else:
             line["cpu_baseline"] = None
+    if args.numerics == 2:
+        # what the opt-in mode costs in accuracy: a token sample against the checker that carries the reference's arithmetic
+        import torch as _t
+        from oco_b200 import moe as _moe
+        import oracle
+        cfg_name, dt = WORKLOADS[args.workload]
+        tk = args.tokens or dt
+        lay = synth.make_config(cfg_name, seed=args.seed)
+        xb, rb = synth.make_tokens(lay.hidden, tk, args.seed + 1000 * rank, "normal")
+        got, routing = _moe.run_layer(lay, xb, rb, numerics=2)
+        pick = np.unique(np.linspace(0, tk - 1, 8).astype(int))
+        ref = oracle.moe_forward(lay, xb[pick], rb[pick], mode=2, trace=False)
+        g = synth.bf16_bits_to_f32(got[pick]).astype(np.float64)
+        r = synth.bf16_bits_to_f32(ref.out).astype(np.float64)
+        moe_part = r - synth.bf16_bits_to_f32(rb[pick]).astype(np.float64)
+        if rank == 0:
+            line["parity"] = dict(ids_exact=bool(np.array_equal(routing["ids"][pick], ref.ids)),
+                                  rel_l2_vs_reference_arithmetic=float(np.linalg.norm(g - r) / np.linalg.norm(r)),
+                                  rel_l2_of_the_layer_term_alone=float(np.linalg.norm(g - r) / max(np.linalg.norm(moe_part), 1e-30)),
+                                  sample=f"{len(pick)} tokens against the CPU checker (reference arithmetic); the mode's own arithmetic "
+                                         "(the same quantised operands in float64) is held to 1e-3 by the GPU tests")
     if extras:
         # the HBM half of the metric: one token through the same layer (three launches replayed as a graph)
         dec = measure_layer(args, ctx, "gpt-oss-20b-decode", 200, 10)

@@ -73,6 +73,12 @@ typedef struct {
     float scale;            /* NEMOTRON: routed scaling factor */
     int32_t gemm_impl;      /* 0 = tcgen05 tiles (the product path); 1 = plain CUDA-core tiles, a
                                slow second implementation kept for cross-checking */
+    int32_t numerics;       /* 0 = the reference's arithmetic (half x half tiles, f32 single-token products; the default
+                               and the only mode whose results are held to the reference). 2 = GPT_OSS, rows > 1: the
+                               expert tiles run on the block-scaled FP4 tensor-core kind (tcgen05 kind::mxf4): MXFP4
+                               weights as stored, ACTIVATIONS quantised to MXFP4 (e2m1, one UE8M0 scale per 32 elements).
+                               Several times faster, and about 1e-1 relative L2 away from mode 0: an explicit trade the
+                               caller opts into, not a drop-in for the reference path. No counterpart in the reference. */
 } oco_moe_desc;
 
 /* Device pointers of one layer (reference `Experts{gate,up,down,router}`, src/weights/gpt_oss.rs:33-38;

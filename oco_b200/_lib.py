@@ -17,7 +17,7 @@ STATUS_NAMES = ["OK", "INVALID_ARGUMENT", "UNSUPPORTED_SHAPE", "CUDA_ERROR", "NC
 class Desc(C.Structure):
     _fields_ = [("arch", C.c_int32), ("hidden", C.c_int32), ("ffn", C.c_int32), ("experts", C.c_int32),
                 ("top_k", C.c_int32), ("shared_ffn", C.c_int32), ("weight_format", C.c_int32),
-                ("normalize", C.c_int32), ("scale", C.c_float), ("gemm_impl", C.c_int32)]
+                ("normalize", C.c_int32), ("scale", C.c_float), ("gemm_impl", C.c_int32), ("numerics", C.c_int32)]
 
 
 class Weights(C.Structure):

@@ -15,6 +15,7 @@
 #include "gemm.cuh"
 #include "gemm_wide.cuh"
 #include "mx.cuh"
+#include "gemm_mx.cuh"
 #include <cmath>
 #include "plan.cuh"
 #include "router.cuh"
@@ -59,6 +60,10 @@ struct Workspace {
     unsigned char* mx_actb = nullptr; //   each route's activations as e2m1 pieces [top_k][..], their scales,
     unsigned char* mx_actsfb = nullptr;
     uint32_t* mx_blk_arrivals = nullptr;   // and one counter per route and block of 32 activations
+    unsigned char* mxq_x = nullptr;   // numerics 2: expert-sorted input rows quantised to e2m1 [R][H / 2], their scale tiles,
+    unsigned char* mxq_xsf = nullptr;
+    unsigned char* mxq_act = nullptr; //   and the same for the activated rows [R][F / 2]
+    unsigned char* mxq_actsf = nullptr;
     uint16_t* host_x = nullptr;   // staging for the host-buffer entry point
     uint16_t* host_res = nullptr;
     size_t total = 0;
@@ -90,6 +95,7 @@ struct oco_moe_plan {
     // block-scaled single-token path (mx.cuh): usable once prepare_mx has built the tensor maps
     bool mx_ready = false, mx_on = false;    // OCO_MOE_TOKEN_MX=1 selects them (measured slower than the mma.sync kernels so far)
     CUtensorMap map_xs[kTileKinds], map_act[kTileKinds], map_xh[kTileKinds], map_mid[kTileKinds];
+    CUtensorMap map_mxq_x, map_mxq_act;   // numerics 2: the quantised rows as bytes
     // Per-phase timestamps (the counterpart of the reference's OCO_PROFILE counter heap,
     // src/gpu/profile.rs:1-31, src/gpu/dispatch.rs:189-208): one event before each kernel.
     cudaStream_t copy_stream = nullptr;   // oco_moe_forward_host: the residual rows' own stream
@@ -217,6 +223,13 @@ Workspace carve(const oco_moe_desc& d, int max_rows, unsigned char* base) {
         w.mx_actsfb = (unsigned char*)take(K * mx_sfb_bytes((uint32_t)(F / 32)));
         w.mx_blk_arrivals = (uint32_t*)take(K * (F / 32) * 4);
     }
+    if (d.numerics == 2) {
+        const size_t tiles128 = R / 128 + E + 1;
+        w.mxq_x = (unsigned char*)take(R * H / 2);
+        w.mxq_xsf = (unsigned char*)take(tiles128 * ((H / 32 + 7) / 8) * 1024);
+        w.mxq_act = (unsigned char*)take(R * F / 2);
+        w.mxq_actsf = (unsigned char*)take(tiles128 * ((F / 32 + 7) / 8) * 1024);
+    }
     w.host_x = (uint16_t*)take(T * H * 2);
     w.host_res = (uint16_t*)take(T * H * 2);
     w.total = off;
@@ -246,6 +259,27 @@ int make_row_map(oco_moe_plan* plan, CUtensorMap* map, void* base, uint64_t rows
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(plan, OCO_CUDA_ERROR, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return OCO_OK;
+}
+
+// The same over rows of bytes (e2m1 pairs): box 128 bytes x box_rows.
+int make_byte_map(oco_moe_plan* plan, CUtensorMap* map, void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+    static const EncodeTiledFn encode = [] {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            fn = nullptr;
+        return (EncodeTiledFn)fn;
+    }();
+    if (!encode) return fail(plan, OCO_CUDA_ERROR, "cuTensorMapEncodeTiled unavailable");
+    cuuint64_t dims[2] = {row_bytes, rows};
+    cuuint64_t strides[1] = {row_bytes};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(plan, OCO_CUDA_ERROR, "cuTensorMapEncodeTiled (byte rows) failed (%d)", (int)r);
     return OCO_OK;
 }
 
@@ -575,6 +609,57 @@ int stage_route(oco_moe_plan* plan, const uint16_t* x, int rows, cudaStream_t st
     return OCO_OK;
 }
 
+// Stage 2 in the opt-in block-scaled numerics (oco_moe_desc.numerics = 2): route plan with 128-route tiles,
+// the input rows gathered and quantised to MXFP4, up tiles on kind::mxf4 with the activation fused (half rows
+// out, as in the reference numerics), those rows quantised, down tiles on kind::mxf4.
+int stage_experts_mx(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, int R, int per_row, uint16_t* y, cudaStream_t st) {
+    const oco_moe_desc& d = plan->d;
+    Workspace& ws = plan->ws;
+    const int H = d.hidden, F = d.ffn, E = d.experts;
+    constexpr int NT = MxGemmShape::kNT;
+    plan->last_tile_rows = NT;
+    mark(plan, st, "route_plan");
+    route_plan_kernel<<<1, 1024, 0, st>>>(ids, (uint32_t)R, (uint32_t)E, (uint32_t)NT, ws.offsets, ws.row_of_route, ws.route_of_row,
+                                          ws.tiles, ws.tile_count);
+    const int max_tiles = R / NT + (E < R ? E : R);
+    mark(plan, st, "quantize_x");
+    mx_quantize_kernel<true><<<max_tiles, 256, 0, st>>>(x, ws.tiles, ws.tile_count, ws.offsets, ws.route_of_row, per_row, H, ws.mxq_x, ws.mxq_xsf);
+    plan->launches += 2;
+    CK(cudaGetLastError());
+    ALLOW_SMEM_ONCE((grouped_gemm_mx_kernel<kEpiSwigluF16>));
+    ALLOW_SMEM_ONCE((grouped_gemm_mx_kernel<kEpiDownBf16>));
+    auto envelope_end = [](const uint8_t* w, size_t rows, uint32_t stride, uint32_t len) {
+        return (const uint8_t*)(((uintptr_t)w + (rows - 1) * stride + len + 15) & ~(uintptr_t)15);
+    };
+    GemmParams up{};
+    up.w0 = plan->gate_rows; up.w1 = plan->up_rows; up.b0 = plan->gate_bias; up.b1 = plan->up_bias;
+    up.n = F; up.K = H; up.row_bytes = plan->up_row_stride; up.bias_stride = plan->up_bias_stride;
+    up.tiles = ws.tiles; up.tile_count = ws.tile_count; up.offsets = ws.offsets; up.route_of_row = nullptr;
+    up.out = ws.act; up.status = ws.status; up.tile_rows = NT; up.sfb = ws.mxq_xsf;
+    up.w0_end = envelope_end(plan->gate_rows, (size_t)E * F, plan->up_row_stride, plan->up_row_bytes);
+    up.w1_end = envelope_end(plan->up_rows, (size_t)E * F, plan->up_row_stride, plan->up_row_bytes);
+    mark(plan, st, "up_tiles");
+    {
+        const int feats = (F + 127) / 128, grid = std::min(plan->sm_count, feats * max_tiles);
+        grouped_gemm_mx_kernel<kEpiSwigluF16><<<grid, MxGemmShape::kThreads, MxGemmShape::kSmemBytes, st>>>(up, plan->map_mxq_x);
+    }
+    mark(plan, st, "quantize_act");
+    mx_quantize_kernel<false><<<max_tiles, 256, 0, st>>>(ws.act, ws.tiles, ws.tile_count, ws.offsets, nullptr, 1, F, ws.mxq_act, ws.mxq_actsf);
+    GemmParams dn{};
+    dn.w0 = plan->w.down_w; dn.b0 = plan->w.down_b; dn.n = H; dn.K = F; dn.row_bytes = plan->down_row_bytes; dn.bias_stride = 1;
+    dn.tiles = ws.tiles; dn.tile_count = ws.tile_count; dn.offsets = ws.offsets; dn.route_of_row = ws.route_of_row;
+    dn.out = y; dn.status = ws.status; dn.tile_rows = NT; dn.sfb = ws.mxq_actsf;
+    dn.w0_end = envelope_end(plan->w.down_w, (size_t)E * H, plan->down_row_bytes, plan->down_row_bytes);
+    mark(plan, st, "down_tiles");
+    {
+        const int feats = (H + 255) / 256, grid = std::min(plan->sm_count, feats * max_tiles);
+        grouped_gemm_mx_kernel<kEpiDownBf16><<<grid, MxGemmShape::kThreads, MxGemmShape::kSmemBytes, st>>>(dn, plan->map_mxq_act);
+    }
+    plan->launches += 3;
+    CK(cudaGetLastError());
+    return OCO_OK;
+}
+
 // Stage 2: expert products of R routes. Route i reads input row i / per_row of x (bf16) and goes
 // to expert ids[i]; its bf16 output lands in row i of y.
 template <int ARCH>
@@ -585,7 +670,7 @@ int stage_experts(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, in
     const oco_moe_desc& d = plan->d;
     Workspace& ws = plan->ws;
     const int H = d.hidden, F = d.ffn, E = d.experts;
-    if (FMT != OCO_FMT_Q4_K && R <= plan->batch_max_avg * E && !plan->no_batch_path &&
+    if (FMT != OCO_FMT_Q4_K && d.numerics == 0 && R <= plan->batch_max_avg * E && !plan->no_batch_path &&
         batch_smem_bytes(H / 32) <= kMaxDynamicSmem && batch_smem_bytes(F / 32) <= kMaxDynamicSmem) {
         // A few routes per expert: memory-bound, streamed with up to eight routes per MMA (batch.cuh).
         // (Layers too wide for the fragments to sit in shared memory take the tiles.)
@@ -623,6 +708,9 @@ int stage_experts(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, in
             CK(cudaGetLastError());
             return OCO_OK;
         }
+    }
+    if constexpr (ARCH == OCO_ARCH_GPT_OSS) {
+        if (d.numerics == 2) return stage_experts_mx(plan, x, ids, R, per_row, y, st);
     }
     const int nt_index = pick_tile_index(R, E, plan->narrow_tiles ? 192 : plan->wide_min_avg);
     const int NT = kTileSizes[nt_index];
@@ -794,6 +882,9 @@ int oco_moe_plan_create(const oco_moe_desc* desc, oco_moe_plan** out) {
     if (d.hidden % 32 || d.ffn % 32) return fail(plan, OCO_UNSUPPORTED_SHAPE, "hidden and ffn must be multiples of 32");
     if (d.shared_ffn && d.arch != OCO_ARCH_NEMOTRON) return fail(plan, OCO_UNSUPPORTED_SHAPE, "shared expert only with NEMOTRON");
     if (d.gemm_impl != 0 && d.gemm_impl != 1) return fail(plan, OCO_INVALID_ARGUMENT, "gemm_impl must be 0 or 1");
+    if (d.numerics != 0 && d.numerics != 2) return fail(plan, OCO_INVALID_ARGUMENT, "numerics must be 0 (reference) or 2 (MXFP4 activations)");
+    if (d.numerics == 2 && (d.arch != OCO_ARCH_GPT_OSS || d.gemm_impl != 0 || d.hidden % 32 || d.ffn % 32))
+        return fail(plan, OCO_UNSUPPORTED_SHAPE, "numerics 2 runs the MXFP4 family on the tensor-core tiles only");
     plan->up_row_bytes = packed_row_bytes(d.weight_format, d.hidden);
     plan->down_row_bytes = packed_row_bytes(d.weight_format, d.ffn);
     if (d.shared_ffn) {
@@ -880,6 +971,12 @@ int oco_moe_bind_workspace(oco_moe_plan* plan, void* workspace, size_t bytes, in
             rc = make_row_map(plan, &plan->map_mid[i], ws.mid, max_rows, d.shared_ffn, kTileSizes[i]);
             if (rc) return rc;
         }
+    }
+    if (d.numerics == 2) {
+        int rc = make_byte_map(plan, &plan->map_mxq_x, ws.mxq_x, R, (uint64_t)d.hidden / 2, 128);
+        if (rc) return rc;
+        rc = make_byte_map(plan, &plan->map_mxq_act, ws.mxq_act, R, (uint64_t)d.ffn / 2, 128);
+        if (rc) return rc;
     }
     CK(cudaDeviceSynchronize());
     int dev = 0, sms = 0;

@@ -56,6 +56,7 @@ struct GemmParams {
     int tile_rows;       // NT
     const uint8_t* w0_end;  // first byte past the 16-byte-aligned envelope of w0 / w1 (wide kernel)
     const uint8_t* w1_end;
+    const unsigned char* sfb;  // block-scaled kernel: the B rows' scale tiles, [tile][K group][1024]
 };
 
 // ---- operand order ---------------------------------------------------------------------------------

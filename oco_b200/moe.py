@@ -63,10 +63,10 @@ class _Plan:
     """Owns the C plan object, its workspace and the bound weights."""
 
     def __init__(self, arch, hidden, ffn, experts, top_k, fmt, shared_ffn=0, normalize=False, scale=1.0,
-                 gemm_impl=0):
+                 gemm_impl=0, numerics=0):
         self.desc = _lib.Desc(arch=arch, hidden=hidden, ffn=ffn, experts=experts, top_k=top_k,
                               shared_ffn=shared_ffn, weight_format=fmt, normalize=int(bool(normalize)),
-                              scale=float(scale), gemm_impl=gemm_impl)
+                              scale=float(scale), gemm_impl=gemm_impl, numerics=numerics)
         self.handle = C.c_void_p()
         rc = _lib.lib().oco_moe_plan_create(C.byref(self.desc), C.byref(self.handle))
         if rc != _lib.OK:
@@ -145,8 +145,8 @@ class ExpertPlan(_Plan):
 
     @classmethod
     def new(cls, hidden: int, ffn_width: int, experts: int = EXPERT_COUNT, active: int = ACTIVE_EXPERTS,
-            gemm_impl: int = 0) -> "ExpertPlan":
-        return cls(synth.ARCH_GPT_OSS, hidden, ffn_width, experts, active, synth.FMT_MXFP4, gemm_impl=gemm_impl)
+            gemm_impl: int = 0, numerics: int = 0) -> "ExpertPlan":
+        return cls(synth.ARCH_GPT_OSS, hidden, ffn_width, experts, active, synth.FMT_MXFP4, gemm_impl=gemm_impl, numerics=numerics)
 
     def width(self) -> int:
         return self.desc.ffn
@@ -316,9 +316,9 @@ class Bindings:
         self._run(w, plan, routing, residual, rows)
 
 
-def plan_for(layer: synth.Layer, gemm_impl: int = 0) -> _Plan:
+def plan_for(layer: synth.Layer, gemm_impl: int = 0, numerics: int = 0) -> _Plan:
     if layer.arch == synth.ARCH_GPT_OSS:
-        return ExpertPlan.new(layer.hidden, layer.ffn, layer.experts, layer.top_k, gemm_impl)
+        return ExpertPlan.new(layer.hidden, layer.ffn, layer.experts, layer.top_k, gemm_impl, numerics)
     if layer.arch == synth.ARCH_NEMOTRON:
         return ReluExpertPlan.new(layer.hidden, layer.ffn, layer.shared_ffn, layer.experts, layer.top_k,
                                   layer.normalize, layer.scale, gemm_impl)
@@ -326,12 +326,12 @@ def plan_for(layer: synth.Layer, gemm_impl: int = 0) -> _Plan:
 
 
 def run_layer(layer: synth.Layer, x_bits: np.ndarray, residual_bits: np.ndarray, gemm_impl: int = 0,
-              device="cuda", state: Optional[dict] = None, misalign: int = 0, interleaved: bool = False):
+              device="cuda", state: Optional[dict] = None, misalign: int = 0, interleaved: bool = False, numerics: int = 0):
     """Convenience used by tests and the benchmark: uploads (or reuses) a layer, runs it on bf16
     bit patterns given as uint16 arrays and returns (residual bits, routing dict)."""
     state = state if state is not None else {}
     if "plan" not in state:
-        state["plan"] = plan_for(layer, gemm_impl)
+        state["plan"] = plan_for(layer, gemm_impl, numerics)
         state["weights"] = _Weights.from_layer(layer, device, misalign, interleaved)
     plan, w = state["plan"], state["weights"]
     rows = x_bits.shape[0]

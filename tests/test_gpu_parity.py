@@ -630,3 +630,62 @@ def test_expert_shard_with_fewer_experts_than_routes_per_token(moe, oracle):
     bad = moe._Plan(synth.ARCH_NEMOTRON, H, F, E, K, synth.FMT_Q4_0, normalize=True, scale=2.5)
     with pytest.raises(moe.OcoError):
         bad.bind(moe._Weights.from_layer(layer))
+
+
+
+# ---- opt-in block-scaled numerics (numerics = 2): MXFP4 activations on tcgen05 kind::mxf4 ---------------
+def _swiglu(gate, up):
+    g = np.minimum(gate, 7.0)
+    u = np.clip(up, -6.0, 8.0)
+    return g / (1.0 + np.exp(-1.702 * g)) * u
+
+
+@pytest.mark.parametrize("hidden,ffn,experts,top_k,tokens", [(256, 256, 4, 2, 300), (320, 288, 8, 2, 700), (96, 96, 4, 2, 200),
+                                                              (640, 384, 32, 4, 40)], ids=["k256", "k320", "k96", "sparse"])
+def test_block_scaled_numerics_match_their_own_arithmetic(moe, oracle, hidden, ffn, experts, top_k, tokens):
+    """The opt-in mode multiplies MXFP4 weights with MXFP4-quantised activations. Its results are held to a
+    checker that multiplies THE SAME quantised operands in float64 (both stages, each fed what the GPU fed
+    it), and the distance to the reference arithmetic is printed beside it: the price of the mode."""
+    from tests import mxq
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, hidden, ffn, experts, top_k, synth.FMT_MXFP4, seed=hidden + tokens)
+    x, res = synth.make_tokens(hidden, tokens, 3, "normal")
+    out, routing = moe.run_layer(layer, x, res, numerics=2)
+    ref = oracle.moe_forward(layer, x, res, mode=2)
+    assert np.array_equal(routing["ids"], ref.ids) and np.array_equal(routing["prob"].view(np.uint32), ref.probs.view(np.uint32))
+    offsets, row_of_route, route_of_row = oracle.permutation(ref.ids, experts)
+    assert np.array_equal(routing["row_of_route"], row_of_route)
+    ids = ref.ids.reshape(-1)
+    E, F, H = experts, ffn, hidden
+    deq = lambda w, rows, k: oracle.dequant(synth.FMT_MXFP4, w.reshape(rows, -1), rows * k).reshape(rows, k).astype(np.float64)
+    gate_w, up_w, down_w = deq(layer.gate_w, E * F, H).reshape(E, F, H), deq(layer.up_w, E * F, H).reshape(E, F, H), deq(layer.down_w, E * H, F).reshape(E, H, F)
+    bf = lambda a: synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(np.asarray(a, np.float32))).astype(np.float64)
+    xq = mxq.quantize_dequantize(synth.bf16_bits_to_f32(x))                     # [T, H]
+    act_gpu = routing["act"].view(np.float16)[row_of_route]                      # route order, element order
+    y_gpu = synth.bf16_bits_to_f32(routing["y"]).astype(np.float64)
+    act_ref = np.empty((ids.size, F)); y_ref = np.empty((ids.size, H))
+    actq_gpu = mxq.quantize_dequantize(act_gpu.astype(np.float32))              # what the GPU's down tiles multiplied
+    for r, e in enumerate(ids):
+        xr = xq[r // top_k]
+        g = gate_w[e] @ xr + bf(layer.gate_b[e])
+        u = up_w[e] @ xr + bf(layer.up_b[e] + np.float32(1.0))
+        act_ref[r] = _swiglu(g, u)
+        y_ref[r] = down_w[e] @ actq_gpu[r] + bf(layer.down_b[e])
+    rel = lambda a, b: np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30)
+    err_act, err_y = rel(act_gpu.astype(np.float64), act_ref.astype(np.float16).astype(np.float64)), rel(y_gpu, bf(y_ref))
+    ref_out = synth.bf16_bits_to_f32(ref.out).astype(np.float64)
+    away = rel(synth.bf16_bits_to_f32(out).astype(np.float64), ref_out)
+    print(f"numerics 2, hidden {hidden}: act rel-L2 {err_act:.2e}, expert outputs {err_y:.2e} against the same quantised operands; "
+          f"layer output {away:.2e} away from the reference arithmetic")
+    assert err_act <= REL_L2 and err_y <= REL_L2   # both sides rounded to the stored type (half rows, bf16 rows)
+    got = oracle.moe_sum(routing["y"], ref.probs, res, top_k)
+    assert np.array_equal(got, out), "combine of the mode's expert outputs"
+    assert away < 0.5
+
+
+def test_block_scaled_numerics_are_refused_where_they_do_not_apply(moe):
+    from oco_b200 import _lib
+    with pytest.raises(moe.OcoError) as e:
+        moe._Plan(synth.ARCH_QWEN, 512, 256, 16, 4, synth.FMT_Q4_K, numerics=2)
+    assert e.value.code == _lib.UNSUPPORTED_SHAPE
+    with pytest.raises(moe.OcoError):
+        moe._Plan(synth.ARCH_GPT_OSS, 512, 256, 16, 4, synth.FMT_MXFP4, numerics=1)
