@@ -37,9 +37,9 @@ struct MxGemmShape {
     static constexpr int kThreads = 18 * 32;
     static constexpr int kATile = 128 * 128;          // 128 rows x 128 bytes (256 e2m1)
     static constexpr int kAStage = 2 * kATile + 2 * 1024;   // both A tiles, then their scale tiles (two 512-byte tiles each)
-    static constexpr int kAStages = 2;
+    static constexpr int kAStages = 3;
     static constexpr int kBStage = kNT * 128 + 1024;  // the B tile, then its scales
-    static constexpr int kBStages = 3;
+    static constexpr int kBStages = 2;
     static constexpr int kRingStages = 2;
     static constexpr int kRingWarp = kRingStages * 16 * kMxSlot;
     static constexpr int kRing = kProducerWarps * kRingWarp;
