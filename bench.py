@@ -221,7 +221,10 @@ class _Replayed:
 
 def run_expert_parallel(args, torch, dist, world, rank, local, workload, steps, warmup, with_cpu=False):
     """Experts sharded over the ranks, the batch split evenly between them (its total is fixed as N
-    grows), dispatch and combine as all-to-all over NCCL. Returns rank 0's record (None elsewhere)."""
+    grows). The timed step is oco_b200.ep.forward_window: the expert stage gathers token rows from
+    the peers' memory and stores route outputs into it, two small collectives order the ranks. The
+    all-to-all form of the same layer (ep.forward) is timed beside it. Returns rank 0's record
+    (None elsewhere)."""
     from oco_b200 import ep
     cfg, default_tokens = WORKLOADS[workload]
     total = (args.tokens if workload == args.workload and args.tokens else default_tokens)
@@ -232,16 +235,24 @@ def run_expert_parallel(args, torch, dist, world, rank, local, workload, steps, 
     E, K, H, F = layer.experts, layer.top_k, layer.hidden, layer.ffn
     be = ep.CudaBackend(layer, rank, world, max_rows=T)
     backend = be.backend()
+    win = ep.Windows(H, K, T)
     x_all, res_all = synth.make_tokens(H, total, args.seed, "normal")
     x_bits, res_bits = x_all[rank * T:(rank + 1) * T], res_all[rank * T:(rank + 1) * T]
     hx = torch.from_numpy(x_bits.view(np.int16).copy()).pin_memory()
     hres = torch.from_numpy(res_bits.view(np.int16).copy()).pin_memory()
-    x, res = hx.cuda(), hres.cuda()
+    x, res = win.x_local[:T], hres.cuda()
+    x.copy_(hx)
     stream = torch.cuda.current_stream()
+
+    def step_window(timings=None):
+        ep.forward_window(x, res, be, win, timings=timings)
+
+    def step_all_to_all(exchange=None):
+        ep.forward(x, res, backend, E, exchange=exchange, uniform=True)
 
     # ---- parity of this rank's rows against the CPU checker (a token sample), before any timing ----
     import oracle
-    ep.forward(x, res, backend, E, uniform=True)
+    step_window()
     torch.cuda.synchronize()
     got = res.cpu().numpy().view(np.uint16)
     ids_gpu, _ = be.route(x)
@@ -260,14 +271,14 @@ def run_expert_parallel(args, torch, dist, world, rank, local, workload, steps, 
                   sample=f"{len(pick)} tokens per rank against the CPU checker; ids of all tokens; worst rank")
     res.copy_(hres)
 
-    def timed(n, exchange=None):
+    def timed(n, fn, count=lambda: be.launches()):
         dist.barrier(); torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(stream)
         launches = 0
         for _ in range(n):
-            ep.forward(x, res, backend, E, exchange=exchange, uniform=True)
-            launches += be.launches()
+            fn()
+            launches += count()
         b.record(stream)
         torch.cuda.synchronize(); dist.barrier()
         t = torch.tensor([a.elapsed_time(b) / n], device="cuda", dtype=torch.float64)
@@ -275,50 +286,60 @@ def run_expert_parallel(args, torch, dist, world, rank, local, workload, steps, 
         return float(t.item()), launches
 
     for _ in range(max(3, warmup)):
-        ep.forward(x, res, backend, E, uniform=True)
+        step_window()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start(); time.sleep(0.2)
-    ms_per_step, launches = timed(steps)
+    ms_per_step, launches = timed(steps, step_window)
     clocks = sampler.stop() if rank == 0 else {}
     clocks.pop("sm_mhz_all", None)
     be.router_plan.poll(); be.expert_plan.poll()
-    # the same step with the exchange replaced by device-local copies of what it delivered
-    rec = _Recorded(dist)
-    ep.forward(x, res, backend, E, exchange=rec)
-    ms_local, _ = timed(steps, exchange=_Replayed(rec.log))
     # per-stage times of single steps
     tm, acc = {}, {}
     be.expert_plan.set_profiling(True)
     for _ in range(min(5, steps)):
-        ep.forward(x, res, backend, E, timings=tm, uniform=True)
+        step_window(tm)
         for k, v in tm.items():
             acc.setdefault(k, []).append(v)
         for k, v in be.expert_plan.phase_times().items():
             acc.setdefault(k, []).append(v)
     be.expert_plan.set_profiling(False)
     phases = {k: float(np.mean(v)) for k, v in acc.items()}
-    routes_here = int(phases.pop("routes_received"))
-    # end to end: pinned host rows in, the layer, residual rows back
+    # routes this rank's shard owned (for the flop count of its tiles)
+    epr = E // world
+    ids_every = torch.empty(world * T * K, dtype=torch.int32, device="cuda")
+    dist.all_gather_into_tensor(ids_every, torch.from_numpy(ids_ref.astype(np.int32).reshape(-1)).cuda())
+    routes_here = int(((ids_every // epr) == rank).sum().item())
+    # the all-to-all form of the same layer, and the same with the exchange replaced by device-local copies
+    for _ in range(3):
+        step_all_to_all()
+    ms_a2a, _ = timed(steps, step_all_to_all)
+    rec = _Recorded(dist)
+    step_all_to_all(rec)
+    ms_local, _ = timed(steps, lambda: step_all_to_all(_Replayed(rec.log)))
+    # end to end: pinned host rows into the window slot, the layer, residual rows back
     e2e_steps = max(3, min(steps, 10))
     dist.barrier(); torch.cuda.synchronize()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         x.copy_(hx, non_blocking=True); res.copy_(hres, non_blocking=True)
-        ep.forward(x, res, backend, E, uniform=True)
+        step_window()
         hres.copy_(res, non_blocking=True)
         torch.cuda.synchronize()
     t = torch.tensor([1e3 * (time.perf_counter() - t0) / e2e_steps], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item())
-    del be, backend
+    x = None
+    win.close()
+    del be, backend, win
     torch.cuda.empty_cache()
     if rank != 0:
         return None
     peaks = measured_peaks()
     row_bytes = T * H * 2
     e2e = dict(value=total / (e2e_ms / 1e3), unit="tokens/s", ms_per_step=e2e_ms, h2d_bytes_per_step=2 * row_bytes,
-               d2h_bytes_per_step=row_bytes, api="oco_b200.ep.forward (pinned host rows in, residual rows back), per rank")
+               d2h_bytes_per_step=row_bytes,
+               api="oco_b200.ep.forward_window (pinned host rows into the rank's window slot, residual rows back), per rank")
     roofline = None
     if "up_tiles" in phases:
         flops = 2.0 * routes_here * 2 * F * H
@@ -329,16 +350,22 @@ def run_expert_parallel(args, torch, dist, world, rank, local, workload, steps, 
     base = None
     if with_cpu:
         base, _ = cpu_baseline(layer, total, args.seed, args.cpu_tokens)
+    remote = (world - 1) / world
     return dict(
         value=total / (ms_per_step / 1e3), unit="tokens/s", n_gpus=world, steps=steps, warmup=warmup, ms_per_step=ms_per_step,
         scaling="strong", dtype="f16",
         config=dict(workload=workload, tokens_total=total, tokens_per_gpu=T, hidden=H, ffn=F, experts=E, top_k=K,
                     weight_format="MXFP4", experts_per_gpu=E // world, parallelism=f"ep{world}",
+                    exchange="windows over peer memory: token rows gathered by the expert stage's own loads, outputs "
+                             "stored to their owners by the down tiles; one all-gather of ids and one one-word all-reduce",
                     cache="every step reads the rank's whole expert shard (%.0f MB), more than the 126 MB L2"
                           % (E // world * layer.expert_bytes() / 1e6)),
-        all_to_all=dict(exposed_ms=ms_per_step - ms_local, ms_per_step_with_local_copies=ms_local,
-                        dispatch_ms=phases.get("dispatch_ms"), combine_ms=phases.get("combine_a2a_ms"),
-                        route_bytes_each_way_per_gpu=T * K * H * 2),
+        peer_traffic=dict(rows_read_from_peers_bytes=int(routes_here * remote * H * 2),
+                          rows_stored_to_peers_bytes=int(routes_here * remote * H * 2),
+                          note="expected share (world - 1) / world of this shard's routes, each way"),
+        all_to_all_form=dict(ms_per_step=ms_a2a, ms_per_step_with_local_copies=ms_local, exposed_ms=ms_a2a - ms_local,
+                             route_bytes_each_way_per_gpu=T * K * H * 2,
+                             note="ep.forward: NCCL all_to_all_single each way, sort/gather/scatter in torch"),
         parity=parity, clocks=clocks, e2e=e2e, gpu_launches=launches, phases_ms=phases, roofline=roofline, cpu_baseline=base)
 
 
@@ -675,7 +702,7 @@ def main():
                                 dict(bf16_cublas_measured=mp["tflops"], f16_tcgen05_measured=pk["f16_tcgen05_tflops"],
                                      fp4_tcgen05_measured=pk["mxfp4_tcgen05_tflops"], fp4_nominal=FP4_NOMINAL_TFLOPS).items()}
         if world > 1:
-            # the configuration that shards: 128 experts over the ranks, all-to-all dispatch and combine; rank 0
+            # the configuration that shards: 128 experts over the ranks, rows through windows over peer memory; rank 0
             # also runs it alone first, for the strong-scaling reference on the same box
             n1 = None
             if rank == 0:
@@ -685,7 +712,6 @@ def main():
             epr = run_expert_parallel(args, torch, dist, world, rank, local, "gpt-oss-120b-prefill", 10, 3)
             if rank == 0:
                 epr["n1_ms_per_step_same_box"] = n1
-                epr["strong_scaling_efficiency"] = n1 / (world * epr["ms_per_step"]) if n1 else None
                 line["expert_parallel"] = epr
     if rank == 0:
         print(json.dumps(line))

@@ -41,7 +41,8 @@ typedef enum {
     OCO_UNSUPPORTED_SHAPE = 2,
     OCO_CUDA_ERROR = 3,
     OCO_NCCL_ERROR = 4,
-    OCO_DEVICE_TIMEOUT = 5
+    OCO_DEVICE_TIMEOUT = 5,
+    OCO_OUT_OF_MEMORY = 6
 } oco_status;
 
 /* Layer families. Each fixes the router, the activation and the combine rule:
@@ -272,6 +273,43 @@ int oco_moe_selftest_wait_timeout(oco_moe_plan* plan, long long wait_cycles, voi
  * M128 N256 on zero operands per SM, dense TFLOP/s in *tflops. Measurement support for the benchmark's
  * roofline fractions; allocates 256 bytes for the call's duration. No counterpart in the reference. */
 int oco_tensor_peak(int kind, int iters, float* tflops);
+
+/* Expert parallelism without a collective on the rows' way. The reference is single-device; nothing
+ * below has a counterpart in it.
+ *
+ * A window is one device address range of `world` slots, `slot_stride` bytes apart, slot g backed by
+ * `backed_bytes` of GPU g's memory (the rest of a slot is unmapped and must not be touched). Every
+ * rank creates its window with the same sizes, hands its descriptor (oco_ep_window_fd; a POSIX file
+ * descriptor of this process, to be passed over a Unix socket with SCM_RIGHTS) to each peer, and
+ * attaches the descriptors it receives. From then on base + g * slot_stride + offset addresses the
+ * same bytes of GPU g's slot on every rank, through plain loads and stores over NVLink.
+ * slot_stride must be a multiple of oco_ep_window_granularity. Set-up calls: they allocate and
+ * synchronise. oco_ep_window_error returns the calling thread's last message. */
+typedef struct oco_ep_window oco_ep_window;
+int oco_ep_window_granularity(size_t* bytes);
+int oco_ep_window_create(int rank, int world, size_t slot_stride, size_t backed_bytes, oco_ep_window** out);
+int oco_ep_window_fd(const oco_ep_window* window);
+int oco_ep_window_attach(oco_ep_window* window, int peer, int fd);
+void* oco_ep_window_base(const oco_ep_window* window);
+size_t oco_ep_window_stride(const oco_ep_window* window);
+size_t oco_ep_window_backed(const oco_ep_window* window);
+void oco_ep_window_destroy(oco_ep_window* window);
+const char* oco_ep_window_error(void);
+
+/* oco_moe_experts over routes numbered in a window. Route i of the call (0 <= i < routes) goes to
+ * expert expert_ids[i] of this plan; an id outside 0 .. experts-1 marks a route that belongs to
+ * another shard and is skipped. The route's label is (i / seg_routes) * seg_stride + i % seg_routes
+ * (seg_routes 0: i itself): its input is row label / routes_per_row of token_rows_bf16, its output
+ * lands in row label of y_bf16. With token rows in one window (slot stride seg_stride /
+ * routes_per_row rows) and outputs in another (slot stride seg_stride rows), source rank g's
+ * seg_routes routes are gathered from GPU g and answered into GPU g's memory by this one call.
+ * routes <= max_rows * top_k; expected_routes (0: all) is how many of them this shard expects to
+ * own, which picks the kernels. Ordering between ranks (inputs written before a peer reads them,
+ * outputs complete before their owner combines them) is the caller's, by collectives or events on
+ * the streams. */
+int oco_moe_experts_window(oco_moe_plan* plan, const uint16_t* token_rows_bf16, const uint32_t* expert_ids, int routes,
+                           int routes_per_row, int seg_routes, int seg_stride, int expected_routes, uint16_t* y_bf16,
+                           void* cuda_stream);
 
 const char* oco_moe_version(void);
 

@@ -10,8 +10,8 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liboco_moe.so")
 
-OK, INVALID_ARGUMENT, UNSUPPORTED_SHAPE, CUDA_ERROR, NCCL_ERROR, DEVICE_TIMEOUT = range(6)
-STATUS_NAMES = ["OK", "INVALID_ARGUMENT", "UNSUPPORTED_SHAPE", "CUDA_ERROR", "NCCL_ERROR", "DEVICE_TIMEOUT"]
+OK, INVALID_ARGUMENT, UNSUPPORTED_SHAPE, CUDA_ERROR, NCCL_ERROR, DEVICE_TIMEOUT, OUT_OF_MEMORY = range(7)
+STATUS_NAMES = ["OK", "INVALID_ARGUMENT", "UNSUPPORTED_SHAPE", "CUDA_ERROR", "NCCL_ERROR", "DEVICE_TIMEOUT", "OUT_OF_MEMORY"]
 
 
 class Desc(C.Structure):
@@ -69,6 +69,17 @@ SIGNATURES = {
     "oco_cuda_event_elapsed_ms": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_float)]),
     "oco_moe_selftest_wait_timeout": (C.c_int, [C.c_void_p, C.c_longlong, C.c_void_p]),
     "oco_tensor_peak": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_float)]),
+    "oco_ep_window_granularity": (C.c_int, [C.POINTER(C.c_size_t)]),
+    "oco_ep_window_create": (C.c_int, [C.c_int, C.c_int, C.c_size_t, C.c_size_t, C.POINTER(C.c_void_p)]),
+    "oco_ep_window_fd": (C.c_int, [C.c_void_p]),
+    "oco_ep_window_attach": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
+    "oco_ep_window_base": (C.c_void_p, [C.c_void_p]),
+    "oco_ep_window_stride": (C.c_size_t, [C.c_void_p]),
+    "oco_ep_window_backed": (C.c_size_t, [C.c_void_p]),
+    "oco_ep_window_destroy": (None, [C.c_void_p]),
+    "oco_ep_window_error": (C.c_char_p, []),
+    "oco_moe_experts_window": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                         C.c_void_p, C.c_void_p]),
     "oco_moe_version": (C.c_char_p, []),
 }
 

@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "liboco_moe.so")
-SOURCES = ["api.cu", "route_static.cu", "peaks.cu"]
+SOURCES = ["api.cu", "route_static.cu", "peaks.cu", "window.cu"]
 HEADERS = ["common.cuh", "router.cuh", "plan.cuh", "decode.cuh", "batch.cuh", "gemm.cuh", "gemm_wide.cuh", "mx.cuh", "mx_pieces.cuh", "gemm_mx.cuh",
            "../../include/oco_moe.h"]
 

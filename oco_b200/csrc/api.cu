@@ -39,6 +39,7 @@ struct Workspace {
     uint32_t* tiles = nullptr;
     uint32_t* row_of_route = nullptr;
     uint32_t* route_of_row = nullptr;
+    uint32_t* chunk_cnt = nullptr;   // many-CTA route plan: per chunk of 1024 routes, the count per expert
     uint16_t* xs = nullptr;       // half [R, H] expert-sorted input rows
     uint16_t* act = nullptr;      // half [R, F] expert-sorted activated rows
     uint16_t* y = nullptr;        // bf16 [R, H] expert outputs, route order
@@ -103,6 +104,7 @@ struct oco_moe_plan {
     bool no_batch_path = false;  // OCO_MOE_NO_BATCH=1: few tokens take the tile kernels too
     int batch_max_avg = 8;       // routes per expert (on average) up to which the streamed few-token kernels run
                                  // (measured: they win up to 16-32 at the gpt-oss shapes; OCO_MOE_BATCH_MAX_AVG overrides)
+    int route_plan_single_max = 2048;   // routes up to which one CTA makes the route plan (OCO_MOE_ROUTE_PLAN_SINGLE_MAX)
     int wide_min_avg = 1;        // OCO_MOE_WIDE_MIN_AVG: routes per expert from which layers take the 256-route tiles
     int router_block_min = 512;  // OCO_MOE_ROUTER_BLOCK_MIN: rows from which the register-blocked router kernel runs
     bool narrow_tiles = false;   // OCO_MOE_NARROW_TILES=1: keep the generic tile kernel for 256-route tiles too
@@ -195,6 +197,7 @@ Workspace carve(const oco_moe_desc& d, int max_rows, unsigned char* base) {
     w.tiles = (uint32_t*)take(2 * (R / 8 + E + 1) * 4);
     w.row_of_route = (uint32_t*)take(R * 4);
     w.route_of_row = (uint32_t*)take(R * 4);
+    w.chunk_cnt = (uint32_t*)take(((R + 1023) / 1024) * E * 4);
     w.xs = (uint16_t*)take(R * H * 2);
     w.act = (uint16_t*)take(R * F * 2);
     w.y = (uint16_t*)take(R * H * 2);
@@ -609,22 +612,48 @@ int stage_route(oco_moe_plan* plan, const uint16_t* x, int rows, cudaStream_t st
     return OCO_OK;
 }
 
+// How the routes handed to the expert stage are numbered outside it. Route i of the call is labelled
+// (i / seg_len) * seg_stride + i % seg_len (seg_len 0: i): its input row is label / per_row, its output
+// row is label. `expected` (0: all of them) says how many of the routes carry an expert of this plan,
+// for the choice of kernels; the others (ids >= experts) get no row.
+struct RouteSpace {
+    uint32_t seg_len = 0, seg_stride = 0;
+    int expected = 0;
+};
+
+// The route plan: one CTA for a few passes' worth of routes, else three many-CTA launches.
+void launch_route_plan(oco_moe_plan* plan, const uint32_t* ids, int R, int E, int tile_rows, const RouteSpace& rs, cudaStream_t st) {
+    Workspace& ws = plan->ws;
+    mark(plan, st, "route_plan");
+    if (R <= plan->route_plan_single_max) {
+        route_plan_kernel<<<1, 1024, 0, st>>>(ids, (uint32_t)R, (uint32_t)E, (uint32_t)tile_rows, ws.offsets, ws.row_of_route,
+                                              ws.route_of_row, ws.tiles, ws.tile_count, rs.seg_len, rs.seg_stride);
+        plan->launches++;
+        return;
+    }
+    const uint32_t chunks = ((uint32_t)R + 1023u) / 1024u;
+    route_count_kernel<<<chunks, 1024, 0, st>>>(ids, (uint32_t)R, (uint32_t)E, ws.row_of_route, ws.chunk_cnt);
+    route_scan_kernel<<<1, 1024, 0, st>>>(chunks, (uint32_t)E, (uint32_t)tile_rows, ws.chunk_cnt, ws.offsets, ws.tiles, ws.tile_count);
+    route_scatter_kernel<<<chunks, 1024, 0, st>>>(ids, (uint32_t)R, (uint32_t)E, ws.chunk_cnt, ws.offsets, rs.seg_len, rs.seg_stride,
+                                                  ws.row_of_route, ws.route_of_row);
+    plan->launches += 3;
+}
+
 // Stage 2 in the opt-in block-scaled numerics (oco_moe_desc.numerics = 2): route plan with 128-route tiles,
 // the input rows gathered and quantised to MXFP4, up tiles on kind::mxf4 with the activation fused (half rows
 // out, as in the reference numerics), those rows quantised, down tiles on kind::mxf4.
-int stage_experts_mx(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, int R, int per_row, uint16_t* y, cudaStream_t st) {
+int stage_experts_mx(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, int R, int per_row, uint16_t* y, cudaStream_t st,
+                     const RouteSpace& rs) {
     const oco_moe_desc& d = plan->d;
     Workspace& ws = plan->ws;
     const int H = d.hidden, F = d.ffn, E = d.experts;
     constexpr int NT = MxGemmShape::kNT;
     plan->last_tile_rows = NT;
-    mark(plan, st, "route_plan");
-    route_plan_kernel<<<1, 1024, 0, st>>>(ids, (uint32_t)R, (uint32_t)E, (uint32_t)NT, ws.offsets, ws.row_of_route, ws.route_of_row,
-                                          ws.tiles, ws.tile_count);
+    launch_route_plan(plan, ids, R, E, NT, rs, st);
     const int max_tiles = R / NT + (E < R ? E : R);
     mark(plan, st, "quantize_x");
     mx_quantize_kernel<true><<<max_tiles, 256, 0, st>>>(x, ws.tiles, ws.tile_count, ws.offsets, ws.route_of_row, per_row, H, ws.mxq_x, ws.mxq_xsf);
-    plan->launches += 2;
+    plan->launches += 1;
     CK(cudaGetLastError());
     ALLOW_SMEM_ONCE((grouped_gemm_mx_kernel<kEpiSwigluF16>));
     ALLOW_SMEM_ONCE((grouped_gemm_mx_kernel<kEpiDownBf16>));
@@ -664,26 +693,25 @@ int stage_experts_mx(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids,
 // to expert ids[i]; its bf16 output lands in row i of y.
 template <int ARCH>
 int stage_experts(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, int R, int per_row, uint16_t* y,
-                  cudaStream_t st) {
+                  cudaStream_t st, const RouteSpace& rs = RouteSpace()) {
     constexpr int FMT = Family<ARCH>::kFmt;
     constexpr int EPI_UP = Family<ARCH>::kEpiUp;
     const oco_moe_desc& d = plan->d;
     Workspace& ws = plan->ws;
     const int H = d.hidden, F = d.ffn, E = d.experts;
-    if (FMT != OCO_FMT_Q4_K && d.numerics == 0 && R <= plan->batch_max_avg * E && !plan->no_batch_path &&
+    const int live = rs.expected > 0 && rs.expected < R ? rs.expected : R;   // routes expected to carry this plan's experts
+    if (FMT != OCO_FMT_Q4_K && d.numerics == 0 && live <= plan->batch_max_avg * E && (rs.expected == 0 || R <= 64 * E) && !plan->no_batch_path &&
         batch_smem_bytes(H / 32) <= kMaxDynamicSmem && batch_smem_bytes(F / 32) <= kMaxDynamicSmem) {
         // A few routes per expert: memory-bound, streamed with up to eight routes per MMA (batch.cuh).
         // (Layers too wide for the fragments to sit in shared memory take the tiles.)
         if constexpr (FMT != OCO_FMT_Q4_K) {
             plan->last_tile_rows = kBatchCols;
-            mark(plan, st, "route_plan");
-            route_plan_kernel<<<1, 1024, 0, st>>>(ids, (uint32_t)R, (uint32_t)E, (uint32_t)kBatchCols, ws.offsets,
-                                                  ws.row_of_route, ws.route_of_row, ws.tiles, ws.tile_count);
+            launch_route_plan(plan, ids, R, E, kBatchCols, rs, st);
             const int groups = (int)batch_max_groups((size_t)R, (size_t)E);
             mark(plan, st, "fragments");
             batch_fragments_kernel<<<groups, 256, 0, st>>>(x, ws.tiles, ws.tile_count, ws.offsets, ws.route_of_row, per_row,
                                                            H, reinterpret_cast<uint4*>(ws.bfrag_in));
-            plan->launches += 2;
+            plan->launches += 1;
             const int parts = std::max(1, std::min(8, (4 * plan->sm_count + groups - 1) / groups));
             ALLOW_SMEM_ONCE((batch_rows_kernel<FMT, EPI_UP>));
             ALLOW_SMEM_ONCE((batch_rows_kernel<FMT, kEpiDownBf16>));
@@ -710,17 +738,15 @@ int stage_experts(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, in
         }
     }
     if constexpr (ARCH == OCO_ARCH_GPT_OSS) {
-        if (d.numerics == 2) return stage_experts_mx(plan, x, ids, R, per_row, y, st);
+        if (d.numerics == 2) return stage_experts_mx(plan, x, ids, R, per_row, y, st, rs);
     }
-    const int nt_index = pick_tile_index(R, E, plan->narrow_tiles ? 192 : plan->wide_min_avg);
+    const int nt_index = pick_tile_index(live, E, plan->narrow_tiles ? 192 : plan->wide_min_avg);
     const int NT = kTileSizes[nt_index];
     plan->last_tile_rows = NT;
-    mark(plan, st, "route_plan");
-    route_plan_kernel<<<1, 1024, 0, st>>>(ids, (uint32_t)R, (uint32_t)E, (uint32_t)NT, ws.offsets, ws.row_of_route,
-                                          ws.route_of_row, ws.tiles, ws.tile_count);
-    plan->launches++;
+    launch_route_plan(plan, ids, R, E, NT, rs, st);
     mark(plan, st, "permute");
-    permute_rows_kernel<<<R, 256, 0, st>>>(x, ws.route_of_row, per_row, H, FMT == OCO_FMT_Q4_K ? 32 : 16, ws.xs);
+    permute_rows_kernel<<<std::min(R, 16 * plan->sm_count), 256, 0, st>>>(x, ws.route_of_row, per_row, H, FMT == OCO_FMT_Q4_K ? 32 : 16, ws.xs,
+                                                                        (uint32_t)R, ws.offsets + E);
     plan->launches++;
     CK(cudaGetLastError());
     const int max_tiles = R / NT + (E < R ? E : R);
@@ -781,7 +807,8 @@ int forward_tiled(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int
         // residual as a bf16 add ahead of the routed sum (compute/nemotron.rs:302-316).
         const int S = d.shared_ffn;
         mark(plan, st, "shared_expert");
-        permute_rows_kernel<<<rows, 256, 0, st>>>(x, nullptr, 1, H, FMT == OCO_FMT_Q4_K ? 32 : 16, ws.xh);  // identity gather
+        permute_rows_kernel<<<std::min(rows, 16 * plan->sm_count), 256, 0, st>>>(x, nullptr, 1, H, FMT == OCO_FMT_Q4_K ? 32 : 16, ws.xh,
+                                                                              (uint32_t)rows, nullptr);  // identity gather
         plan->launches++;
         const int snt = pick_tile_index(rows, 1, plan->narrow_tiles ? 192 : plan->wide_min_avg);
         const int SNT = kTileSizes[snt];
@@ -896,6 +923,7 @@ int oco_moe_plan_create(const oco_moe_desc* desc, oco_moe_plan** out) {
     { const char* e = getenv("OCO_MOE_ROUTER_BLOCK_MIN"); if (e && atoi(e) > 0) plan->router_block_min = atoi(e); }
     { const char* e = getenv("OCO_MOE_NO_BATCH"); plan->no_batch_path = e && e[0] == '1'; }
     { const char* e = getenv("OCO_MOE_TOKEN_MX"); plan->mx_on = e && e[0] == '1'; }
+    { const char* e = getenv("OCO_MOE_ROUTE_PLAN_SINGLE_MAX"); if (e && atoi(e) >= 0) plan->route_plan_single_max = atoi(e); }
     { const char* e = getenv("OCO_MOE_BATCH_MAX_AVG"); if (e && atoi(e) > 0) plan->batch_max_avg = atoi(e) < 64 ? atoi(e) : 64; }
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) == cudaSuccess &&
@@ -1121,6 +1149,35 @@ int oco_moe_experts(oco_moe_plan* plan, const uint16_t* rows_bf16, const uint32_
         case OCO_ARCH_GPT_OSS: rc = stage_experts<OCO_ARCH_GPT_OSS>(plan, rows_bf16, expert_ids, routes, 1, y_bf16, st); break;
         case OCO_ARCH_NEMOTRON: rc = stage_experts<OCO_ARCH_NEMOTRON>(plan, rows_bf16, expert_ids, routes, 1, y_bf16, st); break;
         default: rc = stage_experts<OCO_ARCH_QWEN>(plan, rows_bf16, expert_ids, routes, 1, y_bf16, st); break;
+    }
+    mark(plan, st, "end");
+    return rc;
+}
+
+int oco_moe_experts_window(oco_moe_plan* plan, const uint16_t* token_rows_bf16, const uint32_t* expert_ids, int routes,
+                           int routes_per_row, int seg_routes, int seg_stride, int expected_routes, uint16_t* y_bf16,
+                           void* cuda_stream) {
+    if (!plan) return OCO_INVALID_ARGUMENT;
+    if (!plan->have_ws || !plan->have_experts) return fail(plan, OCO_INVALID_ARGUMENT, "bind a workspace and expert weights first");
+    if (int rc_dev = check_device(plan)) return rc_dev;
+    if (routes == 0) return OCO_OK;
+    if (!token_rows_bf16 || !expert_ids || !y_bf16 || routes < 0 || routes > plan->max_rows * plan->d.top_k)
+        return fail(plan, OCO_INVALID_ARGUMENT, "bad buffers, or more routes than max_rows * top_k");
+    if (routes_per_row < 1 || seg_routes < 0 || expected_routes < 0 || (seg_routes && seg_stride < seg_routes) ||
+        (seg_routes && seg_stride % routes_per_row))
+        return fail(plan, OCO_INVALID_ARGUMENT, "bad route numbering: the segment stride must hold a segment and whole token rows");
+    if (seg_routes && ((uint64_t)((routes - 1) / seg_routes) * (uint64_t)seg_stride + (uint64_t)seg_routes) > 0xffffffffull)
+        return fail(plan, OCO_UNSUPPORTED_SHAPE, "route labels exceed 32 bits");
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    plan->launches = 0;
+    plan->n_marks = 0;
+    RouteSpace rs;
+    rs.seg_len = (uint32_t)seg_routes; rs.seg_stride = (uint32_t)seg_stride; rs.expected = expected_routes ? expected_routes : routes;
+    int rc;
+    switch (plan->d.arch) {
+        case OCO_ARCH_GPT_OSS: rc = stage_experts<OCO_ARCH_GPT_OSS>(plan, token_rows_bf16, expert_ids, routes, routes_per_row, y_bf16, st, rs); break;
+        case OCO_ARCH_NEMOTRON: rc = stage_experts<OCO_ARCH_NEMOTRON>(plan, token_rows_bf16, expert_ids, routes, routes_per_row, y_bf16, st, rs); break;
+        default: rc = stage_experts<OCO_ARCH_QWEN>(plan, token_rows_bf16, expert_ids, routes, routes_per_row, y_bf16, st, rs); break;
     }
     mark(plan, st, "end");
     return rc;

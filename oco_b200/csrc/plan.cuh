@@ -4,6 +4,8 @@
 
 namespace oco {
 
+__device__ __forceinline__ uint32_t route_label(uint32_t i, uint32_t seg_len, uint32_t seg_stride);
+
 // Stable counting sort of route indices by expert id, by one CTA of 1024 threads.
 //
 // Produces what the reference's route plan encodes (route_plan_tiled, shaders/experts/routing.metal:4-39;
@@ -20,7 +22,8 @@ __global__ void __launch_bounds__(1024) route_plan_kernel(const uint32_t* __rest
                                                           uint32_t* __restrict__ row_of_route,
                                                           uint32_t* __restrict__ route_of_row,
                                                           uint32_t* __restrict__ tiles,
-                                                          uint32_t* __restrict__ tile_count) {
+                                                          uint32_t* __restrict__ tile_count, uint32_t seg_len = 0,
+                                                          uint32_t seg_stride = 0) {
     __shared__ uint32_t running[kMaxExperts];
     __shared__ uint32_t warp_cnt[32][kMaxExperts];
     __shared__ uint32_t soff[kMaxExperts + 1];
@@ -71,29 +74,142 @@ __global__ void __launch_bounds__(1024) route_plan_kernel(const uint32_t* __rest
         if (e < E) {
             uint32_t row = soff[e] + row_of_route[i];
             row_of_route[i] = row;
-            route_of_row[row] = i;
+            route_of_row[row] = route_label(i, seg_len, seg_stride);
         }
     }
+}
+
+// The same plan made by many CTAs, for route counts where one CTA's serial passes would dominate the
+// step: chunk c = routes [1024 c, 1024 c + 1024).
+//   route_count_kernel    per chunk: each route's rank among the chunk's routes of its expert (into
+//                         row_of_route) and the chunk's count per expert (chunk_cnt[c][e])
+//   route_scan_kernel     one CTA: per expert an exclusive scan of the chunk counts (in place), the
+//                         expert offsets and the tile list
+//   route_scatter_kernel  per chunk: row = offsets[e] + chunk_cnt[c][e] + rank
+// Ranks come from warp match/ballot and fixed-order scans, so the plan equals route_plan_kernel's bit
+// for bit and does not depend on scheduling.
+//
+// `seg_len`, `seg_stride` (both 0 = off): the value stored for route i in route_of_row is
+// (i / seg_len) * seg_stride + i % seg_len, the route's row in a buffer that holds each source's
+// seg_len routes at a stride of seg_stride rows (the expert-parallel window).
+__device__ __forceinline__ uint32_t route_label(uint32_t i, uint32_t seg_len, uint32_t seg_stride) {
+    return seg_len ? (i / seg_len) * seg_stride + i % seg_len : i;
+}
+
+__global__ void __launch_bounds__(1024) route_count_kernel(const uint32_t* __restrict__ ids, uint32_t R, uint32_t E,
+                                                           uint32_t* __restrict__ row_of_route,
+                                                           uint32_t* __restrict__ chunk_cnt) {
+    __shared__ uint32_t warp_cnt[32][kMaxExperts];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (uint32_t j = lane; j < E; j += 32) warp_cnt[warp][j] = 0;
+    __syncwarp();
+    const uint32_t i = blockIdx.x * 1024u + tid;
+    const uint32_t e = i < R ? ids[i] : 0xffffffffu;
+    const uint32_t peers = __match_any_sync(0xffffffffu, e);
+    const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
+    if (e < E && rank == 0) warp_cnt[warp][e] = __popc(peers);
+    __syncthreads();
+    if (tid < E) {
+        uint32_t acc = 0;
+        for (uint32_t w = 0; w < 32; w++) {
+            const uint32_t c = warp_cnt[w][tid];
+            warp_cnt[w][tid] = acc;
+            acc += c;
+        }
+        chunk_cnt[(size_t)blockIdx.x * E + tid] = acc;
+    }
+    __syncthreads();
+    if (e < E) row_of_route[i] = warp_cnt[warp][e] + rank;
+}
+
+__global__ void __launch_bounds__(1024) route_scan_kernel(uint32_t chunks, uint32_t E, uint32_t tile_rows,
+                                                          uint32_t* __restrict__ chunk_cnt, uint32_t* __restrict__ offsets,
+                                                          uint32_t* __restrict__ tiles, uint32_t* __restrict__ tile_count) {
+    __shared__ uint32_t total[kMaxExperts];
+    __shared__ uint32_t soff[kMaxExperts + 1];
+    __shared__ uint32_t tile_off[kMaxExperts + 1];
+    __shared__ uint32_t part[1024];
+    const uint32_t tid = threadIdx.x;
+    // expert e's chunks split into `lanes` contiguous spans, one per thread; span totals scanned serially
+    const uint32_t lanes = 1024u / kMaxExperts;                       // 8 threads per expert
+    const uint32_t e = tid / lanes, span = tid % lanes;
+    const uint32_t per = (chunks + lanes - 1) / lanes;
+    const uint32_t c0 = span * per, c1 = min(chunks, c0 + per);
+    uint32_t sum = 0;
+    if (e < E)
+        for (uint32_t c = c0; c < c1; c++) sum += chunk_cnt[(size_t)c * E + e];
+    part[tid] = sum;
+    __syncthreads();
+    if (e < E) {
+        uint32_t acc = 0;
+        for (uint32_t s = 0; s < span; s++) acc += part[e * lanes + s];
+        for (uint32_t c = c0; c < c1; c++) {
+            const uint32_t v = chunk_cnt[(size_t)c * E + e];
+            chunk_cnt[(size_t)c * E + e] = acc;
+            acc += v;
+        }
+        if (span == lanes - 1) total[e] = acc;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t acc = 0, nt = 0;
+        for (uint32_t x = 0; x < E; x++) {
+            soff[x] = acc;
+            tile_off[x] = nt;
+            acc += total[x];
+            nt += (total[x] + tile_rows - 1) / tile_rows;
+        }
+        soff[E] = acc;
+        tile_off[E] = nt;
+        *tile_count = nt;
+    }
+    __syncthreads();
+    if (tid <= E) offsets[tid] = soff[tid];
+    if (tid < E) {
+        uint32_t nt = tile_off[tid];
+        for (uint32_t b = 0; b < total[tid]; b += tile_rows, nt++) {
+            tiles[2 * nt] = tid;
+            tiles[2 * nt + 1] = b;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(1024) route_scatter_kernel(const uint32_t* __restrict__ ids, uint32_t R, uint32_t E,
+                                                             const uint32_t* __restrict__ chunk_cnt,
+                                                             const uint32_t* __restrict__ offsets, uint32_t seg_len,
+                                                             uint32_t seg_stride, uint32_t* __restrict__ row_of_route,
+                                                             uint32_t* __restrict__ route_of_row) {
+    const uint32_t i = blockIdx.x * 1024u + threadIdx.x;
+    if (i >= R) return;
+    const uint32_t e = ids[i];
+    if (e >= E) return;
+    const uint32_t row = offsets[e] + chunk_cnt[(size_t)blockIdx.x * E + e] + row_of_route[i];
+    row_of_route[i] = row;
+    route_of_row[row] = route_label(i, seg_len, seg_stride);
 }
 
 // Gathers token rows into expert-sorted order, converting bf16 to the tiles' half operand and
 // laying each block out in the tiles' operand order (see operand_pos in gemm.cuh): `half_span` is
 // the distance between the two elements a code byte holds (16 for MXFP4 / Q4_0, 32 for Q4_K).
 // The reference gathers inside its tiles (shaders/experts/projections.metal:208-233).
-// One CTA per sorted row; each thread emits one half2 = (x[k], x[k + half_span]).
+// CTAs stride over the sorted rows (`rows`, or *live_rows when given: the plan's route total, which
+// may be less than the launch was sized for); each thread emits one half2 = (x[k], x[k + half_span]).
 __global__ void __launch_bounds__(256) permute_rows_kernel(const uint16_t* __restrict__ x,
                                                            const uint32_t* __restrict__ route_of_row, int K,
-                                                           int H, int half_span, uint16_t* __restrict__ xs) {
-    uint32_t row = blockIdx.x;
-    uint32_t token = route_of_row ? route_of_row[row] / (uint32_t)K : row;  // null: rows keep token order
-    const uint16_t* src = x + (size_t)token * H;
-    uint32_t* dst = reinterpret_cast<uint32_t*>(xs + (size_t)row * H);
-    for (int i = threadIdx.x; i < H / 2; i += 256) {
-        int blk = i / half_span, j = i % half_span;           // pair i of the row: block, byte index
-        int k = blk * 2 * half_span + j;
-        __half2 h = __floats2half2_rn(__uint_as_float((uint32_t)src[k] << 16),
-                                      __uint_as_float((uint32_t)src[k + half_span] << 16));
-        dst[i] = *reinterpret_cast<uint32_t*>(&h);
+                                                           int H, int half_span, uint16_t* __restrict__ xs,
+                                                           uint32_t rows, const uint32_t* __restrict__ live_rows) {
+    const uint32_t n = live_rows ? *live_rows : rows;
+    for (uint32_t row = blockIdx.x; row < n; row += gridDim.x) {
+        uint32_t token = route_of_row ? route_of_row[row] / (uint32_t)K : row;  // null: rows keep token order
+        const uint16_t* src = x + (size_t)token * H;
+        uint32_t* dst = reinterpret_cast<uint32_t*>(xs + (size_t)row * H);
+        for (int i = threadIdx.x; i < H / 2; i += 256) {
+            int blk = i / half_span, j = i % half_span;           // pair i of the row: block, byte index
+            int k = blk * 2 * half_span + j;
+            __half2 h = __floats2half2_rn(__uint_as_float((uint32_t)src[k] << 16),
+                                          __uint_as_float((uint32_t)src[k + half_span] << 16));
+            dst[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
     }
 }
 

@@ -16,10 +16,30 @@ between the stages:
 Rank g of N owns experts [g * E/N, (g+1) * E/N). The index arithmetic (`dispatch_layout`) is plain
 integer code shared by the CPU test (gloo ranks, the oracle standing in for the kernels) and the
 GPU path (NCCL over NVLink, the C-ABI stage calls).
+
+`forward_window` is the same layer without a collective on the rows' way (`forward` above is the
+portable form and the one that runs on CPU ranks). Token rows and route outputs live in two windows
+(`Windows`: one address range whose slot g is GPU g's memory, so a row has the same global number
+on every rank):
+
+    1. route        as above, on the rank's own rows, which sit in its slot of the token window
+    2. ids          one all-gather of the expert ids (a few KB per rank); it also orders every
+                    rank's rows before any peer's reads of them
+    3. experts      oco_moe_experts_window over ALL ranks' routes: ids of other shards are skipped by
+                    the route plan, the gather reads the owned routes' token rows from the peers'
+                    slots (plain loads over NVLink), the down tiles store each output row into its
+                    token owner's slot of the output window (plain stores)
+    4. arrive       one all-reduce of a word: every rank's stores are complete
+    5. combine      on the rank's own slot of the output window
+
+No step waits on the host: nothing data-dependent is read back, all five are enqueued on the stream.
 """
 from __future__ import annotations
 
 import ctypes as C
+import math
+import os
+import socket
 from dataclasses import dataclass
 from typing import Callable, Optional
 
@@ -185,6 +205,16 @@ class CudaBackend:
                                                     self._stream()))
         return y
 
+    def experts_window(self, win: "Windows"):
+        """Stage 3 of forward_window: every rank's routes, this shard's experts, rows through the windows."""
+        p = self.expert_plan
+        routes = win.world * win.cap_routes
+        if routes > self.expert_rows * self.K:
+            raise self._moe.OcoError(self._lib.UNSUPPORTED_SHAPE, f"{routes} routes exceed this rank's workspace")
+        p._check(self._lib.lib().oco_moe_experts_window(
+            p.handle, C.c_void_p(win.x_base), C.c_void_p(win.ids_local.data_ptr()), routes, self.K, win.cap_routes,
+            win.slot_routes, win.cap_routes, C.c_void_p(win.y_base), self._stream()))
+
     def combine(self, y_routes, probs, residual):
         p = self.router_plan
         p._check(self._lib.lib().oco_moe_combine(p.handle, C.c_void_p(y_routes.data_ptr()),
@@ -199,3 +229,170 @@ class CudaBackend:
 
     def backend(self) -> Backend:
         return Backend(self.route, self.experts, self.combine)
+
+
+# ---------------------------------------------------------------------------------------------
+# Windows
+
+
+def window_geometry(hidden: int, top_k: int, max_tokens: int, granularity: int):
+    """(slot_tokens, slot_routes): token rows and route rows per window slot. A slot must start on a
+    multiple of the allocation granularity in BOTH windows and hold whole rows, so slot_tokens is the
+    smallest multiple of granularity / gcd(granularity, row bytes) that holds max_tokens; the output
+    window's slot holds top_k rows per token."""
+    row = hidden * 2
+    unit = granularity // math.gcd(granularity, row)
+    slot_tokens = (max_tokens + unit - 1) // unit * unit
+    return slot_tokens, slot_tokens * top_k
+
+
+def window_labels(world: int, cap_routes: int, slot_routes: int) -> np.ndarray:
+    """Label of each entry of the gathered id list (source rank major, cap_routes per rank): the route's
+    row in the output window, top_k times its token's row in the token window. The kernels compute the
+    same from (seg_routes, seg_stride) = (cap_routes, slot_routes)."""
+    i = np.arange(world * cap_routes, dtype=np.int64)
+    return (i // cap_routes) * slot_routes + i % cap_routes
+
+
+def exchange_descriptors(fd: int, group=None) -> list:
+    """Every rank's file descriptor, received by every rank: passed as SCM_RIGHTS over abstract Unix
+    sockets (the ranks are processes of one machine). Returns descriptors indexed by rank (own: fd)."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    tag = [os.urandom(8).hex() if rank == 0 else None]
+    dist.broadcast_object_list(tag, src=0, group=group)
+    name = lambda r: f"\0oco_ep_{tag[0]}_{r}"
+    listener = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+    listener.bind(name(rank))
+    listener.listen(world)
+    _barrier(group)
+    # connect to every peer first (a pending connection needs no accept yet), then serve, then receive
+    conns = {}
+    for r in range(world):
+        if r != rank:
+            c = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+            c.connect(name(r))
+            conns[r] = c
+    for _ in range(world - 1):
+        served, _addr = listener.accept()
+        socket.send_fds(served, [b"f"], [fd])
+        served.close()
+    fds = [fd] * world
+    for r, c in conns.items():
+        _msg, got, _flags, _addr = socket.recv_fds(c, 1, 1)
+        fds[r] = got[0]
+        c.close()
+    listener.close()
+    return fds
+
+
+def _barrier(group):
+    # an object all-gather: works on every backend without touching a device stream
+    out = [None] * dist.get_world_size(group)
+    dist.all_gather_object(out, 0, group=group)
+
+
+class _DevicePointer:
+    """Lets torch wrap device memory it did not allocate (zero copy)."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+class Windows:
+    """The token window and the output window of one expert-parallel group, plus the small buffers of
+    the id exchange. `max_tokens` is the most tokens a rank brings to one step (all ranks agree)."""
+
+    def __init__(self, hidden: int, top_k: int, max_tokens: int, group=None, device=None):
+        from . import _lib, moe
+        self._lib = _lib
+        lib = _lib.lib()
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.hidden, self.top_k, self.max_tokens = hidden, top_k, max_tokens
+        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        gran = C.c_size_t()
+        self._check(lib.oco_ep_window_granularity(C.byref(gran)))
+        self.slot_tokens, self.slot_routes = window_geometry(hidden, top_k, max_tokens, gran.value)
+        self.cap_routes = max_tokens * top_k
+        row = hidden * 2
+        self._handles = []
+        self.x_base = self._make(self.slot_tokens * row, max_tokens * row)
+        self.y_base = self._make(self.slot_routes * row, self.cap_routes * row)
+        self.x_local = torch.as_tensor(_DevicePointer(self.x_base + self.rank * self.slot_tokens * row, (max_tokens, hidden), "<i2"),
+                                       device=self.device)
+        self.y_local = torch.as_tensor(_DevicePointer(self.y_base + self.rank * self.slot_routes * row, (self.cap_routes, hidden), "<i2"),
+                                       device=self.device)
+        self.ids_send = torch.full((self.cap_routes,), -1, dtype=torch.int32, device=self.device)
+        self.ids_all = torch.empty((self.world * self.cap_routes,), dtype=torch.int32, device=self.device)
+        self.ids_local = torch.empty_like(self.ids_all)
+        self.arrived = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._filled = 0
+
+    def _check(self, rc):
+        if rc:
+            from . import moe
+            raise moe.OcoError(rc, self._lib.lib().oco_ep_window_error().decode())
+
+    def _make(self, stride: int, backed: int) -> int:
+        lib = self._lib.lib()
+        h = C.c_void_p()
+        self._check(lib.oco_ep_window_create(self.rank, self.world, stride, backed, C.byref(h)))
+        self._handles.append(h)
+        fds = exchange_descriptors(lib.oco_ep_window_fd(h), self.group)
+        for r, fd in enumerate(fds):
+            if r != self.rank:
+                rc = lib.oco_ep_window_attach(h, r, fd)
+                os.close(fd)
+                self._check(rc)
+        _barrier(self.group)
+        return lib.oco_ep_window_base(h)
+
+    def close(self):
+        torch.cuda.synchronize()
+        _barrier(self.group)      # no peer still reads or writes this rank's slots
+        self.x_local = self.y_local = None
+        for h in self._handles:
+            self._lib.lib().oco_ep_window_destroy(h)
+        self._handles = []
+
+
+def forward_window(x: torch.Tensor, residual: torch.Tensor, backend: "CudaBackend", win: Windows,
+                   timings: Optional[dict] = None) -> None:
+    """One expert-parallel MoE layer over this rank's tokens through the windows. x (int16 [T, H]) is
+    copied into the rank's slot unless it already is `win.x_local[:T]`; residual int16 [T, H] is
+    updated in place. T may differ between ranks and steps, up to win.max_tokens."""
+    T, K = x.shape[0], win.top_k
+    if T > win.max_tokens:
+        raise ValueError(f"{T} tokens exceed the windows' capacity of {win.max_tokens}")
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)] if timings is not None else None
+    if ev:
+        ev[0].record()
+    xs = win.x_local[:T]
+    if T and x.data_ptr() != xs.data_ptr():
+        xs.copy_(x)
+    ids, probs = backend.route(xs)
+    if win._filled > T * K:
+        win.ids_send[T * K: win._filled].fill_(-1)     # ids of a fuller earlier step
+    if T:
+        win.ids_send[: T * K].copy_(ids.reshape(-1))
+    win._filled = T * K
+    dist.all_gather_into_tensor(win.ids_all, win.ids_send, group=win.group)
+    if ev:
+        ev[1].record()
+    # shard numbering: an id of another shard (or the padding) leaves 0 .. experts_per_rank - 1 and is skipped
+    torch.sub(win.ids_all, win.rank * backend.epr, out=win.ids_local)
+    backend.experts_window(win)
+    if ev:
+        ev[2].record()
+    dist.all_reduce(win.arrived, group=win.group)
+    if ev:
+        ev[3].record()
+    if T:
+        backend.combine(win.y_local[: T * K], probs, residual)
+    if ev:
+        ev[4].record()
+        torch.cuda.synchronize()
+        timings["route_ids_ms"] = ev[0].elapsed_time(ev[1])
+        timings["experts_ms"] = ev[1].elapsed_time(ev[2])
+        timings["arrive_ms"] = ev[2].elapsed_time(ev[3])
+        timings["combine_ms"] = ev[3].elapsed_time(ev[4])

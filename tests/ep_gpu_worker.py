@@ -1,5 +1,6 @@
 """Worker of the expert-parallel GPU test: one process per GPU over NCCL, the C-ABI stage calls
-(route, experts, combine) doing the arithmetic. Launched by tests/test_gpu_ep.py through
+(route, experts, combine) doing the arithmetic, first around the all-to-all exchange, then through
+the windows over peer memory. Launched by tests/test_gpu_ep.py through
 torch.distributed.run; the oracle checks each rank's rows."""
 import os
 import sys
@@ -52,6 +53,33 @@ def main():
         assert err <= REL_L2, f"rank {rank} case {n}: rel-L2 {err}"
         ids, _ = be.route(x)
         assert np.array_equal(ids.cpu().numpy().astype(np.uint32), ref.ids[lo:hi].astype(np.uint32)), "expert ids differ"
+        # the same layer through the windows (rows read from and written to the peers' memory by the expert
+        # stage itself), with the route plan made by one CTA and by many; then a step with fewer tokens on
+        # every rank, whose id list is shorter than the one before it
+        cap = int(np.max(np.diff(bounds)))
+        for single_max in ("2048", "0"):
+            os.environ["OCO_MOE_ROUTE_PLAN_SINGLE_MAX"] = single_max
+            bw = ep.CudaBackend(layer, rank, world, max_rows=max(cap, 1))
+            del os.environ["OCO_MOE_ROUTE_PLAN_SINGLE_MAX"]
+            win = ep.Windows(H, K, max(cap, 1))
+            res_w = torch.from_numpy(res_all[lo:hi].view(np.int16).copy()).cuda()
+            ep.forward_window(x, res_w, bw, win)
+            torch.cuda.synchronize()
+            bw.router_plan.poll(); bw.expert_plan.poll()
+            err = rel_l2(res_w.cpu().numpy().view(np.uint16), ref.out[lo:hi])
+            assert err <= REL_L2, f"rank {rank} case {n} (windows, single_max {single_max}): rel-L2 {err}"
+            keep = (hi - lo) // 2
+            tok = np.concatenate([np.arange(bounds[g], bounds[g] + (bounds[g + 1] - bounds[g]) // 2) for g in range(world)])
+            ref2 = oracle.moe_forward(layer, x_all[tok], res_all[tok], mode=2)
+            at = int(sum((bounds[g + 1] - bounds[g]) // 2 for g in range(rank)))
+            res_2 = torch.from_numpy(res_all[lo:lo + keep].view(np.int16).copy()).cuda()
+            ep.forward_window(x[:keep], res_2, bw, win)
+            torch.cuda.synchronize()
+            bw.router_plan.poll(); bw.expert_plan.poll()
+            if keep:
+                err = rel_l2(res_2.cpu().numpy().view(np.uint16), ref2.out[at:at + keep])
+                assert err <= REL_L2, f"rank {rank} case {n} (windows, shorter step): rel-L2 {err}"
+            win.close()
     dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank} ok")

@@ -20,7 +20,7 @@ def lib():
 def test_header_symbols_are_exported(lib):
     header = open(os.path.join(ROOT, "include", "oco_moe.h")).read()
     header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
-    declared = set(re.findall(r"\b(oco_(?:moe|cuda|tensor|dense)_\w+)\s*\(", header))
+    declared = set(re.findall(r"\b(oco_(?:moe|cuda|tensor|dense|ep)_\w+)\s*\(", header))
     assert len(declared) >= 20
     assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
     for name in declared:
