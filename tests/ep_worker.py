@@ -20,6 +20,9 @@ def main():
     # 11 tokens: ranks hold uneven shares; 12: equal shares; 2: with four ranks some hold no token at all
     for T, uniform in ((11, False), (12, True), (2, False)):
         run_case(rank, world, T, uniform)
+    descriptors_reach_every_rank(rank, world)
+    for T in (11, 12, 2):
+        run_window_case(rank, world, T)
     dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank} ok")
@@ -70,6 +73,123 @@ def run_case(rank, world, T, uniform):
         sel = order[dest == g]
         assert torch.all(sel[1:] > sel[:-1])
     assert counts.sum().item() == ids.numel() and torch.all(local < epr)
+
+
+def descriptors_reach_every_rank(rank, world):
+    """ep.exchange_descriptors with plain files standing in for the memory handles."""
+    import tempfile
+    with tempfile.TemporaryFile() as f:
+        f.write(f"slot of rank {rank}".encode())
+        f.flush()
+        fds = ep.exchange_descriptors(f.fileno())
+        assert fds[rank] == f.fileno() and len(fds) == world
+        for r, fd in enumerate(fds):
+            if r == rank:
+                continue
+            assert os.pread(fd, 64, 0) == f"slot of rank {r}".encode()
+            os.close(fd)
+        dist.barrier()       # every peer has read before the file goes away
+
+
+class SharedWindows:
+    """ep.Windows on CPU ranks: the two windows are POSIX shared memory that every rank maps, laid out as
+    the device windows are (slot strides from ep.window_geometry for a 4096-byte granularity)."""
+
+    def __init__(self, hidden, top_k, max_tokens):
+        from multiprocessing import shared_memory
+        self.group = None
+        self.world, self.rank = dist.get_world_size(), dist.get_rank()
+        self.hidden, self.top_k, self.max_tokens = hidden, top_k, max_tokens
+        self.slot_tokens, self.slot_routes = ep.window_geometry(hidden, top_k, max_tokens, 4096)
+        self.cap_routes = max_tokens * top_k
+        tag = [os.urandom(6).hex() if self.rank == 0 else None]
+        dist.broadcast_object_list(tag, src=0)
+        self._shm = []
+        views = []
+        for which, rows in (("x", self.slot_tokens), ("y", self.slot_routes)):
+            name, size = f"oco_ep_test_{tag[0]}_{which}", self.world * rows * hidden * 2
+            if self.rank == 0:
+                shm = shared_memory.SharedMemory(name=name, create=True, size=size)
+            dist.barrier()
+            if self.rank != 0:
+                shm = shared_memory.SharedMemory(name=name)
+            self._shm.append(shm)
+            views.append(np.ndarray((self.world * rows, hidden), dtype=np.int16, buffer=shm.buf))
+        self.x_all, self.y_all = views
+        self.x_local = torch.from_numpy(self.x_all[self.rank * self.slot_tokens:][:max_tokens])
+        self.y_local = torch.from_numpy(self.y_all[self.rank * self.slot_routes:][:self.cap_routes])
+        self.ids_send = torch.full((self.cap_routes,), -1, dtype=torch.int32)
+        self.ids_all = torch.empty((self.world * self.cap_routes,), dtype=torch.int32)
+        self.ids_local = torch.empty_like(self.ids_all)
+        self.arrived = torch.zeros(1)
+        self._filled = 0
+
+    def close(self):
+        dist.barrier()
+        self.x_local = self.y_local = self.x_all = self.y_all = None
+        for shm in self._shm:
+            shm.close()
+        dist.barrier()
+        if self.rank == 0:
+            for shm in self._shm:
+                shm.unlink()
+
+
+def run_window_case(rank, world, T):
+    """ep.forward_window over shared-memory windows, the oracle reading and writing rows by their labels as
+    oco_moe_experts_window does; two steps in a row, the second with fewer tokens per rank."""
+    E, K, H, F = 8, 2, 64, 96
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, H, F, E, K, synth.FMT_MXFP4, seed=78)
+    x_all, res_all = synth.make_tokens(H, T, 6, "normal")
+    bounds = np.linspace(0, T, world + 1).astype(int)
+    cap = max(1, int(np.max(np.diff(bounds))))
+    epr = E // world
+    win = SharedWindows(H, K, cap)
+    labels = ep.window_labels(world, win.cap_routes, win.slot_routes)
+
+    class OracleBackend:
+        pass
+
+    be = OracleBackend()
+    be.epr = epr
+
+    def route(x):
+        if x.shape[0] == 0:
+            return torch.empty((0, K), dtype=torch.int32), torch.empty((0, K), dtype=torch.float32)
+        _, ids, probs = oracle.router_gptoss(x.numpy().view(np.uint16), layer.router_w, layer.router_b, K)
+        return torch.from_numpy(ids.astype(np.int32)), torch.from_numpy(probs)
+
+    def experts_window(w):
+        local = w.ids_local.numpy()
+        mine = np.nonzero((local >= 0) & (local < epr))[0]
+        if len(mine) == 0:
+            return
+        lab = labels[mine]
+        xr = w.x_all[lab // K].view(np.uint16)
+        gids = local[mine].astype(np.uint32) + rank * epr
+        up = oracle.expert_up_tile(layer.up_w, xr, layer.up_b, 1.0, gids, 1, H, F)
+        gate = oracle.expert_up_tile(layer.gate_w, xr, layer.gate_b, 0.0, gids, 1, H, F)
+        y = oracle.expert_down_tile(layer.down_w, oracle.moe_activate(gate, up), layer.down_b, gids, F, H)
+        w.y_all[lab] = y.view(np.int16)
+
+    def combine(y_routes, probs, residual):
+        out = oracle.moe_sum(y_routes.numpy().view(np.uint16), probs.numpy(), residual.numpy().view(np.uint16), K)
+        residual.copy_(torch.from_numpy(out.view(np.int16)))
+
+    be.route, be.experts_window, be.combine = route, experts_window, combine
+    for shrink in (1, 2):
+        counts = [(bounds[g + 1] - bounds[g]) // shrink for g in range(world)]
+        tok = np.concatenate([np.arange(bounds[g], bounds[g] + counts[g]) for g in range(world)]).astype(int)
+        if len(tok) == 0:
+            continue
+        at, n = int(sum(counts[:rank])), counts[rank]
+        x = torch.from_numpy(x_all[tok][at:at + n].view(np.int16).copy())
+        res = torch.from_numpy(res_all[tok][at:at + n].view(np.int16).copy())
+        ep.forward_window(x, res, be, win)
+        ref = oracle.moe_forward(layer, x_all[tok], res_all[tok], mode=2)
+        assert np.array_equal(res.numpy().view(np.uint16), ref.out[at:at + n]), \
+            f"rank {rank}: window protocol differs from the single-process oracle (T {T}, shrink {shrink})"
+    win.close()
 
 
 if __name__ == "__main__":

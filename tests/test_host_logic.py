@@ -119,3 +119,22 @@ def test_add_norm_oracle_against_float64(oracle):
             # one bf16 rounding (2^-9) when the scale is applied in f32, three when both factors are rounded first
             bound = 2.0 ** -8 if full_layer else 2.0 ** -6
             assert np.all(np.abs(got - want) <= np.abs(want) * bound + 1e-30)
+
+
+def test_window_geometry_and_labels():
+    """Slots of both windows start on granularity multiples, hold whole rows and the capacity; labels
+    are a route's row in the output window and top_k times its token's row in the token window."""
+    from oco_b200 import ep
+    for hidden, top_k, cap, gran in ((2880, 4, 4096, 2 << 20), (2880, 4, 100, 2 << 20), (2048, 8, 512, 2 << 20),
+                                     (2688, 6, 1024, 2 << 20), (64, 2, 6, 4096)):
+        st, sr = ep.window_geometry(hidden, top_k, cap, gran)
+        assert st >= cap and sr == st * top_k
+        assert (st * hidden * 2) % gran == 0 and (sr * hidden * 2) % gran == 0
+        unit = gran // np.gcd(gran, hidden * 2)
+        assert st - cap < unit                    # the smallest such slot
+        world = 3
+        lab = ep.window_labels(world, cap * top_k, sr)
+        src, r = np.divmod(np.arange(world * cap * top_k), cap * top_k)
+        assert np.array_equal(lab, src * sr + r)
+        assert np.array_equal(lab // top_k, src * st + r // top_k)      # the token's row in the token window
+        assert len(np.unique(lab)) == len(lab)
