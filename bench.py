@@ -44,6 +44,12 @@ WORKLOADS = {
     "gpt-oss-120b-decode64": ("gpt-oss-120b", 64),
 }
 EXPERT_PARALLEL = {"gpt-oss-120b-prefill", "gpt-oss-120b-decode64"}
+# the dense products either side of the layer (oco_dense_*): name -> (kind, format, hidden, ffn, default rows)
+DENSE_WORKLOADS = {
+    "nemotron-shared-ffn-prefill": ("relu2", "Q4_0", 2688, 3712, 1024),
+    "nemotron-shared-ffn-decode": ("relu2", "Q4_0", 2688, 3712, 1),
+    "qwen3-dense-ffn-prefill": ("silu_gate", "Q4_K", 2048, 6144, 512),
+}
 # DRAM bytes (read + write) of one launch of the dominant kernels, from ncu captures of the same commands
 # (dram__bytes_read.sum + dram__bytes_write.sum of one launch); a profiler is never attached to a timed run.
 NCU_TRAFFIC = {
@@ -369,6 +375,109 @@ def run_expert_parallel(args, torch, dist, world, rank, local, workload, steps, 
         parity=parity, clocks=clocks, e2e=e2e, gpu_launches=launches, phases_ms=phases, roofline=roofline, cpu_baseline=base)
 
 
+def run_dense(args, ctx):
+    """A dense feed-forward (oco_dense_forward) on this rank's GPU: device-timed steps over rotated weight
+    copies (more bytes between reuses than the L2 holds), the end-to-end call with pinned host rows, a token
+    sample against the CPU checker, the checker timed as the CPU baseline. Returns rank 0's record."""
+    torch, dist, world, rank, local = ctx
+    from oco_b200 import dense
+    import oracle
+    kind_name, fmt_name, H, F, default_rows = DENSE_WORKLOADS[args.workload]
+    kind = dict(relu2=dense.FFN_RELU2, silu_gate=dense.FFN_SILU_GATE)[kind_name]
+    fmt = dict(Q4_0=synth.FMT_Q4_0, Q4_K=synth.FMT_Q4_K)[fmt_name]
+    rows = args.tokens or default_rows
+    n_mat = 3 if kind == dense.FFN_SILU_GATE else 2
+    weight_bytes = n_mat * F * synth.row_bytes(fmt, H) if kind != dense.FFN_RELU2 else F * synth.row_bytes(fmt, H) + H * synth.row_bytes(fmt, F)
+    if kind == dense.FFN_SILU_GATE:
+        weight_bytes = 2 * F * synth.row_bytes(fmt, H) + H * synth.row_bytes(fmt, F)
+    copies = max(2, int(np.ceil(600e6 / weight_bytes)))
+    rng = np.random.default_rng(args.seed)
+    gen = synth._RANDOM[fmt]
+    plans, host_w = [], None
+    for c in range(copies):
+        w = (gen(rng, F, H), gen(rng, F, H) if kind == dense.FFN_SILU_GATE else None, gen(rng, H, F))
+        host_w = host_w or w
+        p = dense.DensePlan(kind, fmt, H, F)
+        p.reserve(rows)
+        p.bind(*w)
+        plans.append(p)
+    x_bits, _ = synth.make_tokens(H, rows, args.seed + 1000 * rank, "zero")
+    x_bits = synth.f32_to_bf16_bits(synth.bf16_bits_to_f32(x_bits) * np.float32(0.25))
+    hx = torch.from_numpy(x_bits.view(np.int16).copy()).pin_memory()
+    hy = torch.empty((rows, H), dtype=torch.int16).pin_memory()
+    x, y = hx.cuda(), torch.empty((rows, H), dtype=torch.int16, device="cuda")
+    stream = torch.cuda.current_stream()
+    # parity first: a row sample of the first weight copy against the checker
+    plans[0].forward(x, y, rows)
+    torch.cuda.synchronize(); plans[0].poll()
+    pick = np.unique(np.linspace(0, rows - 1, 8).astype(int))
+    ref = oracle.dense_forward(kind, fmt, H, F, host_w[0], host_w[1], host_w[2], x_bits[pick], tile=rows > 1)
+    g = synth.bf16_bits_to_f32(y.cpu().numpy().view(np.uint16)[pick]).astype(np.float64)
+    r = synth.bf16_bits_to_f32(ref).astype(np.float64)
+    parity = dict(rel_l2=float(np.linalg.norm(g - r) / max(np.linalg.norm(r), 1e-30)), tolerance=1e-3, sample=f"{len(pick)} rows against the CPU checker")
+    for i in range(max(3, args.warmup)):
+        plans[i % copies].forward(x, y, rows)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start(); time.sleep(0.2)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    launches = 0
+    for i in range(args.steps):
+        plans[i % copies].forward(x, y, rows)
+        launches += plans[i % copies].launch_count()
+    b.record(stream)
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) / args.steps], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.barrier()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    clocks = sampler.stop() if rank == 0 else {}
+    clocks.pop("sm_mhz_all", None)
+    plans[0].poll()
+    e2e_steps = max(3, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        x.copy_(hx, non_blocking=True)
+        plans[i % copies].forward(x, y, rows)
+        hy.copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+    e2e_ms = 1e3 * (time.perf_counter() - t0) / e2e_steps
+    if rank != 0:
+        return None
+    peaks = measured_peaks()
+    flops = 2.0 * rows * H * F * n_mat
+    bytes_step = weight_bytes + rows * H * 2 * 2
+    tensor_bound = rows > 64
+    ach = flops / (ms / 1e3) / 1e12 if tensor_bound else bytes_step / (ms / 1e3) / 1e9
+    peak = peaks["tflops"] if tensor_bound else peaks["hbm_gbs"]
+    roofline = dict(bound="tensor" if tensor_bound else "hbm", kernel="whole call (two tile or two token launches plus the row conversion)",
+                    achieved=ach, peak=peak, unit="TFLOP/s" if tensor_bound else "GB/s", frac=ach / peak, traffic=None,
+                    peak_source=f"{peaks['source']} " + ("dense bf16 cuBLAS, burst" if tensor_bound else "HBM copy"),
+                    algorithmic_flops_per_step=flops, algorithmic_bytes_per_step=bytes_step)
+    cpu = None
+    if not args.no_cpu_baseline:
+        n = min(rows, args.cpu_tokens)
+        t0 = time.perf_counter()
+        oracle.dense_forward(kind, fmt, H, F, host_w[0], host_w[1], host_w[2], x_bits[:n], tile=rows > 1)
+        dt = time.perf_counter() - t0
+        cpu = dict(value=n / dt, unit="tokens/s", cores=oracle.num_threads(), kind="port",
+                   sample=f"first {n} of {rows} rows, one pass, {dt:.2f} s wall clock; C++ restatement of the reference's dense products")
+    return dict(metric="dense feed-forward tokens/s (the step beside the MoE layer)", value=world * rows / (ms / 1e3), unit="tokens/s",
+                n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=ms, higher_is_better=True, scaling="weak",
+                vs_baseline=None, dtype="f16" if rows > 1 else "f32", data="synthetic",
+                config=dict(workload=args.workload, rows_per_gpu=rows, hidden=H, ffn=F, kind=kind_name, weight_format=fmt_name,
+                            weight_copies=copies, cache="%d weight copies rotated per step (%.0f MB between reuses)" % (copies, copies * weight_bytes / 1e6),
+                            parallelism="replicas"),
+                clocks=clocks, e2e=dict(value=world * rows / (e2e_ms / 1e3), unit="tokens/s", ms_per_step=e2e_ms, h2d_bytes_per_step=rows * H * 2,
+                                        d2h_bytes_per_step=rows * H * 2, api="oco_dense_forward (pinned host rows in, result rows back)"),
+                gpu_launches=launches, roofline=roofline, parity=parity, cpu_baseline=cpu)
+
+
 def measure_layer(args, ctx, workload, steps, warmup, tokens=0, graph=True, with_norm=False, layers=0, sustained_s=0.0, numerics=0):
     """One workload on this rank's GPU (every rank runs the same layer on its own tokens): device-timed
     steps, per-kernel phase times, the end-to-end call with host buffers and, on request, a seconds-long
@@ -596,7 +705,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gpt-oss-20b-prefill", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="gpt-oss-20b-prefill", choices=sorted(WORKLOADS) + sorted(DENSE_WORKLOADS))
     ap.add_argument("--tokens", type=int, default=0)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--cpu-tokens", type=int, default=256, help="tokens in the CPU baseline's bounded sample")
@@ -611,6 +720,9 @@ def main():
                     help="time the fused entry point: residual add + RMS norm + layer (the step either side of the layer)")
     args = ap.parse_args()
     if args.impl == "reference":
+        if args.workload in DENSE_WORKLOADS:
+            print(json.dumps(dict(impl="reference", unavailable="the reference arm times the MoE layer workloads only")))
+            return 0
         return run_reference(args)
 
     import torch
@@ -631,6 +743,14 @@ def main():
     ctx = (torch, dist, world, rank, local)
     default = args.workload == "gpt-oss-20b-prefill" and not args.tokens and args.numerics == 0
     extras = default and not args.no_extras
+
+    if args.workload in DENSE_WORKLOADS:
+        rec = run_dense(args, ctx)
+        if rank == 0:
+            print(json.dumps(rec))
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
 
     if world > 1 and args.workload in EXPERT_PARALLEL:
         rec = run_expert_parallel(args, torch, dist, world, rank, local, args.workload, args.steps, args.warmup,

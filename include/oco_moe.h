@@ -274,6 +274,44 @@ int oco_moe_selftest_wait_timeout(oco_moe_plan* plan, long long wait_cycles, voi
  * roofline fractions; allocates 256 bytes for the call's duration. No counterpart in the reference. */
 int oco_tensor_peak(int kind, int iters, float* tflops);
 
+/* The dense products either side of the MoE layer: the reference's DenseMatrix::apply
+ * (src/weights/compute/matrix.rs:130-278) composed as its callers compose it.
+ *   OCO_DENSE_PROJECTION     y[rows, ffn] = up_w . x, stored as bf16 (any of the three weight formats)
+ *   OCO_DENSE_FFN_RELU2      Nemotron's always-on expert (compute/nemotron.rs:302-315 for rows > 1,
+ *                            :460-509 for one token): up -> relu^2 -> down, Q4_0; y[rows, hidden]
+ *   OCO_DENSE_FFN_SILU_GATE  the gated feed-forward of dense layers (Compute::feed_forward,
+ *                            compute/feed_forward.rs:97-104; gate kernel shaders/elementwise.metal:70-87):
+ *                            gate, up -> bf16(bf16(silu(g)) * u) -> down, Q4_K; y[rows, hidden]
+ * Weights are packed rows as in the expert banks, one matrix each: up_w [ffn][hidden], gate_w the same
+ * (gated kind only), down_w [hidden][ffn] (the two feed-forward kinds). The result is written, not added:
+ * the reference leaves it in `projected` for the caller's add. rows == 1 runs the single-token kernels
+ * with exact operands, rows > 1 the tiles with half operands, as the MoE layer does. Other pairs of kind
+ * and format answer OCO_UNSUPPORTED_SHAPE. Plan, workspace and weights follow the rules of the oco_moe_
+ * calls of the same names. */
+typedef enum { OCO_DENSE_PROJECTION = 0, OCO_DENSE_FFN_RELU2 = 1, OCO_DENSE_FFN_SILU_GATE = 2 } oco_dense_kind;
+typedef struct {
+    int32_t kind;           /* oco_dense_kind */
+    int32_t weight_format;  /* oco_weight_format */
+    int32_t hidden;         /* input features */
+    int32_t ffn;            /* projection: output features (a multiple of 32); feed-forward kinds: intermediate
+                             * features (a multiple of the format's block, as hidden is) */
+} oco_dense_desc;
+typedef struct {
+    const uint8_t* up_w;
+    const uint8_t* gate_w;
+    const uint8_t* down_w;
+} oco_dense_weights;
+typedef struct oco_dense_plan oco_dense_plan;
+int oco_dense_plan_create(const oco_dense_desc* desc, oco_dense_plan** out);
+void oco_dense_plan_destroy(oco_dense_plan* plan);
+size_t oco_dense_workspace_bytes(const oco_dense_plan* plan, int max_rows);
+int oco_dense_bind_workspace(oco_dense_plan* plan, void* workspace, size_t bytes, int max_rows);
+int oco_dense_bind_weights(oco_dense_plan* plan, const oco_dense_weights* weights);
+int oco_dense_forward(oco_dense_plan* plan, const uint16_t* x_bf16, uint16_t* y_bf16, int rows, void* cuda_stream);
+int oco_dense_poll(oco_dense_plan* plan, void* cuda_stream);
+int oco_dense_last_launch_count(const oco_dense_plan* plan);
+const char* oco_dense_last_error(const oco_dense_plan* plan);
+
 /* Expert parallelism without a collective on the rows' way. The reference is single-device; nothing
  * below has a counterpart in it.
  *

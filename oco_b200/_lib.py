@@ -31,6 +31,14 @@ class RoutingView(C.Structure):
 
 
 # Every symbol include/oco_moe.h declares, with its signature.
+class DenseDesc(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("weight_format", C.c_int32), ("hidden", C.c_int32), ("ffn", C.c_int32)]
+
+
+class DenseWeights(C.Structure):
+    _fields_ = [("up_w", C.POINTER(C.c_uint8)), ("gate_w", C.POINTER(C.c_uint8)), ("down_w", C.POINTER(C.c_uint8))]
+
+
 SIGNATURES = {
     "oco_moe_plan_create": (C.c_int, [C.POINTER(Desc), C.POINTER(C.c_void_p)]),
     "oco_moe_plan_destroy": (None, [C.c_void_p]),
@@ -69,6 +77,15 @@ SIGNATURES = {
     "oco_cuda_event_elapsed_ms": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_float)]),
     "oco_moe_selftest_wait_timeout": (C.c_int, [C.c_void_p, C.c_longlong, C.c_void_p]),
     "oco_tensor_peak": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_float)]),
+    "oco_dense_plan_create": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "oco_dense_plan_destroy": (None, [C.c_void_p]),
+    "oco_dense_workspace_bytes": (C.c_size_t, [C.c_void_p, C.c_int]),
+    "oco_dense_bind_workspace": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]),
+    "oco_dense_bind_weights": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "oco_dense_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "oco_dense_poll": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "oco_dense_last_launch_count": (C.c_int, [C.c_void_p]),
+    "oco_dense_last_error": (C.c_char_p, [C.c_void_p]),
     "oco_ep_window_granularity": (C.c_int, [C.POINTER(C.c_size_t)]),
     "oco_ep_window_create": (C.c_int, [C.c_int, C.c_int, C.c_size_t, C.c_size_t, C.POINTER(C.c_void_p)]),
     "oco_ep_window_fd": (C.c_int, [C.c_void_p]),

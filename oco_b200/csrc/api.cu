@@ -1251,6 +1251,161 @@ int oco_moe_routing(const oco_moe_plan* plan, oco_moe_routing_view* out) {
     return OCO_OK;
 }
 
+}  // extern "C"
+
+// ---- dense products ------------------------------------------------------------------------------------
+// A dense plan is a one-expert plan of the family whose kernels carry the kind's arithmetic: every row
+// is a route to expert 0, the tiles run in their dense mode, the single-token kernels take a null id list.
+struct oco_dense_plan {
+    oco_moe_plan* inner = nullptr;
+    oco_dense_desc d{};
+};
+
+namespace {
+
+template <int ARCH>
+int dense_rows(oco_dense_plan* dp, const uint16_t* x, uint16_t* y, int rows, cudaStream_t st) {
+    constexpr int FMT = Family<ARCH>::kFmt;
+    oco_moe_plan* plan = dp->inner;
+    Workspace& ws = plan->ws;
+    const int H = dp->d.hidden, F = dp->d.ffn, kind = dp->d.kind;
+    if (rows == 1) {
+        mark(plan, st, "fragments");
+        CK(launch_dependent(token_fragments_kernel, dim3((H + 255) / 256), dim3(256), 0, st, x, H, ws.xfrag, (int)FMT));
+        plan->launches++;
+        DecodeDownParams dn{};
+        dn.ids = nullptr; dn.K = 1; dn.status = ws.status;
+        if (kind == OCO_DENSE_PROJECTION) {
+            dn.down_w = plan->w.up_w; dn.actfrag = ws.xfrag; dn.y = y; dn.H = F; dn.F = H; dn.row_bytes = plan->up_row_bytes;
+            mark(plan, st, "project");
+            return launch_down<FMT>(plan, dn, st);
+        }
+        DecodeExpandParams ep{};
+        ep.gate_w = plan->w.gate_w; ep.up_w = plan->w.up_w; ep.bias_stride = 1;
+        ep.xfrag = ws.xfrag; ep.ids = nullptr; ep.act = ws.act1; ep.actfrag = ws.actfrag;
+        ep.H = H; ep.F = F; ep.K = 1; ep.row_bytes = plan->up_row_bytes; ep.status = ws.status;
+        mark(plan, st, "expand");
+        if (int rc = launch_expand<ARCH, FMT>(plan, ep, st)) return rc;
+        dn.down_w = plan->w.down_w; dn.actfrag = ws.actfrag; dn.y = y; dn.H = H; dn.F = F; dn.row_bytes = plan->down_row_bytes;
+        mark(plan, st, "down");
+        return launch_down<FMT>(plan, dn, st);
+    }
+    const int nt_index = pick_tile_index(rows, 1, plan->narrow_tiles ? 192 : plan->wide_min_avg);
+    const int NT = kTileSizes[nt_index], tiles = (rows + NT - 1) / NT;
+    mark(plan, st, "to_half");
+    permute_rows_kernel<<<std::min(rows, 16 * plan->sm_count), 256, 0, st>>>(x, nullptr, 1, H, FMT == OCO_FMT_Q4_K ? 32 : 16, ws.xs,
+                                                                          (uint32_t)rows, nullptr);
+    plan->launches++;
+    CK(cudaGetLastError());
+    GemmParams g{};
+    g.status = ws.status; g.dense_rows = rows; g.tile_rows = NT; g.bias_stride = 1;
+    if (kind == OCO_DENSE_PROJECTION) {
+        g.w0 = plan->w.up_w; g.n = F; g.K = H; g.row_bytes = plan->up_row_bytes; g.xs = ws.xs; g.out = y;
+        mark(plan, st, "project_tiles");
+        return launch_gemm_nt<FMT, kEpiDownBf16>(plan, g, plan->map_xs, nt_index, tiles, st);
+    }
+    constexpr int EPI = ARCH == OCO_ARCH_NEMOTRON ? kEpiRelu2Bf16F16 : kEpiSiluF16;
+    g.w0 = ARCH == OCO_ARCH_NEMOTRON ? plan->w.up_w : plan->w.gate_w;
+    g.w1 = ARCH == OCO_ARCH_NEMOTRON ? nullptr : plan->w.up_w;
+    g.n = F; g.K = H; g.row_bytes = plan->up_row_bytes; g.xs = ws.xs; g.out = ws.act;
+    mark(plan, st, "up_tiles");
+    if constexpr (ARCH != OCO_ARCH_GPT_OSS) {
+        if (int rc = launch_gemm_nt<FMT, EPI>(plan, g, plan->map_xs, nt_index, tiles, st)) return rc;
+    }
+    GemmParams dn{};
+    dn.status = ws.status; dn.dense_rows = rows; dn.tile_rows = NT; dn.bias_stride = 1;
+    dn.w0 = plan->w.down_w; dn.n = H; dn.K = F; dn.row_bytes = plan->down_row_bytes; dn.xs = ws.act; dn.out = y;
+    mark(plan, st, "down_tiles");
+    return launch_gemm_nt<FMT, kEpiDownBf16>(plan, dn, plan->map_act, nt_index, tiles, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+int oco_dense_plan_create(const oco_dense_desc* desc, oco_dense_plan** out) {
+    if (!desc || !out) return OCO_INVALID_ARGUMENT;
+    oco_dense_plan* dp = new (std::nothrow) oco_dense_plan();
+    if (!dp) return OCO_INVALID_ARGUMENT;
+    dp->d = *desc;
+    *out = dp;   // handed out even on failure so that the caller can read the message, then destroy
+    oco_moe_desc md{};
+    md.hidden = desc->hidden; md.ffn = desc->ffn; md.experts = 1; md.top_k = 1; md.weight_format = desc->weight_format;
+    md.scale = 1.0f;
+    if (desc->kind == OCO_DENSE_PROJECTION && desc->ffn > 0 && desc->ffn % 32 == 0) {
+        // a projection's outputs are rows of the matrix, not a contraction length: any multiple of 32 (the inner
+        // plan, which sizes buffers by block multiples, is told the next one)
+        const int be = desc->weight_format == OCO_FMT_Q4_K ? 256 : 32;
+        md.ffn = (desc->ffn + be - 1) / be * be;
+    }
+    switch (desc->weight_format) {
+        case OCO_FMT_MXFP4: md.arch = OCO_ARCH_GPT_OSS; break;
+        case OCO_FMT_Q4_0: md.arch = OCO_ARCH_NEMOTRON; break;
+        default: md.arch = OCO_ARCH_QWEN; break;
+    }
+    int rc = oco_moe_plan_create(&md, &dp->inner);
+    if (rc) return rc;
+    if (desc->kind < OCO_DENSE_PROJECTION || desc->kind > OCO_DENSE_FFN_SILU_GATE) return fail(dp->inner, OCO_INVALID_ARGUMENT, "unknown dense kind %d", desc->kind);
+    if (desc->kind == OCO_DENSE_FFN_RELU2 && desc->weight_format != OCO_FMT_Q4_0)
+        return fail(dp->inner, OCO_UNSUPPORTED_SHAPE, "the relu^2 feed-forward is built for Q4_0 weights");
+    if (desc->kind == OCO_DENSE_FFN_SILU_GATE && desc->weight_format != OCO_FMT_Q4_K)
+        return fail(dp->inner, OCO_UNSUPPORTED_SHAPE, "the gated feed-forward is built for Q4_K weights");
+    return OCO_OK;
+}
+
+void oco_dense_plan_destroy(oco_dense_plan* plan) {
+    if (!plan) return;
+    oco_moe_plan_destroy(plan->inner);
+    delete plan;
+}
+
+size_t oco_dense_workspace_bytes(const oco_dense_plan* plan, int max_rows) {
+    return plan && plan->inner ? oco_moe_workspace_bytes(plan->inner, max_rows) : 0;
+}
+
+int oco_dense_bind_workspace(oco_dense_plan* plan, void* workspace, size_t bytes, int max_rows) {
+    if (!plan || !plan->inner) return OCO_INVALID_ARGUMENT;
+    return oco_moe_bind_workspace(plan->inner, workspace, bytes, max_rows);
+}
+
+int oco_dense_bind_weights(oco_dense_plan* plan, const oco_dense_weights* w) {
+    if (!plan || !plan->inner) return OCO_INVALID_ARGUMENT;
+    oco_moe_plan* in = plan->inner;
+    if (!w || !w->up_w) return fail(in, OCO_INVALID_ARGUMENT, "up_w is required");
+    if (plan->d.kind != OCO_DENSE_PROJECTION && !w->down_w) return fail(in, OCO_INVALID_ARGUMENT, "down_w is required for a feed-forward");
+    if (plan->d.kind == OCO_DENSE_FFN_SILU_GATE && !w->gate_w) return fail(in, OCO_INVALID_ARGUMENT, "gate_w is required for the gated feed-forward");
+    in->w = oco_moe_weights{};
+    in->w.up_w = w->up_w; in->w.gate_w = w->gate_w; in->w.down_w = w->down_w;
+    in->gate_rows = (const uint8_t*)w->gate_w; in->up_rows = (const uint8_t*)w->up_w;
+    in->gate_bias = in->up_bias = nullptr;
+    in->up_row_stride = in->up_row_bytes; in->up_bias_stride = 1;
+    in->have_w = in->have_experts = true;
+    return OCO_OK;
+}
+
+int oco_dense_forward(oco_dense_plan* dp, const uint16_t* x_bf16, uint16_t* y_bf16, int rows, void* cuda_stream) {
+    if (!dp || !dp->inner) return OCO_INVALID_ARGUMENT;
+    oco_moe_plan* plan = dp->inner;
+    if (!plan->have_ws || !plan->have_w) return fail(plan, OCO_INVALID_ARGUMENT, "bind a workspace and weights first");
+    if (int rc_dev = check_device(plan)) return rc_dev;
+    if (!x_bf16 || !y_bf16 || rows < 1 || rows > plan->max_rows) return fail(plan, OCO_INVALID_ARGUMENT, "bad buffers, or rows outside 1 .. max_rows");
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    plan->launches = 0;
+    plan->n_marks = 0;
+    int rc;
+    switch (plan->d.arch) {
+        case OCO_ARCH_GPT_OSS: rc = dense_rows<OCO_ARCH_GPT_OSS>(dp, x_bf16, y_bf16, rows, st); break;
+        case OCO_ARCH_NEMOTRON: rc = dense_rows<OCO_ARCH_NEMOTRON>(dp, x_bf16, y_bf16, rows, st); break;
+        default: rc = dense_rows<OCO_ARCH_QWEN>(dp, x_bf16, y_bf16, rows, st); break;
+    }
+    mark(plan, st, "end");
+    return rc;
+}
+
+int oco_dense_poll(oco_dense_plan* plan, void* cuda_stream) { return plan && plan->inner ? oco_moe_poll(plan->inner, cuda_stream) : OCO_INVALID_ARGUMENT; }
+int oco_dense_last_launch_count(const oco_dense_plan* plan) { return plan && plan->inner ? plan->inner->launches : 0; }
+const char* oco_dense_last_error(const oco_dense_plan* plan) { return plan && plan->inner ? plan->inner->err : "null plan"; }
+
 const char* oco_moe_last_error(const oco_moe_plan* plan) { return plan ? plan->err : "null plan"; }
 int oco_moe_last_launch_count(const oco_moe_plan* plan) { return plan ? plan->launches : 0; }
 

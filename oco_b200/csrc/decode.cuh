@@ -689,6 +689,15 @@ __global__ void __launch_bounds__(tok_warps(FMT) * 32, 1) decode_down_kernel(con
     }
 }
 
+// One token as the B fragments the single-token kernels multiply with (the router kernel does this on the
+// side for the MoE layer; the dense products have no router). grid ceil(H / 256), 256 threads.
+__global__ void __launch_bounds__(256) token_fragments_kernel(const uint16_t* __restrict__ x, int H, __half* __restrict__ xfrag, int fmt) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int k = blockIdx.x * 256 + threadIdx.x;
+    if (k < H) frag_store(xfrag, k, bf16_bits_to_f32(x[k]), fmt);
+}
+
 // Router of one token: logits (one warp per expert, reference router_logits, routing.metal:131-146),
 // then the CTA that finishes last selects the experts and their weights for the whole token
 // (routing.metal:71-94; nemotron.metal:167-211). On the side, the CTAs turn the token into the B

@@ -90,6 +90,7 @@ def lib():
         L.orc_moe_activate.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
         L.orc_moe_sum.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
         L.orc_moe_add.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+        L.orc_dense_forward.argtypes = [C.c_int] * 4 + [C.c_void_p] * 4 + [C.c_int] * 2 + [C.c_void_p]
         L.orc_num_threads.restype = C.c_int
         L.orc_set_num_threads.argtypes = [C.c_int]
         _lib = L
@@ -271,6 +272,14 @@ class Result:
     probs: np.ndarray
     act: np.ndarray        # f32 [R, ffn]
     y: np.ndarray          # bf16 bits [R, H]
+
+
+def dense_forward(kind: int, fmt: int, hidden: int, ffn: int, up_w, gate_w, down_w, x_bf16, tile: bool) -> np.ndarray:
+    """Dense projection (kind 0: bf16 [T, ffn]) or feed-forward (1 relu^2, 2 SiLU gate: bf16 [T, hidden])."""
+    x = _c(x_bf16, np.uint16).reshape(-1, hidden)
+    out = np.empty((x.shape[0], ffn if kind == 0 else hidden), dtype=np.uint16)
+    lib().orc_dense_forward(kind, fmt, hidden, ffn, _p(up_w), _p(gate_w), _p(down_w), _p(x), x.shape[0], int(tile), _p(out))
+    return out
 
 
 def moe_forward(layer, x_bf16, residual_bf16, mode: int = 0, accumulate_f32: bool = False,

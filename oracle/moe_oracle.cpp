@@ -836,6 +836,62 @@ int orc_moe_forward(const OrcLayer* L, const uint16_t* x, uint16_t* residual, in
     return 0;
 }
 
+// The dense products either side of the MoE path (DenseMatrix::apply, src/weights/compute/matrix.rs:130-278),
+// composed as the reference composes them:
+//   kind 0  projection: out[t][c] = bf16(up_w[c] . x[t])                       (weights.metal:28-33 store)
+//   kind 1  relu^2 FFN, Nemotron's always-on expert (compute/nemotron.rs:302-315 for rows > 1,
+//           :460-509 for one token): up stored as bf16, relu^2 on load in f32 (one token,
+//           vector.metal:185-190) or in place as bf16 then to half (tiles, nemotron.metal:214-220), down
+//   kind 2  gated FFN (feed_forward.rs:97-104): gate and up stored as bf16, gate kernel
+//           y = bf16(bf16(silu(g)) * u) (elementwise.metal:70-87), down
+// `tile` selects the operand conversions of the tiled kernels (inputs and decoded weights as half) over
+// the exact ones of the one-token kernels. out is bf16 [T][F] for kind 0, [T][H] otherwise.
+void orc_dense_forward(int kind, int fmt, int H, int F, const uint8_t* up_w, const uint8_t* gate_w,
+                       const uint8_t* down_w, const uint16_t* x, int T, int tile_mode, uint16_t* out) {
+    const bool tile = tile_mode != 0;
+    auto dot = dotd;
+    std::vector<float> xin((size_t)T * H);
+    for (size_t i = 0; i < (size_t)T * H; i++) {
+        float v = orc_bf16_to_f32(x[i]);
+        xin[i] = tile ? f16r(v) : v;
+    }
+    const size_t up_row = row_bytes(fmt, H), down_row = row_bytes(fmt, F);
+    std::vector<float> mid(kind == 0 ? 0 : (size_t)T * F);
+#pragma omp parallel
+    {
+        std::vector<float> wrow(std::max(H, F)), wrow2(std::max(H, F));
+#pragma omp for schedule(static)
+        for (int c = 0; c < F; c++) {
+            decode_row(up_w + (size_t)c * up_row, fmt, H, tile, wrow.data());
+            if (kind == 2) decode_row(gate_w + (size_t)c * up_row, fmt, H, tile, wrow2.data());
+            for (int t = 0; t < T; t++) {
+                const float* xr = xin.data() + (size_t)t * H;
+                float up = dot(wrow.data(), xr, H);
+                if (kind == 0) {
+                    out[(size_t)t * F + c] = orc_f32_to_bf16(up);
+                } else if (kind == 1) {
+                    float v = std::max(bf16r(up), 0.0f);
+                    float a = v * v;
+                    if (bf16r(up) != bf16r(up)) a = bf16r(up);
+                    if (tile) a = f16r(bf16r(a));
+                    mid[(size_t)t * F + c] = a;
+                } else {
+                    float a = silu_gate_bf16(bf16r(dot(wrow2.data(), xr, H)), bf16r(up));
+                    mid[(size_t)t * F + c] = tile ? f16r(a) : a;
+                }
+            }
+        }
+        if (kind != 0) {
+#pragma omp for schedule(static)
+            for (int d = 0; d < H; d++) {
+                decode_row(down_w + (size_t)d * down_row, fmt, F, tile, wrow.data());
+                for (int t = 0; t < T; t++)
+                    out[(size_t)t * H + d] = orc_f32_to_bf16(dot(wrow.data(), mid.data() + (size_t)t * F, F));
+            }
+        }
+    }
+}
+
 int orc_num_threads() {
 #ifdef _OPENMP
     return omp_get_max_threads();

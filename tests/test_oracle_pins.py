@@ -154,3 +154,68 @@ def test_rounding_helpers_match_numpy(oracle):
     ref = np.exp(a.astype(np.float64))
     ok = ref > 1e-37
     assert np.max(np.abs(e[ok] - ref[ok]) / ref[ok]) < 3e-7
+
+
+def _dense_f64(kind, fmt, H, F, up_w, gate_w, down_w, x_bits, tile, orc):
+    """The dense kinds in float64 with the kernels' declared operand conversions and bf16 stores, as the
+    reference's own dense test builds its expectation (product_reference, roundoff_bound:
+    src/weights/dispatch_tests/matrix_precision.rs:119-143). Returns (value, magnitude) of the last product."""
+    def half(a):
+        return a.astype(np.float32).astype(np.float16).astype(np.float64) if tile else a
+    def bf(a):
+        return synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(a.astype(np.float32))).astype(np.float64)
+    x = half(synth.bf16_bits_to_f32(x_bits).astype(np.float64))
+    up = half(orc.dequant(fmt, up_w, F * H).reshape(F, H).astype(np.float64))
+    if kind == 0:
+        return x @ up.T, np.abs(x) @ np.abs(up).T
+    u = bf(x @ up.T)
+    if kind == 1:
+        a = np.maximum(u, 0.0) ** 2
+        a = half(bf(a)) if tile else a.astype(np.float32).astype(np.float64)
+    else:
+        g = bf(x @ half(orc.dequant(fmt, gate_w, F * H).reshape(F, H).astype(np.float64)).T)
+        a = half(bf(bf(g / (1.0 + np.exp(-g))) * u))
+    down = half(orc.dequant(fmt, down_w, H * F).reshape(H, F).astype(np.float64))
+    return a @ down.T, np.abs(a) @ np.abs(down).T
+
+
+@pytest.mark.parametrize("kind,fmt", [(0, synth.FMT_Q4_0), (0, synth.FMT_Q4_K), (0, synth.FMT_MXFP4),
+                                      (1, synth.FMT_Q4_0), (2, synth.FMT_Q4_K)])
+@pytest.mark.parametrize("rows", [2, 21])
+def test_dense_products_stay_within_the_reference_roundoff_bound(oracle, kind, fmt, rows):
+    """The reference checks its dense kernels at K = 512, n = 33, m = 2 (exact operands) and m = 21 (half
+    operands) against gamma_(2K+8) * sum|w||x| plus one bf16 storage rounding; the oracle's dense function
+    must sit inside the same bound (intermediate bf16 stores of the feed-forward kinds are applied to the
+    float64 expectation too, so only the last product is bounded)."""
+    H, F = 512, 64 if kind == 0 else 256
+    tile = rows > 2
+    rng = np.random.default_rng(5 + kind)
+    gen = synth._RANDOM[fmt]
+    up_w, gate_w, down_w = gen(rng, F, H), gen(rng, F, H), gen(rng, H, F)
+    x_bits, _ = synth.make_tokens(H, rows, 3, "zero")
+    got = synth.bf16_bits_to_f32(oracle.dense_forward(kind, fmt, H, F, up_w, gate_w, down_w, x_bits, tile)).astype(np.float64)
+    want, mag = _dense_f64(kind, fmt, H, F, up_w, gate_w, down_w, x_bits, tile, oracle)
+    k = H if kind == 0 else F
+    ops = 2 * k + 8
+    gamma = ops * 2.0 ** -24 / (1 - ops * 2.0 ** -24)
+    bound = (1 + 2.0 ** -8) * gamma * mag + 2.0 ** -8 * np.abs(want)
+    if kind != 0:
+        # an intermediate that sits on a bf16 rounding boundary may round the other way in f32: allow the few
+        # outputs that such a flip moves, by their share of the magnitude
+        bound = bound + 2.0 ** -8 * mag * 4.0 / k
+    assert np.all(np.isfinite(got)) and np.all(np.abs(got - want) <= bound), float(np.max(np.abs(got - want) - bound))
+
+
+@pytest.mark.parametrize("tile", [False, True])
+def test_dense_relu2_equals_the_layer_shared_expert(oracle, tile):
+    """With routed down weights decoding to zero and a zero residual, the Nemotron layer's output is its
+    always-on expert alone: the dense function must reproduce it bit for bit in both operand modes."""
+    H, F, S, E, K = 128, 96, 160, 8, 2
+    layer = synth.make_layer(synth.ARCH_NEMOTRON, H, F, E, K, synth.FMT_Q4_0, seed=12, shared_ffn=S, normalize=True, scale=2.5)
+    layer.down_w = np.zeros_like(layer.down_w)              # scale 0: every routed weight is zero
+    rows = 5 if tile else 1
+    x_bits, res = synth.make_tokens(H, rows, 8, "zero")
+    ref = oracle.moe_forward(layer, x_bits, res, mode=2 if tile else 1)
+    got = oracle.dense_forward(1, synth.FMT_Q4_0, H, S, layer.shared_up_w, None, layer.shared_down_w, x_bits, tile)
+    a, b = synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(ref.out)
+    assert np.array_equal(a, b)                             # (+0 and -0 compare equal)
