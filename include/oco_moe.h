@@ -176,6 +176,11 @@ int oco_moe_experts(oco_moe_plan* plan, const uint16_t* rows_bf16, const uint32_
                     uint16_t* y_bf16, void* cuda_stream);
 int oco_moe_combine(oco_moe_plan* plan, const uint16_t* y_bf16, const float* probs, uint16_t* residual_bf16,
                     int rows, void* cuda_stream);
+/* oco_moe_combine for the family with an always-on expert (NEMOTRON), whose output shared_bf16 [rows, hidden]
+ * (oco_dense_forward, OCO_DENSE_FFN_RELU2, computed where the tokens live) joins the residual as a bf16 add
+ * ahead of the routed sum, as on the reference's tiled path (compute/nemotron.rs:316). */
+int oco_moe_combine_shared(oco_moe_plan* plan, const uint16_t* y_bf16, const float* probs, const uint16_t* shared_bf16,
+                           uint16_t* residual_bf16, int rows, void* cuda_stream);
 
 /* The step either side of the layer, in one call (reference Bindings::add_norm followed by
  * Bindings::experts, src/weights/compute.rs:100-117 and src/weights/gpt_oss.rs:122-123; kernels

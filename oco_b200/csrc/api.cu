@@ -776,11 +776,11 @@ int stage_experts(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, in
 // Stage 3: weighted combine of route-ordered expert outputs onto the residual.
 template <int ARCH>
 int stage_combine(oco_moe_plan* plan, const uint16_t* y, const float* probs, uint16_t* residual, int rows,
-                  int shared_mode, cudaStream_t st) {
+                  int shared_mode, cudaStream_t st, const uint16_t* shared = nullptr) {
     const oco_moe_desc& d = plan->d;
     const size_t pairs = (size_t)rows * d.hidden / 2;
     mark(plan, st, "combine");
-    moe_combine_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, st>>>(y, probs, residual, plan->ws.shared_out,
+    moe_combine_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, st>>>(y, probs, residual, shared ? shared : plan->ws.shared_out,
                                                                         d.hidden, rows, d.top_k,
                                                                         ARCH == OCO_ARCH_GPT_OSS ? 1 : 0, shared_mode,
                                                                         plan->have_ws ? plan->ws.status : nullptr);
@@ -1196,6 +1196,19 @@ int oco_moe_combine(oco_moe_plan* plan, const uint16_t* y_bf16, const float* pro
         case OCO_ARCH_NEMOTRON: rc = stage_combine<OCO_ARCH_NEMOTRON>(plan, y_bf16, probs, residual_bf16, rows, 0, st); break;
         default: rc = stage_combine<OCO_ARCH_QWEN>(plan, y_bf16, probs, residual_bf16, rows, 0, st); break;
     }
+    mark(plan, st, "end");
+    return rc;
+}
+
+int oco_moe_combine_shared(oco_moe_plan* plan, const uint16_t* y_bf16, const float* probs, const uint16_t* shared_bf16,
+                           uint16_t* residual_bf16, int rows, void* cuda_stream) {
+    if (!plan) return OCO_INVALID_ARGUMENT;
+    if (!y_bf16 || !probs || !shared_bf16 || !residual_bf16 || rows < 1) return fail(plan, OCO_INVALID_ARGUMENT, "bad buffers or rows");
+    if (plan->d.arch != OCO_ARCH_NEMOTRON) return fail(plan, OCO_UNSUPPORTED_SHAPE, "only the NEMOTRON family has an always-on expert");
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    plan->launches = 0;
+    plan->n_marks = 0;
+    int rc = stage_combine<OCO_ARCH_NEMOTRON>(plan, y_bf16, probs, residual_bf16, rows, 2, st, shared_bf16);
     mark(plan, st, "end");
     return rc;
 }

@@ -64,11 +64,14 @@ def dispatch_layout(ids: torch.Tensor, n_ranks: int, experts_per_rank: int):
 @dataclass
 class Backend:
     """The three compute stages. route(x) -> (ids [T,K], probs [T,K]); experts(rows [R,H], local
-    ids [R]) -> y [R,H]; combine(y_routes [T*K,H], probs [T,K], residual [T,H]) updates residual in
-    place. Rows are bf16 bit patterns held in int16 tensors."""
+    ids [R]) -> y [R,H]; combine(y_routes [T*K,H], probs [T,K], residual [T,H], shared) updates
+    residual in place. `shared` (optional): x [T,H] -> the always-on expert's output [T,H], computed
+    by the rank that owns the tokens while the routed rows travel; combine receives it (else None).
+    Rows are bf16 bit patterns held in int16 tensors."""
     route: Callable
     experts: Callable
     combine: Callable
+    shared: Optional[Callable] = None
 
 
 def forward(x: torch.Tensor, residual: torch.Tensor, backend: Backend, experts_total: int,
@@ -85,6 +88,7 @@ def forward(x: torch.Tensor, residual: torch.Tensor, backend: Backend, experts_t
     epr = experts_total // world
     T, H = x.shape
     ids, probs = backend.route(x)         # a rank without tokens still takes part in every exchange
+    shared_out = backend.shared(x) if backend.shared is not None and T else None
     K = ids.shape[1]
     order, send_counts, local_ids = dispatch_layout(ids, world, epr)
     send_rows = x.index_select(0, order // K)
@@ -126,7 +130,7 @@ def forward(x: torch.Tensor, residual: torch.Tensor, backend: Backend, experts_t
     y_routes = torch.empty_like(y_back)
     y_routes.index_copy_(0, order, y_back)           # back to route order
     if T:
-        backend.combine(y_routes, probs, residual)
+        backend.combine(y_routes, probs, residual, shared_out)
     if ev:
         torch.cuda.synchronize()
         timings["dispatch_ms"] = ev[0].elapsed_time(ev[1])
@@ -144,10 +148,18 @@ class CudaBackend:
         self._lib, self._moe = _lib, moe
         E = layer.experts
         assert E % world == 0, "experts must divide evenly over the ranks"
+        self.shared = None
         if layer.shared_ffn:
-            # the always-on expert belongs to the token-owning rank, beside the routed sum; this protocol moves
-            # routed rows only, so a layer with a shared expert is refused rather than silently losing that term
-            raise moe.OcoError(_lib.UNSUPPORTED_SHAPE, "expert parallelism does not run layers with a shared expert")
+            # the always-on expert belongs to the rank that owns the tokens: a dense feed-forward beside the routed
+            # rows' journey, joined in the combine. At least two rows are reserved so that a rank with one token
+            # still takes the tiles' arithmetic, as every other rank does.
+            from . import dense
+            self._shared_plan = dense.DensePlan(dense.FFN_RELU2, layer.fmt, layer.hidden, layer.shared_ffn)
+            self._shared_plan.reserve(max(max_rows, 2), device)
+            self._shared_plan.bind(layer.shared_up_w, None, layer.shared_down_w, device)
+            self._shared_x = torch.zeros((2, layer.hidden), dtype=torch.int16, device=device)
+            self._shared_y = torch.empty((max(max_rows, 2), layer.hidden), dtype=torch.int16, device=device)
+            self.shared = self._shared_expert
         self.epr = E // world
         lo, hi = rank * self.epr, (rank + 1) * self.epr
         self.layer = layer
@@ -166,6 +178,7 @@ class CudaBackend:
             a = getattr(layer, name)
             setattr(shard, name, None if a is None else a[lo:hi])
         shard.router_w = shard.router_b = None
+        shard.shared_ffn, shard.shared_up_w, shard.shared_down_w = 0, None, None
         self.expert_plan = moe._Plan(layer.arch, layer.hidden, layer.ffn, self.epr, layer.top_k, layer.fmt,
                                      normalize=layer.normalize, scale=layer.scale)
         self.expert_w = moe._Weights.from_layer(shard, device)
@@ -215,8 +228,21 @@ class CudaBackend:
             p.handle, C.c_void_p(win.x_base), C.c_void_p(win.ids_local.data_ptr()), routes, self.K, win.cap_routes,
             win.slot_routes, win.cap_routes, C.c_void_p(win.y_base), self._stream()))
 
-    def combine(self, y_routes, probs, residual):
+    def _shared_expert(self, x):
+        T = x.shape[0]
+        if T == 1:
+            self._shared_x[0].copy_(x[0])
+            x, T = self._shared_x, 2
+        self._shared_plan.forward(x, self._shared_y, T)
+        return self._shared_y
+
+    def combine(self, y_routes, probs, residual, shared=None):
         p = self.router_plan
+        if shared is not None:
+            p._check(self._lib.lib().oco_moe_combine_shared(p.handle, C.c_void_p(y_routes.data_ptr()),
+                                                           C.c_void_p(probs.contiguous().data_ptr()), C.c_void_p(shared.data_ptr()),
+                                                           C.c_void_p(residual.data_ptr()), residual.shape[0], self._stream()))
+            return
         p._check(self._lib.lib().oco_moe_combine(p.handle, C.c_void_p(y_routes.data_ptr()),
                                                 C.c_void_p(probs.contiguous().data_ptr()),
                                                 C.c_void_p(residual.data_ptr()), residual.shape[0], self._stream()))
@@ -228,7 +254,7 @@ class CudaBackend:
         return self.router_plan.launch_count() + 1 + self.expert_plan.launch_count()
 
     def backend(self) -> Backend:
-        return Backend(self.route, self.experts, self.combine)
+        return Backend(self.route, self.experts, self.combine, self.shared)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -379,6 +405,8 @@ def forward_window(x: torch.Tensor, residual: torch.Tensor, backend: "CudaBacken
     dist.all_gather_into_tensor(win.ids_all, win.ids_send, group=win.group)
     if ev:
         ev[1].record()
+    shared = getattr(backend, "shared", None)
+    shared_out = shared(xs) if shared is not None and T else None
     # shard numbering: an id of another shard (or the padding) leaves 0 .. experts_per_rank - 1 and is skipped
     torch.sub(win.ids_all, win.rank * backend.epr, out=win.ids_local)
     backend.experts_window(win)
@@ -388,7 +416,7 @@ def forward_window(x: torch.Tensor, residual: torch.Tensor, backend: "CudaBacken
     if ev:
         ev[3].record()
     if T:
-        backend.combine(win.y_local[: T * K], probs, residual)
+        backend.combine(win.y_local[: T * K], probs, residual, shared_out)
     if ev:
         ev[4].record()
         torch.cuda.synchronize()

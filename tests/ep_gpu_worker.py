@@ -34,10 +34,12 @@ def main():
              (synth.ARCH_GPT_OSS, 16, 4, 320, 288, 200, synth.FMT_MXFP4),
              (synth.ARCH_GPT_OSS, 8, 2, 64, 96, 11, synth.FMT_MXFP4),
              (synth.ARCH_GPT_OSS, 32, 4, 320, 288, 16, synth.FMT_MXFP4),
-             (synth.ARCH_NEMOTRON, 16, 6, 256, 192, 150, synth.FMT_Q4_0)]
+             (synth.ARCH_NEMOTRON, 16, 6, 256, 192, 150, synth.FMT_Q4_0),
+             (synth.ARCH_NEMOTRON, 16, 6, 256, 192, 3, synth.FMT_Q4_0)]
     for n, (arch, E, K, H, F, T, fmt) in enumerate(cases):
-        layer = synth.make_layer(arch, H, F, E, K, fmt, seed=31 + n)
-        layer.shared_ffn, layer.shared_up_w, layer.shared_down_w = 0, None, None   # routed experts only
+        # the Nemotron cases carry the always-on expert, computed by the rank that owns the tokens
+        layer = synth.make_layer(arch, H, F, E, K, fmt, seed=31 + n, shared_ffn=320 if arch == synth.ARCH_NEMOTRON else 0,
+                                 normalize=arch == synth.ARCH_NEMOTRON, scale=2.5 if arch == synth.ARCH_NEMOTRON else 1.0)
         x_all, res_all = synth.make_tokens(H, T, 9 + n, "normal")
         bounds = np.linspace(0, T, world + 1).astype(int)
         lo, hi = bounds[rank], bounds[rank + 1]

@@ -20,6 +20,7 @@ def main():
     # 11 tokens: ranks hold uneven shares; 12: equal shares; 2: with four ranks some hold no token at all
     for T, uniform in ((11, False), (12, True), (2, False)):
         run_case(rank, world, T, uniform)
+    run_shared_case(rank, world, 9)
     descriptors_reach_every_rank(rank, world)
     for T in (11, 12, 2):
         run_window_case(rank, world, T)
@@ -54,7 +55,7 @@ def run_case(rank, world, T, uniform):
         y = oracle.expert_down_tile(layer.down_w, act, layer.down_b, gids, F, H)
         return torch.from_numpy(y.view(np.int16))
 
-    def combine(y_routes, probs, residual):
+    def combine(y_routes, probs, residual, shared_out=None):
         out = oracle.moe_sum(y_routes.numpy().view(np.uint16), probs.numpy(), residual.numpy().view(np.uint16), K)
         residual.copy_(torch.from_numpy(out.view(np.int16)))
 
@@ -73,6 +74,50 @@ def run_case(rank, world, T, uniform):
         sel = order[dest == g]
         assert torch.all(sel[1:] > sel[:-1])
     assert counts.sum().item() == ids.numel() and torch.all(local < epr)
+
+
+def run_shared_case(rank, world, T):
+    """A layer with an always-on expert (Nemotron): the token owner computes it beside the exchange and the
+    combine joins it as the tiled path does (bf16 add ahead of the routed sum)."""
+    E, K, H, F, S = 8, 2, 64, 96, 128
+    layer = synth.make_layer(synth.ARCH_NEMOTRON, H, F, E, K, synth.FMT_Q4_0, seed=79, shared_ffn=S, normalize=True, scale=2.5)
+    x_all, res_all = synth.make_tokens(H, T, 7, "normal")
+    bounds = np.linspace(0, T, world + 1).astype(int)
+    lo, hi = bounds[rank], bounds[rank + 1]
+    e_lo = rank * (E // world)
+
+    def route(x):
+        if x.shape[0] == 0:
+            return torch.empty((0, K), dtype=torch.int32), torch.empty((0, K), dtype=torch.float32)
+        _, ids, probs = oracle.router_sigmoid(x.numpy().view(np.uint16), layer.router_w, layer.router_b, K, True, 2.5)
+        return torch.from_numpy(ids.astype(np.int32)), torch.from_numpy(probs)
+
+    def experts(rows, local_ids):
+        if rows.shape[0] == 0:
+            return torch.empty_like(rows)
+        gids = local_ids.numpy().astype(np.uint32) + e_lo
+        up = oracle.expert_up_tile(layer.up_w, rows.numpy().view(np.uint16), None, 0.0, gids, 1, H, F, fmt=synth.FMT_Q4_0)
+        v = np.maximum(synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(up)), 0.0)
+        act = (v * v).astype(np.float32).astype(np.float16).view(np.uint16)
+        y = oracle.expert_down_tile(layer.down_w, act, None, gids, F, H, fmt=synth.FMT_Q4_0)
+        return torch.from_numpy(y.view(np.int16))
+
+    def shared(x):
+        out = oracle.dense_forward(1, synth.FMT_Q4_0, H, S, layer.shared_up_w, None, layer.shared_down_w,
+                                   x.numpy().view(np.uint16), tile=True)
+        return torch.from_numpy(out.view(np.int16))
+
+    def combine(y_routes, probs, residual, shared_out=None):
+        res = residual.numpy().view(np.uint16)
+        res = synth.f32_to_bf16_bits(synth.bf16_bits_to_f32(res) + synth.bf16_bits_to_f32(shared_out.numpy().view(np.uint16)[: len(res)]))
+        out = oracle.moe_add(y_routes.numpy().view(np.uint16), probs.numpy(), res, None, K)
+        residual.copy_(torch.from_numpy(out.view(np.int16)))
+
+    x = torch.from_numpy(x_all[lo:hi].view(np.int16).copy())
+    res = torch.from_numpy(res_all[lo:hi].view(np.int16).copy())
+    ep.forward(x, res, ep.Backend(route, experts, combine, shared), E)
+    ref = oracle.moe_forward(layer, x_all, res_all, mode=2)
+    assert np.array_equal(res.numpy().view(np.uint16), ref.out[lo:hi]), f"rank {rank}: shared-expert layer differs from the single-process oracle"
 
 
 def descriptors_reach_every_rank(rank, world):
@@ -172,7 +217,7 @@ def run_window_case(rank, world, T):
         y = oracle.expert_down_tile(layer.down_w, oracle.moe_activate(gate, up), layer.down_b, gids, F, H)
         w.y_all[lab] = y.view(np.int16)
 
-    def combine(y_routes, probs, residual):
+    def combine(y_routes, probs, residual, shared_out=None):
         out = oracle.moe_sum(y_routes.numpy().view(np.uint16), probs.numpy(), residual.numpy().view(np.uint16), K)
         residual.copy_(torch.from_numpy(out.view(np.int16)))
 
