@@ -193,15 +193,44 @@ __global__ void __launch_bounds__(1024) route_scatter_kernel(const uint32_t* __r
 // the distance between the two elements a code byte holds (16 for MXFP4 / Q4_0, 32 for Q4_K).
 // The reference gathers inside its tiles (shaders/experts/projections.metal:208-233).
 // CTAs stride over the sorted rows (`rows`, or *live_rows when given: the plan's route total, which
-// may be less than the launch was sized for); each thread emits one half2 = (x[k], x[k + half_span]).
+// may be less than the launch was sized for). A thread takes eight pairs of one block: two 16-byte
+// loads (elements 8q .. 8q + 7 of the block's two halves; the row may sit in another GPU's memory, where
+// small loads would waste the link) and two 16-byte stores of half2 = (x[k], x[k + half_span]). Rows that
+// are not 16-byte aligned take the element-wise form.
 __global__ void __launch_bounds__(256) permute_rows_kernel(const uint16_t* __restrict__ x,
                                                            const uint32_t* __restrict__ route_of_row, int K,
                                                            int H, int half_span, uint16_t* __restrict__ xs,
                                                            uint32_t rows, const uint32_t* __restrict__ live_rows) {
     const uint32_t n = live_rows ? *live_rows : rows;
+    const bool wide = (((uintptr_t)x | (uintptr_t)xs) & 15u) == 0 && (H & 7) == 0;
+    const int per_block = half_span >> 3;                        // threads per block of 2 * half_span elements
+    const int chunks = (H / (2 * half_span)) * per_block;        // 16-byte pieces of pairs per row
     for (uint32_t row = blockIdx.x; row < n; row += gridDim.x) {
         uint32_t token = route_of_row ? route_of_row[row] / (uint32_t)K : row;  // null: rows keep token order
         const uint16_t* src = x + (size_t)token * H;
+        if (wide) {
+            uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)row * H);
+            for (int c = threadIdx.x; c < chunks; c += 256) {
+                const int blk = c / per_block, q = c - blk * per_block;
+                const uint16_t* at = src + (size_t)blk * 2 * half_span + 8 * q;
+                const uint4 a = *reinterpret_cast<const uint4*>(at);
+                const uint4 b = *reinterpret_cast<const uint4*>(at + half_span);
+                const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+                uint32_t o[8];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    __half2 lo = __floats2half2_rn(__uint_as_float(aw[j] << 16), __uint_as_float(bw[j] << 16));
+                    __half2 hi = __floats2half2_rn(__uint_as_float(aw[j] & 0xffff0000u), __uint_as_float(bw[j] & 0xffff0000u));
+                    o[2 * j] = *reinterpret_cast<uint32_t*>(&lo);
+                    o[2 * j + 1] = *reinterpret_cast<uint32_t*>(&hi);
+                }
+                // pairs 8q .. 8q + 7 of the block: two pieces of the block's 2 * half_span halves
+                uint4* out = dst + ((size_t)blk * half_span + 8 * q) / 4;
+                out[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                out[1] = make_uint4(o[4], o[5], o[6], o[7]);
+            }
+            continue;
+        }
         uint32_t* dst = reinterpret_cast<uint32_t*>(xs + (size_t)row * H);
         for (int i = threadIdx.x; i < H / 2; i += 256) {
             int blk = i / half_span, j = i % half_span;           // pair i of the row: block, byte index
