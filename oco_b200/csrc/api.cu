@@ -780,10 +780,17 @@ int stage_combine(oco_moe_plan* plan, const uint16_t* y, const float* probs, uin
     const oco_moe_desc& d = plan->d;
     const size_t pairs = (size_t)rows * d.hidden / 2;
     mark(plan, st, "combine");
-    moe_combine_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, st>>>(y, probs, residual, shared ? shared : plan->ws.shared_out,
-                                                                        d.hidden, rows, d.top_k,
-                                                                        ARCH == OCO_ARCH_GPT_OSS ? 1 : 0, shared_mode,
-                                                                        plan->have_ws ? plan->ws.status : nullptr);
+    const uint16_t* sh = shared ? shared : plan->ws.shared_out;
+    const uint32_t* status = plan->have_ws ? plan->ws.status : nullptr;
+    const int round_sum = ARCH == OCO_ARCH_GPT_OSS ? 1 : 0;
+    if (d.hidden % 8 == 0 && (((uintptr_t)y | (uintptr_t)residual | (uintptr_t)sh) & 15u) == 0) {
+        const size_t octets = pairs / 4;
+        moe_combine8_kernel<<<(unsigned)((octets + 255) / 256), 256, 0, st>>>(y, probs, residual, sh, d.hidden, rows, d.top_k, round_sum,
+                                                                             shared_mode, status);
+    } else {
+        moe_combine_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, st>>>(y, probs, residual, sh, d.hidden, rows, d.top_k, round_sum,
+                                                                            shared_mode, status);
+    }
     plan->launches++;
     CK(cudaGetLastError());
     return OCO_OK;

@@ -332,6 +332,57 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __rest
     *reinterpret_cast<uint32_t*>(out + (size_t)t * H + d) = o;
 }
 
+// The same combine with eight elements per thread (16-byte loads of the expert outputs and the residual):
+// identical arithmetic per element, for hidden sizes that are multiples of eight.
+__global__ void __launch_bounds__(256) moe_combine8_kernel(const uint16_t* __restrict__ y, const float* __restrict__ probs,
+                                                           uint16_t* __restrict__ out, const uint16_t* __restrict__ shared,
+                                                           int H, int T, int K, int round_sum, int shared_mode,
+                                                           const uint32_t* __restrict__ status) {
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    const size_t octets = (size_t)T * H / 8;
+    if (i >= octets) return;
+    if (status && *reinterpret_cast<const volatile uint32_t*>(status) != 0u) return;
+    const int per_row = H / 8;
+    const int t = (int)(i / per_row), d = (int)(i % per_row) * 8;
+    uint4 rw = *reinterpret_cast<const uint4*>(out + (size_t)t * H + d);
+    uint32_t res[4] = {rw.x, rw.y, rw.z, rw.w};
+    float r[8], s[8];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        r[2 * j] = __uint_as_float(res[j] << 16);
+        r[2 * j + 1] = __uint_as_float(res[j] & 0xffff0000u);
+        s[2 * j] = s[2 * j + 1] = 0.f;
+    }
+    if (shared_mode) {
+        const uint4 sw4 = *reinterpret_cast<const uint4*>(shared + (size_t)t * H + d);
+        const uint32_t sw[4] = {sw4.x, sw4.y, sw4.z, sw4.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float h0 = __uint_as_float(sw[j] << 16), h1 = __uint_as_float(sw[j] & 0xffff0000u);
+            if (shared_mode == 1) { s[2 * j] = h0; s[2 * j + 1] = h1; }
+            else { r[2 * j] = bf16_round(__fadd_rn(r[2 * j], h0)); r[2 * j + 1] = bf16_round(__fadd_rn(r[2 * j + 1], h1)); }
+        }
+    }
+    for (int k = 0; k < K; k++) {
+        const uint4 yw4 = *reinterpret_cast<const uint4*>(y + ((size_t)t * K + k) * H + d);
+        const uint32_t yw[4] = {yw4.x, yw4.y, yw4.z, yw4.w};
+        const float p = probs[(size_t)t * K + k];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            s[2 * j] = __fmaf_rn(__uint_as_float(yw[j] << 16), p, s[2 * j]);
+            s[2 * j + 1] = __fmaf_rn(__uint_as_float(yw[j] & 0xffff0000u), p, s[2 * j + 1]);
+        }
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        float a = s[2 * j], b = s[2 * j + 1];
+        if (round_sum) { a = bf16_round(a); b = bf16_round(b); }
+        o[j] = (uint32_t)f32_to_bf16_bits(__fadd_rn(r[2 * j], a)) | ((uint32_t)f32_to_bf16_bits(__fadd_rn(r[2 * j + 1], b)) << 16);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * H + d) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 // The bounded wait, run on a barrier that nobody arrives at: one warp waits `limit` clock cycles, gives
 // up, sets the status word and returns normally. Lets a host test see the whole give-up path
 // (status word -> oco_moe_poll -> OCO_DEVICE_TIMEOUT) without any fault on the device.
