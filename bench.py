@@ -241,7 +241,16 @@ def run_expert_parallel(args, torch, dist, world, rank, local, workload, steps, 
     E, K, H, F = layer.experts, layer.top_k, layer.hidden, layer.ffn
     be = ep.CudaBackend(layer, rank, world, max_rows=T)
     backend = be.backend()
-    win = ep.Windows(H, K, T)
+    # every rank must have its windows, or none uses them
+    win, why = None, ""
+    try:
+        win = ep.Windows(H, K, T)
+    except Exception as e:     # the driver's virtual-memory calls or descriptor passing are unavailable here
+        why = f"{type(e).__name__}: {e}"[:200]
+    ok = torch.tensor([1.0 if win is not None else 0.0], device="cuda")
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if ok.item() == 0.0:
+        raise RuntimeError("expert-parallel windows could not be set up on every rank" + (f" ({why})" if why else ""))
     x_all, res_all = synth.make_tokens(H, total, args.seed, "normal")
     x_bits, res_bits = x_all[rank * T:(rank + 1) * T], res_all[rank * T:(rank + 1) * T]
     hx = torch.from_numpy(x_bits.view(np.int16).copy()).pin_memory()
@@ -829,7 +838,10 @@ def main():
                 solo = measure_layer(args, (torch, dist, 1, 0, local), "gpt-oss-120b-prefill", 10, 3)
                 n1 = solo["ms_per_step"]
             dist.barrier()
-            epr = run_expert_parallel(args, torch, dist, world, rank, local, "gpt-oss-120b-prefill", 10, 3)
+            try:
+                epr = run_expert_parallel(args, torch, dist, world, rank, local, "gpt-oss-120b-prefill", 10, 3)
+            except Exception as e:      # the headline line is printed whatever happens to this block
+                epr = dict(error=f"{type(e).__name__}: {e}"[:300])
             if rank == 0:
                 epr["n1_ms_per_step_same_box"] = n1
                 line["expert_parallel"] = epr

@@ -310,6 +310,21 @@ cudaError_t allow_smem(Kern k) {
                                 (int)(kMaxDynamicSmem - attr.sharedSizeBytes));
 }
 
+// Launches a kernel with programmatic stream serialization: it may be scheduled (and, where it does so
+// before its griddepcontrol.wait, set up its shared memory and barriers) while its predecessor in the stream
+// still runs, and waits for it inside. Every kernel launched this way calls pdl_wait() before it touches
+// anything a predecessor wrote or still reads.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <int FMT, int EPI, int NT>
 int launch_gemm(oco_moe_plan* plan, const GemmParams& gp, const CUtensorMap& map, int max_tiles, cudaStream_t st) {
     using S = GemmShape<EPI, NT>;
@@ -338,7 +353,8 @@ int launch_gemm_wide(oco_moe_plan* plan, GemmParams gp, const CUtensorMap* maps,
     // persistent: one CTA per SM walks the (route tile, feature tile) items; never more CTAs than items can exist
     const int feats = (gp.n + (epi_gated(EPI) ? 127 : 255)) / (epi_gated(EPI) ? 128 : 256);
     const int grid = std::min(plan->sm_count, feats * max_tiles);
-    grouped_gemm_wide_kernel<FMT, EPI><<<grid, WideShapeT<FMT>::kThreads, WideShapeT<FMT>::kSmemBytes, st>>>(gp, maps[0], maps[1], maps[2], maps[3]);
+    CK(launch_dependent(grouped_gemm_wide_kernel<FMT, EPI>, dim3(grid), dim3(WideShapeT<FMT>::kThreads), WideShapeT<FMT>::kSmemBytes, st, gp, maps[0], maps[1],
+                        maps[2], maps[3]));
     plan->launches++;
     CK(cudaGetLastError());
     return OCO_OK;
@@ -365,19 +381,6 @@ int pick_ksplit(int units, int ctas, int warps_per_cta) {
 }
 
 // Ring depth of the single-token kernels by what fits in shared memory (0: nothing fits).
-
-// Launches a single-token kernel with programmatic stream serialization: it may start (and set up
-// its shared memory and barriers) while its predecessor still runs, and waits for it inside.
-template <typename... KArgs, typename... Args>
-cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
-}
 
 template <int ARCH, int FMT>
 int launch_expand(oco_moe_plan* plan, DecodeExpandParams ep, cudaStream_t st) {
@@ -580,11 +583,11 @@ int stage_route(oco_moe_plan* plan, const uint16_t* x, int rows, cudaStream_t st
                 if (waste < best - 1e-9) { best = waste; splits = sp; }
                 if (waste < 1.05) break;
             }
-            router_block_kernel<ARCH><<<dim3(ctas, splits), kRouterBlockThreads, router_block_smem_bytes(H), st>>>(
-                x, rw, plan->w.router_b, rows, H, E, K, d.normalize, d.scale, ws.logits, ws.ids, ws.probs);
+            CK(launch_dependent(router_block_kernel<ARCH>, dim3(ctas, splits), dim3(kRouterBlockThreads), router_block_smem_bytes(H), st,
+                                x, rw, plan->w.router_b, rows, H, E, K, d.normalize, d.scale, ws.logits, ws.ids, ws.probs));
             if (splits > 1) {
-                router_select_kernel<ARCH><<<rows, 32, 0, st>>>(ws.logits, ARCH == OCO_ARCH_NEMOTRON ? plan->w.router_b : nullptr, E, K,
-                                                               d.normalize, d.scale, ws.ids, ws.probs);
+                CK(launch_dependent(router_select_kernel<ARCH>, dim3(rows), dim3(32), 0, st, ws.logits,
+                                    ARCH == OCO_ARCH_NEMOTRON ? plan->w.router_b : (const float*)nullptr, E, K, d.normalize, d.scale, ws.ids, ws.probs));
                 plan->launches++;
             }
         } else {
@@ -592,11 +595,11 @@ int stage_route(oco_moe_plan* plan, const uint16_t* x, int rows, cudaStream_t st
             const int ctas = (rows + 7) / 8;
             int splits = 1;
             while (splits * 2 * ctas <= plan->sm_count && E / (splits * 2) >= 4) splits *= 2;
-            router_stream_kernel<ARCH, 24, 1><<<dim3(ctas, splits), 256, (size_t)6 * H * 4, st>>>(
-                x, rw, plan->w.router_b, rows, H, E, K, d.normalize, d.scale, ws.logits, ws.ids, ws.probs);
+            CK(launch_dependent(router_stream_kernel<ARCH, 24, 1>, dim3(ctas, splits), dim3(256), (size_t)6 * H * 4, st,
+                                x, rw, plan->w.router_b, rows, H, E, K, d.normalize, d.scale, ws.logits, ws.ids, ws.probs));
             if (splits > 1) {
-                router_select_kernel<ARCH><<<rows, 32, 0, st>>>(ws.logits, ARCH == OCO_ARCH_NEMOTRON ? plan->w.router_b : nullptr, E, K,
-                                                               d.normalize, d.scale, ws.ids, ws.probs);
+                CK(launch_dependent(router_select_kernel<ARCH>, dim3(rows), dim3(32), 0, st, ws.logits,
+                                    ARCH == OCO_ARCH_NEMOTRON ? plan->w.router_b : (const float*)nullptr, E, K, d.normalize, d.scale, ws.ids, ws.probs));
                 plan->launches++;
             }
         }
@@ -626,16 +629,17 @@ void launch_route_plan(oco_moe_plan* plan, const uint32_t* ids, int R, int E, in
     Workspace& ws = plan->ws;
     mark(plan, st, "route_plan");
     if (R <= plan->route_plan_single_max) {
-        route_plan_kernel<<<1, 1024, 0, st>>>(ids, (uint32_t)R, (uint32_t)E, (uint32_t)tile_rows, ws.offsets, ws.row_of_route,
-                                              ws.route_of_row, ws.tiles, ws.tile_count, rs.seg_len, rs.seg_stride);
+        (void)launch_dependent(route_plan_kernel, dim3(1), dim3(1024), 0, st, ids, (uint32_t)R, (uint32_t)E, (uint32_t)tile_rows, ws.offsets,
+                               ws.row_of_route, ws.route_of_row, ws.tiles, ws.tile_count, rs.seg_len, rs.seg_stride);
         plan->launches++;
         return;
     }
     const uint32_t chunks = ((uint32_t)R + 1023u) / 1024u;
-    route_count_kernel<<<chunks, 1024, 0, st>>>(ids, (uint32_t)R, (uint32_t)E, ws.row_of_route, ws.chunk_cnt);
-    route_scan_kernel<<<1, 1024, 0, st>>>(chunks, (uint32_t)E, (uint32_t)tile_rows, ws.chunk_cnt, ws.offsets, ws.tiles, ws.tile_count);
-    route_scatter_kernel<<<chunks, 1024, 0, st>>>(ids, (uint32_t)R, (uint32_t)E, ws.chunk_cnt, ws.offsets, rs.seg_len, rs.seg_stride,
-                                                  ws.row_of_route, ws.route_of_row);
+    (void)launch_dependent(route_count_kernel, dim3(chunks), dim3(1024), 0, st, ids, (uint32_t)R, (uint32_t)E, ws.row_of_route, ws.chunk_cnt);
+    (void)launch_dependent(route_scan_kernel, dim3(1), dim3(1024), 0, st, chunks, (uint32_t)E, (uint32_t)tile_rows, ws.chunk_cnt, ws.offsets, ws.tiles,
+                           ws.tile_count);
+    (void)launch_dependent(route_scatter_kernel, dim3(chunks), dim3(1024), 0, st, ids, (uint32_t)R, (uint32_t)E, ws.chunk_cnt, ws.offsets, rs.seg_len,
+                           rs.seg_stride, ws.row_of_route, ws.route_of_row);
     plan->launches += 3;
 }
 
@@ -745,8 +749,8 @@ int stage_experts(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, in
     plan->last_tile_rows = NT;
     launch_route_plan(plan, ids, R, E, NT, rs, st);
     mark(plan, st, "permute");
-    permute_rows_kernel<<<std::min(R, 16 * plan->sm_count), 256, 0, st>>>(x, ws.route_of_row, per_row, H, FMT == OCO_FMT_Q4_K ? 32 : 16, ws.xs,
-                                                                        (uint32_t)R, ws.offsets + E);
+    CK(launch_dependent(permute_rows_kernel, dim3(std::min(R, 16 * plan->sm_count)), dim3(256), 0, st, x, ws.route_of_row, per_row, H,
+                        FMT == OCO_FMT_Q4_K ? 32 : 16, ws.xs, (uint32_t)R, ws.offsets + E));
     plan->launches++;
     CK(cudaGetLastError());
     const int max_tiles = R / NT + (E < R ? E : R);
@@ -785,8 +789,8 @@ int stage_combine(oco_moe_plan* plan, const uint16_t* y, const float* probs, uin
     const int round_sum = ARCH == OCO_ARCH_GPT_OSS ? 1 : 0;
     if (d.hidden % 8 == 0 && (((uintptr_t)y | (uintptr_t)residual | (uintptr_t)sh) & 15u) == 0) {
         const size_t octets = pairs / 4;
-        moe_combine8_kernel<<<(unsigned)((octets + 255) / 256), 256, 0, st>>>(y, probs, residual, sh, d.hidden, rows, d.top_k, round_sum,
-                                                                             shared_mode, status);
+        CK(launch_dependent(moe_combine8_kernel, dim3((unsigned)((octets + 255) / 256)), dim3(256), 0, st, y, probs, residual, sh, d.hidden, rows,
+                            d.top_k, round_sum, shared_mode, status));
     } else {
         moe_combine_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, st>>>(y, probs, residual, sh, d.hidden, rows, d.top_k, round_sum,
                                                                             shared_mode, status);

@@ -65,6 +65,8 @@ __global__ void __launch_bounds__(WideShapeT<FMT>::kThreads, 1)
 grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_b32,
                          const __grid_constant__ CUtensorMap tmap_b64, const __grid_constant__ CUtensorMap tmap_b128,
                          const __grid_constant__ CUtensorMap tmap_b) {
+    pdl_launch_dependents();   // the next kernel of the step may be set up beside this one
+    pdl_wait();                // the kernel before has completed and its writes are visible
     using S = WideShapeT<FMT>;
     constexpr bool GATED = epi_gated(EPI);
     constexpr int NT = S::kNT;

@@ -24,6 +24,8 @@ __global__ void __launch_bounds__(1024) route_plan_kernel(const uint32_t* __rest
                                                           uint32_t* __restrict__ tiles,
                                                           uint32_t* __restrict__ tile_count, uint32_t seg_len = 0,
                                                           uint32_t seg_stride = 0) {
+    pdl_launch_dependents();   // the next kernel of the step may be set up beside this one
+    pdl_wait();                // the kernel before has completed and its writes are visible
     __shared__ uint32_t running[kMaxExperts];
     __shared__ uint32_t warp_cnt[32][kMaxExperts];
     __shared__ uint32_t soff[kMaxExperts + 1];
@@ -99,6 +101,8 @@ __device__ __forceinline__ uint32_t route_label(uint32_t i, uint32_t seg_len, ui
 __global__ void __launch_bounds__(1024) route_count_kernel(const uint32_t* __restrict__ ids, uint32_t R, uint32_t E,
                                                            uint32_t* __restrict__ row_of_route,
                                                            uint32_t* __restrict__ chunk_cnt) {
+    pdl_launch_dependents();   // the next kernel of the step may be set up beside this one
+    pdl_wait();                // the kernel before has completed and its writes are visible
     __shared__ uint32_t warp_cnt[32][kMaxExperts];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     for (uint32_t j = lane; j < E; j += 32) warp_cnt[warp][j] = 0;
@@ -125,6 +129,8 @@ __global__ void __launch_bounds__(1024) route_count_kernel(const uint32_t* __res
 __global__ void __launch_bounds__(1024) route_scan_kernel(uint32_t chunks, uint32_t E, uint32_t tile_rows,
                                                           uint32_t* __restrict__ chunk_cnt, uint32_t* __restrict__ offsets,
                                                           uint32_t* __restrict__ tiles, uint32_t* __restrict__ tile_count) {
+    pdl_launch_dependents();   // the next kernel of the step may be set up beside this one
+    pdl_wait();                // the kernel before has completed and its writes are visible
     __shared__ uint32_t total[kMaxExperts];
     __shared__ uint32_t soff[kMaxExperts + 1];
     __shared__ uint32_t tile_off[kMaxExperts + 1];
@@ -179,6 +185,8 @@ __global__ void __launch_bounds__(1024) route_scatter_kernel(const uint32_t* __r
                                                              const uint32_t* __restrict__ offsets, uint32_t seg_len,
                                                              uint32_t seg_stride, uint32_t* __restrict__ row_of_route,
                                                              uint32_t* __restrict__ route_of_row) {
+    pdl_launch_dependents();   // the next kernel of the step may be set up beside this one
+    pdl_wait();                // the kernel before has completed and its writes are visible
     const uint32_t i = blockIdx.x * 1024u + threadIdx.x;
     if (i >= R) return;
     const uint32_t e = ids[i];
@@ -201,6 +209,8 @@ __global__ void __launch_bounds__(256) permute_rows_kernel(const uint16_t* __res
                                                            const uint32_t* __restrict__ route_of_row, int K,
                                                            int H, int half_span, uint16_t* __restrict__ xs,
                                                            uint32_t rows, const uint32_t* __restrict__ live_rows) {
+    pdl_launch_dependents();   // the next kernel of the step may be set up beside this one
+    pdl_wait();                // the kernel before has completed and its writes are visible
     const uint32_t n = live_rows ? *live_rows : rows;
     const bool wide = (((uintptr_t)x | (uintptr_t)xs) & 15u) == 0 && (H & 7) == 0;
     const int per_block = half_span >> 3;                        // threads per block of 2 * half_span elements
@@ -306,6 +316,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __rest
                                                           const uint16_t* __restrict__ shared, int H, int T, int K,
                                                           int round_sum, int shared_mode,
                                                           const uint32_t* __restrict__ status) {
+    pdl_launch_dependents();   // the next kernel of the step may be set up beside this one
+    pdl_wait();                // the kernel before has completed and its writes are visible
     size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     size_t pairs = (size_t)T * H / 2;
     if (i >= pairs) return;
@@ -338,6 +350,8 @@ __global__ void __launch_bounds__(256) moe_combine8_kernel(const uint16_t* __res
                                                            uint16_t* __restrict__ out, const uint16_t* __restrict__ shared,
                                                            int H, int T, int K, int round_sum, int shared_mode,
                                                            const uint32_t* __restrict__ status) {
+    pdl_launch_dependents();   // the next kernel of the step may be set up beside this one
+    pdl_wait();                // the kernel before has completed and its writes are visible
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     const size_t octets = (size_t)T * H / 8;
     if (i >= octets) return;

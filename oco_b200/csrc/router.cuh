@@ -216,6 +216,8 @@ __global__ void __launch_bounds__(32) router_select_kernel(const float* __restri
                                                            const float* __restrict__ sel_bias, int E, int K,
                                                            int normalize, float scale, uint32_t* __restrict__ ids,
                                                            float* __restrict__ probs) {
+    pdl_launch_dependents();   // the next kernel of the step may be set up beside this one
+    pdl_wait();                // the kernel before has completed and its writes are visible
     int t = blockIdx.x, lane = threadIdx.x;
     float v[4];
     load_logits(logits + (size_t)t * E, E, lane, v);
@@ -237,6 +239,8 @@ __global__ void __launch_bounds__(256) router_batched_kernel(const uint16_t* __r
                                                              int K, int normalize, float scale,
                                                              float* __restrict__ logits, uint32_t* __restrict__ ids,
                                                              float* __restrict__ probs) {
+    pdl_launch_dependents();   // the next kernel of the step may be set up beside this one
+    pdl_wait();                // the kernel before has completed and its writes are visible
     extern __shared__ __align__(16) unsigned char smem[];
     float* ws = reinterpret_cast<float*>(smem);                      // [H]
     uint16_t* xs = reinterpret_cast<uint16_t*>(smem + (size_t)H * 4);  // [8][H]
@@ -298,6 +302,8 @@ __global__ void __launch_bounds__(256, TOK == 1 ? 2 : 1) router_stream_kernel(co
                                                                const float* __restrict__ bias, int T, int H, int E, int K,
                                                                int normalize, float scale, float* __restrict__ logits,
                                                                uint32_t* __restrict__ ids, float* __restrict__ probs) {
+    pdl_launch_dependents();   // the next kernel of the step may be set up beside this one
+    pdl_wait();                // the kernel before has completed and its writes are visible
     extern __shared__ __align__(16) unsigned char smem[];
     float* ring = reinterpret_cast<float*>(smem);                  // [3][2][H]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -425,6 +431,8 @@ __global__ void __launch_bounds__(kRouterBlockThreads, 256 / kRouterBlockThreads
                                                               const float* __restrict__ bias, int T, int H, int E, int K,
                                                               int normalize, float scale, float* __restrict__ logits,
                                                               uint32_t* __restrict__ ids, float* __restrict__ probs) {
+    pdl_launch_dependents();   // the next kernel of the step may be set up beside this one
+    pdl_wait();                // the kernel before has completed and its writes are visible
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int KC = kRouterBlockCols, STEPS = KC / 128;
     uint16_t* xs = reinterpret_cast<uint16_t*>(smem);                                   // [32][H] bf16
