@@ -533,21 +533,24 @@ def measure_layer(args, ctx, workload, steps, warmup, tokens=0, graph=True, with
     torch.cuda.synchronize()
     plans[0].poll()
     if decode and graph:
-        # A single token is a handful of microsecond kernels: capture each weight copy's step in a
-        # CUDA graph so the timed region measures the GPU, not the host's launch rate.
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
+        # A single token is a handful of microsecond kernels: record each weight copy's step as a graph of the
+        # library (oco_moe_graph_capture) so the timed region measures the GPU, not the host's launch rate.
+        # (The fused add-norm entry point has no graph call of its own and is captured through torch.)
+        if not with_norm:
             for c in range(copies):
                 plans[c].set_profiling(False)
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=side):
-                    if with_norm:
+                graphs[c] = plans[c].capture(x, res, tokens)
+        else:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for c in range(copies):
+                    plans[c].set_profiling(False)
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
                         plans[c].add_norm_forward(res, x, norm_w, 1e-5, layer.arch == synth.ARCH_GPT_OSS, tokens)
-                    else:
-                        plans[c].forward(x, res, tokens)
-                graphs[c] = g
-        torch.cuda.current_stream().wait_stream(side)
+                    graphs[c] = g
+            torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
     # routing of this batch (for the algorithmic byte count)
     routing = moe.Routing(); routing.plan, routing.rows = plans[(warmup - 1) % copies if warmup else 0], tokens

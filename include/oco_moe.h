@@ -279,6 +279,19 @@ int oco_moe_selftest_wait_timeout(oco_moe_plan* plan, long long wait_cycles, voi
  * roofline fractions; allocates 256 bytes for the call's duration. No counterpart in the reference. */
 int oco_tensor_peak(int kind, int iters, float* tflops);
 
+/* One forward call recorded as a CUDA graph and replayed with one launch: the counterpart of the
+ * reference encoding a step's dispatches into one command buffer and committing it
+ * (Compute::submit, src/weights/compute/submission.rs:21-107). A single-token step is three to five small
+ * kernels and is bound by the host's launch rate when they are launched one by one.
+ *   oco_moe_graph_capture  records oco_moe_forward(plan, x, residual, rows) (the same pointers on every
+ *                          replay: the caller refreshes their contents). Set-up call: synchronises.
+ *   oco_moe_graph_launch   enqueues one replay on the stream.
+ * The plan, its workspace and its weights must outlive the graph and must not be re-bound while it lives. */
+typedef struct oco_moe_graph oco_moe_graph;
+int oco_moe_graph_capture(oco_moe_plan* plan, const uint16_t* x_bf16, uint16_t* residual_bf16, int rows, oco_moe_graph** out);
+int oco_moe_graph_launch(oco_moe_graph* graph, void* cuda_stream);
+void oco_moe_graph_destroy(oco_moe_graph* graph);
+
 /* The dense products either side of the MoE layer: the reference's DenseMatrix::apply
  * (src/weights/compute/matrix.rs:130-278) composed as its callers compose it.
  *   OCO_DENSE_PROJECTION     y[rows, ffn] = up_w . x, stored as bf16 (any of the three weight formats)

@@ -115,6 +115,11 @@ struct oco_moe_plan {
     char err[256] = {0};
 };
 
+struct oco_moe_graph {
+    cudaGraphExec_t exec = nullptr;
+    oco_moe_plan* plan = nullptr;
+};
+
 namespace {
 
 int fail(oco_moe_plan* p, int code, const char* fmt, ...) {
@@ -1222,6 +1227,52 @@ int oco_moe_combine_shared(oco_moe_plan* plan, const uint16_t* y_bf16, const flo
     int rc = stage_combine<OCO_ARCH_NEMOTRON>(plan, y_bf16, probs, residual_bf16, rows, 2, st, shared_bf16);
     mark(plan, st, "end");
     return rc;
+}
+
+int oco_moe_graph_capture(oco_moe_plan* plan, const uint16_t* x_bf16, uint16_t* residual_bf16, int rows, oco_moe_graph** out) {
+    if (!plan || !out) return OCO_INVALID_ARGUMENT;
+    *out = nullptr;
+    if (plan->profiling) return fail(plan, OCO_INVALID_ARGUMENT, "switch profiling off before recording a graph");
+    if (int rc_dev = check_device(plan)) return rc_dev;
+    cudaStream_t side = nullptr;
+    CK(cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking));
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int rc = OCO_OK;
+    if (cudaStreamBeginCapture(side, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+        cudaStreamDestroy(side);
+        return fail(plan, OCO_CUDA_ERROR, "cudaStreamBeginCapture failed");
+    }
+    rc = oco_moe_forward(plan, x_bf16, residual_bf16, rows, side);
+    const cudaError_t end = cudaStreamEndCapture(side, &graph);      // always ends the capture, also after a refused call
+    if (rc == OCO_OK && (end != cudaSuccess || !graph)) rc = fail(plan, OCO_CUDA_ERROR, "cudaStreamEndCapture: %s", cudaGetErrorString(end));
+    if (rc == OCO_OK && cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) rc = fail(plan, OCO_CUDA_ERROR, "cudaGraphInstantiate failed");
+    if (graph) cudaGraphDestroy(graph);
+    cudaStreamDestroy(side);
+    (void)cudaGetLastError();
+    if (rc != OCO_OK) return rc;
+    oco_moe_graph* g = new (std::nothrow) oco_moe_graph();
+    if (!g) { cudaGraphExecDestroy(exec); return OCO_OUT_OF_MEMORY; }
+    g->exec = exec;
+    g->plan = plan;
+    *out = g;
+    return OCO_OK;
+}
+
+int oco_moe_graph_launch(oco_moe_graph* graph, void* cuda_stream) {
+    if (!graph || !graph->exec) return OCO_INVALID_ARGUMENT;
+    if (int rc_dev = check_device(graph->plan)) return rc_dev;
+    if (cudaGraphLaunch(graph->exec, (cudaStream_t)cuda_stream) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return fail(graph->plan, OCO_CUDA_ERROR, "cudaGraphLaunch failed");
+    }
+    return OCO_OK;
+}
+
+void oco_moe_graph_destroy(oco_moe_graph* graph) {
+    if (!graph) return;
+    if (graph->exec) cudaGraphExecDestroy(graph->exec);
+    delete graph;
 }
 
 int oco_moe_forward_host(oco_moe_plan* plan, const uint16_t* x_host, uint16_t* residual_host, int rows,

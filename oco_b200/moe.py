@@ -59,6 +59,24 @@ def _dev_bytes(a: Optional[np.ndarray], device, misalign: int = 0) -> Optional[t
     return buf[misalign:misalign + flat.numel()]
 
 
+class StepGraph:
+    """A recorded forward step (oco_moe_graph_*); keeps its plan and buffers alive."""
+
+    def __init__(self, plan, handle, keep):
+        self.plan, self.handle, self._keep = plan, handle, keep
+
+    def replay(self):
+        self.plan._check(_lib.lib().oco_moe_graph_launch(self.handle, _stream_ptr()))
+
+    def __del__(self):
+        try:
+            if self.handle:
+                _lib.lib().oco_moe_graph_destroy(self.handle)
+                self.handle = C.c_void_p()
+        except Exception:
+            pass
+
+
 class _Plan:
     """Owns the C plan object, its workspace and the bound weights."""
 
@@ -114,6 +132,12 @@ class _Plan:
     def forward_host(self, x: np.ndarray, residual: np.ndarray, rows: int):
         self._check(_lib.lib().oco_moe_forward_host(self.handle, x.ctypes.data_as(C.c_void_p),
                                                     residual.ctypes.data_as(C.c_void_p), rows, _stream_ptr()))
+
+    def capture(self, x: torch.Tensor, residual: torch.Tensor, rows: int) -> "StepGraph":
+        """The forward call on these buffers as a graph of the library (one launch per replay)."""
+        g = C.c_void_p()
+        self._check(_lib.lib().oco_moe_graph_capture(self.handle, _ptr(x), _ptr(residual), rows, C.byref(g)))
+        return StepGraph(self, g, (x, residual))
 
     def poll(self):
         self._check(_lib.lib().oco_moe_poll(self.handle, _stream_ptr()))

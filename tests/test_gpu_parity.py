@@ -689,3 +689,39 @@ def test_block_scaled_numerics_are_refused_where_they_do_not_apply(moe):
     assert e.value.code == _lib.UNSUPPORTED_SHAPE
     with pytest.raises(moe.OcoError):
         moe._Plan(synth.ARCH_GPT_OSS, 512, 256, 16, 4, synth.FMT_MXFP4, numerics=1)
+
+
+def test_recorded_step_replays_the_forward_call(moe, oracle):
+    """oco_moe_graph_capture / _launch: one token's step recorded once and replayed on fresh buffer contents
+    gives what the direct call gives, bit for bit; a refused call leaves no capture open."""
+    import torch
+    from oco_b200 import _lib
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, 256, 192, 32, 4, synth.FMT_MXFP4, seed=71)
+    plan = moe.plan_for(layer)
+    plan.reserve(4)
+    w = moe._Weights.from_layer(layer)
+    plan.bind(w)
+    x = torch.zeros((1, layer.hidden), dtype=torch.int16, device="cuda")
+    res = torch.zeros((1, layer.hidden), dtype=torch.int16, device="cuda")
+    g = plan.capture(x, res, 1)
+    for seed in (3, 4):
+        xb, rb = synth.make_tokens(layer.hidden, 1, seed, "normal")
+        x.copy_(torch.from_numpy(xb.view(np.int16)))
+        res.copy_(torch.from_numpy(rb.view(np.int16)))
+        g.replay()
+        torch.cuda.synchronize()
+        got = res.cpu().numpy().view(np.uint16).copy()
+        res.copy_(torch.from_numpy(rb.view(np.int16)))
+        plan.forward(x, res, 1)
+        torch.cuda.synchronize()
+        assert np.array_equal(got, res.cpu().numpy().view(np.uint16))
+        ref = oracle.moe_forward(layer, xb, rb)
+        assert rel_l2(got, ref.out) <= REL_L2
+    plan.poll()
+    # more rows than reserved: refused, and the next direct call still works (the capture was closed)
+    with pytest.raises(moe.OcoError) as e:
+        plan.capture(x, res, 9)
+    assert e.value.code == _lib.INVALID_ARGUMENT
+    plan.forward(x, res, 1)
+    torch.cuda.synchronize()
+    plan.poll()
