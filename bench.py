@@ -631,7 +631,7 @@ def measure_layer(args, ctx, workload, steps, warmup, tokens=0, graph=True, with
     hres = torch.from_numpy(res_bits.view(np.int16).copy()).pin_memory()
     hx_np, hres_np = hx.numpy().view(np.uint16), hres.numpy().view(np.uint16)
     e2e_steps = max(3, min(steps, 20))
-    for i in range(2):
+    for i in range(max(2, copies)):      # every weight copy's plan once: its first call sets up its copy stream and events
         plans[i % copies].forward_host(hx_np, hres_np, tokens)
     if world > 1:
         dist.barrier()
