@@ -725,3 +725,75 @@ def test_recorded_step_replays_the_forward_call(moe, oracle):
     plan.forward(x, res, 1)
     torch.cuda.synchronize()
     plan.poll()
+
+
+@pytest.mark.parametrize("tokens_per_source,single_max", [(40, "2048"), (700, "0"), (700, "2048")], ids=["few", "many_cta_plan", "one_cta_plan"])
+def test_expert_stage_over_a_window_numbering(moe, oracle, tokens_per_source, single_max, monkeypatch):
+    """oco_moe_experts_window on one GPU, three sources' rows and outputs in one buffer laid out as the
+    expert-parallel windows are (slot strides wider than the slots' contents): routes of this shard are read
+    at label / top_k and answered at label exactly as oco_moe_experts answers the same rows handed over
+    compactly; routes of other shards and the padding leave their output rows untouched."""
+    import ctypes as C
+    import torch
+    from oco_b200 import _lib, ep
+    monkeypatch.setenv("OCO_MOE_ROUTE_PLAN_SINGLE_MAX", single_max)
+    E, K, H, F = 16, 4, 320, 288
+    sources, cap = 3, tokens_per_source
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, H, F, E, K, synth.FMT_MXFP4, seed=91)
+    lo, epr = 4, 8                                            # this shard: experts 4 .. 11
+    shard = synth.Layer(**{**layer.__dict__})
+    shard.experts = epr
+    for name in ("gate_w", "up_w", "down_w", "gate_b", "up_b", "down_b"):
+        setattr(shard, name, getattr(layer, name)[lo:lo + epr])
+    shard.router_w = shard.router_b = None
+    plan = moe._Plan(synth.ARCH_GPT_OSS, H, F, epr, K, synth.FMT_MXFP4)
+    plan.reserve(sources * cap)
+    plan.bind(moe._Weights.from_layer(shard))
+    slot_tokens, slot_routes = ep.window_geometry(H, K, cap, 4096)       # any granularity: one buffer stands for the windows
+    assert slot_tokens > cap or tokens_per_source % 32 == 0
+    cap_routes = cap * K
+    x_bits, _ = synth.make_tokens(H, sources * cap, 5, "normal")
+    _, ids, _ = oracle.router_gptoss(x_bits, layer.router_w, layer.router_b, K)
+    live = [cap, cap - 7, 1]                                             # tokens each source brings; the rest is padding
+    xw = np.zeros((sources * slot_tokens, H), np.uint16)
+    ids_all = np.full((sources, cap_routes), 0xffffffff, np.uint32)
+    for g in range(sources):
+        xw[g * slot_tokens: g * slot_tokens + live[g]] = x_bits[g * cap: g * cap + live[g]]
+        ids_all[g, : live[g] * K] = ids[g * cap: g * cap + live[g]].reshape(-1)
+    local = (ids_all.reshape(-1) - np.uint32(lo)).astype(np.uint32)     # other shards' ids wrap out of 0 .. epr - 1
+    labels = ep.window_labels(sources, cap_routes, slot_routes)
+    mine = np.nonzero(local < epr)[0]
+    xd = torch.from_numpy(xw.view(np.int16)).cuda()
+    idd = torch.from_numpy(local.view(np.int32)).cuda()
+    sentinel = np.int16(0x7fc1)          # the canary the reference's tests put around their outputs
+    yw = torch.full((sources * slot_routes, H), int(sentinel), dtype=torch.int16, device="cuda")
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = _lib.lib().oco_moe_experts_window(plan.handle, C.c_void_p(xd.data_ptr()), C.c_void_p(idd.data_ptr()), sources * cap_routes, K,
+                                           cap_routes, slot_routes, len(mine), C.c_void_p(yw.data_ptr()), st)
+    assert rc == _lib.OK, _lib.lib().oco_moe_last_error(plan.handle)
+    torch.cuda.synchronize(); plan.poll()
+    got = yw.cpu().numpy()
+    # the same routes handed over compactly, in the same order
+    rows = torch.from_numpy(xw[labels[mine] // K].view(np.int16)).cuda()
+    cid = torch.from_numpy(local[mine].view(np.int32)).cuda()
+    yc = torch.zeros((len(mine), H), dtype=torch.int16, device="cuda")
+    rc = _lib.lib().oco_moe_experts(plan.handle, C.c_void_p(rows.data_ptr()), C.c_void_p(cid.data_ptr()), len(mine), C.c_void_p(yc.data_ptr()), st)
+    assert rc == _lib.OK, _lib.lib().oco_moe_last_error(plan.handle)
+    torch.cuda.synchronize(); plan.poll()
+    assert np.array_equal(got[labels[mine]], yc.cpu().numpy()), "window numbering changes the result"
+    untouched = np.ones(len(got), bool)
+    untouched[labels[mine]] = False
+    assert np.all(got[untouched] == sentinel), "rows that belong to other shards, to padding or to slot gaps were written"
+    # and against the oracle
+    gids = local[mine] + np.uint32(lo)
+    xr = xw[labels[mine] // K]
+    up = oracle.expert_up_tile(layer.up_w, xr, layer.up_b, 1.0, gids, 1, H, F)
+    gate = oracle.expert_up_tile(layer.gate_w, xr, layer.gate_b, 0.0, gids, 1, H, F)
+    ref = oracle.expert_down_tile(layer.down_w, oracle.moe_activate(gate, up), layer.down_b, gids, F, H)
+    assert rel_l2(got[labels[mine]].view(np.uint16), ref) <= REL_L2
+    # refused numberings
+    for bad in (dict(per=0), dict(seg=cap_routes, stride=cap_routes - 1), dict(seg=cap_routes, stride=cap_routes + 1)):
+        rc = _lib.lib().oco_moe_experts_window(plan.handle, C.c_void_p(xd.data_ptr()), C.c_void_p(idd.data_ptr()), sources * cap_routes,
+                                               bad.get("per", K), bad.get("seg", cap_routes), bad.get("stride", slot_routes), 0,
+                                               C.c_void_p(yw.data_ptr()), st)
+        assert rc == _lib.INVALID_ARGUMENT
