@@ -148,13 +148,13 @@ def algorithmic(layer: synth.Layer, tokens: int, ids: np.ndarray):
     return total_bytes, layer.flops(tokens), touched
 
 
-def cpu_baseline(layer, tokens, seed, budget_tokens, threads=None):
+def cpu_baseline(layer, tokens, seed, sample_tokens, threads=None):
     """Times the CPU restatement (f32 FMA accumulation, all host threads) on a bounded sample of
-    the same workload: the first `budget_tokens` tokens of the batch."""
+    the same workload: the first `sample_tokens` tokens of the batch."""
     import oracle
     # all the cores this process may use, whatever OMP_NUM_THREADS says (torchrun sets it to 1)
     oracle.set_num_threads(threads or len(os.sched_getaffinity(0)))
-    n = max(1, min(tokens, budget_tokens))
+    n = max(1, min(tokens, sample_tokens))
     x, res = synth.make_tokens(layer.hidden, tokens, seed, "normal")
     x, res = x[:n], res[:n]
     mode = 1 if tokens == 1 else 2
