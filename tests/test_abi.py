@@ -71,3 +71,42 @@ def test_product_package_does_not_touch_the_oracle():
                 text = open(os.path.join(dirpath, f)).read()
                 assert "import oracle" not in text and "from oracle" not in text, f
                 assert "moe_oracle" not in text, f
+
+
+def test_dense_window_and_graph_calls_check_their_arguments(lib):
+    """The entry points added beside the layer answer bad arguments with a status and a message on a machine
+    without a GPU too: nothing is dereferenced, nothing aborts."""
+    h = C.c_void_p()
+    for kind, fmt, code in ((0, 39, _lib.OK), (1, 2, _lib.OK), (2, 12, _lib.OK), (1, 12, _lib.UNSUPPORTED_SHAPE),
+                            (2, 2, _lib.UNSUPPORTED_SHAPE), (1, 39, _lib.UNSUPPORTED_SHAPE), (5, 2, _lib.INVALID_ARGUMENT)):
+        desc = _lib.DenseDesc(kind=kind, weight_format=fmt, hidden=512, ffn=512)
+        rc = lib.oco_dense_plan_create(C.byref(desc), C.byref(h))
+        assert rc == code, (kind, fmt, rc, lib.oco_dense_last_error(h))
+        if rc != _lib.OK:
+            assert lib.oco_dense_last_error(h)
+        else:
+            assert lib.oco_dense_workspace_bytes(h, 16) > 16 * 512 * 2
+            assert lib.oco_dense_forward(h, None, None, 1, None) == _lib.INVALID_ARGUMENT      # nothing bound
+        lib.oco_dense_plan_destroy(h)
+    desc = _lib.DenseDesc(kind=0, weight_format=12, hidden=512, ffn=48)        # a projection's width: multiples of 32
+    assert lib.oco_dense_plan_create(C.byref(desc), C.byref(h)) == _lib.UNSUPPORTED_SHAPE
+    lib.oco_dense_plan_destroy(h)
+    assert lib.oco_dense_plan_create(None, None) == _lib.INVALID_ARGUMENT
+    # windows: rank outside the world, no backing, backing larger than the slot
+    w = C.c_void_p()
+    for rank, world, stride, backed in ((2, 2, 1 << 21, 1 << 20), (0, 0, 1 << 21, 1 << 20), (0, 2, 1 << 21, 0), (0, 2, 1 << 20, 1 << 21)):
+        assert lib.oco_ep_window_create(rank, world, stride, backed, C.byref(w)) == _lib.INVALID_ARGUMENT
+        assert lib.oco_ep_window_error()
+    assert lib.oco_ep_window_fd(None) == -1 and lib.oco_ep_window_base(None) is None and lib.oco_ep_window_stride(None) == 0
+    assert lib.oco_ep_window_attach(None, 0, 0) == _lib.INVALID_ARGUMENT
+    lib.oco_ep_window_destroy(None)
+    # graphs and the windowed expert stage on a plan without buffers
+    rc, plan, _ = _create(lib)
+    assert rc == _lib.OK
+    g = C.c_void_p()
+    assert lib.oco_moe_graph_capture(plan, None, None, 1, C.byref(g)) != _lib.OK and not g
+    assert lib.oco_moe_graph_launch(None, None) == _lib.INVALID_ARGUMENT
+    lib.oco_moe_graph_destroy(None)
+    assert lib.oco_moe_experts_window(plan, None, None, 4, 1, 0, 0, 0, None, None) == _lib.INVALID_ARGUMENT
+    assert lib.oco_moe_combine_shared(plan, None, None, None, None, 1, None) == _lib.INVALID_ARGUMENT
+    lib.oco_moe_plan_destroy(plan)
