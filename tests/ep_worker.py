@@ -19,7 +19,7 @@ def main():
     rank, world = dist.get_rank(), dist.get_world_size()
     # 11 tokens: ranks hold uneven shares; 12: equal shares; 2: with four ranks some hold no token at all
     for T, uniform in ((11, False), (12, True), (2, False)):
-        run_case(rank, world, T, uniform)
+        run_case(rank, world, T, uniform and T % world == 0)     # equal shares only when the tokens divide evenly
     run_shared_case(rank, world, 9)
     descriptors_reach_every_rank(rank, world)
     for T in (11, 12, 2):
@@ -158,6 +158,11 @@ class SharedWindows:
             dist.barrier()
             if self.rank != 0:
                 shm = shared_memory.SharedMemory(name=name)
+                try:      # rank 0 owns the segment: the other ranks' resource trackers must not unlink it again
+                    from multiprocessing import resource_tracker
+                    resource_tracker.unregister(shm._name, "shared_memory")
+                except Exception:
+                    pass
             self._shm.append(shm)
             views.append(np.ndarray((self.world * rows, hidden), dtype=np.int16, buffer=shm.buf))
         self.x_all, self.y_all = views

@@ -1,4 +1,4 @@
-"""Expert parallelism on CPU: two and four gloo ranks dispatch, compute (oracle) and combine; every
+"""Expert parallelism on CPU: two, four and eight gloo ranks dispatch, compute (oracle) and combine; every
 rank's rows must equal the single-process oracle bit for bit."""
 import os
 import socket
@@ -16,7 +16,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_expert_parallel_matches_single_process(oracle, world):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), os.path.join(ROOT, "tests", "ep_worker.py")]
