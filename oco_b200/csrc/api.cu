@@ -582,19 +582,18 @@ int stage_route(oco_moe_plan* plan, const uint16_t* x, int rows, cudaStream_t st
             // last round of CTAs is nearly full (the fewest splits that waste under 5 % of it, else the best)
             int splits = 1;
             double best = 1e9;
-            for (int sp = 1; sp <= 8 && E / sp >= 4 && E % (4 * sp) == 0; sp *= 2) {
-                const double rounds = (double)ctas * sp / (plan->sm_count * (256 / kRouterBlockThreads));
+            for (int sp = 1; sp <= 8 && E / sp >= kRouterBlockExperts && E % (kRouterBlockExperts * sp) == 0; sp *= 2) {
+                const double rounds = (double)ctas * sp / plan->sm_count;
                 const double waste = std::ceil(rounds) / rounds;
                 if (waste < best - 1e-9) { best = waste; splits = sp; }
                 if (waste < 1.05) break;
             }
             CK(launch_dependent(router_block_kernel<ARCH>, dim3(ctas, splits), dim3(kRouterBlockThreads), router_block_smem_bytes(H), st,
                                 x, rw, plan->w.router_b, rows, H, E, K, d.normalize, d.scale, ws.logits, ws.ids, ws.probs));
-            if (splits > 1) {
-                CK(launch_dependent(router_select_kernel<ARCH>, dim3(rows), dim3(32), 0, st, ws.logits,
-                                    ARCH == OCO_ARCH_NEMOTRON ? plan->w.router_b : (const float*)nullptr, E, K, d.normalize, d.scale, ws.ids, ws.probs));
-                plan->launches++;
-            }
+            // the logits of a token are spread over the kernel's warps (and CTAs): the selection is a launch of its own
+            CK(launch_dependent(router_select_kernel<ARCH>, dim3(rows), dim3(32), 0, st, ws.logits,
+                                ARCH == OCO_ARCH_NEMOTRON ? plan->w.router_b : (const float*)nullptr, E, K, d.normalize, d.scale, ws.ids, ws.probs));
+            plan->launches++;
         } else {
             // few tokens: split the experts over several CTAs per token group so that the grid fills the GPU
             const int ctas = (rows + 7) / 8;

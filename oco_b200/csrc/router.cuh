@@ -420,14 +420,15 @@ __global__ void __launch_bounds__(256, TOK == 1 ? 2 : 1) router_stream_kernel(co
 // the same butterfly, so the logits are bit-identical to canonical_logit.
 // grid (ceil(T / 32), splits) as router_stream_kernel; hidden <= 3072 and a multiple of 8.
 // Dynamic shared memory: router_block_smem_bytes(H).
-constexpr int kRouterBlockTokens = 32, kRouterBlockCols = 640, kRouterBlockStages = 3;
-constexpr int kRouterBlockThreads = kRouterBlockTokens * 8;
+constexpr int kRouterBlockTokens = 32, kRouterBlockCols = 384, kRouterBlockStages = 3;
+constexpr int kRouterBlockExperts = 8;                              // experts per ring stage: two warps share four tokens, four experts each
+constexpr int kRouterBlockThreads = kRouterBlockTokens * 8 * (kRouterBlockExperts / 4);
 __host__ __device__ inline size_t router_block_smem_bytes(int H) {
-    return (size_t)kRouterBlockTokens * H * 2 + (size_t)kRouterBlockStages * 4 * kRouterBlockCols * 4;
+    return (size_t)kRouterBlockTokens * H * 2 + (size_t)kRouterBlockStages * kRouterBlockExperts * kRouterBlockCols * 4;
 }
 
 template <int ARCH>
-__global__ void __launch_bounds__(kRouterBlockThreads, 256 / kRouterBlockThreads) router_block_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w,
+__global__ void __launch_bounds__(kRouterBlockThreads, 1) router_block_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w,
                                                               const float* __restrict__ bias, int T, int H, int E, int K,
                                                               int normalize, float scale, float* __restrict__ logits,
                                                               uint32_t* __restrict__ ids, float* __restrict__ probs) {
@@ -436,11 +437,13 @@ __global__ void __launch_bounds__(kRouterBlockThreads, 256 / kRouterBlockThreads
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int KC = kRouterBlockCols, STEPS = KC / 128;
     uint16_t* xs = reinterpret_cast<uint16_t*>(smem);                                   // [32][H] bf16
-    float* ring = reinterpret_cast<float*>(smem + (size_t)kRouterBlockTokens * H * 2);  // [3][4][KC]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int EB = kRouterBlockExperts;
+    float* ring = reinterpret_cast<float*>(smem + (size_t)kRouterBlockTokens * H * 2);  // [3][EB][KC]
+    const int warp = (threadIdx.x >> 5) & 7, lane = threadIdx.x & 31;                   // token group of four
+    const int esub = (threadIdx.x >> 8) * 4;                                            // this warp's four experts of a block
     const int t0 = blockIdx.x * kRouterBlockTokens;
     const int e_begin = (int)(((long long)blockIdx.y * E) / gridDim.y), e_end = (int)(((long long)(blockIdx.y + 1) * E) / gridDim.y);
-    const int nblocks = (e_end - e_begin + 3) / 4;          // expert blocks of this CTA
+    const int nblocks = (e_end - e_begin + EB - 1) / EB;    // expert blocks of this CTA
     const int nkc = (H + KC - 1) / KC;                      // column chunks of a router row
     const int steps = nblocks * nkc;
 
@@ -456,9 +459,9 @@ __global__ void __launch_bounds__(kRouterBlockThreads, 256 / kRouterBlockThreads
     auto issue = [&](int s) {                               // step s: expert block s / nkc, column chunk s % nkc
         if (s < steps) {
             const int eb = s / nkc, kc = s - eb * nkc;
-            const int e0 = e_begin + 4 * eb, rows = min(4, e_end - e0);
+            const int e0 = e_begin + EB * eb, rows = min(EB, e_end - e0);
             const int cols = min(KC, H - kc * KC), pieces = cols / 4;
-            const uint32_t dst = smem_u32(ring + (size_t)(s % kRouterBlockStages) * 4 * KC);
+            const uint32_t dst = smem_u32(ring + (size_t)(s % kRouterBlockStages) * EB * KC);
             for (int c = threadIdx.x; c < rows * pieces; c += kRouterBlockThreads) {
                 const int r = c / pieces, j = c - r * pieces;
                 cp_async16(dst + (uint32_t)(r * KC + 4 * j) * 4u, w + (size_t)(e0 + r) * H + kc * KC + 4 * j);
@@ -477,7 +480,7 @@ __global__ void __launch_bounds__(kRouterBlockThreads, 256 / kRouterBlockThreads
         __syncthreads();                                    // step s has landed for everyone; step s - 1 is no longer read
         issue(s + 2);
         const int eb = s / nkc, kc = s - eb * nkc;
-        const float* wr = ring + (size_t)(s % kRouterBlockStages) * 4 * KC;
+        const float* wr = ring + (size_t)(s % kRouterBlockStages) * EB * KC + (size_t)esub * KC;
         if (kc == 0) {
 #pragma unroll
             for (int j = 0; j < 4; j++)
@@ -509,7 +512,7 @@ __global__ void __launch_bounds__(kRouterBlockThreads, 256 / kRouterBlockThreads
             }
         }
         if (kc == nkc - 1) {
-            const int e0 = e_begin + 4 * eb;
+            const int e0 = e_begin + EB * eb + esub;
 #pragma unroll
             for (int q = 0; q < 4; q++) {
                 const int e = e0 + q;
@@ -528,24 +531,16 @@ __global__ void __launch_bounds__(kRouterBlockThreads, 256 / kRouterBlockThreads
         }
     }
     cp_async_wait<0>();
+    // each warp stores the logits of the experts it computed; router_select_kernel picks from the complete rows
 #pragma unroll
     for (int j = 0; j < 4; j++) {
         const int t = t0 + 4 * warp + j;
         if (t >= T) continue;
-        if (logits) {
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
-                const int e = lane + 32 * q;
-                if (e >= e_begin && e < e_end) logits[(size_t)t * E + e] = v[j][q];
-            }
+        for (int q = 0; q < 4; q++) {
+            const int e = lane + 32 * q;
+            if (e >= e_begin && e < e_end && (((e - e_begin) % EB) >> 2) * 4 == esub) logits[(size_t)t * E + e] = v[j][q];
         }
-        if (gridDim.y > 1) continue;
-        uint32_t id[kMaxTopK];
-        float pr[kMaxTopK];
-        select_experts<ARCH>(v[j], E, K, ARCH == OCO_ARCH_NEMOTRON ? bias : nullptr, normalize, scale, lane, id, pr);
-#pragma unroll
-        for (int r = 0; r < kMaxTopK; r++)
-            if (r < K && lane == r) { ids[(size_t)t * K + r] = id[r]; probs[(size_t)t * K + r] = pr[r]; }
     }
 }
 
