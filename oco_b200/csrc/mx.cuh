@@ -235,7 +235,6 @@ __global__ void __launch_bounds__(kMxThreads, 1) mx_rows_kernel(const MxParams p
     for (int u0 = u_begin; u0 < u_end; pass++) {
         const int u1 = mx_pass_end(u0, u_end, upr, p.pass_units, !EXPAND);
         const int r_first = u0 / upr;
-        const int n_units = u1 - u0;
         __syncthreads();      // the pass before is finished with the B image
         const bool load_b = EXPAND ? pass == 0 : r_first != b_route;
         if (tid == 0 && load_b) {
