@@ -508,6 +508,8 @@ def measure_layer(args, ctx, workload, steps, warmup, tokens=0, graph=True, with
         p = moe.plan_for(layer, numerics=numerics)
         p.reserve(tokens)
         p.bind(w)
+        if numerics == 2 and getattr(args, "repacked", False):
+            p.repack()        # the optional second form of the expert tensors: every operand of the tiles by TMA
         plans.append(p)
     x_bits, res_bits = synth.make_tokens(layer.hidden, tokens, args.seed + 1000 * rank, "normal")
     x = torch.from_numpy(x_bits.view(np.int16)).cuda()
@@ -706,6 +708,7 @@ def measure_layer(args, ctx, workload, steps, warmup, tokens=0, graph=True, with
                     cache="every step reads all expert weights (%.0f MB), more than the 126 MB L2" % (per_step_bytes / 1e6)
                     if not decode else "%d weight copies rotated per step (%.0f MB between reuses)" % (copies, copies * per_step_bytes / 1e6),
                     cuda_graph=bool(decode and graph), fused_add_norm=bool(with_norm), numerics=numerics,
+                    repacked_weights=bool(numerics == 2 and getattr(args, "repacked", False)),
                     parallelism="replicas" if world > 1 else "single"),
         clocks=clocks, e2e=e2e, gpu_launches=launches, phases_ms=phases, roofline=roofline, sustained=sustained,
         step_ms_min=min(step_ms), step_ms_max=max(step_ms))
@@ -728,6 +731,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="distinct weight copies rotated per step (0 = auto)")
     ap.add_argument("--numerics", type=int, default=0, choices=[0, 2],
                     help="2: the opt-in block-scaled mode (MXFP4 activations on tcgen05 kind::mxf4); never the headline")
+    ap.add_argument("--repacked", action="store_true",
+                    help="with --numerics 2: give the tiles the repacked form of the expert tensors (oco_moe_bind_repacked)")
     ap.add_argument("--with-norm", action="store_true",
                     help="time the fused entry point: residual add + RMS norm + layer (the step either side of the layer)")
     args = ap.parse_args()
@@ -799,7 +804,7 @@ def main():
         tk = args.tokens or dt
         lay = synth.make_config(cfg_name, seed=args.seed)
         xb, rb = synth.make_tokens(lay.hidden, tk, args.seed + 1000 * rank, "normal")
-        got, routing = _moe.run_layer(lay, xb, rb, numerics=2)
+        got, routing = _moe.run_layer(lay, xb, rb, numerics=2, repacked=args.repacked)
         pick = np.unique(np.linspace(0, tk - 1, 8).astype(int))
         ref = oracle.moe_forward(lay, xb[pick], rb[pick], mode=2, trace=False)
         g = synth.bf16_bits_to_f32(got[pick]).astype(np.float64)

@@ -279,6 +279,19 @@ int oco_moe_selftest_wait_timeout(oco_moe_plan* plan, long long wait_cycles, voi
  * roofline fractions; allocates 256 bytes for the call's duration. No counterpart in the reference. */
 int oco_tensor_peak(int kind, int iters, float* tflops);
 
+/* Optional second form of the expert tensors for the block-scaled numerics (numerics = 2, GPT_OSS): the
+ * blocks' code bytes and scale bytes in two planes per tensor, laid out so that TMA and tcgen05.cp can take them
+ * as they are. The staging step of the reference keeps the checkpoint's spans unchanged and repacks only what
+ * its kernels cannot read in place (Buffer::from_bytes for repacked operands, src/gpu/buffer.rs:223); here the
+ * repack is optional: without it the same numerics run from the GGUF spans, with producer warps moving bytes.
+ *   oco_moe_repack_bytes   size of the caller's buffer (0: the plan has no use for it)
+ *   oco_moe_bind_repacked  repacks the bound gate / up / down tensors into `buffer` (1024-byte aligned) and makes
+ *                          the tiled path of this plan read them; buffer == NULL goes back to the spans.
+ * Set-up call: synchronises the stream. Bind the weights first; bind again after re-binding weights. The
+ * original tensors must stay bound (single-token calls and the router read them). */
+size_t oco_moe_repack_bytes(const oco_moe_plan* plan);
+int oco_moe_bind_repacked(oco_moe_plan* plan, void* buffer, size_t bytes, void* cuda_stream);
+
 /* One forward call recorded as a CUDA graph and replayed with one launch: the counterpart of the
  * reference encoding a step's dispatches into one command buffer and committing it
  * (Compute::submit, src/weights/compute/submission.rs:21-107). A single-token step is three to five small

@@ -78,6 +78,8 @@ SIGNATURES = {
     "oco_moe_selftest_wait_timeout": (C.c_int, [C.c_void_p, C.c_longlong, C.c_void_p]),
     "oco_tensor_peak": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_float)]),
     "oco_moe_combine_shared": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "oco_moe_repack_bytes": (C.c_size_t, [C.c_void_p]),
+    "oco_moe_bind_repacked": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "oco_moe_graph_capture": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_void_p)]),
     "oco_moe_graph_launch": (C.c_int, [C.c_void_p, C.c_void_p]),
     "oco_moe_graph_destroy": (None, [C.c_void_p]),

@@ -97,6 +97,11 @@ struct oco_moe_plan {
     bool mx_ready = false, mx_on = false;    // OCO_MOE_TOKEN_MX=1 selects them (measured slower than the mma.sync kernels so far)
     CUtensorMap map_xs[kTileKinds], map_act[kTileKinds], map_xh[kTileKinds], map_mid[kTileKinds];
     CUtensorMap map_mxq_x, map_mxq_act;   // numerics 2: the quantised rows as bytes
+    // numerics 2 with repacked weights (oco_moe_bind_repacked): code planes and scale tiles of gate, up, down
+    bool rp_ready = false;
+    unsigned char* rp_codes[3] = {nullptr, nullptr, nullptr};
+    unsigned char* rp_sf[3] = {nullptr, nullptr, nullptr};
+    CUtensorMap map_rp[3];
     // Per-phase timestamps (the counterpart of the reference's OCO_PROFILE counter heap,
     // src/gpu/profile.rs:1-31, src/gpu/dispatch.rs:189-208): one event before each kernel.
     cudaStream_t copy_stream = nullptr;   // oco_moe_forward_host: the residual rows' own stream
@@ -678,7 +683,14 @@ int stage_experts_mx(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids,
     mark(plan, st, "up_tiles");
     {
         const int feats = (F + 127) / 128, grid = std::min(plan->sm_count, feats * max_tiles);
-        grouped_gemm_mx_kernel<kEpiSwigluF16><<<grid, MxGemmShape::kThreads, MxGemmShape::kSmemBytes, st>>>(up, plan->map_mxq_x);
+        if (plan->rp_ready) {
+            ALLOW_SMEM_ONCE((grouped_gemm_mxr_kernel<kEpiSwigluF16>));
+            up.sfa0 = plan->rp_sf[0]; up.sfa1 = plan->rp_sf[1]; up.sfa_tiles = (F + 127) / 128;
+            grouped_gemm_mxr_kernel<kEpiSwigluF16><<<grid, MxrGemmShape::kThreads, MxrGemmShape::kSmemBytes, st>>>(up, plan->map_rp[0], plan->map_rp[1],
+                                                                                                                 plan->map_mxq_x);
+        } else {
+            grouped_gemm_mx_kernel<kEpiSwigluF16><<<grid, MxGemmShape::kThreads, MxGemmShape::kSmemBytes, st>>>(up, plan->map_mxq_x);
+        }
     }
     mark(plan, st, "quantize_act");
     mx_quantize_kernel<false><<<max_tiles, 256, 0, st>>>(ws.act, ws.tiles, ws.tile_count, ws.offsets, nullptr, 1, F, ws.mxq_act, ws.mxq_actsf);
@@ -690,7 +702,14 @@ int stage_experts_mx(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids,
     mark(plan, st, "down_tiles");
     {
         const int feats = (H + 255) / 256, grid = std::min(plan->sm_count, feats * max_tiles);
-        grouped_gemm_mx_kernel<kEpiDownBf16><<<grid, MxGemmShape::kThreads, MxGemmShape::kSmemBytes, st>>>(dn, plan->map_mxq_act);
+        if (plan->rp_ready) {
+            ALLOW_SMEM_ONCE((grouped_gemm_mxr_kernel<kEpiDownBf16>));
+            dn.sfa0 = plan->rp_sf[2]; dn.sfa1 = plan->rp_sf[2]; dn.sfa_tiles = (H + 127) / 128;
+            grouped_gemm_mxr_kernel<kEpiDownBf16><<<grid, MxrGemmShape::kThreads, MxrGemmShape::kSmemBytes, st>>>(dn, plan->map_rp[2], plan->map_rp[2],
+                                                                                                                plan->map_mxq_act);
+        } else {
+            grouped_gemm_mx_kernel<kEpiDownBf16><<<grid, MxGemmShape::kThreads, MxGemmShape::kSmemBytes, st>>>(dn, plan->map_mxq_act);
+        }
     }
     plan->launches += 3;
     CK(cudaGetLastError());
@@ -1039,6 +1058,7 @@ int oco_moe_bind_weights(oco_moe_plan* plan, const oco_moe_weights* w) {
     const oco_moe_desc& d = plan->d;
     // A plan may hold only a router (it then serves oco_moe_route), only experts (oco_moe_experts),
     // or both (oco_moe_forward needs both).
+    plan->rp_ready = false;      // a repacked form belongs to the weights it was made from
     const bool has_router = w->router_w != nullptr;
     const bool interleaved = w->gate_up_w != nullptr;
     const bool has_experts = w->up_w != nullptr || w->down_w != nullptr || w->gate_w != nullptr || interleaved;
@@ -1226,6 +1246,49 @@ int oco_moe_combine_shared(oco_moe_plan* plan, const uint16_t* y_bf16, const flo
     int rc = stage_combine<OCO_ARCH_NEMOTRON>(plan, y_bf16, probs, residual_bf16, rows, 2, st, shared_bf16);
     mark(plan, st, "end");
     return rc;
+}
+
+// Sizes of the repacked form of one tensor of `n` rows per expert and rows of K elements.
+static size_t rp_codes_bytes(const oco_moe_desc& d, int n, int K) { return align_up((size_t)d.experts * n * (K / 2), 1024); }
+static size_t rp_sf_bytes(const oco_moe_desc& d, int n, int K) {
+    return (size_t)d.experts * ((n + 127) / 128) * (((K >> 5) + 7) >> 3) * 1024;
+}
+
+size_t oco_moe_repack_bytes(const oco_moe_plan* plan) {
+    if (!plan || plan->d.arch != OCO_ARCH_GPT_OSS || plan->d.numerics != 2) return 0;
+    const oco_moe_desc& d = plan->d;
+    return 2 * (rp_codes_bytes(d, d.ffn, d.hidden) + rp_sf_bytes(d, d.ffn, d.hidden)) + rp_codes_bytes(d, d.hidden, d.ffn) +
+           rp_sf_bytes(d, d.hidden, d.ffn);
+}
+
+int oco_moe_bind_repacked(oco_moe_plan* plan, void* buffer, size_t bytes, void* cuda_stream) {
+    if (!plan) return OCO_INVALID_ARGUMENT;
+    const oco_moe_desc& d = plan->d;
+    if (d.arch != OCO_ARCH_GPT_OSS || d.numerics != 2) return fail(plan, OCO_UNSUPPORTED_SHAPE, "repacked weights serve numerics 2 (MXFP4) only");
+    if (!plan->have_experts) return fail(plan, OCO_INVALID_ARGUMENT, "bind the expert weights first");
+    if (int rc_dev = check_device(plan)) return rc_dev;
+    if (!buffer) { plan->rp_ready = false; return OCO_OK; }                      // back to the weights as stored
+    if (((uintptr_t)buffer & 1023u) != 0) return fail(plan, OCO_INVALID_ARGUMENT, "the buffer must be 1024-byte aligned");
+    if (bytes < oco_moe_repack_bytes(plan)) return fail(plan, OCO_INVALID_ARGUMENT, "buffer too small: %zu < %zu", bytes, oco_moe_repack_bytes(plan));
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    const int H = d.hidden, F = d.ffn, E = d.experts;
+    unsigned char* at = (unsigned char*)buffer;
+    const uint8_t* src[3] = {plan->gate_rows, plan->up_rows, plan->w.down_w};
+    const size_t stride[3] = {plan->up_row_stride, plan->up_row_stride, plan->down_row_bytes};
+    const int n[3] = {F, F, H}, K[3] = {H, H, F};
+    for (int t = 0; t < 3; t++) {
+        plan->rp_codes[t] = at; at += rp_codes_bytes(d, n[t], K[t]);
+        plan->rp_sf[t] = at; at += rp_sf_bytes(d, n[t], K[t]);
+        CK(cudaMemsetAsync(plan->rp_sf[t], 0, rp_sf_bytes(d, n[t], K[t]), st));
+        const size_t total = (size_t)E * n[t] * (K[t] >> 5);
+        const unsigned blocks = (unsigned)std::min<size_t>((total + 255) / 256, (size_t)plan->sm_count * 32);
+        mx_repack_kernel<<<blocks, 256, 0, st>>>(src[t], stride[t], n[t], E, K[t], plan->rp_codes[t], plan->rp_sf[t]);
+        CK(cudaGetLastError());
+        if (int rc = make_byte_map(plan, &plan->map_rp[t], plan->rp_codes[t], (uint64_t)E * n[t], (uint64_t)K[t] / 2, 128)) return rc;
+    }
+    CK(cudaStreamSynchronize(st));
+    plan->rp_ready = true;
+    return OCO_OK;
 }
 
 int oco_moe_graph_capture(oco_moe_plan* plan, const uint16_t* x_bf16, uint16_t* residual_bf16, int rows, oco_moe_graph** out) {

@@ -57,6 +57,9 @@ struct GemmParams {
     const uint8_t* w0_end;  // first byte past the 16-byte-aligned envelope of w0 / w1 (wide kernel)
     const uint8_t* w1_end;
     const unsigned char* sfb;  // block-scaled kernel: the B rows' scale tiles, [tile][K group][1024]
+    const unsigned char* sfa0; // repacked weights (grouped_gemm_mxr_kernel): the scale tiles of w0 / w1,
+    const unsigned char* sfa1; //   [expert][feature tile][K group][1024]
+    int sfa_tiles;             //   feature tiles per expert
 };
 
 // ---- operand order ---------------------------------------------------------------------------------

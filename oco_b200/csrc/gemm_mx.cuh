@@ -413,4 +413,241 @@ grouped_gemm_mx_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
     }
 }
 
+// ---- the same product over REPACKED weights: every operand by TMA, no producer warps ----------------------
+// The GGUF layout (17-byte blocks) is what forces the producers above. A host that can afford a second form
+// of the expert tensors (made once, oco_moe_bind_repacked) gets them as two planes per tensor:
+//   codes   [experts * n rows][K / 2 bytes]        the blocks' sixteen code bytes, rows 16-byte aligned
+//   scales  [expert][feature tile][K group][1024]  the blocks' scale bytes in the layout tcgen05.cp wants
+//                                                  (two 512-byte tiles of four blocks each per K group)
+// and then a stage of the pipeline is five copies issued by one thread: two weight tiles (TMA, 128 bytes x 128
+// rows, 128-byte swizzle), their scale tiles and the activation tile with its scales. Nothing in the SM touches
+// the weight bytes. mx_repack_kernel makes the planes; rows of a feature tile past the expert's last row keep a
+// zero scale byte (their products land in accumulator lanes nobody reads).
+__global__ void __launch_bounds__(256) mx_repack_kernel(const uint8_t* __restrict__ w, size_t row_stride, int n, int experts, int K,
+                                                        unsigned char* __restrict__ codes, unsigned char* __restrict__ sf) {
+    const int nkb = K >> 5, nkg = (nkb + 7) >> 3, nt = (n + 127) >> 7;
+    const size_t total = (size_t)experts * n * nkb;
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) {
+        const size_t row = i / nkb;
+        const uint32_t blk = (uint32_t)(i - row * nkb);
+        const uint32_t e = (uint32_t)(row / n), r = (uint32_t)(row - (size_t)e * n);
+        const uint8_t* b = w + row * row_stride + (size_t)blk * 17;
+        uint32_t words[4];
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+            words[c] = (uint32_t)b[1 + 4 * c] | ((uint32_t)b[2 + 4 * c] << 8) | ((uint32_t)b[3 + 4 * c] << 16) | ((uint32_t)b[4 + 4 * c] << 24);
+        *reinterpret_cast<uint4*>(codes + row * (size_t)(K / 2) + (size_t)blk * 16) = make_uint4(words[0], words[1], words[2], words[3]);
+        const uint32_t t = r >> 7, rr = r & 127u;
+        sf[(((size_t)e * nt + t) * nkg + (blk >> 3)) * 1024 + ((blk >> 2) & 1u) * 512 + (rr & 31u) * 16 + (rr >> 5) * 4 + (blk & 3u)] = b[0];
+    }
+}
+
+struct MxrGemmShape {
+    static constexpr int kNT = 128;
+    static constexpr int kEpilogueWarps = 16;
+    static constexpr int kMmaWarp = 16, kTmaWarp = 17;
+    static constexpr int kThreads = 18 * 32;
+    static constexpr int kATile = 128 * 128;
+    static constexpr int kOffSfa = 2 * kATile;                 // the two A tiles, their scale tiles (1 KB each),
+    static constexpr int kOffB = kOffSfa + 2 * 1024;           // the B tile, its scales
+    static constexpr int kOffSfb = kOffB + kNT * 128;
+    static constexpr int kStage = kOffSfb + 1024;              // 52224 bytes
+    static constexpr int kStages = 4;
+    static constexpr int kCtrl = 512 + kNT * 4;
+    static constexpr int kSmemBytes = kStages * kStage + kCtrl + 1024;
+    static constexpr int kTmemCols = 512;
+    static constexpr int kColSf = 256;                          // 24 scale columns per stage from here
+    static_assert(kSmemBytes <= 232448, "shared memory of one CTA");
+    static_assert(kStage % 1024 == 0, "stages keep the tiles' 1024-byte alignment");
+};
+
+// EPI as in gemm.cuh. tmap_a0 / tmap_a1: the code planes of w0 / w1 as bytes [experts * n][K / 2], box 128 bytes x
+// 128 rows (for the down projection both are the same plane: the item's two feature tiles). tmap_b: the quantised
+// activation rows. p.sfa0 / p.sfa1 / p.sfb: the scale tiles.
+template <int EPI>
+__global__ void __launch_bounds__(MxrGemmShape::kThreads, 1)
+grouped_gemm_mxr_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__ CUtensorMap tmap_a1,
+                        const __grid_constant__ CUtensorMap tmap_b) {
+    using S = MxrGemmShape;
+    constexpr bool GATED = epi_gated(EPI);
+    constexpr int NT = S::kNT;
+    constexpr int kFeatPerItem = GATED ? 128 : 256;
+    extern __shared__ unsigned char smem_raw[];
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+    if (__syncthreads_or(tid == 0 && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u)) return;
+
+    const int nfeat = (p.n + kFeatPerItem - 1) / kFeatPerItem;
+    const int ntiles = (int)*p.tile_count;
+    const int total = nfeat * ntiles;
+    struct Item { uint32_t expert, row0, nv; int f0, tile; };
+    auto load_item = [&](int item) {
+        Item r;
+        r.tile = item / nfeat;
+        r.f0 = (item - r.tile * nfeat) * kFeatPerItem;
+        r.expert = p.tiles[2 * r.tile];
+        const uint32_t begin = p.tiles[2 * r.tile + 1];
+        r.row0 = p.offsets[r.expert] + begin;
+        r.nv = min((uint32_t)NT, p.offsets[r.expert + 1] - p.offsets[r.expert] - begin);
+        return r;
+    };
+    const int nkb = p.K >> 5, nkg = (nkb + 7) >> 3;
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t ctrl = base + S::kStages * S::kStage;
+    unsigned char* ctrl_gen = gen + (ctrl - base);
+    auto full = [&](int s) { return ctrl + 8u * s; };
+    auto empty = [&](int s) { return ctrl + 8u * (S::kStages + s); };
+    const uint32_t accum_bar = ctrl + 8u * (2 * S::kStages);
+    const uint32_t tmem_free = accum_bar + 8u;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl_gen + 128);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    uint32_t* out_rows = reinterpret_cast<uint32_t*>(ctrl_gen + 512);
+
+    if (tid == 0) {
+        for (int s = 0; s < S::kStages; s++) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
+        mbar_init(accum_bar, 1);
+        mbar_init(tmem_free, S::kEpilogueWarps);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == S::kMmaWarp) {
+        tmem_alloc(smem_u32(tmem_slot), S::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < S::kEpilogueWarps) {
+        // ===== epilogue: warp -> tensor-memory lanes 32 * (warp & 3) (tile rows = features), columns [32 * (warp >> 2), +32)
+        const int erow = (warp & 3) * 32 + lane;
+        const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t c_begin = (uint32_t)(warp >> 2) * 32u;
+        int seq = 0;
+        for (int item = blockIdx.x; item < total; item += gridDim.x, seq++) {
+            const Item done = load_item(item);
+            asm volatile("bar.sync 1, %0;" ::"n"(S::kEpilogueWarps * 32) : "memory");     // nobody still reads the row map of the item before
+            for (uint32_t i = tid; i < done.nv; i += S::kEpilogueWarps * 32)
+                out_rows[i] = (EPI == kEpiDownBf16 && p.route_of_row) ? p.route_of_row[done.row0 + i] : done.row0 + i;
+            asm volatile("bar.sync 1, %0;" ::"n"(S::kEpilogueWarps * 32) : "memory");
+            if (lane == 0) mbar_wait(accum_bar, (uint32_t)seq & 1u, abort_flag, p.status);
+            __syncwarp();
+            tc_fence_after();
+            const uint32_t c_end = min(done.nv, c_begin + 32u);
+            const int fa = done.f0 + erow, fb = GATED ? fa : fa + 128;
+            float bias_a = 0.f, bias_b = 0.f;
+            if (fa < p.n && p.b0) bias_a = bf16_round(p.b0[((size_t)done.expert * p.n + fa) * p.bias_stride]);
+            if (GATED) {
+                if (EPI == kEpiSwigluF16 && fa < p.n) bias_b = bf16_round(__fadd_rn(p.b1[((size_t)done.expert * p.n + fa) * p.bias_stride], 1.0f));
+            } else if (fb < p.n && p.b0) {
+                bias_b = bf16_round(p.b0[((size_t)done.expert * p.n + fb) * p.bias_stride]);
+            }
+            const int col_a = EPI == kEpiDownBf16 ? fa : operand_pos(OCO_FMT_MXFP4, fa);
+            const int col_b = EPI == kEpiDownBf16 ? fb : operand_pos(OCO_FMT_MXFP4, fb);
+            for (uint32_t c = c_begin; c < c_begin + 32u; c += 16) {
+                uint32_t ra[16], rb[16];
+                tmem_ld16(taddr + c, ra);
+                tmem_ld16(taddr + NT + c, rb);
+                tmem_ld_wait();
+                if (c + 16 >= c_begin + 32u) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tmem_free);
+                }
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    if (c + j < c_end) {
+                        const size_t orow = (size_t)out_rows[c + j] * p.n;
+                        const float a = __fadd_rn(__uint_as_float(ra[j]), bias_a);
+                        const float b = __fadd_rn(__uint_as_float(rb[j]), bias_b);
+                        if (GATED) {
+                            if (fa < p.n) p.out[orow + col_a] = epilogue_value<EPI>(a, b);
+                        } else {
+                            if (fa < p.n) p.out[orow + col_a] = epilogue_value<EPI>(a, 0.f);
+                            if (fb < p.n) p.out[orow + col_b] = epilogue_value<EPI>(b, 0.f);
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == S::kMmaWarp) {
+        if (lane == 0) {
+            int seq = 0;
+            for (int item = blockIdx.x; item < total; item += gridDim.x, seq++) {
+                const Item it = load_item(item);
+                const uint32_t n_mma = max(16u, (it.nv + 15u) & ~15u);
+                if (seq > 0) {
+                    mbar_wait(tmem_free, (uint32_t)(seq - 1) & 1u, abort_flag, p.status);
+                    tc_fence_after();
+                }
+                const int g0 = seq * nkg;
+                for (int g = 0; g < nkg; g++) {
+                    const int G = g0 + g, s = G % S::kStages;
+                    mbar_wait(full(s), (uint32_t)(G / S::kStages) & 1u, abort_flag, p.status);
+                    tc_fence_after();
+                    const uint32_t stage = base + (uint32_t)s * S::kStage;
+                    const uint32_t sf_t = tmem_base + S::kColSf + 24u * (uint32_t)s;        // SFB 8 columns, then SFA 8 per matrix
+                    mx_cp_scales(sf_t, mx_sf_desc(stage + S::kOffSfb));
+                    mx_cp_scales(sf_t + 4u, mx_sf_desc(stage + S::kOffSfb + 512u));
+                    const uint64_t bd = umma_desc(stage + S::kOffB);
+#pragma unroll
+                    for (int mat = 0; mat < 2; mat++) {
+                        const uint32_t sfa_t = sf_t + 8u + 8u * (uint32_t)mat;
+                        const uint32_t sfa_smem = stage + S::kOffSfa + (uint32_t)mat * 1024u;
+                        mx_cp_scales(sfa_t, mx_sf_desc(sfa_smem));
+                        mx_cp_scales(sfa_t + 4u, mx_sf_desc(sfa_smem + 512u));
+                        const uint64_t ad = umma_desc(stage + (uint32_t)mat * S::kATile);
+#pragma unroll
+                        for (int kk = 0; kk < 4; kk++)
+                            umma_mxf4(tmem_base + (uint32_t)mat * NT, ad + 2u * kk, bd + 2u * kk, mx_idesc(n_mma, (uint32_t)(kk & 1) * 2u),
+                                      sfa_t + 4u * (kk >> 1), sf_t + 4u * (kk >> 1), (g | kk) ? 1u : 0u);
+                    }
+                    umma_commit(empty(s));
+                }
+                umma_commit(accum_bar);
+            }
+            if (seq > 0) mbar_wait(accum_bar, (uint32_t)(seq - 1) & 1u, abort_flag, p.status);
+            tc_fence_before();
+        }
+    } else if (lane == 0) {
+        // ===== every operand of a stage: five copies ======================================================
+        int seq = 0;
+        for (int item = blockIdx.x; item < total; item += gridDim.x, seq++) {
+            const Item it = load_item(item);
+            const int g0 = seq * nkg;
+            const int row_a0 = (int)it.expert * p.n + it.f0, row_a1 = GATED ? row_a0 : row_a0 + 128;
+            const int ft0 = it.f0 >> 7, ft1 = GATED ? ft0 : min(ft0 + 1, p.sfa_tiles - 1);
+            const unsigned char* sf0 = p.sfa0 + ((size_t)it.expert * p.sfa_tiles + ft0) * nkg * 1024;
+            const unsigned char* sf1 = (GATED ? p.sfa1 : p.sfa0) + ((size_t)it.expert * p.sfa_tiles + ft1) * nkg * 1024;
+            for (int g = 0; g < nkg; g++) {
+                const int G = g0 + g, s = G % S::kStages;
+                const uint32_t stage = base + (uint32_t)s * S::kStage;
+                mbar_wait(empty(s), ((uint32_t)(G / S::kStages) & 1u) ^ 1u, abort_flag, p.status);
+                mbar_arrive_expect_tx(full(s), 2u * S::kATile + 2u * 1024u + NT * 128u + 1024u);
+                tma_load_2d(stage, &tmap_a0, g * 128, row_a0, full(s));
+                tma_load_2d(stage + S::kATile, GATED ? &tmap_a1 : &tmap_a0, g * 128, row_a1, full(s));
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(stage + S::kOffSfa),
+                             "l"(sf0 + (size_t)g * 1024), "r"(1024u), "r"(full(s)) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(stage + S::kOffSfa + 1024u),
+                             "l"(sf1 + (size_t)g * 1024), "r"(1024u), "r"(full(s)) : "memory");
+                tma_load_2d(stage + S::kOffB, &tmap_b, g * 128, (int)it.row0, full(s));
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(stage + S::kOffSfb),
+                             "l"(p.sfb + ((size_t)it.tile * nkg + g) * 1024), "r"(1024u), "r"(full(s)) : "memory");
+            }
+        }
+    }
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 64; i++) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == S::kMmaWarp) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, S::kTmemCols);
+    }
+}
+
 }  // namespace oco

@@ -133,6 +133,16 @@ class _Plan:
         self._check(_lib.lib().oco_moe_forward_host(self.handle, x.ctypes.data_as(C.c_void_p),
                                                     residual.ctypes.data_as(C.c_void_p), rows, _stream_ptr()))
 
+    def repack(self, device="cuda"):
+        """The optional second form of the expert tensors for numerics 2 (oco_moe_bind_repacked)."""
+        nbytes = _lib.lib().oco_moe_repack_bytes(self.handle)
+        if nbytes == 0:
+            raise OcoError(_lib.UNSUPPORTED_SHAPE, "this plan has no use for repacked weights")
+        self._repacked = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
+        base = (self._repacked.data_ptr() + 1023) & ~1023
+        self._check(_lib.lib().oco_moe_bind_repacked(self.handle, C.c_void_p(base), nbytes, _stream_ptr()))
+        return base, nbytes
+
     def capture(self, x: torch.Tensor, residual: torch.Tensor, rows: int) -> "StepGraph":
         """The forward call on these buffers as a graph of the library (one launch per replay)."""
         g = C.c_void_p()
@@ -350,7 +360,8 @@ def plan_for(layer: synth.Layer, gemm_impl: int = 0, numerics: int = 0) -> _Plan
 
 
 def run_layer(layer: synth.Layer, x_bits: np.ndarray, residual_bits: np.ndarray, gemm_impl: int = 0,
-              device="cuda", state: Optional[dict] = None, misalign: int = 0, interleaved: bool = False, numerics: int = 0):
+              device="cuda", state: Optional[dict] = None, misalign: int = 0, interleaved: bool = False, numerics: int = 0,
+              repacked: bool = False):
     """Convenience used by tests and the benchmark: uploads (or reuses) a layer, runs it on bf16
     bit patterns given as uint16 arrays and returns (residual bits, routing dict)."""
     state = state if state is not None else {}
@@ -358,6 +369,11 @@ def run_layer(layer: synth.Layer, x_bits: np.ndarray, residual_bits: np.ndarray,
         state["plan"] = plan_for(layer, gemm_impl, numerics)
         state["weights"] = _Weights.from_layer(layer, device, misalign, interleaved)
     plan, w = state["plan"], state["weights"]
+    if repacked and not state.get("repacked"):
+        plan.reserve(x_bits.shape[0], device)
+        plan.bind(w)
+        plan.repack(device)
+        state["repacked"] = True
     rows = x_bits.shape[0]
     x = torch.from_numpy(np.ascontiguousarray(x_bits).view(np.int16)).to(device)
     res = torch.from_numpy(np.ascontiguousarray(residual_bits).view(np.int16).copy()).to(device)

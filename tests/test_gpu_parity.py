@@ -640,16 +640,22 @@ def _swiglu(gate, up):
     return g / (1.0 + np.exp(-1.702 * g)) * u
 
 
+@pytest.mark.parametrize("repacked", [False, True], ids=["spans", "repacked"])
 @pytest.mark.parametrize("hidden,ffn,experts,top_k,tokens", [(256, 256, 4, 2, 300), (320, 288, 8, 2, 700), (96, 96, 4, 2, 200),
                                                               (640, 384, 32, 4, 40)], ids=["k256", "k320", "k96", "sparse"])
-def test_block_scaled_numerics_match_their_own_arithmetic(moe, oracle, hidden, ffn, experts, top_k, tokens):
+def test_block_scaled_numerics_match_their_own_arithmetic(moe, oracle, hidden, ffn, experts, top_k, tokens, repacked):
     """The opt-in mode multiplies MXFP4 weights with MXFP4-quantised activations. Its results are held to a
     checker that multiplies THE SAME quantised operands in float64 (both stages, each fed what the GPU fed
     it), and the distance to the reference arithmetic is printed beside it: the price of the mode."""
     from tests import mxq
     layer = synth.make_layer(synth.ARCH_GPT_OSS, hidden, ffn, experts, top_k, synth.FMT_MXFP4, seed=hidden + tokens)
     x, res = synth.make_tokens(hidden, tokens, 3, "normal")
-    out, routing = moe.run_layer(layer, x, res, numerics=2)
+    out, routing = moe.run_layer(layer, x, res, numerics=2, repacked=repacked)
+    if repacked:
+        # the weights as stored (producer warps move the bytes) and their repacked form (every operand by TMA) feed
+        # the same MMAs with the same operands: the two must agree bit for bit
+        out_spans, routing_spans = moe.run_layer(layer, x, res, numerics=2)
+        assert np.array_equal(out, out_spans) and np.array_equal(routing["y"], routing_spans["y"]), "repacked weights change the result"
     ref = oracle.moe_forward(layer, x, res, mode=2)
     assert np.array_equal(routing["ids"], ref.ids) and np.array_equal(routing["prob"].view(np.uint32), ref.probs.view(np.uint32))
     offsets, row_of_route, route_of_row = oracle.permutation(ref.ids, experts)
@@ -825,3 +831,41 @@ def test_repeated_steps_are_bit_identical(moe, config, tokens, numerics):
     assert not np.array_equal(first, rb.view(np.int16)), "the step did nothing"
     for i, o in enumerate(outs[1:], 1):
         assert np.array_equal(first, o.cpu().numpy()), f"step {i} differs from step 0"
+
+
+def test_repacked_planes_hold_the_blocks_bytes(moe):
+    """oco_moe_bind_repacked: every block's sixteen code bytes at [row][16 * block], its scale byte in the tile
+    tcgen05.cp reads (tile of 128 rows, K group of 8 blocks, 512-byte half, (row % 32) * 16 + (row / 32) * 4 +
+    block % 4), zero where a feature tile runs past the expert's last row; plans that have no use for it refuse."""
+    import torch
+    from oco_b200 import _lib
+    H, F, E, K = 320, 288, 4, 2
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, H, F, E, K, synth.FMT_MXFP4, seed=5)
+    plan = moe.plan_for(layer, numerics=2)
+    plan.reserve(64)
+    plan.bind(moe._Weights.from_layer(layer))
+    base, nbytes = plan.repack()
+    torch.cuda.synchronize()
+    off = base - plan._repacked.data_ptr()
+    buf = plan._repacked[off: off + nbytes].cpu().numpy()
+    at = 0
+    for w, n, k in ((layer.gate_w, F, H), (layer.up_w, F, H), (layer.down_w, H, F)):
+        nkb, nt = k // 32, (n + 127) // 128
+        nkg = (nkb + 7) // 8
+        blocks = np.ascontiguousarray(w).reshape(E, n, nkb, 17)
+        codes_bytes = (E * n * (k // 2) + 1023) // 1024 * 1024
+        codes = buf[at: at + E * n * (k // 2)].reshape(E, n, nkb, 16)
+        assert np.array_equal(codes, blocks[..., 1:])
+        at += codes_bytes
+        sf = buf[at: at + E * nt * nkg * 1024].reshape(E, nt, nkg, 2, 32, 16)
+        want = np.zeros_like(sf)
+        r = np.arange(n)
+        for blk in range(nkb):
+            want[:, r // 128, blk // 8, (blk // 4) % 2, r % 32, ((r % 128) // 32) * 4 + blk % 4] = blocks[:, :, blk, 0]
+        assert np.array_equal(sf, want)
+        at += E * nt * nkg * 1024
+    assert at == nbytes
+    plain = moe.plan_for(layer)
+    assert _lib.lib().oco_moe_repack_bytes(plain.handle) == 0
+    with pytest.raises(moe.OcoError):
+        plain.repack()
