@@ -665,7 +665,7 @@ int stage_experts_mx(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids,
     launch_route_plan(plan, ids, R, E, NT, rs, st);
     const int max_tiles = R / NT + (E < R ? E : R);
     mark(plan, st, "quantize_x");
-    mx_quantize_kernel<true><<<max_tiles, 256, 0, st>>>(x, ws.tiles, ws.tile_count, ws.offsets, ws.route_of_row, per_row, H, ws.mxq_x, ws.mxq_xsf);
+    mx_quantize_kernel<true><<<4 * max_tiles, 256, 0, st>>>(x, ws.tiles, ws.tile_count, ws.offsets, ws.route_of_row, per_row, H, ws.mxq_x, ws.mxq_xsf);
     plan->launches += 1;
     CK(cudaGetLastError());
     ALLOW_SMEM_ONCE((grouped_gemm_mx_kernel<kEpiSwigluF16>));
@@ -693,7 +693,7 @@ int stage_experts_mx(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids,
         }
     }
     mark(plan, st, "quantize_act");
-    mx_quantize_kernel<false><<<max_tiles, 256, 0, st>>>(ws.act, ws.tiles, ws.tile_count, ws.offsets, nullptr, 1, F, ws.mxq_act, ws.mxq_actsf);
+    mx_quantize_kernel<false><<<4 * max_tiles, 256, 0, st>>>(ws.act, ws.tiles, ws.tile_count, ws.offsets, nullptr, 1, F, ws.mxq_act, ws.mxq_actsf);
     GemmParams dn{};
     dn.w0 = plan->w.down_w; dn.b0 = plan->w.down_b; dn.n = H; dn.K = F; dn.row_bytes = plan->down_row_bytes; dn.bias_stride = 1;
     dn.tiles = ws.tiles; dn.tile_count = ws.tile_count; dn.offsets = ws.offsets; dn.route_of_row = ws.route_of_row;

@@ -62,14 +62,15 @@ __global__ void __launch_bounds__(256) mx_quantize_kernel(const uint16_t* __rest
                                                           const uint32_t* __restrict__ tile_count, const uint32_t* __restrict__ offsets,
                                                           const uint32_t* __restrict__ route_of_row, int per_row, int K,
                                                           unsigned char* __restrict__ q, unsigned char* __restrict__ sf) {
-    const uint32_t tile = blockIdx.x;
+    // four CTAs per tile, 32 rows each (gridDim.x = 4 x the tiles the launch was sized for)
+    const uint32_t tile = blockIdx.x >> 2, part = blockIdx.x & 3u;
     if (tile >= *tile_count) return;
     const uint32_t expert = tiles[2 * tile], begin = tiles[2 * tile + 1];
     const uint32_t row0 = offsets[expert] + begin;
     const uint32_t nv = min(128u, offsets[expert + 1] - offsets[expert] - begin);
     const int nkb = K >> 5, nkg = (nkb + 7) >> 3, nblk = nkg * 8;
-    for (uint32_t i = threadIdx.x; i < 128u * (uint32_t)nblk; i += 256) {
-        const uint32_t n = i / (uint32_t)nblk, blk = i - n * (uint32_t)nblk;
+    for (uint32_t i = threadIdx.x; i < 32u * (uint32_t)nblk; i += 256) {
+        const uint32_t n = part * 32u + i / (uint32_t)nblk, blk = i % (uint32_t)nblk;
         unsigned char* sfp = sf + ((size_t)tile * nkg + (blk >> 3)) * 1024 + ((blk >> 2) & 1u) * 512 + (n & 31u) * 16 + (n >> 5) * 4 + (blk & 3u);
         if (n >= nv || blk >= (uint32_t)nkb) { *sfp = 127; continue; }    // rows and blocks past the end: operand zeros, scale one
         const uint16_t* row = GATHER ? src + (size_t)(route_of_row[row0 + n] / (uint32_t)per_row) * K : src + (size_t)(row0 + n) * K;
@@ -445,8 +446,8 @@ __global__ void __launch_bounds__(256) mx_repack_kernel(const uint8_t* __restric
 struct MxrGemmShape {
     static constexpr int kNT = 128;
     static constexpr int kEpilogueWarps = 16;
-    static constexpr int kMmaWarp = 16, kTmaWarp = 17;
-    static constexpr int kThreads = 18 * 32;
+    static constexpr int kMmaWarp = 16, kTmaWarp = 17, kMmaWarp2 = 18;   // one issuing thread per weight tile
+    static constexpr int kThreads = 19 * 32;
     static constexpr int kATile = 128 * 128;
     static constexpr int kOffSfa = 2 * kATile;                 // the two A tiles, their scale tiles (1 KB each),
     static constexpr int kOffB = kOffSfa + 2 * 1024;           // the B tile, its scales
@@ -456,7 +457,7 @@ struct MxrGemmShape {
     static constexpr int kCtrl = 512 + kNT * 4;
     static constexpr int kSmemBytes = kStages * kStage + kCtrl + 1024;
     static constexpr int kTmemCols = 512;
-    static constexpr int kColSf = 256;                          // 24 scale columns per stage from here
+    static constexpr int kColSf = 256;                          // 32 scale columns per stage from here
     static_assert(kSmemBytes <= 232448, "shared memory of one CTA");
     static_assert(kStage % 1024 == 0, "stages keep the tiles' 1024-byte alignment");
 };
@@ -506,8 +507,8 @@ grouped_gemm_mxr_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
     uint32_t* out_rows = reinterpret_cast<uint32_t*>(ctrl_gen + 512);
 
     if (tid == 0) {
-        for (int s = 0; s < S::kStages; s++) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
-        mbar_init(accum_bar, 1);
+        for (int s = 0; s < S::kStages; s++) { mbar_init(full(s), 1); mbar_init(empty(s), 2); }   // both issuing threads commit
+        mbar_init(accum_bar, 2);
         mbar_init(tmem_free, S::kEpilogueWarps);
         *abort_flag = 0;
         fence_barrier_init();
@@ -573,8 +574,14 @@ grouped_gemm_mxr_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
                 }
             }
         }
-    } else if (warp == S::kMmaWarp) {
+    } else if (warp == S::kMmaWarp || warp == S::kMmaWarp2) {
         if (lane == 0) {
+            // ===== MMA issue: one thread per weight tile and accumulator =====================================
+            // A tcgen05 instruction costs its issuing thread about 80 cycles whatever it does, and a K group is
+            // six scale copies, eight MMAs and a commit: one thread would spend 1.8 times the MMAs' tensor time
+            // issuing them. Each thread copies the activation scales into columns of its own (the order of two
+            // threads' tcgen05 operations is not defined) and its weight tile's scales, then issues its four MMAs.
+            const int mat = warp == S::kMmaWarp ? 0 : 1;
             int seq = 0;
             for (int item = blockIdx.x; item < total; item += gridDim.x, seq++) {
                 const Item it = load_item(item);
@@ -589,22 +596,19 @@ grouped_gemm_mxr_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
                     mbar_wait(full(s), (uint32_t)(G / S::kStages) & 1u, abort_flag, p.status);
                     tc_fence_after();
                     const uint32_t stage = base + (uint32_t)s * S::kStage;
-                    const uint32_t sf_t = tmem_base + S::kColSf + 24u * (uint32_t)s;        // SFB 8 columns, then SFA 8 per matrix
-                    mx_cp_scales(sf_t, mx_sf_desc(stage + S::kOffSfb));
-                    mx_cp_scales(sf_t + 4u, mx_sf_desc(stage + S::kOffSfb + 512u));
+                    const uint32_t sfb_t = tmem_base + S::kColSf + 32u * (uint32_t)s + 16u * (uint32_t)mat;   // SFB 8 columns, then SFA 8
+                    const uint32_t sfa_t = sfb_t + 8u;
+                    mx_cp_scales(sfb_t, mx_sf_desc(stage + S::kOffSfb));
+                    mx_cp_scales(sfb_t + 4u, mx_sf_desc(stage + S::kOffSfb + 512u));
+                    const uint32_t sfa_smem = stage + S::kOffSfa + (uint32_t)mat * 1024u;
+                    mx_cp_scales(sfa_t, mx_sf_desc(sfa_smem));
+                    mx_cp_scales(sfa_t + 4u, mx_sf_desc(sfa_smem + 512u));
                     const uint64_t bd = umma_desc(stage + S::kOffB);
+                    const uint64_t ad = umma_desc(stage + (uint32_t)mat * S::kATile);
 #pragma unroll
-                    for (int mat = 0; mat < 2; mat++) {
-                        const uint32_t sfa_t = sf_t + 8u + 8u * (uint32_t)mat;
-                        const uint32_t sfa_smem = stage + S::kOffSfa + (uint32_t)mat * 1024u;
-                        mx_cp_scales(sfa_t, mx_sf_desc(sfa_smem));
-                        mx_cp_scales(sfa_t + 4u, mx_sf_desc(sfa_smem + 512u));
-                        const uint64_t ad = umma_desc(stage + (uint32_t)mat * S::kATile);
-#pragma unroll
-                        for (int kk = 0; kk < 4; kk++)
-                            umma_mxf4(tmem_base + (uint32_t)mat * NT, ad + 2u * kk, bd + 2u * kk, mx_idesc(n_mma, (uint32_t)(kk & 1) * 2u),
-                                      sfa_t + 4u * (kk >> 1), sf_t + 4u * (kk >> 1), (g | kk) ? 1u : 0u);
-                    }
+                    for (int kk = 0; kk < 4; kk++)
+                        umma_mxf4(tmem_base + (uint32_t)mat * NT, ad + 2u * kk, bd + 2u * kk, mx_idesc(n_mma, (uint32_t)(kk & 1) * 2u),
+                                  sfa_t + 4u * (kk >> 1), sfb_t + 4u * (kk >> 1), (g | kk) ? 1u : 0u);
                     umma_commit(empty(s));
                 }
                 umma_commit(accum_bar);
