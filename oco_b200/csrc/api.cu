@@ -237,7 +237,7 @@ Workspace carve(const oco_moe_desc& d, int max_rows, unsigned char* base) {
         w.mx_blk_arrivals = (uint32_t*)take(K * (F / 32) * 4);
     }
     if (d.numerics == 2) {
-        const size_t tiles128 = R / 128 + E + 1;
+        const size_t tiles128 = R / 112 + E + 1;      // tiles of 128 routes (weights as stored) or 112 (repacked weights)
         w.mxq_x = (unsigned char*)take(R * H / 2);
         w.mxq_xsf = (unsigned char*)take(tiles128 * ((H / 32 + 7) / 8) * 1024);
         w.mxq_act = (unsigned char*)take(R * F / 2);
@@ -660,12 +660,12 @@ int stage_experts_mx(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids,
     const oco_moe_desc& d = plan->d;
     Workspace& ws = plan->ws;
     const int H = d.hidden, F = d.ffn, E = d.experts;
-    constexpr int NT = MxGemmShape::kNT;
+    const int NT = plan->rp_ready ? MxrGemmShape::kNT : MxGemmShape::kNT;
     plan->last_tile_rows = NT;
     launch_route_plan(plan, ids, R, E, NT, rs, st);
     const int max_tiles = R / NT + (E < R ? E : R);
     mark(plan, st, "quantize_x");
-    mx_quantize_kernel<true><<<4 * max_tiles, 256, 0, st>>>(x, ws.tiles, ws.tile_count, ws.offsets, ws.route_of_row, per_row, H, ws.mxq_x, ws.mxq_xsf);
+    mx_quantize_kernel<true><<<4 * max_tiles, 256, 0, st>>>(x, ws.tiles, ws.tile_count, ws.offsets, ws.route_of_row, per_row, H, ws.mxq_x, ws.mxq_xsf, (uint32_t)NT);
     plan->launches += 1;
     CK(cudaGetLastError());
     ALLOW_SMEM_ONCE((grouped_gemm_mx_kernel<kEpiSwigluF16>));
@@ -693,7 +693,7 @@ int stage_experts_mx(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids,
         }
     }
     mark(plan, st, "quantize_act");
-    mx_quantize_kernel<false><<<4 * max_tiles, 256, 0, st>>>(ws.act, ws.tiles, ws.tile_count, ws.offsets, nullptr, 1, F, ws.mxq_act, ws.mxq_actsf);
+    mx_quantize_kernel<false><<<4 * max_tiles, 256, 0, st>>>(ws.act, ws.tiles, ws.tile_count, ws.offsets, nullptr, 1, F, ws.mxq_act, ws.mxq_actsf, (uint32_t)NT);
     GemmParams dn{};
     dn.w0 = plan->w.down_w; dn.b0 = plan->w.down_b; dn.n = H; dn.K = F; dn.row_bytes = plan->down_row_bytes; dn.bias_stride = 1;
     dn.tiles = ws.tiles; dn.tile_count = ws.tile_count; dn.offsets = ws.offsets; dn.route_of_row = ws.route_of_row;

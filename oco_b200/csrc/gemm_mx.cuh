@@ -61,13 +61,13 @@ template <bool GATHER>
 __global__ void __launch_bounds__(256) mx_quantize_kernel(const uint16_t* __restrict__ src, const uint32_t* __restrict__ tiles,
                                                           const uint32_t* __restrict__ tile_count, const uint32_t* __restrict__ offsets,
                                                           const uint32_t* __restrict__ route_of_row, int per_row, int K,
-                                                          unsigned char* __restrict__ q, unsigned char* __restrict__ sf) {
+                                                          unsigned char* __restrict__ q, unsigned char* __restrict__ sf, uint32_t tile_rows) {
     // four CTAs per tile, 32 rows each (gridDim.x = 4 x the tiles the launch was sized for)
     const uint32_t tile = blockIdx.x >> 2, part = blockIdx.x & 3u;
     if (tile >= *tile_count) return;
     const uint32_t expert = tiles[2 * tile], begin = tiles[2 * tile + 1];
     const uint32_t row0 = offsets[expert] + begin;
-    const uint32_t nv = min(128u, offsets[expert + 1] - offsets[expert] - begin);
+    const uint32_t nv = min(tile_rows, offsets[expert + 1] - offsets[expert] - begin);       // tile_rows <= 128
     const int nkb = K >> 5, nkg = (nkb + 7) >> 3, nblk = nkg * 8;
     for (uint32_t i = threadIdx.x; i < 32u * (uint32_t)nblk; i += 256) {
         const uint32_t n = part * 32u + i / (uint32_t)nblk, blk = i % (uint32_t)nblk;
@@ -444,20 +444,22 @@ __global__ void __launch_bounds__(256) mx_repack_kernel(const uint8_t* __restric
 }
 
 struct MxrGemmShape {
-    static constexpr int kNT = 128;
+    static constexpr int kNT = 112;                            // routes per tile: two accumulator sets of 2 x 112 columns and
+                                                               // 32 scale columns fill the 512 columns of tensor memory
+    static constexpr int kBRows = 128;                         // rows of the B box (the tile's rows and 16 that are not read)
     static constexpr int kEpilogueWarps = 16;
     static constexpr int kMmaWarp = 16, kTmaWarp = 17, kMmaWarp2 = 18;   // one issuing thread per weight tile
     static constexpr int kThreads = 19 * 32;
     static constexpr int kATile = 128 * 128;
     static constexpr int kOffSfa = 2 * kATile;                 // the two A tiles, their scale tiles (1 KB each),
     static constexpr int kOffB = kOffSfa + 2 * 1024;           // the B tile, its scales
-    static constexpr int kOffSfb = kOffB + kNT * 128;
+    static constexpr int kOffSfb = kOffB + kBRows * 128;
     static constexpr int kStage = kOffSfb + 1024;              // 52224 bytes
     static constexpr int kStages = 4;
-    static constexpr int kCtrl = 512 + kNT * 4;
+    static constexpr int kCtrl = 512 + 2 * 128 * 4;            // barriers, tmem slot, abort flag, two row maps
     static constexpr int kSmemBytes = kStages * kStage + kCtrl + 1024;
     static constexpr int kTmemCols = 512;
-    static constexpr int kColSf = 256;                          // 32 scale columns per stage from here
+    static constexpr int kColSf = 4 * kNT;                      // 16 scale columns per issuing thread from here
     static_assert(kSmemBytes <= 232448, "shared memory of one CTA");
     static_assert(kStage % 1024 == 0, "stages keep the tiles' 1024-byte alignment");
 };
@@ -500,16 +502,16 @@ grouped_gemm_mxr_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
     unsigned char* ctrl_gen = gen + (ctrl - base);
     auto full = [&](int s) { return ctrl + 8u * s; };
     auto empty = [&](int s) { return ctrl + 8u * (S::kStages + s); };
-    const uint32_t accum_bar = ctrl + 8u * (2 * S::kStages);
-    const uint32_t tmem_free = accum_bar + 8u;
+    // two accumulator sets: while the epilogue warps drain one, the MMAs of the next item fill the other
+    auto accum_bar = [&](uint32_t set) { return ctrl + 8u * (2 * S::kStages + set); };
+    auto tmem_free = [&](uint32_t set) { return ctrl + 8u * (2 * S::kStages + 2 + set); };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl_gen + 128);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     uint32_t* out_rows = reinterpret_cast<uint32_t*>(ctrl_gen + 512);
 
     if (tid == 0) {
         for (int s = 0; s < S::kStages; s++) { mbar_init(full(s), 1); mbar_init(empty(s), 2); }   // both issuing threads commit
-        mbar_init(accum_bar, 2);
-        mbar_init(tmem_free, S::kEpilogueWarps);
+        for (uint32_t b = 0; b < 2; b++) { mbar_init(accum_bar(b), 2); mbar_init(tmem_free(b), S::kEpilogueWarps); }
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -523,10 +525,11 @@ grouped_gemm_mxr_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp < S::kEpilogueWarps) {
-        // ===== epilogue: warp -> tensor-memory lanes 32 * (warp & 3) (tile rows = features), columns [32 * (warp >> 2), +32)
+        // ===== epilogue: warp -> tensor-memory lanes 32 * (warp & 3) (tile rows = features), columns [28 * (warp >> 2), +28)
         const int erow = (warp & 3) * 32 + lane;
         const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-        const uint32_t c_begin = (uint32_t)(warp >> 2) * 32u;
+        constexpr uint32_t kColsPerWarp = NT / 4;
+        const uint32_t c_begin = (uint32_t)(warp >> 2) * kColsPerWarp;
         int seq = 0;
         for (int item = blockIdx.x; item < total; item += gridDim.x, seq++) {
             const Item done = load_item(item);
@@ -534,10 +537,12 @@ grouped_gemm_mxr_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
             for (uint32_t i = tid; i < done.nv; i += S::kEpilogueWarps * 32)
                 out_rows[i] = (EPI == kEpiDownBf16 && p.route_of_row) ? p.route_of_row[done.row0 + i] : done.row0 + i;
             asm volatile("bar.sync 1, %0;" ::"n"(S::kEpilogueWarps * 32) : "memory");
-            if (lane == 0) mbar_wait(accum_bar, (uint32_t)seq & 1u, abort_flag, p.status);
+            const uint32_t set = (uint32_t)seq & 1u, use = (uint32_t)seq >> 1;
+            const uint32_t tset = taddr + set * 2u * NT;
+            if (lane == 0) mbar_wait(accum_bar(set), use & 1u, abort_flag, p.status);
             __syncwarp();
             tc_fence_after();
-            const uint32_t c_end = min(done.nv, c_begin + 32u);
+            const uint32_t c_end = min(done.nv, c_begin + kColsPerWarp);
             const int fa = done.f0 + erow, fb = GATED ? fa : fa + 128;
             float bias_a = 0.f, bias_b = 0.f;
             if (fa < p.n && p.b0) bias_a = bf16_round(p.b0[((size_t)done.expert * p.n + fa) * p.bias_stride]);
@@ -548,15 +553,15 @@ grouped_gemm_mxr_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
             }
             const int col_a = EPI == kEpiDownBf16 ? fa : operand_pos(OCO_FMT_MXFP4, fa);
             const int col_b = EPI == kEpiDownBf16 ? fb : operand_pos(OCO_FMT_MXFP4, fb);
-            for (uint32_t c = c_begin; c < c_begin + 32u; c += 16) {
+            for (uint32_t c = c_begin; c < c_begin + kColsPerWarp; c += 16) {      // the second read runs past the warp's columns: unused
                 uint32_t ra[16], rb[16];
-                tmem_ld16(taddr + c, ra);
-                tmem_ld16(taddr + NT + c, rb);
+                tmem_ld16(tset + c, ra);
+                tmem_ld16(tset + NT + c, rb);
                 tmem_ld_wait();
-                if (c + 16 >= c_begin + 32u) {
+                if (c + 16 >= c_begin + kColsPerWarp) {
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(tmem_free);
+                    if (lane == 0) mbar_arrive(tmem_free(set));
                 }
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
@@ -586,8 +591,9 @@ grouped_gemm_mxr_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
             for (int item = blockIdx.x; item < total; item += gridDim.x, seq++) {
                 const Item it = load_item(item);
                 const uint32_t n_mma = max(16u, (it.nv + 15u) & ~15u);
-                if (seq > 0) {
-                    mbar_wait(tmem_free, (uint32_t)(seq - 1) & 1u, abort_flag, p.status);
+                const uint32_t set = (uint32_t)seq & 1u, use = (uint32_t)seq >> 1;
+                if (use > 0) {                                                // this set's item before last is drained
+                    mbar_wait(tmem_free(set), (use - 1u) & 1u, abort_flag, p.status);
                     tc_fence_after();
                 }
                 const int g0 = seq * nkg;
@@ -596,7 +602,9 @@ grouped_gemm_mxr_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
                     mbar_wait(full(s), (uint32_t)(G / S::kStages) & 1u, abort_flag, p.status);
                     tc_fence_after();
                     const uint32_t stage = base + (uint32_t)s * S::kStage;
-                    const uint32_t sfb_t = tmem_base + S::kColSf + 32u * (uint32_t)s + 16u * (uint32_t)mat;   // SFB 8 columns, then SFA 8
+                    // one set of scale columns per issuing thread, rewritten every K group: a thread's tcgen05.cp and
+                    // tcgen05.mma execute in the order it issued them
+                    const uint32_t sfb_t = tmem_base + S::kColSf + 16u * (uint32_t)mat;                      // SFB 8 columns, then SFA 8
                     const uint32_t sfa_t = sfb_t + 8u;
                     mx_cp_scales(sfb_t, mx_sf_desc(stage + S::kOffSfb));
                     mx_cp_scales(sfb_t + 4u, mx_sf_desc(stage + S::kOffSfb + 512u));
@@ -607,13 +615,13 @@ grouped_gemm_mxr_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
                     const uint64_t ad = umma_desc(stage + (uint32_t)mat * S::kATile);
 #pragma unroll
                     for (int kk = 0; kk < 4; kk++)
-                        umma_mxf4(tmem_base + (uint32_t)mat * NT, ad + 2u * kk, bd + 2u * kk, mx_idesc(n_mma, (uint32_t)(kk & 1) * 2u),
+                        umma_mxf4(tmem_base + set * 2u * NT + (uint32_t)mat * NT, ad + 2u * kk, bd + 2u * kk, mx_idesc(n_mma, (uint32_t)(kk & 1) * 2u),
                                   sfa_t + 4u * (kk >> 1), sfb_t + 4u * (kk >> 1), (g | kk) ? 1u : 0u);
                     umma_commit(empty(s));
                 }
-                umma_commit(accum_bar);
+                umma_commit(accum_bar(set));
             }
-            if (seq > 0) mbar_wait(accum_bar, (uint32_t)(seq - 1) & 1u, abort_flag, p.status);
+            if (seq > 0) mbar_wait(accum_bar((uint32_t)(seq - 1) & 1u), ((uint32_t)(seq - 1) >> 1) & 1u, abort_flag, p.status);   // every MMA has retired
             tc_fence_before();
         }
     } else if (lane == 0) {
@@ -630,7 +638,7 @@ grouped_gemm_mxr_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
                 const int G = g0 + g, s = G % S::kStages;
                 const uint32_t stage = base + (uint32_t)s * S::kStage;
                 mbar_wait(empty(s), ((uint32_t)(G / S::kStages) & 1u) ^ 1u, abort_flag, p.status);
-                mbar_arrive_expect_tx(full(s), 2u * S::kATile + 2u * 1024u + NT * 128u + 1024u);
+                mbar_arrive_expect_tx(full(s), 2u * S::kATile + 2u * 1024u + S::kBRows * 128u + 1024u);
                 tma_load_2d(stage, &tmap_a0, g * 128, row_a0, full(s));
                 tma_load_2d(stage + S::kATile, GATED ? &tmap_a1 : &tmap_a0, g * 128, row_a1, full(s));
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(stage + S::kOffSfa),

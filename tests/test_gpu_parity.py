@@ -805,19 +805,22 @@ def test_expert_stage_over_a_window_numbering(moe, oracle, tokens_per_source, si
         assert rc == _lib.INVALID_ARGUMENT
 
 
-@pytest.mark.parametrize("config,tokens,numerics", [("gpt-oss-20b", 2048, 0), ("gpt-oss-20b", 1, 0), ("gpt-oss-20b", 2048, 2),
+@pytest.mark.parametrize("config,tokens,numerics", [("gpt-oss-20b", 2048, 0), ("gpt-oss-20b", 1, 0), ("gpt-oss-20b", 2048, 2), ("gpt-oss-20b", 2048, 3),
                                                     ("gpt-oss-120b", 64, 0), ("nemotron-h", 300, 0), ("qwen3-30b-a3b", 1, 0)],
-                         ids=["prefill", "token", "prefill_block_scaled", "few_token", "nemotron", "qwen_token"])
+                         ids=["prefill", "token", "prefill_block_scaled", "prefill_block_scaled_repacked", "few_token", "nemotron", "qwen_token"])
 def test_repeated_steps_are_bit_identical(moe, config, tokens, numerics):
     """The same step enqueued back to back on one plan, with no host synchronisation between the steps (so
     that each step's kernels are launched while the step before still runs), gives the same bits every time:
     no result depends on scheduling, on leftovers in the workspace or on how the launches overlap."""
     import torch
     layer = synth.make_config(config, seed=3)
+    repacked, numerics = numerics == 3, min(numerics, 2)         # 3: numerics 2 over the repacked weights
     plan = moe.plan_for(layer, numerics=numerics)
     plan.reserve(tokens)
     w = moe._Weights.from_layer(layer)
     plan.bind(w)
+    if repacked:
+        plan.repack()
     xb, rb = synth.make_tokens(layer.hidden, tokens, 17, "normal")
     x = torch.from_numpy(xb.view(np.int16)).cuda()
     r0 = torch.from_numpy(rb.view(np.int16)).cuda()
@@ -831,6 +834,16 @@ def test_repeated_steps_are_bit_identical(moe, config, tokens, numerics):
     assert not np.array_equal(first, rb.view(np.int16)), "the step did nothing"
     for i, o in enumerate(outs[1:], 1):
         assert np.array_equal(first, o.cpu().numpy()), f"step {i} differs from step 0"
+    if repacked:
+        # at the benchmark's size too, the repacked form and the spans give the same bits
+        spans = moe.plan_for(layer, numerics=2)
+        spans.reserve(tokens)
+        spans.bind(w)
+        o = r0.clone()
+        spans.forward(x, o, tokens)
+        torch.cuda.synchronize()
+        spans.poll()
+        assert np.array_equal(first, o.cpu().numpy()), "repacked weights change the result at full size"
 
 
 def test_repacked_planes_hold_the_blocks_bytes(moe):
