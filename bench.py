@@ -508,8 +508,10 @@ def measure_layer(args, ctx, workload, steps, warmup, tokens=0, graph=True, with
         p = moe.plan_for(layer, numerics=numerics)
         p.reserve(tokens)
         p.bind(w)
-        if numerics == 2 and getattr(args, "repacked", False):
-            p.repack()        # the optional second form of the expert tensors: every operand of the tiles by TMA
+        if getattr(args, "repacked", False) and layer.arch == synth.ARCH_GPT_OSS and (numerics == 2 or decode):
+            # the optional second form of the expert tensors: the block-scaled tiles (numerics 2) and, with
+            # OCO_MOE_REPACKED_TOKEN=1, the single-token kernels (any numerics) then get every operand by bulk copies
+            p.repack()
         plans.append(p)
     x_bits, res_bits = synth.make_tokens(layer.hidden, tokens, args.seed + 1000 * rank, "normal")
     x = torch.from_numpy(x_bits.view(np.int16)).cuda()
@@ -708,7 +710,7 @@ def measure_layer(args, ctx, workload, steps, warmup, tokens=0, graph=True, with
                     cache="every step reads all expert weights (%.0f MB), more than the 126 MB L2" % (per_step_bytes / 1e6)
                     if not decode else "%d weight copies rotated per step (%.0f MB between reuses)" % (copies, copies * per_step_bytes / 1e6),
                     cuda_graph=bool(decode and graph), fused_add_norm=bool(with_norm), numerics=numerics,
-                    repacked_weights=bool(numerics == 2 and getattr(args, "repacked", False)),
+                    repacked_weights=bool(getattr(args, "repacked", False) and layer.arch == synth.ARCH_GPT_OSS and (numerics == 2 or decode)),
                     parallelism="replicas" if world > 1 else "single"),
         clocks=clocks, e2e=e2e, gpu_launches=launches, phases_ms=phases, roofline=roofline, sustained=sustained,
         step_ms_min=min(step_ms), step_ms_max=max(step_ms))
@@ -732,7 +734,8 @@ def main():
     ap.add_argument("--numerics", type=int, default=0, choices=[0, 2],
                     help="2: the opt-in block-scaled mode (MXFP4 activations on tcgen05 kind::mxf4); never the headline")
     ap.add_argument("--repacked", action="store_true",
-                    help="with --numerics 2: give the tiles the repacked form of the expert tensors (oco_moe_bind_repacked)")
+                    help="bind the repacked form of the MXFP4 expert tensors (oco_moe_bind_repacked): read by the tiles of --numerics 2 "
+                         "and by single-token workloads in the reference numerics")
     ap.add_argument("--with-norm", action="store_true",
                     help="time the fused entry point: residual add + RMS norm + layer (the step either side of the layer)")
     args = ap.parse_args()

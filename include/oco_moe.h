@@ -279,12 +279,15 @@ int oco_moe_selftest_wait_timeout(oco_moe_plan* plan, long long wait_cycles, voi
  * roofline fractions; allocates 256 bytes for the call's duration. No counterpart in the reference. */
 int oco_tensor_peak(int kind, int iters, float* tflops);
 
-/* Optional second form of the expert tensors for the block-scaled numerics (numerics = 2, GPT_OSS): the
- * blocks' code bytes and scale bytes in two planes per tensor, laid out so that TMA and tcgen05.cp can take them
- * as they are. The staging step of the reference keeps the checkpoint's spans unchanged and repacks only what
+/* Optional second form of the MXFP4 expert tensors (GPT_OSS): the blocks' code bytes and scale bytes in two
+ * planes per tensor, laid out so that TMA and tcgen05.cp can take them as they are. The tiled path of the
+ * block-scaled numerics (numerics = 2) reads it. Single-token calls can read it too, in ANY numerics (the
+ * activations ride as exact e2m1 pieces, so the results keep the reference's single-token arithmetic), but only
+ * when OCO_MOE_REPACKED_TOKEN=1 is set: those kernels measured slower than the default ones and exist for
+ * measurement. The staging step of the reference keeps the checkpoint's spans unchanged and repacks only what
  * its kernels cannot read in place (Buffer::from_bytes for repacked operands, src/gpu/buffer.rs:223); here the
  * repack is optional: without it the same numerics run from the GGUF spans, with producer warps moving bytes.
- *   oco_moe_repack_bytes   size of the caller's buffer (0: the plan has no use for it)
+ *   oco_moe_repack_bytes   size of the caller's buffer (0: the plan's family has no use for it)
  *   oco_moe_bind_repacked  repacks the bound gate / up / down tensors into `buffer` (1024-byte aligned) and makes
  *                          the tiled path of this plan read them; buffer == NULL goes back to the spans.
  * Set-up call: synchronises the stream. Bind the weights first; bind again after re-binding weights. The

@@ -99,9 +99,10 @@ struct oco_moe_plan {
     CUtensorMap map_mxq_x, map_mxq_act;   // numerics 2: the quantised rows as bytes
     // numerics 2 with repacked weights (oco_moe_bind_repacked): code planes and scale tiles of gate, up, down
     bool rp_ready = false;
+    bool rp_token = false;       // single-token calls read the repacked form too
+    bool rp_token_on = false;    // OCO_MOE_REPACKED_TOKEN=1 (measured slower than the default single-token kernels: off unless asked for)
     unsigned char* rp_codes[3] = {nullptr, nullptr, nullptr};
     unsigned char* rp_sf[3] = {nullptr, nullptr, nullptr};
-    CUtensorMap map_rp[3];
     // Per-phase timestamps (the counterpart of the reference's OCO_PROFILE counter heap,
     // src/gpu/profile.rs:1-31, src/gpu/dispatch.rs:189-208): one event before each kernel.
     cudaStream_t copy_stream = nullptr;   // oco_moe_forward_host: the residual rows' own stream
@@ -452,6 +453,19 @@ int launch_mx(oco_moe_plan* plan, MxParams mp, cudaStream_t st) {
     return OCO_OK;
 }
 
+template <bool EXPAND>
+int launch_mx_tma(oco_moe_plan* plan, const MxParams& mp, const MxTmaParams& tp, cudaStream_t st) {
+    const int n_mat = EXPAND ? 2 : 1;
+    const int tiles_total = mp.routes * tp.row_tiles;
+    const int grid = std::min(plan->sm_count, tiles_total);
+    const size_t smem = mx_tma_smem(n_mat, (uint32_t)(mp.K / 32));
+    ALLOW_SMEM_ONCE((mx_rows_tma_kernel<EXPAND>));
+    CK(launch_dependent(mx_rows_tma_kernel<EXPAND>, dim3(grid), dim3(mx_tma_warps(n_mat) * 32), smem, st, mp, tp));
+    plan->launches++;
+    CK(cudaGetLastError());
+    return OCO_OK;
+}
+
 template <int ARCH>
 struct Family;
 template <>
@@ -477,7 +491,8 @@ int forward_single(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, cu
     Workspace& ws = plan->ws;
     const int H = d.hidden, F = d.ffn, E = d.experts, K = d.top_k;
     // logits, then (in the CTA that finishes last) the token's experts and weights
-    const bool mx = ARCH == OCO_ARCH_GPT_OSS && plan->mx_ready;
+    const bool mx_tma = ARCH == OCO_ARCH_GPT_OSS && plan->rp_token;
+    const bool mx = mx_tma || (ARCH == OCO_ARCH_GPT_OSS && plan->mx_ready);
     mark(plan, st, "router_logits");
     CK(launch_dependent(router_token_kernel<ARCH>, dim3((E + 7) / 8), dim3(256), 0, st, x, plan->w.router_w, plan->w.router_b, H, E, K,
                         d.normalize, d.scale, ws.logits, ws.ids, ws.probs, ws.xfrag, (int)FMT, ws.arrivals + H,
@@ -499,7 +514,11 @@ int forward_single(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, cu
         ex.act_b_route_bytes = mx_b_bytes(8, (uint32_t)(F / 32)); ex.act_sfb_route_bytes = mx_sfb_bytes((uint32_t)(F / 32));
         ex.status = ws.status;
         mark(plan, st, "expand");
-        int rc = launch_mx<true>(plan, ex, st);
+        MxTmaParams tx{}, td{};
+        tx.sf[0] = plan->rp_sf[0]; tx.sf[1] = plan->rp_sf[1]; tx.codes[0] = plan->rp_codes[0]; tx.codes[1] = plan->rp_codes[1];
+        tx.row_tiles = (F + 127) / 128;
+        td.sf[0] = plan->rp_sf[2]; td.codes[0] = plan->rp_codes[2]; td.row_tiles = (H + 127) / 128;
+        int rc = mx_tma ? launch_mx_tma<true>(plan, ex, tx, st) : launch_mx<true>(plan, ex, st);
         if (rc) return rc;
         MxParams dn{};
         dn.w[0] = plan->w.down_w; dn.w_end[0] = envelope_end(plan->w.down_w, (size_t)E * H, plan->down_row_bytes, plan->down_row_bytes);
@@ -508,7 +527,7 @@ int forward_single(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, cu
         dn.b0 = plan->w.down_b; dn.bias_stride = 1; dn.y = ws.y; dn.arrivals = ws.arrivals; dn.probs = ws.probs; dn.residual = residual;
         dn.round_sum = 1; dn.status = ws.status;
         mark(plan, st, "down_combine");
-        rc = launch_mx<false>(plan, dn, st);
+        rc = mx_tma ? launch_mx_tma<false>(plan, dn, td, st) : launch_mx<false>(plan, dn, st);
         if (rc) return rc;
         mark(plan, st, "end");
         return OCO_OK;
@@ -686,8 +705,8 @@ int stage_experts_mx(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids,
         if (plan->rp_ready) {
             ALLOW_SMEM_ONCE((grouped_gemm_mxr_kernel<kEpiSwigluF16>));
             up.sfa0 = plan->rp_sf[0]; up.sfa1 = plan->rp_sf[1]; up.sfa_tiles = (F + 127) / 128;
-            grouped_gemm_mxr_kernel<kEpiSwigluF16><<<grid, MxrGemmShape::kThreads, MxrGemmShape::kSmemBytes, st>>>(up, plan->map_rp[0], plan->map_rp[1],
-                                                                                                                 plan->map_mxq_x);
+            up.w0 = plan->rp_codes[0]; up.w1 = plan->rp_codes[1];
+            grouped_gemm_mxr_kernel<kEpiSwigluF16><<<grid, MxrGemmShape::kThreads, MxrGemmShape::kSmemBytes, st>>>(up, plan->map_mxq_x);
         } else {
             grouped_gemm_mx_kernel<kEpiSwigluF16><<<grid, MxGemmShape::kThreads, MxGemmShape::kSmemBytes, st>>>(up, plan->map_mxq_x);
         }
@@ -705,8 +724,8 @@ int stage_experts_mx(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids,
         if (plan->rp_ready) {
             ALLOW_SMEM_ONCE((grouped_gemm_mxr_kernel<kEpiDownBf16>));
             dn.sfa0 = plan->rp_sf[2]; dn.sfa1 = plan->rp_sf[2]; dn.sfa_tiles = (H + 127) / 128;
-            grouped_gemm_mxr_kernel<kEpiDownBf16><<<grid, MxrGemmShape::kThreads, MxrGemmShape::kSmemBytes, st>>>(dn, plan->map_rp[2], plan->map_rp[2],
-                                                                                                                plan->map_mxq_act);
+            dn.w0 = plan->rp_codes[2]; dn.w1 = plan->rp_codes[2];
+            grouped_gemm_mxr_kernel<kEpiDownBf16><<<grid, MxrGemmShape::kThreads, MxrGemmShape::kSmemBytes, st>>>(dn, plan->map_mxq_act);
         } else {
             grouped_gemm_mx_kernel<kEpiDownBf16><<<grid, MxGemmShape::kThreads, MxGemmShape::kSmemBytes, st>>>(dn, plan->map_mxq_act);
         }
@@ -958,6 +977,7 @@ int oco_moe_plan_create(const oco_moe_desc* desc, oco_moe_plan** out) {
     { const char* e = getenv("OCO_MOE_NO_BATCH"); plan->no_batch_path = e && e[0] == '1'; }
     { const char* e = getenv("OCO_MOE_TOKEN_MX"); plan->mx_on = e && e[0] == '1'; }
     { const char* e = getenv("OCO_MOE_ROUTE_PLAN_SINGLE_MAX"); if (e && atoi(e) >= 0) plan->route_plan_single_max = atoi(e); }
+    { const char* e = getenv("OCO_MOE_REPACKED_TOKEN"); plan->rp_token_on = e && e[0] == '1'; }
     { const char* e = getenv("OCO_MOE_BATCH_MAX_AVG"); if (e && atoi(e) > 0) plan->batch_max_avg = atoi(e) < 64 ? atoi(e) : 64; }
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) == cudaSuccess &&
@@ -1058,7 +1078,7 @@ int oco_moe_bind_weights(oco_moe_plan* plan, const oco_moe_weights* w) {
     const oco_moe_desc& d = plan->d;
     // A plan may hold only a router (it then serves oco_moe_route), only experts (oco_moe_experts),
     // or both (oco_moe_forward needs both).
-    plan->rp_ready = false;      // a repacked form belongs to the weights it was made from
+    plan->rp_ready = plan->rp_token = false;      // a repacked form belongs to the weights it was made from
     const bool has_router = w->router_w != nullptr;
     const bool interleaved = w->gate_up_w != nullptr;
     const bool has_experts = w->up_w != nullptr || w->down_w != nullptr || w->gate_w != nullptr || interleaved;
@@ -1249,13 +1269,13 @@ int oco_moe_combine_shared(oco_moe_plan* plan, const uint16_t* y_bf16, const flo
 }
 
 // Sizes of the repacked form of one tensor of `n` rows per expert and rows of K elements.
-static size_t rp_codes_bytes(const oco_moe_desc& d, int n, int K) { return align_up((size_t)d.experts * n * (K / 2), 1024); }
+static size_t rp_codes_bytes(const oco_moe_desc& d, int n, int K) { return (size_t)d.experts * ((n + 127) / 128) * (((K >> 5) + 7) >> 3) * 16384; }
 static size_t rp_sf_bytes(const oco_moe_desc& d, int n, int K) {
     return (size_t)d.experts * ((n + 127) / 128) * (((K >> 5) + 7) >> 3) * 1024;
 }
 
 size_t oco_moe_repack_bytes(const oco_moe_plan* plan) {
-    if (!plan || plan->d.arch != OCO_ARCH_GPT_OSS || plan->d.numerics != 2) return 0;
+    if (!plan || plan->d.arch != OCO_ARCH_GPT_OSS) return 0;
     const oco_moe_desc& d = plan->d;
     return 2 * (rp_codes_bytes(d, d.ffn, d.hidden) + rp_sf_bytes(d, d.ffn, d.hidden)) + rp_codes_bytes(d, d.hidden, d.ffn) +
            rp_sf_bytes(d, d.hidden, d.ffn);
@@ -1264,10 +1284,10 @@ size_t oco_moe_repack_bytes(const oco_moe_plan* plan) {
 int oco_moe_bind_repacked(oco_moe_plan* plan, void* buffer, size_t bytes, void* cuda_stream) {
     if (!plan) return OCO_INVALID_ARGUMENT;
     const oco_moe_desc& d = plan->d;
-    if (d.arch != OCO_ARCH_GPT_OSS || d.numerics != 2) return fail(plan, OCO_UNSUPPORTED_SHAPE, "repacked weights serve numerics 2 (MXFP4) only");
+    if (d.arch != OCO_ARCH_GPT_OSS) return fail(plan, OCO_UNSUPPORTED_SHAPE, "repacked weights serve the MXFP4 family only");
     if (!plan->have_experts) return fail(plan, OCO_INVALID_ARGUMENT, "bind the expert weights first");
     if (int rc_dev = check_device(plan)) return rc_dev;
-    if (!buffer) { plan->rp_ready = false; return OCO_OK; }                      // back to the weights as stored
+    if (!buffer) { plan->rp_ready = plan->rp_token = false; return OCO_OK; }                      // back to the weights as stored
     if (((uintptr_t)buffer & 1023u) != 0) return fail(plan, OCO_INVALID_ARGUMENT, "the buffer must be 1024-byte aligned");
     if (bytes < oco_moe_repack_bytes(plan)) return fail(plan, OCO_INVALID_ARGUMENT, "buffer too small: %zu < %zu", bytes, oco_moe_repack_bytes(plan));
     cudaStream_t st = (cudaStream_t)cuda_stream;
@@ -1279,15 +1299,18 @@ int oco_moe_bind_repacked(oco_moe_plan* plan, void* buffer, size_t bytes, void* 
     for (int t = 0; t < 3; t++) {
         plan->rp_codes[t] = at; at += rp_codes_bytes(d, n[t], K[t]);
         plan->rp_sf[t] = at; at += rp_sf_bytes(d, n[t], K[t]);
+        CK(cudaMemsetAsync(plan->rp_codes[t], 0, rp_codes_bytes(d, n[t], K[t]), st));
         CK(cudaMemsetAsync(plan->rp_sf[t], 0, rp_sf_bytes(d, n[t], K[t]), st));
         const size_t total = (size_t)E * n[t] * (K[t] >> 5);
         const unsigned blocks = (unsigned)std::min<size_t>((total + 255) / 256, (size_t)plan->sm_count * 32);
         mx_repack_kernel<<<blocks, 256, 0, st>>>(src[t], stride[t], n[t], E, K[t], plan->rp_codes[t], plan->rp_sf[t]);
         CK(cudaGetLastError());
-        if (int rc = make_byte_map(plan, &plan->map_rp[t], plan->rp_codes[t], (uint64_t)E * n[t], (uint64_t)K[t] / 2, 128)) return rc;
     }
     CK(cudaStreamSynchronize(st));
     plan->rp_ready = true;
+    // single-token calls take the block-scaled kernels over the repacked form when the shape fits them
+    plan->rp_token = plan->have_ws && plan->ws.mx_xb && F % 32 == 0 && H % 32 == 0 && H <= 12288 && F <= 12288 &&
+                     mx_tma_smem(2, (uint32_t)(H / 32)) <= kMaxDynamicSmem && mx_tma_smem(1, (uint32_t)(F / 32)) <= kMaxDynamicSmem && plan->rp_token_on;
     return OCO_OK;
 }
 

@@ -417,13 +417,17 @@ grouped_gemm_mx_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
 // ---- the same product over REPACKED weights: every operand by TMA, no producer warps ----------------------
 // The GGUF layout (17-byte blocks) is what forces the producers above. A host that can afford a second form
 // of the expert tensors (made once, oco_moe_bind_repacked) gets them as two planes per tensor:
-//   codes   [experts * n rows][K / 2 bytes]        the blocks' sixteen code bytes, rows 16-byte aligned
-//   scales  [expert][feature tile][K group][1024]  the blocks' scale bytes in the layout tcgen05.cp wants
-//                                                  (two 512-byte tiles of four blocks each per K group)
-// and then a stage of the pipeline is five copies issued by one thread: two weight tiles (TMA, 128 bytes x 128
-// rows, 128-byte swizzle), their scale tiles and the activation tile with its scales. Nothing in the SM touches
-// the weight bytes. mx_repack_kernel makes the planes; rows of a feature tile past the expert's last row keep a
-// zero scale byte (their products land in accumulator lanes nobody reads).
+//   codes   [expert][feature tile][K group][16384]  the code bytes of 128 rows x 256 elements as the MMA reads
+//                                                   them from shared memory (K-major, 128-byte swizzle: row r,
+//                                                   16-byte piece c at (r / 8) * 1024 + (r % 8) * 128 + ((c ^ (r % 8)) * 16))
+//   scales  [expert][feature tile][K group][1024]   the blocks' scale bytes in the layout tcgen05.cp wants
+//                                                   (two 512-byte tiles of four blocks each per K group)
+// so that a weight tile is one contiguous 16 KB and arrives with ONE bulk copy (a tensor copy of 128 rows of 128
+// bytes from a row-major plane runs at the copy engine's rate per row, several times slower). A stage of the
+// pipeline is then five copies issued by one thread: two weight tiles, their scale tiles and the activation
+// tile (TMA) with its scales. Nothing in the SM touches the weight bytes. mx_repack_kernel makes the planes
+// (zeroed first: rows of a feature tile past the expert's last row and blocks past K hold zero codes and a zero
+// scale byte; their products land in accumulator lanes nobody reads, or add zero).
 __global__ void __launch_bounds__(256) mx_repack_kernel(const uint8_t* __restrict__ w, size_t row_stride, int n, int experts, int K,
                                                         unsigned char* __restrict__ codes, unsigned char* __restrict__ sf) {
     const int nkb = K >> 5, nkg = (nkb + 7) >> 3, nt = (n + 127) >> 7;
@@ -437,8 +441,9 @@ __global__ void __launch_bounds__(256) mx_repack_kernel(const uint8_t* __restric
 #pragma unroll
         for (int c = 0; c < 4; c++)
             words[c] = (uint32_t)b[1 + 4 * c] | ((uint32_t)b[2 + 4 * c] << 8) | ((uint32_t)b[3 + 4 * c] << 16) | ((uint32_t)b[4 + 4 * c] << 24);
-        *reinterpret_cast<uint4*>(codes + row * (size_t)(K / 2) + (size_t)blk * 16) = make_uint4(words[0], words[1], words[2], words[3]);
         const uint32_t t = r >> 7, rr = r & 127u;
+        unsigned char* tile = codes + ((((size_t)e * nt + t) * nkg + (blk >> 3)) << 14);
+        *reinterpret_cast<uint4*>(tile + (rr >> 3) * 1024u + (rr & 7u) * 128u + (((blk & 7u) ^ (rr & 7u)) << 4)) = make_uint4(words[0], words[1], words[2], words[3]);
         sf[(((size_t)e * nt + t) * nkg + (blk >> 3)) * 1024 + ((blk >> 2) & 1u) * 512 + (rr & 31u) * 16 + (rr >> 5) * 4 + (blk & 3u)] = b[0];
     }
 }
@@ -464,13 +469,12 @@ struct MxrGemmShape {
     static_assert(kStage % 1024 == 0, "stages keep the tiles' 1024-byte alignment");
 };
 
-// EPI as in gemm.cuh. tmap_a0 / tmap_a1: the code planes of w0 / w1 as bytes [experts * n][K / 2], box 128 bytes x
-// 128 rows (for the down projection both are the same plane: the item's two feature tiles). tmap_b: the quantised
-// activation rows. p.sfa0 / p.sfa1 / p.sfb: the scale tiles.
+// EPI as in gemm.cuh. p.w0 / p.w1: the code planes of the two matrices (for the down projection both are the same
+// plane: the item's two feature tiles), p.sfa0 / p.sfa1 their scale tiles; tmap_b: the quantised activation rows,
+// p.sfb their scale tiles.
 template <int EPI>
 __global__ void __launch_bounds__(MxrGemmShape::kThreads, 1)
-grouped_gemm_mxr_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__ CUtensorMap tmap_a1,
-                        const __grid_constant__ CUtensorMap tmap_b) {
+grouped_gemm_mxr_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_b) {
     using S = MxrGemmShape;
     constexpr bool GATED = epi_gated(EPI);
     constexpr int NT = S::kNT;
@@ -630,17 +634,21 @@ grouped_gemm_mxr_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
         for (int item = blockIdx.x; item < total; item += gridDim.x, seq++) {
             const Item it = load_item(item);
             const int g0 = seq * nkg;
-            const int row_a0 = (int)it.expert * p.n + it.f0, row_a1 = GATED ? row_a0 : row_a0 + 128;
             const int ft0 = it.f0 >> 7, ft1 = GATED ? ft0 : min(ft0 + 1, p.sfa_tiles - 1);
-            const unsigned char* sf0 = p.sfa0 + ((size_t)it.expert * p.sfa_tiles + ft0) * nkg * 1024;
-            const unsigned char* sf1 = (GATED ? p.sfa1 : p.sfa0) + ((size_t)it.expert * p.sfa_tiles + ft1) * nkg * 1024;
+            const size_t t0 = ((size_t)it.expert * p.sfa_tiles + ft0) * nkg, t1 = ((size_t)it.expert * p.sfa_tiles + ft1) * nkg;
+            const unsigned char* sf0 = p.sfa0 + t0 * 1024;
+            const unsigned char* sf1 = (GATED ? p.sfa1 : p.sfa0) + t1 * 1024;
+            const uint8_t* c0 = p.w0 + (t0 << 14);
+            const uint8_t* c1 = (GATED ? p.w1 : p.w0) + (t1 << 14);
             for (int g = 0; g < nkg; g++) {
                 const int G = g0 + g, s = G % S::kStages;
                 const uint32_t stage = base + (uint32_t)s * S::kStage;
                 mbar_wait(empty(s), ((uint32_t)(G / S::kStages) & 1u) ^ 1u, abort_flag, p.status);
                 mbar_arrive_expect_tx(full(s), 2u * S::kATile + 2u * 1024u + S::kBRows * 128u + 1024u);
-                tma_load_2d(stage, &tmap_a0, g * 128, row_a0, full(s));
-                tma_load_2d(stage + S::kATile, GATED ? &tmap_a1 : &tmap_a0, g * 128, row_a1, full(s));
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(stage),
+                             "l"(c0 + ((size_t)g << 14)), "r"(16384u), "r"(full(s)) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(stage + S::kATile),
+                             "l"(c1 + ((size_t)g << 14)), "r"(16384u), "r"(full(s)) : "memory");
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(stage + S::kOffSfa),
                              "l"(sf0 + (size_t)g * 1024), "r"(1024u), "r"(full(s)) : "memory");
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(stage + S::kOffSfa + 1024u),

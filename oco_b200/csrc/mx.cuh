@@ -473,4 +473,229 @@ __global__ void __launch_bounds__(kMxThreads, 1) mx_rows_kernel(const MxParams p
     }
 }
 
+// ---- the same products over REPACKED weights (oco_moe_bind_repacked): every operand by TMA ---------------------
+// With the code bytes in a plane of 16-byte-aligned rows and the scale bytes as ready-made tiles (gemm_mx.cuh,
+// mx_repack_kernel) nothing has to be moved inside the SM: a copy thread brings a tile of 128 weight rows and its
+// scale tile per K group, the MMA threads multiply it with the activation's pieces as above. A pass is one tile of
+// 128 consecutive rows of one route (of both matrices for the expand kernel); CTA c takes the tiles
+// [c T / G, (c + 1) T / G). Tile row t is row 128 * tile + t of the expert's matrix, so a block of 32 activations is
+// exactly one epilogue warp's 32 lanes of one pass: the warp that computed it splits it into pieces for the down
+// kernel on the spot (no counters, no queue). The down kernel's weighted sum onto the residual is the one above.
+struct MxTmaParams {
+    const unsigned char* codes[2];   // code tiles of each matrix, [expert][row tile][K group][16384], as shared memory wants them
+    const unsigned char* sf[2];      // scale tiles of each matrix, [expert][row tile][K group][1024]
+    int row_tiles;                   // row tiles per expert (ceil(rows_per_route / 128))
+};
+constexpr int kMxTmaStages = 4;
+constexpr int kMxTmaSplit = 4;                       // MMA-issuing threads per matrix: thread i takes the K groups g = i mod 4 into
+                                                     // accumulator columns of its own (a tcgen05 instruction costs its thread 70-90
+                                                     // cycles and a tile's K groups in one thread were the longest part of the kernel)
+__host__ __device__ constexpr int mx_tma_warps(int n_mat) { return 4 + n_mat * kMxTmaSplit + 1; }   // epilogue, issuers, copy
+__host__ __device__ inline uint32_t mx_tma_smem(int n_mat, uint32_t nkb) {
+    return (uint32_t)kMxTmaStages * n_mat * (16384u + 1024u) + mx_b_bytes(8, nkb) + mx_sfb_bytes(nkb) + kMxCtrlBytes + 1024u;
+}
+
+template <bool EXPAND>
+__global__ void __launch_bounds__(mx_tma_warps(EXPAND ? 2 : 1) * 32, 1)
+mx_rows_tma_kernel(const MxParams p, const MxTmaParams q) {
+    constexpr int NMAT = EXPAND ? 2 : 1;
+    constexpr int kIssuers = NMAT * kMxTmaSplit, kCopyWarp = 4 + kIssuers;
+    constexpr uint32_t kColMat = 8u * kMxTmaSplit;               // accumulator columns of one matrix: eight per issuing thread
+    constexpr uint32_t NCOL = 8u;
+    constexpr uint32_t kStage = NMAT * (16384u + 1024u);       // the matrices' tiles, then their scale tiles
+    extern __shared__ unsigned char smem_raw[];
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+    const int nkb = p.K >> 5, nkg = (nkb + 7) >> 3;
+    const int tpr = q.row_tiles;                               // tiles per route
+    const int tiles_total = p.routes * tpr;
+    const int t_begin = (int)((long long)blockIdx.x * tiles_total / gridDim.x);
+    const int t_end = (int)((long long)(blockIdx.x + 1) * tiles_total / gridDim.x);
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t a_base = base;                                               // [stage] NMAT tiles of 16 KB, NMAT scale tiles of 1 KB
+    const uint32_t b_base = a_base + kMxTmaStages * kStage;
+    const uint32_t b_bytes = mx_b_bytes(NCOL, nkb), sfb_bytes = mx_sfb_bytes(nkb);
+    const uint32_t sfb_base = b_base + b_bytes;
+    const uint32_t ctrl = sfb_base + sfb_bytes;
+    unsigned char* ctrl_gen = gen + (ctrl - base);
+    auto a_full = [&](int s) { return ctrl + 8u * s; };
+    auto a_empty = [&](int s) { return ctrl + 8u * (kMxTmaStages + s); };
+    const uint32_t accum_bar = ctrl + 8u * (2 * kMxTmaStages), b_bar = accum_bar + 8u, tmem_free = accum_bar + 16u, sfb_ready = accum_bar + 24u;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl_gen + 128);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    pdl_launch_dependents();
+    if (tid == 0) {
+        for (int s = 0; s < kMxTmaStages; s++) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), NMAT); }
+        mbar_init(accum_bar, kIssuers);
+        mbar_init(sfb_ready, 1);
+        mbar_init(b_bar, 1);
+        mbar_init(tmem_free, 4);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 4) {
+        tmem_alloc(smem_u32(tmem_slot), kMxTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                       // ids, activations and pieces written by the kernels before are complete
+
+    int step0 = 0, pass = 0, b_loads = 0, b_route = -1;
+    (void)sfb_ready;
+    for (int tile = t_begin; tile < t_end; tile++, pass++) {
+        const int route = tile / tpr, rt = tile - route * tpr;          // row tile rt of this route's expert
+        const uint32_t e = p.ids ? p.ids[route] : 0u;
+        __syncthreads();      // the pass before is finished with the B image
+        const bool load_b = EXPAND ? pass == 0 : route != b_route;
+        if (tid == 0 && load_b) {
+            const size_t r = EXPAND ? 0 : (size_t)route;
+            mbar_arrive_expect_tx(b_bar, b_bytes + sfb_bytes);
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(b_base), "l"(p.b_img + r * p.b_route_bytes), "r"(b_bytes), "r"(b_bar) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(sfb_base), "l"(p.sfb_img + r * p.sfb_route_bytes), "r"(sfb_bytes), "r"(b_bar) : "memory");
+        }
+        if (load_b) { b_route = route; b_loads++; }
+
+        if (warp < 4) {
+            // ===== epilogue: tile row t = 32 * warp + lane =================================================
+            if (lane == 0) mbar_wait(accum_bar, (uint32_t)pass & 1u, abort_flag, p.status);
+            __syncwarp();
+            tc_fence_after();
+            const int row = rt * 128 + warp * 32 + lane;                 // row within the route's matrix
+            const bool live = row < p.rows_per_route;
+            const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + kMxColD;
+            // the pieces' columns (smallest piece first within a thread's eight) of the issuing threads' partial sums
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int i = kMxTmaSplit - 1; i >= 0; i--) {
+                if (i >= nkg) continue;                                  // fewer K groups than issuing threads: nothing was accumulated there
+                uint32_t d0[8], d1[8];
+                tmem_ld8(taddr + 8u * i, d0);
+                if (EXPAND) tmem_ld8(taddr + kColMat + 8u * i, d1);
+                tmem_ld_wait();
+                float t0 = 0.f, t1 = 0.f;
+#pragma unroll
+                for (int c = 7; c >= 0; c--) { t0 = __fadd_rn(t0, __uint_as_float(d0[c])); if (EXPAND) t1 = __fadd_rn(t1, __uint_as_float(d1[c])); }
+                s0 = __fadd_rn(s0, t0); s1 = __fadd_rn(s1, t1);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_free);
+            if (EXPAND) {
+                float a = 0.f;
+                if (live) {
+                    const float sg = s0, su = s1;
+                    const size_t bi = ((size_t)e * p.rows_per_route + row) * p.bias_stride;
+                    const float gate = __fadd_rn(sg, bf16_round(p.b0[bi]));
+                    const float up = __fadd_rn(su, bf16_round(__fadd_rn(p.b1[bi], 1.0f)));
+                    a = swiglu_clipped(gate, up);
+                    p.act_out[(size_t)route * p.rows_per_route + row] = a;
+                }
+                // this warp's 32 rows are one block of the down kernel's contraction: split it into pieces here
+                // (lane l of the split holds element (l >> 1) + 16 * (l & 1) of the block)
+                const int first = rt * 128 + warp * 32;
+                if (first < p.rows_per_route) {                          // rows_per_route is a multiple of 32: the block is whole or absent
+                    const float v = __shfl_sync(0xffffffffu, a, (lane >> 1) + 16 * (lane & 1));
+                    mx_split_block(v, lane, p.act_b + (size_t)route * p.act_b_route_bytes, p.act_sfb + (size_t)route * p.act_sfb_route_bytes, 8u, 0u,
+                                   (uint32_t)first >> 5);
+                }
+            } else if (live) {
+                float sy = s0;
+                if (p.b0) sy = __fadd_rn(sy, bf16_round(p.b0[((size_t)e * p.rows_per_route + row) * p.bias_stride]));
+                p.y[(size_t)route * p.rows_per_route + row] = f32_to_bf16_bits(sy);
+                if (p.residual) {
+                    __threadfence();
+                    const uint32_t seen = atomicAdd(p.arrivals + row, 1u);
+                    if (seen == (uint32_t)(p.routes - 1)) {
+                        p.arrivals[row] = 0;                                            // ready for the next call
+                        if (*reinterpret_cast<volatile uint32_t*>(p.status) == 0u) {
+                            __threadfence();
+                            float sres = 0.0f;
+                            for (int r = 0; r < p.routes; r++)
+                                sres = __fmaf_rn(bf16_bits_to_f32(__ldcg(p.y + (size_t)r * p.rows_per_route + row)), p.probs[r], sres);
+                            if (p.round_sum) sres = bf16_round(sres);
+                            p.residual[row] = f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(p.residual[row]), sres));
+                        }
+                    }
+                }
+            }
+        } else if (warp < kCopyWarp) {
+            if (lane == 0) {
+                // ===== MMA issue: kMxTmaSplit threads per matrix, thread ki takes the K groups g = ki mod kMxTmaSplit =====
+                const int mat = (warp - 4) / kMxTmaSplit, ki = (warp - 4) % kMxTmaSplit;
+                if (pass > 0) mbar_wait(tmem_free, (uint32_t)(pass - 1) & 1u, abort_flag, p.status);
+                if (load_b) {
+                    mbar_wait(b_bar, (uint32_t)(b_loads - 1) & 1u, abort_flag, p.status);
+                    tc_fence_after();
+                }
+                const uint32_t d_t = tmem_base + kMxColD + (uint32_t)mat * kColMat + 8u * (uint32_t)ki;
+                // scale columns of this thread alone (a thread's tcgen05.cp and mma run in the order it issued them): 8 of the
+                // weights, 8 of the activation's pieces, rewritten every K group
+                const uint32_t sfa_t = tmem_base + kMxColSfa + 16u * (uint32_t)(warp - 4), sfb_t = sfa_t + 8u;
+                bool first = true;
+                for (int g = ki; g < nkg; g += kMxTmaSplit) {
+                    const int n = step0 + g, as = n % kMxTmaStages;
+                    mbar_wait(a_full(as), (uint32_t)(n / kMxTmaStages) & 1u, abort_flag, p.status);
+                    tc_fence_after();
+                    const uint32_t stage = a_base + (uint32_t)as * kStage;
+                    const uint32_t sfa_smem = stage + NMAT * 16384u + (uint32_t)mat * 1024u;
+                    mx_cp_scales(sfa_t, mx_sf_desc(sfa_smem));
+                    mx_cp_scales(sfa_t + 4u, mx_sf_desc(sfa_smem + 512u));
+                    mx_cp_scales(sfb_t, mx_sf_desc(sfb_base + 1024u * (uint32_t)g));
+                    mx_cp_scales(sfb_t + 4u, mx_sf_desc(sfb_base + 1024u * (uint32_t)g + 512u));
+                    const uint64_t ad = umma_desc(stage + (uint32_t)mat * 16384u);
+                    const uint64_t bd = umma_desc(b_base + (uint32_t)g * (NCOL * 128u));
+#pragma unroll
+                    for (int kk = 0; kk < 4; kk++) {
+                        const uint32_t sfid = (uint32_t)(kk & 1) * 2u;
+                        umma_mxf4(d_t, ad + 2u * kk, bd + 2u * kk, mx_idesc(NCOL, sfid), sfa_t + 4u * (kk >> 1), sfb_t + 4u * (kk >> 1),
+                                  (!first || kk) ? 1u : 0u);
+                    }
+                    first = false;
+                    umma_commit(a_empty(as));
+                }
+                umma_commit(accum_bar);
+            }
+        } else if (warp == kCopyWarp && lane == 0) {
+            // ===== the weight tiles and their scale tiles, one K group per stage ================================
+            const size_t t0 = ((size_t)e * tpr + rt) * nkg;
+            const unsigned char* sf0 = q.sf[0] + t0 * 1024;
+            const unsigned char* sf1 = NMAT > 1 ? q.sf[1] + t0 * 1024 : nullptr;
+            const unsigned char* c0 = q.codes[0] + (t0 << 14);
+            const unsigned char* c1 = NMAT > 1 ? q.codes[1] + (t0 << 14) : nullptr;
+            for (int g = 0; g < nkg; g++) {
+                const int n = step0 + g, as = n % kMxTmaStages;
+                const uint32_t stage = a_base + (uint32_t)as * kStage;
+                mbar_wait(a_empty(as), ((uint32_t)(n / kMxTmaStages) & 1u) ^ 1u, abort_flag, p.status);
+                mbar_arrive_expect_tx(a_full(as), kStage);
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(stage),
+                             "l"(c0 + ((size_t)g << 14)), "r"(16384u), "r"(a_full(as)) : "memory");
+                if (NMAT > 1)
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(stage + 16384u),
+                                 "l"(c1 + ((size_t)g << 14)), "r"(16384u), "r"(a_full(as)) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(stage + NMAT * 16384u),
+                             "l"(sf0 + (size_t)g * 1024), "r"(1024u), "r"(a_full(as)) : "memory");
+                if (NMAT > 1)
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(stage + NMAT * 16384u + 1024u),
+                                 "l"(sf1 + (size_t)g * 1024), "r"(1024u), "r"(a_full(as)) : "memory");
+            }
+        }
+        step0 += nkg;
+    }
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 64; i++) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 4) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kMxTmemCols);
+    }
+}
+
 }  // namespace oco

@@ -847,7 +847,8 @@ def test_repeated_steps_are_bit_identical(moe, config, tokens, numerics):
 
 
 def test_repacked_planes_hold_the_blocks_bytes(moe):
-    """oco_moe_bind_repacked: every block's sixteen code bytes at [row][16 * block], its scale byte in the tile
+    """oco_moe_bind_repacked: every block's sixteen code bytes where the MMA reads them from shared memory (tile of 128
+    rows and 8 blocks, K-major with the 128-byte swizzle), its scale byte in the tile
     tcgen05.cp reads (tile of 128 rows, K group of 8 blocks, 512-byte half, (row % 32) * 16 + (row / 32) * 4 +
     block % 4), zero where a feature tile runs past the expert's last row; plans that have no use for it refuse."""
     import torch
@@ -866,19 +867,56 @@ def test_repacked_planes_hold_the_blocks_bytes(moe):
         nkb, nt = k // 32, (n + 127) // 128
         nkg = (nkb + 7) // 8
         blocks = np.ascontiguousarray(w).reshape(E, n, nkb, 17)
-        codes_bytes = (E * n * (k // 2) + 1023) // 1024 * 1024
-        codes = buf[at: at + E * n * (k // 2)].reshape(E, n, nkb, 16)
-        assert np.array_equal(codes, blocks[..., 1:])
-        at += codes_bytes
+        codes = buf[at: at + E * nt * nkg * 16384].reshape(E, nt, nkg, 16384)
+        want_c = np.zeros_like(codes)
+        r = np.arange(n)
+        for blk in range(nkb):
+            off = ((r % 128) // 8) * 1024 + (r % 8) * 128 + (((blk % 8) ^ (r % 8)) * 16)
+            for j in range(16):
+                want_c[:, r // 128, blk // 8, off + j] = blocks[:, :, blk, 1 + j]
+        assert np.array_equal(codes, want_c)
+        at += E * nt * nkg * 16384
         sf = buf[at: at + E * nt * nkg * 1024].reshape(E, nt, nkg, 2, 32, 16)
         want = np.zeros_like(sf)
-        r = np.arange(n)
         for blk in range(nkb):
             want[:, r // 128, blk // 8, (blk // 4) % 2, r % 32, ((r % 128) // 32) * 4 + blk % 4] = blocks[:, :, blk, 0]
         assert np.array_equal(sf, want)
         at += E * nt * nkg * 1024
     assert at == nbytes
-    plain = moe.plan_for(layer)
-    assert _lib.lib().oco_moe_repack_bytes(plain.handle) == 0
+    other = moe._Plan(synth.ARCH_NEMOTRON, 256, 192, 8, 2, synth.FMT_Q4_0)
+    assert _lib.lib().oco_moe_repack_bytes(other.handle) == 0
     with pytest.raises(moe.OcoError):
-        plain.repack()
+        other.repack()
+
+
+@pytest.mark.parametrize("hidden,ffn,experts,misalign", [(96, 96, 32, 0), (640, 384, 32, 0), (256, 160, 32, 7), (2880, 2880, 32, 0),
+                                                          (4096, 256, 8, 3)],
+                         ids=["k96", "k640", "unaligned", "20b", "k4096"])
+def test_gpt_oss_single_token_over_repacked_weights(moe, oracle, monkeypatch, hidden, ffn, experts, misalign):
+    """One token with the repacked form of the expert tensors bound (reference numerics): every weight tile
+    reaches the block-scaled MMA by TMA, the token and the activations ride as exact e2m1 pieces. Same bars as
+    the default single-token kernels (ids and weights bit-exact, outputs rel-L2 <= 1e-3 against the oracle's
+    single-token arithmetic), last row tiles past the expert's rows, partly filled K groups, two calls in a row."""
+    import torch
+    monkeypatch.setenv("OCO_MOE_REPACKED_TOKEN", "1")          # opt-in: the default single-token kernels are faster
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, hidden, ffn, experts, min(4, experts), synth.FMT_MXFP4, seed=91)
+    plan = moe.plan_for(layer)
+    plan.reserve(4)
+    w = moe._Weights.from_layer(layer, misalign=misalign)
+    plan.bind(w)
+    plan.repack()
+    for seed in (hidden, hidden + 1):
+        xb, rb = synth.make_tokens(hidden, 1, seed, "normal")
+        x = torch.from_numpy(xb.view(np.int16)).cuda()
+        res = torch.from_numpy(rb.view(np.int16).copy()).cuda()
+        plan.forward(x, res, 1)
+        torch.cuda.synchronize()
+        plan.poll()
+        assert plan.launch_count() == 3
+        ref = oracle.moe_forward(layer, xb, rb, mode=1)
+        routing = moe.Routing()
+        routing.plan, routing.rows = plan, 1
+        r = routing.read()
+        assert np.array_equal(r["ids"], ref.ids) and np.array_equal(r["prob"].view(np.uint32), ref.probs.view(np.uint32))
+        assert rel_l2(r["y"], ref.y) <= REL_L2
+        assert rel_l2(res.cpu().numpy().view(np.uint16), ref.out) <= REL_L2
