@@ -487,6 +487,28 @@ def run_dense(args, ctx):
                 gpu_launches=launches, roofline=roofline, parity=parity, cpu_baseline=cpu)
 
 
+def block_scaled_distance(workload, tokens, seed, repacked):
+    """What the opt-in block-scaled mode costs in accuracy: a token sample of its output against the checker that
+    carries the reference's arithmetic."""
+    from oco_b200 import moe as _moe
+    import oracle
+    cfg_name, dt = WORKLOADS[workload]
+    tk = tokens or dt
+    lay = synth.make_config(cfg_name, seed=0 if seed is None else seed % 1000)
+    xb, rb = synth.make_tokens(lay.hidden, tk, seed, "normal")
+    got, routing = _moe.run_layer(lay, xb, rb, numerics=2, repacked=repacked)
+    pick = np.unique(np.linspace(0, tk - 1, 8).astype(int))
+    ref = oracle.moe_forward(lay, xb[pick], rb[pick], mode=2, trace=False)
+    g = synth.bf16_bits_to_f32(got[pick]).astype(np.float64)
+    r = synth.bf16_bits_to_f32(ref.out).astype(np.float64)
+    moe_part = r - synth.bf16_bits_to_f32(rb[pick]).astype(np.float64)
+    return dict(ids_exact=bool(np.array_equal(routing["ids"][pick], ref.ids)),
+                rel_l2_vs_reference_arithmetic=float(np.linalg.norm(g - r) / np.linalg.norm(r)),
+                rel_l2_of_the_layer_term_alone=float(np.linalg.norm(g - r) / max(np.linalg.norm(moe_part), 1e-30)),
+                sample=f"{len(pick)} tokens against the CPU checker (reference arithmetic); the mode's own arithmetic "
+                       "(the same quantised operands in float64) is held to 1e-3 by the GPU tests")
+
+
 def measure_layer(args, ctx, workload, steps, warmup, tokens=0, graph=True, with_norm=False, layers=0, sustained_s=0.0, numerics=0):
     """One workload on this rank's GPU (every rank runs the same layer on its own tokens): device-timed
     steps, per-kernel phase times, the end-to-end call with host buffers and, on request, a seconds-long
@@ -799,26 +821,9 @@ def main():
         else:
             line["cpu_baseline"] = None
     if args.numerics == 2:
-        # what the opt-in mode costs in accuracy: a token sample against the checker that carries the reference's arithmetic
-        import torch as _t
-        from oco_b200 import moe as _moe
-        import oracle
-        cfg_name, dt = WORKLOADS[args.workload]
-        tk = args.tokens or dt
-        lay = synth.make_config(cfg_name, seed=args.seed)
-        xb, rb = synth.make_tokens(lay.hidden, tk, args.seed + 1000 * rank, "normal")
-        got, routing = _moe.run_layer(lay, xb, rb, numerics=2, repacked=args.repacked)
-        pick = np.unique(np.linspace(0, tk - 1, 8).astype(int))
-        ref = oracle.moe_forward(lay, xb[pick], rb[pick], mode=2, trace=False)
-        g = synth.bf16_bits_to_f32(got[pick]).astype(np.float64)
-        r = synth.bf16_bits_to_f32(ref.out).astype(np.float64)
-        moe_part = r - synth.bf16_bits_to_f32(rb[pick]).astype(np.float64)
+        par = block_scaled_distance(args.workload, args.tokens, args.seed + 1000 * rank, args.repacked)
         if rank == 0:
-            line["parity"] = dict(ids_exact=bool(np.array_equal(routing["ids"][pick], ref.ids)),
-                                  rel_l2_vs_reference_arithmetic=float(np.linalg.norm(g - r) / np.linalg.norm(r)),
-                                  rel_l2_of_the_layer_term_alone=float(np.linalg.norm(g - r) / max(np.linalg.norm(moe_part), 1e-30)),
-                                  sample=f"{len(pick)} tokens against the CPU checker (reference arithmetic); the mode's own arithmetic "
-                                         "(the same quantised operands in float64) is held to 1e-3 by the GPU tests")
+            line["parity"] = par
     if extras:
         # the HBM half of the metric: one token through the same layer (three launches replayed as a graph)
         dec = measure_layer(args, ctx, "gpt-oss-20b-decode", 200, 10)
@@ -829,6 +834,22 @@ def main():
                                   per_kernel_hbm=rl.get("per_kernel"), phases_ms=dec["phases_ms"], gpu_launches=dec["gpu_launches"],
                                   e2e_us_per_token=1e3 * dec["e2e"]["ms_per_step"], config=dec["config"],
                                   hbm_peak_gbs=measured_peaks()["hbm_gbs"], hbm_nominal_gbs=8000.0)
+        # the FP4 half of the metric's tensor roofline: the same workload in the opt-in block-scaled numerics (MXFP4
+        # activations; NOT the reference's arithmetic, never the headline) over the repacked form of the expert tensors
+        import copy as _copy
+        bs_args = _copy.copy(args)
+        bs_args.repacked = True
+        bs = measure_layer(bs_args, ctx, "gpt-oss-20b-prefill", 20, 5, numerics=2)
+        if rank == 0:
+            bs_par = block_scaled_distance("gpt-oss-20b-prefill", 0, args.seed, True)
+            brl = bs["roofline"] or {}
+            line["block_scaled"] = dict(numerics=2, repacked_weights=True, ms_per_step=bs["ms_per_step"], tokens_per_s=bs["value"] / world,
+                                        phases_ms=bs["phases_ms"], up_tiles_tflops=brl.get("achieved"),
+                                        frac_of_fp4_tcgen05_measured=brl.get("frac"), frac_of_fp4_nominal=brl.get("frac_of_fp4_nominal"),
+                                        parity=bs_par, gpu_launches=bs["gpu_launches"],
+                                        note="opt-in numerics: MXFP4 activations on tcgen05 kind::mxf4; its own arithmetic is held to 1e-3 by "
+                                             "the GPU tests, the distance to the reference's arithmetic is parity.rel_l2_vs_reference_arithmetic")
+        if rank == 0:
             # every tensor fraction against the measured and the nominal ceilings
             pk = tensor_peaks()
             mp = measured_peaks()
