@@ -456,16 +456,28 @@ __global__ void __launch_bounds__(kRouterBlockThreads, 1) router_block_kernel(co
             else *reinterpret_cast<uint4*>(xs + (size_t)r * H + 8 * j) = make_uint4(0u, 0u, 0u, 0u);
         }
     }
+    // copy role: a ring stage is EB rows of KC / 4 pieces; thread t takes pieces t and t + threads of that grid
+    // (row = piece / (KC / 4), column piece % (KC / 4): fixed per thread, so no division in the loop)
+    constexpr int kPiecesPerRow = KC / 4, kPiecesPerThread = (EB * kPiecesPerRow + kRouterBlockThreads - 1) / kRouterBlockThreads;
+    int prow[kPiecesPerThread], pcol[kPiecesPerThread];
+#pragma unroll
+    for (int u = 0; u < kPiecesPerThread; u++) {
+        const int c = threadIdx.x + u * kRouterBlockThreads;
+        prow[u] = c / kPiecesPerRow;
+        pcol[u] = c - prow[u] * kPiecesPerRow;
+    }
+    int is_eb = 0, is_kc = 0;                                  // the (expert block, column chunk) of the next step to issue
     auto issue = [&](int s) {                               // step s: expert block s / nkc, column chunk s % nkc
         if (s < steps) {
-            const int eb = s / nkc, kc = s - eb * nkc;
-            const int e0 = e_begin + EB * eb, rows = min(EB, e_end - e0);
-            const int cols = min(KC, H - kc * KC), pieces = cols / 4;
+            const int e0 = e_begin + EB * is_eb, rows = min(EB, e_end - e0);
+            const int cols = min(KC, H - is_kc * KC);
             const uint32_t dst = smem_u32(ring + (size_t)(s % kRouterBlockStages) * EB * KC);
-            for (int c = threadIdx.x; c < rows * pieces; c += kRouterBlockThreads) {
-                const int r = c / pieces, j = c - r * pieces;
-                cp_async16(dst + (uint32_t)(r * KC + 4 * j) * 4u, w + (size_t)(e0 + r) * H + kc * KC + 4 * j);
-            }
+            const float* src = w + (size_t)e0 * H + is_kc * KC;
+#pragma unroll
+            for (int u = 0; u < kPiecesPerThread; u++)
+                if (prow[u] < rows && 4 * pcol[u] < cols)
+                    cp_async16(dst + (uint32_t)(prow[u] * KC + 4 * pcol[u]) * 4u, src + (size_t)prow[u] * H + 4 * pcol[u]);
+            if (++is_kc == nkc) { is_kc = 0; is_eb++; }
         }
         cp_async_commit();
     };
@@ -475,11 +487,13 @@ __global__ void __launch_bounds__(kRouterBlockThreads, 1) router_block_kernel(co
     for (int j = 0; j < 4; j++) v[j][0] = v[j][1] = v[j][2] = v[j][3] = 0.f;
     float acc[4][4][4];                                     // [token][expert][chain]
     const uint16_t* xw = xs + (size_t)(4 * warp) * H;
+    int cur_eb = 0, cur_kc = 0;
     for (int s = 0; s < steps; s++) {
         cp_async_wait<1>();
         __syncthreads();                                    // step s has landed for everyone; step s - 1 is no longer read
         issue(s + 2);
-        const int eb = s / nkc, kc = s - eb * nkc;
+        const int eb = cur_eb, kc = cur_kc;
+        if (++cur_kc == nkc) { cur_kc = 0; cur_eb++; }
         const float* wr = ring + (size_t)(s % kRouterBlockStages) * EB * KC + (size_t)esub * KC;
         if (kc == 0) {
 #pragma unroll
