@@ -194,11 +194,22 @@ int oco_moe_combine_shared(oco_moe_plan* plan, const uint16_t* y_bf16, const flo
 int oco_moe_add_norm_forward(oco_moe_plan* plan, uint16_t* hidden_bf16, const uint16_t* projected_bf16,
                              const float* norm_weight, float epsilon, int full_layer, int rows, void* cuda_stream);
 
-/* The same call for host buffers: copies x to the device on `cuda_stream`, the residual rows on a
- * second stream the plan owns (they are needed by the last kernel only, so their copy overlaps the
- * router and the expert products), runs the layer, copies the residual back on `cuda_stream` and
- * waits for it. Uses staging space inside the bound workspace. Pinned host buffers make the
- * copies asynchronous. */
+/* The same call for host buffers, submitted eagerly (reference Compute::submit,
+ * src/weights/compute/submission.rs:17-24: work is submitted at once and completion is signalled later; the
+ * caller gives up host access to the writable buffer until then). _begin queues, without waiting: the copy
+ * of x and then of the residual rows to the device on a stream the plan owns (the residual rows are needed
+ * by the last kernel only, so their copy runs beside the router and the expert products), the layer on
+ * `cuda_stream`, and the copy of the residual rows back on a second stream of the plan. _end waits until the
+ * oldest begun call has its rows back in `residual_bf16_host`. Up to two calls may be in flight (the third
+ * _begin is refused with OCO_INVALID_ARGUMENT): the copies of call c + 1 then cross the bus beside the
+ * kernels of call c. All calls of a plan go to one `cuda_stream`. Staging space (two slots) lies inside the
+ * bound workspace; pinned host buffers make the copies asynchronous. */
+int oco_moe_forward_host_begin(oco_moe_plan* plan, const uint16_t* x_bf16_host, uint16_t* residual_bf16_host,
+                               int rows, void* cuda_stream);
+int oco_moe_forward_host_end(oco_moe_plan* plan);
+
+/* _begin followed by _end (calls begun earlier are ended first): one layer call on host buffers that
+ * returns with the result in `residual_bf16_host`. */
 int oco_moe_forward_host(oco_moe_plan* plan, const uint16_t* x_bf16_host, uint16_t* residual_bf16_host,
                          int rows, void* cuda_stream);
 

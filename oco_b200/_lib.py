@@ -51,6 +51,8 @@ SIGNATURES = {
     "oco_moe_experts": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "oco_moe_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "oco_moe_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "oco_moe_forward_host_begin": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "oco_moe_forward_host_end": (C.c_int, [C.c_void_p]),
     "oco_moe_poll": (C.c_int, [C.c_void_p, C.c_void_p]),
     "oco_moe_routing": (C.c_int, [C.c_void_p, C.POINTER(RoutingView)]),
     "oco_moe_last_error": (C.c_char_p, [C.c_void_p]),

@@ -65,8 +65,8 @@ struct Workspace {
     unsigned char* mxq_xsf = nullptr;
     unsigned char* mxq_act = nullptr; //   and the same for the activated rows [R][F / 2]
     unsigned char* mxq_actsf = nullptr;
-    uint16_t* host_x = nullptr;   // staging for the host-buffer entry point
-    uint16_t* host_res = nullptr;
+    uint16_t* host_x[2] = {nullptr, nullptr};     // staging for the host-buffer entry points: two calls may be in flight
+    uint16_t* host_res[2] = {nullptr, nullptr};
     size_t total = 0;
 };
 
@@ -105,8 +105,12 @@ struct oco_moe_plan {
     unsigned char* rp_sf[3] = {nullptr, nullptr, nullptr};
     // Per-phase timestamps (the counterpart of the reference's OCO_PROFILE counter heap,
     // src/gpu/profile.rs:1-31, src/gpu/dispatch.rs:189-208): one event before each kernel.
-    cudaStream_t copy_stream = nullptr;   // oco_moe_forward_host: the residual rows' own stream
-    cudaEvent_t ev_fork = nullptr, ev_residual = nullptr;
+    // oco_moe_forward_host_begin / _end: the rows travel on two streams of the plan's own (one per direction);
+    // call c uses staging slot c % 2, whose events say when its x rows, its residual rows, its kernels and its
+    // copy back are done
+    cudaStream_t in_stream = nullptr, out_stream = nullptr;
+    cudaEvent_t ev_x[2] = {}, ev_res[2] = {}, ev_done[2] = {}, ev_out[2] = {};
+    uint64_t host_begun = 0, host_ended = 0;
     bool no_batch_path = false;  // OCO_MOE_NO_BATCH=1: few tokens take the tile kernels too
     int batch_max_avg = 8;       // routes per expert (on average) up to which the streamed few-token kernels run
                                  // (measured: they win up to 16-32 at the gpt-oss shapes; OCO_MOE_BATCH_MAX_AVG overrides)
@@ -244,8 +248,10 @@ Workspace carve(const oco_moe_desc& d, int max_rows, unsigned char* base) {
         w.mxq_act = (unsigned char*)take(R * F / 2);
         w.mxq_actsf = (unsigned char*)take(tiles128 * ((F / 32 + 7) / 8) * 1024);
     }
-    w.host_x = (uint16_t*)take(T * H * 2);
-    w.host_res = (uint16_t*)take(T * H * 2);
+    for (int i = 0; i < 2; i++) {
+        w.host_x[i] = (uint16_t*)take(T * H * 2);
+        w.host_res[i] = (uint16_t*)take(T * H * 2);
+    }
     w.total = off;
     return w;
 }
@@ -991,9 +997,14 @@ void oco_moe_plan_destroy(oco_moe_plan* plan) {
     if (!plan) return;
     for (int i = 0; i < kMaxMarks; i++)
         if (plan->marks[i]) cudaEventDestroy(plan->marks[i]);
-    if (plan->ev_fork) cudaEventDestroy(plan->ev_fork);
-    if (plan->ev_residual) cudaEventDestroy(plan->ev_residual);
-    if (plan->copy_stream) cudaStreamDestroy(plan->copy_stream);
+    for (int i = 0; i < 2; i++) {
+        if (plan->ev_x[i]) cudaEventDestroy(plan->ev_x[i]);
+        if (plan->ev_res[i]) cudaEventDestroy(plan->ev_res[i]);
+        if (plan->ev_done[i]) cudaEventDestroy(plan->ev_done[i]);
+        if (plan->ev_out[i]) cudaEventDestroy(plan->ev_out[i]);
+    }
+    if (plan->in_stream) cudaStreamDestroy(plan->in_stream);
+    if (plan->out_stream) cudaStreamDestroy(plan->out_stream);
     delete plan;
 }
 
@@ -1360,32 +1371,66 @@ void oco_moe_graph_destroy(oco_moe_graph* graph) {
     delete graph;
 }
 
-int oco_moe_forward_host(oco_moe_plan* plan, const uint16_t* x_host, uint16_t* residual_host, int rows,
-                         void* cuda_stream) {
+int oco_moe_forward_host_begin(oco_moe_plan* plan, const uint16_t* x_host, uint16_t* residual_host, int rows,
+                               void* cuda_stream) {
     if (!plan) return OCO_INVALID_ARGUMENT;
     if (!plan->have_ws) return fail(plan, OCO_INVALID_ARGUMENT, "bind a workspace first");
     if (int rc_dev = check_device(plan)) return rc_dev;
     if (!x_host || !residual_host || rows < 1 || rows > plan->max_rows) return fail(plan, OCO_INVALID_ARGUMENT, "bad host buffers or rows");
+    if (!plan->have_w) return fail(plan, OCO_INVALID_ARGUMENT, "bind weights first");
+    if (plan->host_begun - plan->host_ended >= 2) return fail(plan, OCO_INVALID_ARGUMENT, "two host calls are in flight: end one first");
     cudaStream_t st = (cudaStream_t)cuda_stream;
     const size_t bytes = (size_t)rows * plan->d.hidden * 2;
-    if (!plan->have_w) return fail(plan, OCO_INVALID_ARGUMENT, "bind weights first");
-    // The residual rows are only needed by the last kernel: they travel on a second stream while
-    // the router and the expert products run.
-    if (!plan->copy_stream) {
-        CK(cudaStreamCreateWithFlags(&plan->copy_stream, cudaStreamNonBlocking));
-        CK(cudaEventCreateWithFlags(&plan->ev_fork, cudaEventDisableTiming));
-        CK(cudaEventCreateWithFlags(&plan->ev_residual, cudaEventDisableTiming));
+    if (!plan->in_stream) {
+        CK(cudaStreamCreateWithFlags(&plan->in_stream, cudaStreamNonBlocking));
+        CK(cudaStreamCreateWithFlags(&plan->out_stream, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; i++) {
+            CK(cudaEventCreateWithFlags(&plan->ev_x[i], cudaEventDisableTiming));
+            CK(cudaEventCreateWithFlags(&plan->ev_res[i], cudaEventDisableTiming));
+            CK(cudaEventCreateWithFlags(&plan->ev_done[i], cudaEventDisableTiming));
+            CK(cudaEventCreateWithFlags(&plan->ev_out[i], cudaEventDisableTiming));
+        }
     }
-    CK(cudaMemcpyAsync(plan->ws.host_x, x_host, bytes, cudaMemcpyHostToDevice, st));
-    CK(cudaEventRecord(plan->ev_fork, st));       // the bus is free for the residual rows once x has arrived
-    CK(cudaStreamWaitEvent(plan->copy_stream, plan->ev_fork, 0));
-    CK(cudaMemcpyAsync(plan->ws.host_res, residual_host, bytes, cudaMemcpyHostToDevice, plan->copy_stream));
-    CK(cudaEventRecord(plan->ev_residual, plan->copy_stream));
-    int rc = forward_any(plan, plan->ws.host_x, plan->ws.host_res, rows, st, plan->ev_residual);
+    const int s = (int)(plan->host_begun & 1);
+    uint16_t* dx = plan->ws.host_x[s];
+    uint16_t* dres = plan->ws.host_res[s];
+    // In: the slot is free once the call that used it last has copied its rows back (which follows its
+    // kernels); x goes first, the residual rows, which only the last kernel needs, behind it.
+    CK(cudaStreamWaitEvent(plan->in_stream, plan->ev_out[s], 0));
+    CK(cudaMemcpyAsync(dx, x_host, bytes, cudaMemcpyHostToDevice, plan->in_stream));
+    CK(cudaEventRecord(plan->ev_x[s], plan->in_stream));
+    CK(cudaMemcpyAsync(dres, residual_host, bytes, cudaMemcpyHostToDevice, plan->in_stream));
+    CK(cudaEventRecord(plan->ev_res[s], plan->in_stream));
+    // The layer, on the caller's stream, behind whatever that stream already holds (the call before).
+    CK(cudaStreamWaitEvent(st, plan->ev_x[s], 0));
+    int rc = forward_any(plan, dx, dres, rows, st, plan->ev_res[s]);
     if (rc) return rc;
-    CK(cudaMemcpyAsync(residual_host, plan->ws.host_res, bytes, cudaMemcpyDeviceToHost, st));
-    CK(cudaStreamSynchronize(st));
+    CK(cudaEventRecord(plan->ev_done[s], st));
+    // Out: the residual rows back, beside the kernels of the next call.
+    CK(cudaStreamWaitEvent(plan->out_stream, plan->ev_done[s], 0));
+    CK(cudaMemcpyAsync(residual_host, dres, bytes, cudaMemcpyDeviceToHost, plan->out_stream));
+    CK(cudaEventRecord(plan->ev_out[s], plan->out_stream));
+    plan->host_begun++;
     return OCO_OK;
+}
+
+int oco_moe_forward_host_end(oco_moe_plan* plan) {
+    if (!plan) return OCO_INVALID_ARGUMENT;
+    if (plan->host_begun == plan->host_ended) return fail(plan, OCO_INVALID_ARGUMENT, "no host call is in flight");
+    if (int rc_dev = check_device(plan)) return rc_dev;
+    const int s = (int)(plan->host_ended & 1);
+    plan->host_ended++;
+    CK(cudaEventSynchronize(plan->ev_out[s]));
+    return OCO_OK;
+}
+
+int oco_moe_forward_host(oco_moe_plan* plan, const uint16_t* x_host, uint16_t* residual_host, int rows,
+                         void* cuda_stream) {
+    if (!plan) return OCO_INVALID_ARGUMENT;
+    while (plan->host_begun != plan->host_ended)                 // calls begun earlier finish first
+        if (int rc = oco_moe_forward_host_end(plan)) return rc;
+    if (int rc = oco_moe_forward_host_begin(plan, x_host, residual_host, rows, cuda_stream)) return rc;
+    return oco_moe_forward_host_end(plan);
 }
 
 int oco_moe_poll(oco_moe_plan* plan, void* cuda_stream) {

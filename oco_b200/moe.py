@@ -133,6 +133,15 @@ class _Plan:
         self._check(_lib.lib().oco_moe_forward_host(self.handle, x.ctypes.data_as(C.c_void_p),
                                                     residual.ctypes.data_as(C.c_void_p), rows, _stream_ptr()))
 
+    def forward_host_begin(self, x: np.ndarray, residual: np.ndarray, rows: int):
+        """Queue the layer on host buffers (up to two calls in flight); `residual` is the caller's again after
+        the matching forward_host_end."""
+        self._check(_lib.lib().oco_moe_forward_host_begin(self.handle, x.ctypes.data_as(C.c_void_p),
+                                                          residual.ctypes.data_as(C.c_void_p), rows, _stream_ptr()))
+
+    def forward_host_end(self):
+        self._check(_lib.lib().oco_moe_forward_host_end(self.handle))
+
     def repack(self, device="cuda"):
         """The optional second form of the expert tensors for numerics 2 (oco_moe_bind_repacked)."""
         nbytes = _lib.lib().oco_moe_repack_bytes(self.handle)

@@ -286,6 +286,42 @@ def test_host_buffer_entry_point(moe, oracle):
         plan.forward_host(x, got, 51)      # beyond the reserved rows: a status, not a crash
 
 
+def test_host_calls_in_flight(moe, oracle):
+    """Two host calls in flight (oco_moe_forward_host_begin / _end): six calls on different rows, each ended
+    only after the next one was begun, give what the one-call-at-a-time entry point gives, bit for bit, and
+    that equals the oracle; a third call in flight and an end without a call are refused with a status."""
+    import torch
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, 256, 192, 32, 4, synth.FMT_MXFP4, seed=16)
+    rows = 300
+    plan = moe.plan_for(layer)
+    plan.reserve(rows)
+    plan.bind(moe._Weights.from_layer(layer))
+    with pytest.raises(moe.OcoError):
+        plan.forward_host_end()
+    calls = []
+    for c in range(6):
+        n = rows - 37 * c                                   # ragged: every call has its own row count
+        x, res = synth.make_tokens(256, n, 40 + c, "normal")
+        hx = torch.from_numpy(x.view(np.int16)).pin_memory().numpy().view(np.uint16)
+        hres = torch.from_numpy(res.view(np.int16).copy()).pin_memory().numpy().view(np.uint16)
+        calls.append((n, x, res, hx, hres))
+    for c, (n, x, res, hx, hres) in enumerate(calls):
+        plan.forward_host_begin(hx, hres, n)
+        if c == 1:
+            with pytest.raises(moe.OcoError):               # calls 0 and 1 are in flight
+                plan.forward_host_begin(hx, hres, n)
+        if c >= 1:
+            plan.forward_host_end()                         # call c - 1
+    plan.forward_host_end()
+    plan.poll()
+    for n, x, res, hx, hres in calls:
+        one = res.copy()
+        plan.forward_host(x, one, n)
+        assert np.array_equal(hres, one)
+    n, x, res, hx, hres = calls[0]
+    assert rel_l2(hres, oracle.moe_forward(layer, x, res).out) <= REL_L2
+
+
 def selection_margin(layer, x_bits, logits_f32, ids):
     """Smallest gap, over the tokens, between the last selected and the first rejected expert, measured on
     logits recomputed in float64 from the same rounded operands (bf16 x; bf16 router weights and bias for the
