@@ -14,6 +14,7 @@
 #include "batch.cuh"
 #include "gemm.cuh"
 #include "gemm_wide.cuh"
+#include "gemm_pair.cuh"
 #include "mx.cuh"
 #include "gemm_mx.cuh"
 #include <cmath>
@@ -117,6 +118,7 @@ struct oco_moe_plan {
     int route_plan_single_max = 2048;   // routes up to which one CTA makes the route plan (OCO_MOE_ROUTE_PLAN_SINGLE_MAX)
     int wide_min_avg = 1;        // OCO_MOE_WIDE_MIN_AVG: routes per expert from which layers take the 256-route tiles
     int router_block_min = 512;  // OCO_MOE_ROUTER_BLOCK_MIN: rows from which the register-blocked router kernel runs
+    bool pair_tiles = false;     // OCO_MOE_PAIR_TILES=1: 256-route tiles on SM pairs (grouped_gemm_pair_kernel)
     bool narrow_tiles = false;   // OCO_MOE_NARROW_TILES=1: keep the generic tile kernel for 256-route tiles too
     bool profiling = false;
     int n_marks = 0;
@@ -342,6 +344,20 @@ cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// The same for a kernel that runs in clusters of two CTAs.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent_pairs(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <int FMT, int EPI, int NT>
 int launch_gemm(oco_moe_plan* plan, const GemmParams& gp, const CUtensorMap& map, int max_tiles, cudaStream_t st) {
     using S = GemmShape<EPI, NT>;
@@ -366,6 +382,17 @@ int launch_gemm_wide(oco_moe_plan* plan, GemmParams gp, const CUtensorMap* maps,
     const size_t bytes = (size_t)experts * gp.n * gp.row_bytes - (gp.row_bytes - packed_row_bytes(FMT, gp.K));
     gp.w0_end = (const uint8_t*)(((uintptr_t)gp.w0 + bytes + 15) & ~(uintptr_t)15);
     gp.w1_end = gp.w1 ? (const uint8_t*)(((uintptr_t)gp.w1 + bytes + 15) & ~(uintptr_t)15) : nullptr;
+    if (gp.tile_rows > 256) {
+        // SM pairs on route tiles of up to 512 routes: an even, persistent grid of two-CTA clusters
+        ALLOW_SMEM_ONCE((grouped_gemm_pair_kernel<FMT, EPI>));
+        const int per = epi_gated(EPI) ? 128 : 256;
+        const int pairs = std::min(plan->sm_count / 2, ((gp.n + per - 1) / per) * max_tiles);
+        CK(launch_dependent_pairs(grouped_gemm_pair_kernel<FMT, EPI>, dim3(2 * pairs), dim3(PairShapeT<FMT>::kThreads), PairShapeT<FMT>::kSmemBytes, st, gp,
+                                  maps[0], maps[1], maps[2]));
+        plan->launches++;
+        CK(cudaGetLastError());
+        return OCO_OK;
+    }
     ALLOW_SMEM_ONCE((grouped_gemm_wide_kernel<FMT, EPI>));
     // persistent: one CTA per SM walks the (route tile, feature tile) items; never more CTAs than items can exist
     const int feats = (gp.n + (epi_gated(EPI) ? 127 : 255)) / (epi_gated(EPI) ? 128 : 256);
@@ -793,7 +820,9 @@ int stage_experts(oco_moe_plan* plan, const uint16_t* x, const uint32_t* ids, in
         if (d.numerics == 2) return stage_experts_mx(plan, x, ids, R, per_row, y, st, rs);
     }
     const int nt_index = pick_tile_index(live, E, plan->narrow_tiles ? 192 : plan->wide_min_avg);
-    const int NT = kTileSizes[nt_index];
+    // SM pairs (grouped_gemm_pair_kernel) take route tiles of up to 512 routes
+    const bool pair = plan->pair_tiles && nt_index == 3 && plan->d.gemm_impl == 0 && !plan->narrow_tiles;
+    const int NT = pair ? 512 : kTileSizes[nt_index];
     plan->last_tile_rows = NT;
     launch_route_plan(plan, ids, R, E, NT, rs, st);
     mark(plan, st, "permute");
@@ -979,6 +1008,7 @@ int oco_moe_plan_create(const oco_moe_desc* desc, oco_moe_plan** out) {
     }
     { const char* e = getenv("OCO_MOE_NARROW_TILES"); plan->narrow_tiles = e && e[0] == '1'; }
     { const char* e = getenv("OCO_MOE_WIDE_MIN_AVG"); if (e && atoi(e) > 0) plan->wide_min_avg = atoi(e); }
+    { const char* e = getenv("OCO_MOE_PAIR_TILES"); if (e) plan->pair_tiles = atoi(e) != 0; }
     { const char* e = getenv("OCO_MOE_ROUTER_BLOCK_MIN"); if (e && atoi(e) > 0) plan->router_block_min = atoi(e); }
     { const char* e = getenv("OCO_MOE_NO_BATCH"); plan->no_batch_path = e && e[0] == '1'; }
     { const char* e = getenv("OCO_MOE_TOKEN_MX"); plan->mx_on = e && e[0] == '1'; }

@@ -166,6 +166,37 @@ def test_gpt_oss_forced_routes_reference_ids(moe, oracle):
     assert rel_l2(out, ref.out) <= REL_L2
 
 
+@pytest.mark.parametrize("arch", ["gpt_oss", "nemotron", "qwen"])
+def test_pair_tiles(moe, oracle, arch, monkeypatch):
+    """The tile kernel on SM pairs (opt-in, OCO_MOE_PAIR_TILES=1: route tiles of up to 512 routes, two CTAs per
+    tile): same ids, same tolerance as the default kernels, on experts with 1..128, 129..256, 257..384 and
+    385..512 routes and more than 512 (a second tile), and a feature count that is no multiple of 128."""
+    monkeypatch.setenv("OCO_MOE_PAIR_TILES", "1")
+    if arch == "gpt_oss":
+        layer = synth.make_layer(synth.ARCH_GPT_OSS, 192, 160, 8, 2, synth.FMT_MXFP4, seed=81)
+    elif arch == "nemotron":
+        layer = synth.make_layer(synth.ARCH_NEMOTRON, 256, 192, 8, 2, synth.FMT_Q4_0, seed=82)
+    else:
+        layer = synth.make_layer(synth.ARCH_QWEN, 512, 256, 8, 2, synth.FMT_Q4_K, seed=83)
+    # a skewed router: the bias spreads the expert loads from a few routes to more than 512
+    skewed = layer.router_b is not None
+    if skewed:
+        layer.router_b[:] = np.linspace(-1.5, 2.5, 8).astype(np.float32)
+    for tokens in (700, 1100):
+        x, res = synth.make_tokens(layer.hidden, tokens, 900 + tokens, "normal")
+        if arch == "qwen":
+            x = synth.f32_to_bf16_bits(synth.bf16_bits_to_f32(x) * 0.125)
+        out, routing = moe.run_layer(layer, x, res)
+        ref = oracle.moe_forward(layer, x, res)
+        assert np.array_equal(routing["ids"], ref.ids)
+        counts = np.bincount(ref.ids.ravel(), minlength=8)
+        if skewed:
+            assert counts.max() > 512 and counts.min() < 257      # one-half, two-half and two-tile experts all occur
+        tiles = routing["tiles"]
+        assert len(tiles) == int(np.sum(-(-counts // 512)))       # tiles of 512 routes
+        assert rel_l2(out, ref.out) <= REL_L2
+
+
 def test_gpt_oss_unaligned_weights(moe, oracle):
     """Packed tensors placed 7 bytes off alignment, as the reference tests them (mxfp4.rs:16)."""
     layer = synth.make_layer(synth.ARCH_GPT_OSS, 256, 160, 32, 4, synth.FMT_MXFP4, seed=21)
