@@ -202,7 +202,8 @@ int oco_moe_add_norm_forward(oco_moe_plan* plan, uint16_t* hidden_bf16, const ui
  * `cuda_stream`, and the copy of the residual rows back on a second stream of the plan. _end waits until the
  * oldest begun call has its rows back in `residual_bf16_host`. Up to two calls may be in flight (the third
  * _begin is refused with OCO_INVALID_ARGUMENT): the copies of call c + 1 then cross the bus beside the
- * kernels of call c. All calls of a plan go to one `cuda_stream`. Staging space (two slots) lies inside the
+ * kernels of call c (calls of up to 256 KB per buffer run on `cuda_stream` alone: their copies take
+ * microseconds and a hand-over between streams would cost more). All calls of a plan go to one `cuda_stream`. Staging space (two slots) lies inside the
  * bound workspace; pinned host buffers make the copies asynchronous. */
 int oco_moe_forward_host_begin(oco_moe_plan* plan, const uint16_t* x_bf16_host, uint16_t* residual_bf16_host,
                                int rows, void* cuda_stream);
@@ -316,6 +317,13 @@ int oco_moe_bind_repacked(oco_moe_plan* plan, void* buffer, size_t bytes, void* 
  * The plan, its workspace and its weights must outlive the graph and must not be re-bound while it lives. */
 typedef struct oco_moe_graph oco_moe_graph;
 int oco_moe_graph_capture(oco_moe_plan* plan, const uint16_t* x_bf16, uint16_t* residual_bf16, int rows, oco_moe_graph** out);
+/* The same for pinned host buffers: the graph also holds the copies of x and the residual rows into the
+ * workspace's first staging slot and the copy of the residual rows back, so one oco_moe_graph_launch (then a
+ * wait on the stream) is a whole oco_moe_forward_host call: for single tokens the launches and copies of that
+ * call cost the host about as much as the kernels take. The buffers must stay where they are while the graph
+ * lives; no host call may be in flight while it is recorded or runs (they share the staging slot). */
+int oco_moe_graph_capture_host(oco_moe_plan* plan, const uint16_t* x_bf16_host, uint16_t* residual_bf16_host, int rows,
+                               oco_moe_graph** out);
 int oco_moe_graph_launch(oco_moe_graph* graph, void* cuda_stream);
 void oco_moe_graph_destroy(oco_moe_graph* graph);
 

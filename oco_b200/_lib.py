@@ -83,6 +83,7 @@ SIGNATURES = {
     "oco_moe_repack_bytes": (C.c_size_t, [C.c_void_p]),
     "oco_moe_bind_repacked": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "oco_moe_graph_capture": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_void_p)]),
+    "oco_moe_graph_capture_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_void_p)]),
     "oco_moe_graph_launch": (C.c_int, [C.c_void_p, C.c_void_p]),
     "oco_moe_graph_destroy": (None, [C.c_void_p]),
     "oco_dense_plan_create": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),

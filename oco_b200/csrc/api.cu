@@ -1355,11 +1355,18 @@ int oco_moe_bind_repacked(oco_moe_plan* plan, void* buffer, size_t bytes, void* 
     return OCO_OK;
 }
 
-int oco_moe_graph_capture(oco_moe_plan* plan, const uint16_t* x_bf16, uint16_t* residual_bf16, int rows, oco_moe_graph** out) {
+// Records one forward call as an executable graph. host = true: x and the residual rows are host buffers;
+// the graph then also holds their copies into staging slot 0 and the copy of the residual rows back.
+static int capture_forward(oco_moe_plan* plan, const uint16_t* x, uint16_t* residual, int rows, bool host, oco_moe_graph** out) {
     if (!plan || !out) return OCO_INVALID_ARGUMENT;
     *out = nullptr;
     if (plan->profiling) return fail(plan, OCO_INVALID_ARGUMENT, "switch profiling off before recording a graph");
     if (int rc_dev = check_device(plan)) return rc_dev;
+    if (host) {
+        if (!plan->have_ws || !plan->have_w) return fail(plan, OCO_INVALID_ARGUMENT, "bind a workspace and weights first");
+        if (!x || !residual || rows < 1 || rows > plan->max_rows) return fail(plan, OCO_INVALID_ARGUMENT, "bad host buffers or rows");
+        if (plan->host_begun != plan->host_ended) return fail(plan, OCO_INVALID_ARGUMENT, "end the host calls in flight first");
+    }
     cudaStream_t side = nullptr;
     CK(cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking));
     cudaGraph_t graph = nullptr;
@@ -1369,7 +1376,17 @@ int oco_moe_graph_capture(oco_moe_plan* plan, const uint16_t* x_bf16, uint16_t* 
         cudaStreamDestroy(side);
         return fail(plan, OCO_CUDA_ERROR, "cudaStreamBeginCapture failed");
     }
-    rc = oco_moe_forward(plan, x_bf16, residual_bf16, rows, side);
+    if (host) {
+        const size_t bytes = (size_t)rows * plan->d.hidden * 2;
+        cudaError_t e = cudaMemcpyAsync(plan->ws.host_x[0], x, bytes, cudaMemcpyHostToDevice, side);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(plan->ws.host_res[0], residual, bytes, cudaMemcpyHostToDevice, side);
+        if (e != cudaSuccess) rc = fail(plan, OCO_CUDA_ERROR, "cudaMemcpyAsync in capture: %s", cudaGetErrorString(e));
+        if (rc == OCO_OK) rc = oco_moe_forward(plan, plan->ws.host_x[0], plan->ws.host_res[0], rows, side);
+        if (rc == OCO_OK && cudaMemcpyAsync(residual, plan->ws.host_res[0], bytes, cudaMemcpyDeviceToHost, side) != cudaSuccess)
+            rc = fail(plan, OCO_CUDA_ERROR, "cudaMemcpyAsync in capture failed");
+    } else {
+        rc = oco_moe_forward(plan, x, residual, rows, side);
+    }
     const cudaError_t end = cudaStreamEndCapture(side, &graph);      // always ends the capture, also after a refused call
     if (rc == OCO_OK && (end != cudaSuccess || !graph)) rc = fail(plan, OCO_CUDA_ERROR, "cudaStreamEndCapture: %s", cudaGetErrorString(end));
     if (rc == OCO_OK && cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) rc = fail(plan, OCO_CUDA_ERROR, "cudaGraphInstantiate failed");
@@ -1383,6 +1400,15 @@ int oco_moe_graph_capture(oco_moe_plan* plan, const uint16_t* x_bf16, uint16_t* 
     g->plan = plan;
     *out = g;
     return OCO_OK;
+}
+
+int oco_moe_graph_capture(oco_moe_plan* plan, const uint16_t* x_bf16, uint16_t* residual_bf16, int rows, oco_moe_graph** out) {
+    return capture_forward(plan, x_bf16, residual_bf16, rows, false, out);
+}
+
+int oco_moe_graph_capture_host(oco_moe_plan* plan, const uint16_t* x_bf16_host, uint16_t* residual_bf16_host, int rows,
+                               oco_moe_graph** out) {
+    return capture_forward(plan, x_bf16_host, residual_bf16_host, rows, true, out);
 }
 
 int oco_moe_graph_launch(oco_moe_graph* graph, void* cuda_stream) {
@@ -1400,6 +1426,9 @@ void oco_moe_graph_destroy(oco_moe_graph* graph) {
     if (graph->exec) cudaGraphExecDestroy(graph->exec);
     delete graph;
 }
+
+// Host calls of up to this many bytes per buffer run on the caller's stream alone.
+constexpr size_t kHostOneStreamBytes = 256 * 1024;
 
 int oco_moe_forward_host_begin(oco_moe_plan* plan, const uint16_t* x_host, uint16_t* residual_host, int rows,
                                void* cuda_stream) {
@@ -1424,6 +1453,19 @@ int oco_moe_forward_host_begin(oco_moe_plan* plan, const uint16_t* x_host, uint1
     const int s = (int)(plan->host_begun & 1);
     uint16_t* dx = plan->ws.host_x[s];
     uint16_t* dres = plan->ws.host_res[s];
+    if (bytes <= kHostOneStreamBytes) {
+        // Few rows: the copies take microseconds, a hand-over between streams costs more than it could hide.
+        // Everything goes to the caller's stream, in order, behind the copy back of the slot's last user.
+        if (plan->host_begun >= 2) CK(cudaStreamWaitEvent(st, plan->ev_out[s], 0));
+        CK(cudaMemcpyAsync(dx, x_host, bytes, cudaMemcpyHostToDevice, st));
+        CK(cudaMemcpyAsync(dres, residual_host, bytes, cudaMemcpyHostToDevice, st));
+        int rc = forward_any(plan, dx, dres, rows, st, nullptr);
+        if (rc) return rc;
+        CK(cudaMemcpyAsync(residual_host, dres, bytes, cudaMemcpyDeviceToHost, st));
+        CK(cudaEventRecord(plan->ev_out[s], st));
+        plan->host_begun++;
+        return OCO_OK;
+    }
     // In: the slot is free once the call that used it last has copied its rows back (which follows its
     // kernels); x goes first, the residual rows, which only the last kernel needs, behind it.
     CK(cudaStreamWaitEvent(plan->in_stream, plan->ev_out[s], 0));

@@ -158,6 +158,13 @@ class _Plan:
         self._check(_lib.lib().oco_moe_graph_capture(self.handle, _ptr(x), _ptr(residual), rows, C.byref(g)))
         return StepGraph(self, g, (x, residual))
 
+    def capture_host(self, x: np.ndarray, residual: np.ndarray, rows: int) -> "StepGraph":
+        """The forward call on these pinned host buffers, copies included, as a graph of the library."""
+        g = C.c_void_p()
+        self._check(_lib.lib().oco_moe_graph_capture_host(self.handle, x.ctypes.data_as(C.c_void_p),
+                                                          residual.ctypes.data_as(C.c_void_p), rows, C.byref(g)))
+        return StepGraph(self, g, (x, residual))
+
     def poll(self):
         self._check(_lib.lib().oco_moe_poll(self.handle, _stream_ptr()))
 

@@ -317,6 +317,33 @@ def test_host_buffer_entry_point(moe, oracle):
         plan.forward_host(x, got, 51)      # beyond the reserved rows: a status, not a crash
 
 
+def test_host_graph(moe, oracle):
+    """oco_moe_graph_capture_host: one replay copies the pinned rows in, runs the layer and copies the residual
+    rows back; refreshed host contents give the result of oco_moe_forward_host on them, bit for bit."""
+    import torch
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, 256, 192, 32, 4, synth.FMT_MXFP4, seed=17)
+    plan = moe.plan_for(layer)
+    plan.reserve(8)
+    plan.bind(moe._Weights.from_layer(layer))
+    for rows in (1, 8):
+        x, res = synth.make_tokens(256, rows, 60 + rows, "normal")
+        hx = torch.from_numpy(x.view(np.int16).copy()).pin_memory().numpy().view(np.uint16)
+        hres = torch.from_numpy(res.view(np.int16).copy()).pin_memory().numpy().view(np.uint16)
+        g = plan.capture_host(hx, hres, rows)
+        for seed in (1, 2):
+            x2, res2 = synth.make_tokens(256, rows, 70 + seed, "normal")
+            hx[:] = x2
+            hres[:] = res2
+            g.replay()
+            torch.cuda.current_stream().synchronize()
+            one = res2.copy()
+            plan.forward_host(x2, one, rows)
+            assert np.array_equal(hres, one)
+            assert rel_l2(hres, oracle.moe_forward(layer, x2, res2).out) <= REL_L2
+        del g
+    plan.poll()
+
+
 def test_host_calls_in_flight(moe, oracle):
     """Two host calls in flight (oco_moe_forward_host_begin / _end): six calls on different rows, each ended
     only after the next one was begun, give what the one-call-at-a-time entry point gives, bit for bit, and
