@@ -866,8 +866,16 @@ int stage_combine(oco_moe_plan* plan, const uint16_t* y, const float* probs, uin
     const int round_sum = ARCH == OCO_ARCH_GPT_OSS ? 1 : 0;
     if (d.hidden % 8 == 0 && (((uintptr_t)y | (uintptr_t)residual | (uintptr_t)sh) & 15u) == 0) {
         const size_t octets = pairs / 4;
-        CK(launch_dependent(moe_combine8_kernel, dim3((unsigned)((octets + 255) / 256)), dim3(256), 0, st, y, probs, residual, sh, d.hidden, rows,
-                            d.top_k, round_sum, shared_mode, status));
+        const dim3 grid((unsigned)((octets + 255) / 256));
+        auto go = [&](auto kernel) {
+            return launch_dependent(kernel, grid, dim3(256), 0, st, y, probs, residual, sh, d.hidden, rows, d.top_k, round_sum, shared_mode, status);
+        };
+        switch (d.top_k) {      // the families' route counts get their loads unrolled
+            case 4: CK(go(moe_combine8_kernel<4>)); break;
+            case 6: CK(go(moe_combine8_kernel<6>)); break;
+            case 8: CK(go(moe_combine8_kernel<8>)); break;
+            default: CK(go(moe_combine8_kernel<0>)); break;
+        }
     } else {
         moe_combine_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, st>>>(y, probs, residual, sh, d.hidden, rows, d.top_k, round_sum,
                                                                             shared_mode, status);

@@ -345,7 +345,9 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __rest
 }
 
 // The same combine with eight elements per thread (16-byte loads of the expert outputs and the residual):
-// identical arithmetic per element, for hidden sizes that are multiples of eight.
+// identical arithmetic per element, for hidden sizes that are multiples of eight. KT: the number of routes
+// per token when it is known at compile time (their loads then go out together), 0: taken from K.
+template <int KT>
 __global__ void __launch_bounds__(256) moe_combine8_kernel(const uint16_t* __restrict__ y, const float* __restrict__ probs,
                                                            uint16_t* __restrict__ out, const uint16_t* __restrict__ shared,
                                                            int H, int T, int K, int round_sum, int shared_mode,
@@ -377,14 +379,33 @@ __global__ void __launch_bounds__(256) moe_combine8_kernel(const uint16_t* __res
             else { r[2 * j] = bf16_round(__fadd_rn(r[2 * j], h0)); r[2 * j + 1] = bf16_round(__fadd_rn(r[2 * j + 1], h1)); }
         }
     }
-    for (int k = 0; k < K; k++) {
-        const uint4 yw4 = *reinterpret_cast<const uint4*>(y + ((size_t)t * K + k) * H + d);
-        const uint32_t yw[4] = {yw4.x, yw4.y, yw4.z, yw4.w};
-        const float p = probs[(size_t)t * K + k];
+    if (KT > 0) {
+        uint4 yw4[KT > 0 ? KT : 1];
+        float p[KT > 0 ? KT : 1];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            s[2 * j] = __fmaf_rn(__uint_as_float(yw[j] << 16), p, s[2 * j]);
-            s[2 * j + 1] = __fmaf_rn(__uint_as_float(yw[j] & 0xffff0000u), p, s[2 * j + 1]);
+        for (int k = 0; k < KT; k++) {
+            yw4[k] = *reinterpret_cast<const uint4*>(y + ((size_t)t * KT + k) * H + d);
+            p[k] = probs[(size_t)t * KT + k];
+        }
+#pragma unroll
+        for (int k = 0; k < KT; k++) {                     // the same order of additions as the loop below
+            const uint32_t yw[4] = {yw4[k].x, yw4[k].y, yw4[k].z, yw4[k].w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                s[2 * j] = __fmaf_rn(__uint_as_float(yw[j] << 16), p[k], s[2 * j]);
+                s[2 * j + 1] = __fmaf_rn(__uint_as_float(yw[j] & 0xffff0000u), p[k], s[2 * j + 1]);
+            }
+        }
+    } else {
+        for (int k = 0; k < K; k++) {
+            const uint4 yw4 = *reinterpret_cast<const uint4*>(y + ((size_t)t * K + k) * H + d);
+            const uint32_t yw[4] = {yw4.x, yw4.y, yw4.z, yw4.w};
+            const float p = probs[(size_t)t * K + k];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                s[2 * j] = __fmaf_rn(__uint_as_float(yw[j] << 16), p, s[2 * j]);
+                s[2 * j + 1] = __fmaf_rn(__uint_as_float(yw[j] & 0xffff0000u), p, s[2 * j + 1]);
+            }
         }
     }
     uint32_t o[4];
