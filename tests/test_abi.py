@@ -92,6 +92,12 @@ def test_dense_window_and_graph_calls_check_their_arguments(lib):
     assert lib.oco_dense_plan_create(C.byref(desc), C.byref(h)) == _lib.UNSUPPORTED_SHAPE
     lib.oco_dense_plan_destroy(h)
     assert lib.oco_dense_plan_create(None, None) == _lib.INVALID_ARGUMENT
+    # host-buffer entry points: no plan, nothing in flight
+    g = C.c_void_p()
+    assert lib.oco_moe_forward_host_begin(None, None, None, 1, None) == _lib.INVALID_ARGUMENT
+    assert lib.oco_moe_forward_host_end(None) == _lib.INVALID_ARGUMENT
+    assert lib.oco_moe_forward_host(None, None, None, 1, None) == _lib.INVALID_ARGUMENT
+    assert lib.oco_moe_graph_capture_host(None, None, None, 1, C.byref(g)) == _lib.INVALID_ARGUMENT
     # windows: rank outside the world, no backing, backing larger than the slot
     w = C.c_void_p()
     for rank, world, stride, backed in ((2, 2, 1 << 21, 1 << 20), (0, 0, 1 << 21, 1 << 20), (0, 2, 1 << 21, 0), (0, 2, 1 << 20, 1 << 21)):
