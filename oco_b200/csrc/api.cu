@@ -118,6 +118,7 @@ struct oco_moe_plan {
     int route_plan_single_max = 2048;   // routes up to which one CTA makes the route plan (OCO_MOE_ROUTE_PLAN_SINGLE_MAX)
     int wide_min_avg = 1;        // OCO_MOE_WIDE_MIN_AVG: routes per expert from which layers take the 256-route tiles
     int router_block_min = 512;  // OCO_MOE_ROUTER_BLOCK_MIN: rows from which the register-blocked router kernel runs
+    bool static_tiles = false;   // OCO_MOE_STATIC_TILES=1: the wide tile kernel's CTA c takes items c, c + grid, ... (no counter)
     bool pair_tiles = false;     // OCO_MOE_PAIR_TILES=1: 256-route tiles on SM pairs (grouped_gemm_pair_kernel)
     bool narrow_tiles = false;   // OCO_MOE_NARROW_TILES=1: keep the generic tile kernel for 256-route tiles too
     bool profiling = false;
@@ -397,6 +398,9 @@ int launch_gemm_wide(oco_moe_plan* plan, GemmParams gp, const CUtensorMap* maps,
     // persistent: one CTA per SM walks the (route tile, feature tile) items; never more CTAs than items can exist
     const int feats = (gp.n + (epi_gated(EPI) ? 127 : 255)) / (epi_gated(EPI) ? 128 : 256);
     const int grid = std::min(plan->sm_count, feats * max_tiles);
+    // With many items per CTA they are handed out as CTAs become free (two words of the zeroed status block count
+    // items and leavers); with few (measured: four per CTA) the fixed deal c, c + grid, ... is as even and cheaper.
+    gp.sched = (plan->static_tiles || feats * max_tiles < 5 * grid) ? nullptr : plan->ws.status + 16;
     CK(launch_dependent(grouped_gemm_wide_kernel<FMT, EPI>, dim3(grid), dim3(WideShapeT<FMT>::kThreads), WideShapeT<FMT>::kSmemBytes, st, gp, maps[0], maps[1],
                         maps[2], maps[3]));
     plan->launches++;
@@ -1016,6 +1020,7 @@ int oco_moe_plan_create(const oco_moe_desc* desc, oco_moe_plan** out) {
     }
     { const char* e = getenv("OCO_MOE_NARROW_TILES"); plan->narrow_tiles = e && e[0] == '1'; }
     { const char* e = getenv("OCO_MOE_WIDE_MIN_AVG"); if (e && atoi(e) > 0) plan->wide_min_avg = atoi(e); }
+    { const char* e = getenv("OCO_MOE_STATIC_TILES"); if (e) plan->static_tiles = atoi(e) != 0; }
     { const char* e = getenv("OCO_MOE_PAIR_TILES"); if (e) plan->pair_tiles = atoi(e) != 0; }
     { const char* e = getenv("OCO_MOE_ROUTER_BLOCK_MIN"); if (e && atoi(e) > 0) plan->router_block_min = atoi(e); }
     { const char* e = getenv("OCO_MOE_NO_BATCH"); plan->no_batch_path = e && e[0] == '1'; }

@@ -60,6 +60,8 @@ struct GemmParams {
     const unsigned char* sfa0; // repacked weights (grouped_gemm_mxr_kernel): the scale tiles of w0 / w1,
     const unsigned char* sfa1; //   [expert][feature tile][K group][1024]
     int sfa_tiles;             //   feature tiles per expert
+    uint32_t* sched;           // wide kernel: two zeroed words (items handed out, CTAs finished) for handing out work
+                               //   items as CTAs become free; null = item c, c + grid, ... for CTA c
 };
 
 // ---- operand order ---------------------------------------------------------------------------------

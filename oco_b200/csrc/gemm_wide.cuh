@@ -14,7 +14,11 @@
 //   * A and B stages are separate rings: A tiles are produced in the SM just in time, B tiles travel
 //     from L2 by TMA (the smallest box that holds the tile's live routes). A dedicated warp issues
 //     the TMA loads, one thread issues the MMAs, each barrier has one arrival per warp.
-//   * The grid is persistent: one CTA per SM walks the list of (route tile, feature tile) items.
+//   * The grid is persistent: one CTA per SM takes (route tile, feature tile) items from the list, the first by
+//     its index, the following ones from a counter in global memory as it becomes free: items cost between 0.6
+//     (a thinly filled tile) and 1 (a full one) of the same time, and a fixed deal leaves some CTAs with a fifth
+//     more work than the average. Items are still handed out in list order, so CTAs that run at the same time
+//     work on neighbouring items (one route tile's rows in L2, one expert's weight rows in DRAM pages).
 //
 // All waits are bounded (see mbar_wait); a wait that gives up sets the status word.
 #pragma once
@@ -76,7 +80,15 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
     constexpr int kFeatPerItem = GATED ? 128 : 256;
     extern __shared__ unsigned char smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (__syncthreads_or(tid == 0 && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u)) return;
+    const bool dyn = p.sched != nullptr;
+    // The last CTA to leave puts the two scheduling words back to zero for the next launch.
+    auto leave = [&]() {
+        if (dyn && tid == 0) {
+            __threadfence();
+            if (atomicAdd(p.sched + 1, 1u) == gridDim.x - 1) { p.sched[0] = 0u; p.sched[1] = 0u; __threadfence(); }
+        }
+    };
+    if (__syncthreads_or(tid == 0 && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u)) { leave(); return; }
 
     // ---- the work list ---------------------------------------------------------------------------
     const int nfeat = (p.n + kFeatPerItem - 1) / kFeatPerItem;
@@ -117,6 +129,14 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
     const uint32_t tmem_free = accum_bar + 8u;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl_gen + 128);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    // item of step `seq` of this CTA: slot seq & 1, published by lane 0 of producer warp 0 (one arrival on item_full)
+    volatile uint32_t* item_slot = tmem_slot + 4;
+    auto item_full = [&](int q) { return ctrl + 8u * (2 * S::kAStages + 2 * S::kBStages + 2 + q); };
+    // read by one thread of a role: waits for the item of step seq; the end of the list once a wait has given up
+    auto item_of = [&](int seq) -> int {
+        mbar_wait(item_full(seq & 1), (uint32_t)(seq >> 1) & 1u, abort_flag, p.status);
+        return *abort_flag ? total : (int)item_slot[seq & 1];
+    };
     uint32_t* out_rows = reinterpret_cast<uint32_t*>(ctrl_gen + 512);
 
     if (tid == 0) {
@@ -124,6 +144,7 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
         for (int s = 0; s < S::kBStages; s++) { mbar_init(full_b(s), 1); mbar_init(empty_b(s), 1); }
         mbar_init(accum_bar, 1);
         mbar_init(tmem_free, S::kProducerWarps);
+        mbar_init(item_full(0), 1); mbar_init(item_full(1), 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -195,7 +216,14 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
         Item cur;
         bool started = false;                 // the first ring buffer of `cur` is already on its way
         int seq = 0;
-        for (int item = blockIdx.x; item < total; item += gridDim.x, seq++) {
+        const bool fetcher = warp == 0 && lane == 0;
+        if (fetcher) { item_slot[0] = blockIdx.x; mbar_arrive(item_full(0)); }
+        // the chunk during which the fetcher asks for the CTA's next item: late, so that a CTA holds no item it
+        // will not start soon, yet a few slices before the end, so that the answer is there when the item ends
+        const int fetch_chunk = max(0, nchunks - 4);
+        uint32_t fetched = 0;
+        int next = 0;
+        for (int item = blockIdx.x; item < total; item = next, seq++) {
             if (!started) {
                 cur = load_item(item);
 #pragma unroll
@@ -205,6 +233,13 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
             const uint32_t a_lo = (uint32_t)(uintptr_t)row_ptr(cur, r) & 15u;   // alignment of the row start
             const int g0 = seq * nkb;                                           // slices of earlier items
             for (int chunk = 0; chunk < nchunks; chunk++) {
+                if (fetcher) {
+                    if (chunk == fetch_chunk) fetched = dyn ? gridDim.x + atomicAdd(p.sched, 1u) : (uint32_t)item + gridDim.x;
+                    if (chunk == min(fetch_chunk + 2, nchunks - 1)) {
+                        item_slot[(seq + 1) & 1] = min(fetched, (uint32_t)total);
+                        mbar_arrive(item_full((seq + 1) & 1));
+                    }
+                }
                 issue(csrc, chunk + 1);                                          // other buffer: decoded one chunk ago
                 cp_async_wait<1>();                                              // this chunk's copies have landed
                 __syncwarp();
@@ -266,9 +301,11 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
             cp_async_wait<0>();
             // the next item's first bytes travel while this item's accumulators are drained
             const Item done = cur;
-            started = item + (int)gridDim.x < total;
+            if (lane == 0) next = item_of(seq + 1);
+            next = __shfl_sync(0xffffffffu, next, 0);
+            started = next < total;
             if (started) {
-                cur = load_item(item + gridDim.x);
+                cur = load_item(next);
 #pragma unroll
                 for (int i = 0; i < NC; i++) csrc[i] = row_ptr(cur, crow[i]);
                 issue(csrc, 0);
@@ -327,7 +364,7 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
         if (lane == 0) {
             // ===== MMA issue ======================================================================
             int seq = 0;
-            for (int item = blockIdx.x; item < total; item += gridDim.x, seq++) {
+            for (int item = item_of(0); item < total; item = item_of(++seq)) {
                 const Item it = load_item(item);
                 const uint32_t n_mma = max(16u, (it.nv + 15u) & ~15u);
                 const uint32_t idesc = umma_idesc_f16(n_mma);
@@ -361,7 +398,7 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
     } else if (lane == 0) {
         // ===== B tiles by TMA =========================================================================
         int seq = 0;
-        for (int item = blockIdx.x; item < total; item += gridDim.x, seq++) {
+        for (int item = item_of(0); item < total; item = item_of(++seq)) {
             const Item it = load_item(item);
             const int g0 = seq * nkb;
             // the smallest box (32, 64, 128 or 256 rows of 64 halves) that holds the tile's live rows
@@ -384,6 +421,7 @@ grouped_gemm_wide_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
         tc_fence_after();
         tmem_dealloc(tmem_base, S::kTmemCols);
     }
+    leave();
 }
 
 }  // namespace oco
