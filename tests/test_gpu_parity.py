@@ -166,6 +166,29 @@ def test_gpt_oss_forced_routes_reference_ids(moe, oracle):
     assert rel_l2(out, ref.out) <= REL_L2
 
 
+def test_item_counter_and_fixed_deal_agree(moe, oracle, monkeypatch):
+    """The wide tile kernel hands its work items out from a counter where a CTA gets five or more (here: 64
+    experts x 36 feature tiles on at most 148 CTAs) and deals them c, c + grid, ... otherwise or with
+    OCO_MOE_STATIC_TILES=1: the same items either way, so the same bits; three calls in a row on one plan also
+    show that the last CTA to leave has put the counter back."""
+    layer = synth.make_layer(synth.ARCH_GPT_OSS, 128, 4608, 64, 4, synth.FMT_MXFP4, seed=91)
+    x, res = synth.make_tokens(128, 900, 17, "normal")
+    plan = moe.plan_for(layer)
+    plan.reserve(900)
+    plan.bind(moe._Weights.from_layer(layer))
+    outs = []
+    for _ in range(3):
+        got = res.copy()
+        plan.forward_host(x, got, 900)
+        outs.append(got)
+    plan.poll()
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+    monkeypatch.setenv("OCO_MOE_STATIC_TILES", "1")
+    fixed, routing = moe.run_layer(layer, x, res)
+    assert np.array_equal(outs[0], fixed)
+    assert rel_l2(fixed, oracle.moe_forward(layer, x, res).out) <= REL_L2
+
+
 @pytest.mark.parametrize("arch", ["gpt_oss", "nemotron", "qwen"])
 def test_pair_tiles(moe, oracle, arch, monkeypatch):
     """The tile kernel on SM pairs (opt-in, OCO_MOE_PAIR_TILES=1: route tiles of up to 512 routes, two CTAs per
