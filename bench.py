@@ -692,8 +692,15 @@ def measure_layer(args, ctx, workload, steps, warmup, tokens=0, graph=True, with
     if tokens > 64:
         # throughput workloads: two calls in flight. With one weight copy per plan rotation the two calls may
         # belong to different plans: each plan owns its staging slots and copy streams, and all share the stream.
-        e2e_ms = timed_host_steps(2)
-        api = "oco_moe_forward_host_begin/_end, two calls in flight (pinned host buffers in, residual rows back, every step)"
+        two_ms = timed_host_steps(2)
+        # on a host whose memory or PCIe root is shared by many ranks the second call in flight can cost more than it
+        # hides: the line carries the faster of the two ways of calling, and both figures
+        if two_ms <= one_ms:
+            e2e_ms = two_ms
+            api = "oco_moe_forward_host_begin/_end, two calls in flight (pinned host buffers in, residual rows back, every step)"
+        else:
+            e2e_ms = one_ms
+            api = "oco_moe_forward_host, one call at a time (pinned host buffers in, residual rows back); two calls in flight were slower here"
     else:
         # latency workloads: the whole host call (copies in, kernels, copy back) as one graph of the library per plan
         hgraphs = [plans[c].capture_host(hx_np, hres_np, tokens) for c in range(copies)]
@@ -717,6 +724,9 @@ def measure_layer(args, ctx, workload, steps, warmup, tokens=0, graph=True, with
                h2d_bytes_per_step=2 * row_bytes, d2h_bytes_per_step=row_bytes, api=api,
                one_call_at_a_time=dict(ms_per_step=one_ms, tokens_per_s=world * tokens / (one_ms / 1e3),
                                        api="oco_moe_forward_host"))
+    if tokens > 64:
+        e2e["two_calls_in_flight"] = dict(ms_per_step=two_ms, tokens_per_s=world * tokens / (two_ms / 1e3),
+                                          api="oco_moe_forward_host_begin/_end")
     del plans, weights, graphs
     torch.cuda.empty_cache()
     if rank != 0:
