@@ -1038,6 +1038,8 @@ int oco_moe_plan_create(const oco_moe_desc* desc, oco_moe_plan** out) {
 
 void oco_moe_plan_destroy(oco_moe_plan* plan) {
     if (!plan) return;
+    while (plan->host_begun != plan->host_ended)        // host calls still in flight: their rows come back first
+        if (oco_moe_forward_host_end(plan) != OCO_OK) break;
     for (int i = 0; i < kMaxMarks; i++)
         if (plan->marks[i]) cudaEventDestroy(plan->marks[i]);
     for (int i = 0; i < 2; i++) {
